@@ -1,0 +1,329 @@
+// LayerNorm / RMSNorm forward and backward with the residual add folded in.
+//
+//   forward :  x = x0 (+ residual);  z = (x - mean) * rstd * gamma (+ beta)
+//              optionally writes x back as the new residual stream
+//   backward:  dx = rstd * (dz*gamma - mean(dz*gamma) - xhat * mean(dz*gamma*xhat)) (+ dres_in)
+//              dgamma / dbeta reduced per CTA into a scratch matrix, then summed by
+//              a second kernel
+//
+// Same operator family as the reference's dropout_add_ln extension
+// (reference: csrc/layer_norm/ln_api.cpp:832-846, ln_fwd_kernels.cuh:18-20,
+// ln_bwd_kernels.cuh:10-12,301-303) but written for one shape-generic kernel:
+// rows are kept in registers as 16-byte vectors, `tpr` threads cooperate on a
+// row and several rows share a CTA, the grid is persistent over row groups.
+// The kernels are bandwidth bound; they touch each element once per pass.
+#include "common.cuh"
+
+namespace {
+
+constexpr int VPT = 4;  // 16-byte vectors per thread (covers hidden <= 8 * VPT * tpr)
+
+// Sum over the `tpr` threads that share a row.  `red` holds [rows_per_cta][8] floats.
+template <int NVAL>
+__device__ __forceinline__ void row_reduce(float (&v)[NVAL], float* red, int tpr, int rl, int tr) {
+#pragma unroll
+  for (int i = 0; i < NVAL; ++i) v[i] = mb::warp_sum(v[i]);
+  if (tpr > 32) {
+    const int wpr = tpr >> 5;  // warps per row
+    const int w = tr >> 5;
+    __syncthreads();
+    if ((tr & 31) == 0) {
+#pragma unroll
+      for (int i = 0; i < NVAL; ++i) red[(rl * 8 + w) * NVAL + i] = v[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NVAL; ++i) {
+      float s = 0.f;
+      for (int j = 0; j < wpr; ++j) s += red[(rl * 8 + j) * NVAL + i];
+      v[i] = s;
+    }
+  }
+}
+
+template <bool RMS>
+__global__ void __launch_bounds__(256)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ residual,
+                const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
+                __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ x_out,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int h,
+                float eps, int tpr, int rpc) {
+  __shared__ float red[8 * 8 * 2];
+  const int rl = threadIdx.x / tpr;  // row slot in this CTA
+  const int tr = threadIdx.x % tpr;  // thread within the row
+  const int nvec = h >> 3;
+  const int groups = (rows + rpc - 1) / rpc;
+
+  // gamma / beta stay in registers across the rows of the persistent loop
+  float g[VPT][8], b[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int vi = tr + i * tpr;
+    if (vi < nvec) {
+      mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(gamma + 8 * vi), g[i]);
+      if (!RMS && beta) mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(beta + 8 * vi), b[i]);
+      else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) b[i][k] = 0.f;
+      }
+    }
+  }
+
+  for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+    const int row = grp * rpc + rl;
+    const bool active = row < rows;
+    float x[VPT][8];
+    float acc[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int vi = tr + i * tpr;
+      if (active && vi < nvec) {
+        size_t off = static_cast<size_t>(row) * h + 8 * vi;
+        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(x0 + off), x[i]);
+        if (residual) {
+          float r[8];
+          mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(residual + off), r);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) x[i][k] += r[k];
+        }
+        if (x_out) {
+          mb::bf16x8 pk = mb::pack8(x[i]);
+          *reinterpret_cast<mb::bf16x8*>(x_out + off) = pk;
+          // keep what later passes will re-read: the rounded value
+          mb::unpack8(pk, x[i]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          acc[0] += x[i][k];
+          acc[1] += x[i][k] * x[i][k];
+        }
+      }
+    }
+    row_reduce<2>(acc, red, tpr, rl, tr);
+    float mean = RMS ? 0.f : acc[0] / h;
+    float var = acc[1] / h - mean * mean;
+    float rstd = rsqrtf(fmaxf(var, 0.f) + eps);
+    if (active && tr == 0) {
+      if (mean_out) mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int vi = tr + i * tpr;
+      if (active && vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = (x[i][k] - mean) * rstd * g[i][k] + b[i][k];
+        *reinterpret_cast<mb::bf16x8*>(z + static_cast<size_t>(row) * h + 8 * vi) = mb::pack8(o);
+      }
+    }
+  }
+}
+
+template <bool RMS>
+__global__ void __launch_bounds__(256)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ x,
+                const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
+                const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres_in,
+                __nv_bfloat16* __restrict__ dx, float* __restrict__ part_dgamma,
+                float* __restrict__ part_dbeta, int rows, int h, int tpr, int rpc) {
+  __shared__ float red[8 * 8 * 2];
+  const int rl = threadIdx.x / tpr;
+  const int tr = threadIdx.x % tpr;
+  const int nvec = h >> 3;
+  const int groups = (rows + rpc - 1) / rpc;
+
+  float g[VPT][8], dg[VPT][8], db[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int vi = tr + i * tpr;
+    if (vi < nvec) mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(gamma + 8 * vi), g[i]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) dg[i][k] = db[i][k] = 0.f;
+  }
+
+  for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+    const int row = grp * rpc + rl;
+    const bool active = row < rows;
+    const float mean = (active && !RMS) ? mean_in[row] : 0.f;
+    const float rstd = active ? rstd_in[row] : 0.f;
+    float xh[VPT][8], dy[VPT][8];
+    float acc[2] = {0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int vi = tr + i * tpr;
+      if (active && vi < nvec) {
+        size_t off = static_cast<size_t>(row) * h + 8 * vi;
+        float xv[8], dzv[8];
+        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(x + off), xv);
+        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(dz + off), dzv);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          xh[i][k] = (xv[k] - mean) * rstd;
+          dy[i][k] = dzv[k] * g[i][k];
+          dg[i][k] += dzv[k] * xh[i][k];
+          db[i][k] += dzv[k];
+          acc[0] += dy[i][k];
+          acc[1] += dy[i][k] * xh[i][k];
+        }
+      }
+    }
+    row_reduce<2>(acc, red, tpr, rl, tr);
+    const float m1 = RMS ? 0.f : acc[0] / h;
+    const float m2 = acc[1] / h;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int vi = tr + i * tpr;
+      if (active && vi < nvec) {
+        size_t off = static_cast<size_t>(row) * h + 8 * vi;
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = rstd * (dy[i][k] - m1 - xh[i][k] * m2);
+        if (dres_in) {
+          float r[8];
+          mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(dres_in + off), r);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] += r[k];
+        }
+        *reinterpret_cast<mb::bf16x8*>(dx + off) = mb::pack8(o);
+      }
+    }
+  }
+  // one partial row per (CTA, row slot)
+  const size_t prow = static_cast<size_t>(blockIdx.x) * rpc + rl;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int vi = tr + i * tpr;
+    if (vi < nvec) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        part_dgamma[prow * h + 8 * vi + k] = dg[i][k];
+        if (!RMS && part_dbeta) part_dbeta[prow * h + 8 * vi + k] = db[i][k];
+      }
+    }
+  }
+}
+
+// Column sums of the partial matrices -> bf16 (or accumulate into fp32) gradients.
+__global__ void norm_bwd_finalize_kernel(const float* __restrict__ part_dgamma,
+                                         const float* __restrict__ part_dbeta,
+                                         __nv_bfloat16* __restrict__ dgamma,
+                                         __nv_bfloat16* __restrict__ dbeta, int nparts, int h,
+                                         int accumulate) {
+  __shared__ float sg[8][33], sb[8][33];
+  const int col = blockIdx.x * 32 + threadIdx.x;
+  float ag = 0.f, ab = 0.f;
+  if (col < h) {
+    for (int r = threadIdx.y; r < nparts; r += 8) {
+      ag += part_dgamma[static_cast<size_t>(r) * h + col];
+      if (part_dbeta) ab += part_dbeta[static_cast<size_t>(r) * h + col];
+    }
+  }
+  sg[threadIdx.y][threadIdx.x] = ag;
+  sb[threadIdx.y][threadIdx.x] = ab;
+  __syncthreads();
+  if (threadIdx.y == 0 && col < h) {
+#pragma unroll
+    for (int r = 1; r < 8; ++r) {
+      ag += sg[r][threadIdx.x];
+      ab += sb[r][threadIdx.x];
+    }
+    if (accumulate) {
+      ag += __bfloat162float(dgamma[col]);
+      if (dbeta) ab += __bfloat162float(dbeta[col]);
+    }
+    dgamma[col] = __float2bfloat16(ag);
+    if (dbeta && part_dbeta) dbeta[col] = __float2bfloat16(ab);
+  }
+}
+
+int g_sms = 0;
+int num_sms() {
+  if (!g_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_sms;
+}
+
+void pick_shape(int h, int& tpr, int& rpc) {
+  int nvec = h / 8;
+  tpr = ((nvec + VPT - 1) / VPT + 31) / 32 * 32;
+  if (tpr > 256) tpr = 256;
+  rpc = 256 / tpr;
+  if (rpc < 1) rpc = 1;
+  if (rpc > 8) rpc = 8;
+}
+
+}  // namespace
+
+// Number of scratch rows (each of `h` floats, once for dgamma and once for dbeta)
+// that mb_norm_bwd needs for a given problem.
+MB_API int mb_norm_bwd_scratch_rows(int rows, int h) {
+  int tpr, rpc;
+  pick_shape(h, tpr, rpc);
+  int groups = (rows + rpc - 1) / rpc;
+  int grid = num_sms() * 2;
+  if (grid > groups) grid = groups;
+  return grid * rpc;
+}
+
+// rms != 0 selects RMSNorm (no mean, no beta).  residual / x_out / beta / mean may be null.
+MB_API int mb_norm_fwd(const void* x0, const void* residual, const void* gamma, const void* beta,
+                       void* z, void* x_out, float* mean, float* rstd, int rows, int h, float eps,
+                       int rms, cudaStream_t stream) {
+  if (h % 8 != 0 || h > 8 * VPT * 256) return -1;
+  if (rows == 0) return 0;
+  int tpr, rpc;
+  pick_shape(h, tpr, rpc);
+  int groups = (rows + rpc - 1) / rpc;
+  int grid = num_sms() * 4;
+  if (grid > groups) grid = groups;
+  auto a = reinterpret_cast<const __nv_bfloat16*>(x0);
+  auto r = reinterpret_cast<const __nv_bfloat16*>(residual);
+  auto g = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  auto b = reinterpret_cast<const __nv_bfloat16*>(beta);
+  auto zz = reinterpret_cast<__nv_bfloat16*>(z);
+  auto xo = reinterpret_cast<__nv_bfloat16*>(x_out);
+  if (rms)
+    norm_fwd_kernel<true><<<grid, tpr * rpc, 0, stream>>>(a, r, g, b, zz, xo, mean, rstd, rows, h,
+                                                          eps, tpr, rpc);
+  else
+    norm_fwd_kernel<false><<<grid, tpr * rpc, 0, stream>>>(a, r, g, b, zz, xo, mean, rstd, rows, h,
+                                                           eps, tpr, rpc);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// scratch: 2 * mb_norm_bwd_scratch_rows(rows, h) * h floats (first half dgamma, second dbeta).
+MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const float* mean,
+                       const float* rstd, const void* dres_in, void* dx, void* dgamma, void* dbeta,
+                       float* scratch, int rows, int h, int rms, int accumulate,
+                       cudaStream_t stream) {
+  if (h % 8 != 0 || h > 8 * VPT * 256) return -1;
+  if (rows == 0) return 0;
+  int tpr, rpc;
+  pick_shape(h, tpr, rpc);
+  int groups = (rows + rpc - 1) / rpc;
+  int grid = num_sms() * 2;
+  if (grid > groups) grid = groups;
+  int nparts = grid * rpc;
+  float* pg = scratch;
+  float* pb = rms ? nullptr : scratch + static_cast<size_t>(nparts) * h;
+  auto dzz = reinterpret_cast<const __nv_bfloat16*>(dz);
+  auto xx = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto g = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  auto dr = reinterpret_cast<const __nv_bfloat16*>(dres_in);
+  auto dxx = reinterpret_cast<__nv_bfloat16*>(dx);
+  if (rms)
+    norm_bwd_kernel<true><<<grid, tpr * rpc, 0, stream>>>(dzz, xx, g, mean, rstd, dr, dxx, pg, pb,
+                                                          rows, h, tpr, rpc);
+  else
+    norm_bwd_kernel<false><<<grid, tpr * rpc, 0, stream>>>(dzz, xx, g, mean, rstd, dr, dxx, pg, pb,
+                                                           rows, h, tpr, rpc);
+  dim3 fb(32, 8);
+  norm_bwd_finalize_kernel<<<(h + 31) / 32, fb, 0, stream>>>(
+      pg, pb, reinterpret_cast<__nv_bfloat16*>(dgamma), reinterpret_cast<__nv_bfloat16*>(dbeta),
+      nparts, h, accumulate);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

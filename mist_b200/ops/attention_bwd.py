@@ -1,0 +1,77 @@
+"""Attention backward dispatch.
+
+Given ``dout`` and what the forward saved (q, k, v, o and the per-row logsumexp) this
+produces dq, dk, dv.  On CUDA the tcgen05 backward kernel is used when the library
+exports it; otherwise the gradients come from a library attention kernel
+(``torch`` scaled-dot-product attention re-run under autograd), which is the A/B
+baseline and the interim path.  On CPU a plain fp32 recomputation is used.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .native import call, ptr, stream
+
+
+def _reference(dout, q, k, v, scale, causal):
+    from .functional import _ref_attention
+    qq, kk, vv = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    with torch.enable_grad():
+        out, _ = _ref_attention(qq, kk, vv, scale, causal)
+    dq, dk, dv = torch.autograd.grad(out, (qq, kk, vv), dout.float())
+    return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+
+def _library(dout, q, k, v, scale, causal):
+    qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
+    with torch.enable_grad():
+        out = F.scaled_dot_product_attention(
+            qq.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=causal, scale=scale,
+            enable_gqa=(q.shape[2] != k.shape[2]))
+    return torch.autograd.grad(out, (qq, kk, vv), dout.transpose(1, 2))
+
+
+def has_native_backward() -> bool:
+    lib = native.kernels()
+    return lib is not None and hasattr(lib, "mb_attn_bwd")
+
+
+def backward(dout, q, k, v, o, lse, scale, causal, out=None):
+    """Returns (dq, dk, dv); with ``out=(dq, dk, dv)`` writes into those (possibly strided) views."""
+    if not q.is_cuda:
+        grads = _reference(dout, q, k, v, scale, causal)
+    elif has_native_backward() and q.shape[2] == k.shape[2]:
+        from .functional import Settings
+        if Settings.attn_backend == "tcgen05":
+            return _native_backward(dout, q, k, v, o, lse, scale, causal, out)
+        grads = _library(dout, q, k, v, scale, causal)
+    else:
+        grads = _library(dout, q, k, v, scale, causal)
+    if out is not None:
+        for dst, src in zip(out, grads):
+            dst.copy_(src)
+        return out
+    return grads
+
+
+def _native_backward(dout, q, k, v, o, lse, scale, causal, out):
+    b, sq, nh, d = q.shape
+    sk = k.shape[1]
+    if out is None:
+        dq = torch.empty(b, sq, nh, d, dtype=q.dtype, device=q.device)
+        dk = torch.empty(b, sk, nh, d, dtype=q.dtype, device=q.device)
+        dv = torch.empty(b, sk, nh, d, dtype=q.dtype, device=q.device)
+    else:
+        dq, dk, dv = out
+    dout = dout.contiguous()
+    delta = torch.empty(b, nh, sq, dtype=torch.float32, device=q.device)
+    dq_acc = torch.zeros(b, nh, sq, d, dtype=torch.float32, device=q.device)
+    call("mb_attn_bwd", ptr(dout), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(dq_acc),
+         ptr(dq), ptr(dk), ptr(dv), b, sq, sk, nh, d,
+         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+         v.stride(0), v.stride(1), v.stride(2),
+         dq.stride(0), dq.stride(1), dq.stride(2), dk.stride(0), dk.stride(1), dk.stride(2),
+         dv.stride(0), dv.stride(1), dv.stride(2), float(scale), int(causal), stream())
+    return dq, dk, dv

@@ -1,0 +1,767 @@
+"""Differentiable front ends of the sm_100a kernels.
+
+Every op has two implementations with the same semantics:
+
+* CUDA tensors run the hand-written kernels of ``mist_b200/csrc`` (through
+  :mod:`mist_b200.ops.native`); a missing library on a GPU machine raises.
+* CPU tensors run a plain PyTorch reference, which is also the oracle that the GPU
+  numerics tests compare against.
+
+The ops mirror the fused operators the reference's module library is built on
+(reference: mist/modules/fused_dense.py:41-186 FusedDenseFunc, mist/modules/layer_norm.py:
+19-118 dropout_add_layer_norm, mist/modules/rotary.py:44-65, mist/modules/activations.py:
+115-149 swiglu, mist/modules/losses.py:48-176, mist/modules/flash_attn.py:46-213).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .native import call, ptr, stream, use_native
+
+# --------------------------------------------------------------------------- settings
+EPI_BIAS, EPI_GELU, EPI_SAVE_PRE, EPI_ACCUM, EPI_DGELU, EPI_OUT_FP32, EPI_RESIDUAL = 1, 2, 4, 8, 16, 32, 64
+
+
+class Settings:
+    """Process-wide kernel selection switches."""
+    gemm_backend = "tcgen05"      # "tcgen05" (ours) | "cublas" (library, A/B baseline)
+    attn_backend = "tcgen05"      # "tcgen05" (ours) | "sdpa" (library, A/B baseline)
+    attn_block_n = 64
+    gemm_max_ctas = 0             # >0 leaves SMs free for a concurrent communication kernel
+
+
+_scratch = {}
+
+
+def _get_scratch(numel: int, device, key="default") -> torch.Tensor:
+    """fp32 scratch that grows on demand; one buffer per (device, key)."""
+    k = (device, key)
+    buf = _scratch.get(k)
+    if buf is None or buf.numel() < numel:
+        buf = torch.empty(max(numel, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[k] = buf
+    return buf
+
+
+# ------------------------------------------------------------------------------ GEMM
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, bias=None, aux=None,
+         flags: int = 0, alpha: float = 1.0, tile_n: int = 0) -> torch.Tensor:
+    """``C[M,N] = A * B^T`` on tcgen05.
+
+    ``a`` is ``[M,K]`` (K-major) or, with ``a_mn``, stored ``[K,M]``; ``b`` is ``[N,K]``
+    or, with ``b_mn``, stored ``[K,N]``.  Both must be 2-D bf16 with unit inner stride.
+    """
+    assert a.dim() == 2 and b.dim() == 2 and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    assert K == Kb, (a.shape, b.shape, a_mn, b_mn)
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    assert out.stride(1) == 1 and out.shape == (M, N)
+    if out.dtype == torch.float32:
+        flags |= EPI_OUT_FP32
+    if bias is not None:
+        flags |= EPI_BIAS
+    call("mb_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+         int(a_mn), int(b_mn), flags, ptr(bias), ptr(aux), float(alpha), tile_n,
+         Settings.gemm_max_ctas, stream())
+    return out
+
+
+def _ref_act(x, activation):
+    if activation == "gelu":
+        return F.gelu(x, approximate="tanh")
+    return x
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = act(x W^T + b); wgrad may accumulate straight into a flat gradient bucket."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, activation, residual):
+        ctx.activation = activation
+        ctx.has_bias = bias is not None
+        ctx.has_residual = residual is not None
+        xs = x.shape
+        x2 = x.reshape(-1, xs[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        pre = None
+        if not use_native(x2):
+            y = F.linear(x2.float(), weight.float(), None if bias is None else bias.float())
+            if activation == "gelu":
+                pre = y.to(x.dtype)
+                y = _ref_act(pre.float(), activation)
+            if residual is not None:
+                y = y + residual.reshape(-1, weight.shape[0]).float()
+            y = y.to(x.dtype)
+        elif Settings.gemm_backend == "cublas":
+            y = F.linear(x2, weight, bias)
+            if activation == "gelu":
+                pre = y
+                y = F.gelu(pre, approximate="tanh")
+            if residual is not None:
+                y = y + residual.reshape(-1, weight.shape[0])
+        else:
+            flags = 0
+            aux = None
+            if activation == "gelu":
+                pre = torch.empty(x2.shape[0], weight.shape[0], dtype=x.dtype, device=x.device)
+                aux = pre
+                flags |= EPI_GELU | EPI_SAVE_PRE
+            elif residual is not None:
+                aux = residual.reshape(-1, weight.shape[0])
+                assert aux.is_contiguous()
+                flags |= EPI_RESIDUAL
+            y = gemm(x2, weight, bias=bias, aux=aux, flags=flags)
+        ctx.save_for_backward(x2, weight, pre)
+        return y.reshape(*xs[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, pre = ctx.saved_tensors
+        dys = dy.shape
+        dy2 = dy.reshape(-1, dys[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        native_path = use_native(dy2)
+        tc = native_path and Settings.gemm_backend != "cublas"
+        d_res = dy if ctx.has_residual else None
+        # activation backward (standalone kernel; the pre-activation was saved by the forward)
+        if ctx.activation == "gelu":
+            dy2 = gelu_bwd(dy2, pre)
+        dbias = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            dbias = colsum(dy2)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            if tc:
+                dx = gemm(dy2, weight, b_mn=True)
+            else:
+                dx = (dy2.float() @ weight.float()).to(dy.dtype) if not native_path else dy2 @ weight
+            dx = dx.reshape(*dys[:-1], weight.shape[1])
+        dw = None
+        if ctx.needs_input_grad[1]:
+            bucket = getattr(weight, "grad_bucket", None)
+            if bucket is not None:
+                accumulate = bool(getattr(weight, "grad_accumulate", False))
+                if tc:
+                    gemm(dy2, x2, a_mn=True, b_mn=True, out=bucket,
+                         flags=EPI_ACCUM if accumulate else 0)
+                else:
+                    g = dy2.t().float() @ x2.float() if not native_path else dy2.t() @ x2
+                    if accumulate:
+                        bucket.add_(g.to(bucket.dtype))
+                    else:
+                        bucket.copy_(g)
+                weight.grad_accumulate = True
+            else:
+                if tc:
+                    dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+                else:
+                    dw = (dy2.t().float() @ x2.float()).to(weight.dtype) if not native_path \
+                        else dy2.t() @ x2
+        return dx, dw, dbias, None, d_res
+
+
+def linear(x, weight, bias=None, activation: Optional[str] = None, residual=None):
+    """``act(x @ weight.T + bias) (+ residual)`` with the three GEMMs on tcgen05."""
+    return _LinearFn.apply(x, weight, bias, activation, residual)
+
+
+# ---------------------------------------------------------------- column sum (bias grad)
+def colsum(x2: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False):
+    rows, cols = x2.shape
+    if not use_native(x2):
+        s = x2.float().sum(0)
+        if out is None:
+            return s.to(x2.dtype)
+        out.copy_(out.float() + s if accumulate else s)
+        return out
+    if out is None:
+        out = torch.empty(cols, dtype=x2.dtype, device=x2.device)
+    parts = (rows + 255) // 256
+    scratch = _get_scratch(parts * cols, x2.device, "colsum")
+    call("mb_colsum", ptr(x2), ptr(out), ptr(scratch), rows, cols, int(out.dtype == torch.float32),
+         int(accumulate), stream())
+    return out
+
+
+# ------------------------------------------------------------------------- activations
+def gelu_fwd(x, bias=None):
+    if not use_native(x):
+        xx = x.float() if bias is None else x.float() + bias.float()
+        return F.gelu(xx, approximate="tanh").to(x.dtype)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    call("mb_gelu_fwd", ptr(x), ptr(bias), ptr(y), x.numel() // x.shape[-1], x.shape[-1], stream())
+    return y
+
+
+def gelu_bwd(dy, x, bias=None):
+    if not use_native(dy):
+        xx = (x.float() if bias is None else x.float() + bias.float()).requires_grad_(True)
+        with torch.enable_grad():
+            y = F.gelu(xx, approximate="tanh")
+        (g,) = torch.autograd.grad(y, xx, dy.float())
+        return g.to(dy.dtype)
+    dy = dy.contiguous()
+    dx = torch.empty_like(dy)
+    call("mb_gelu_bwd", ptr(dy), ptr(x), ptr(bias), ptr(dx), dy.numel() // dy.shape[-1], dy.shape[-1],
+         stream())
+    return dx
+
+
+class _GeluFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias):
+        ctx.save_for_backward(x, bias)
+        return gelu_fwd(x, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, bias = ctx.saved_tensors
+        dx = gelu_bwd(dy, x, bias)
+        db = colsum(dx.reshape(-1, dx.shape[-1])) if bias is not None else None
+        return dx, db
+
+
+def gelu(x, bias=None):
+    return _GeluFn.apply(x, bias)
+
+
+class _SwigluFn(torch.autograd.Function):
+    """[..., 2F] = [gate | up]  ->  silu(gate) * up"""
+
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        F_ = x.shape[-1] // 2
+        if not use_native(x):
+            g, u = x.float().chunk(2, dim=-1)
+            return (F.silu(g) * u).to(x.dtype)
+        x = x.contiguous()
+        out = torch.empty(*x.shape[:-1], F_, dtype=x.dtype, device=x.device)
+        call("mb_swiglu_fwd", ptr(x), ptr(out), x.numel() // x.shape[-1], F_, stream())
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (x,) = ctx.saved_tensors
+        F_ = x.shape[-1] // 2
+        if not use_native(x):
+            g, u = x.float().chunk(2, dim=-1)
+            s = torch.sigmoid(g)
+            d = dout.float()
+            dg = d * u * (s + g * s * (1 - s))
+            du = d * g * s
+            return torch.cat([dg, du], dim=-1).to(x.dtype)
+        dout = dout.contiguous()
+        din = torch.empty_like(x)
+        call("mb_swiglu_bwd", ptr(dout), ptr(x), ptr(din), x.numel() // x.shape[-1], F_, stream())
+        return din
+
+
+def swiglu(x):
+    return _SwigluFn.apply(x)
+
+
+class _BiasDropoutAddFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias, residual, p, seed):
+        ctx.p, ctx.seed = p, seed
+        ctx.has_bias, ctx.has_res = bias is not None, residual is not None
+        if not use_native(x):
+            y = x.float() if bias is None else x.float() + bias.float()
+            if p > 0:
+                gen = torch.Generator(device=x.device).manual_seed(seed)
+                mask = (torch.rand(y.shape, generator=gen, device=x.device) >= p).float() / (1 - p)
+                ctx.mask = mask
+                y = y * mask
+            if residual is not None:
+                y = y + residual.float()
+            return y.to(x.dtype)
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        call("mb_bias_dropout_add", ptr(x), ptr(bias), ptr(residual), ptr(out),
+             x.numel() // x.shape[-1], x.shape[-1], float(p), int(seed), stream())
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        dres = dout if ctx.has_res else None
+        if ctx.p > 0:
+            if not use_native(dout):
+                dx = (dout.float() * ctx.mask).to(dout.dtype)
+            else:
+                dout = dout.contiguous()
+                dx = torch.empty_like(dout)
+                call("mb_dropout_bwd", ptr(dout), ptr(dx), dout.numel(), float(ctx.p), int(ctx.seed),
+                     stream())
+        else:
+            dx = dout
+        db = colsum(dx.reshape(-1, dx.shape[-1])) if ctx.has_bias else None
+        return dx, db, dres, None, None
+
+
+def bias_dropout_add(x, bias, residual, p: float = 0.0, seed: int = 0):
+    """``residual + dropout(x + bias, p)``; the mask is regenerated, not stored."""
+    return _BiasDropoutAddFn.apply(x, bias, residual, float(p), int(seed))
+
+
+# ------------------------------------------------------------------------------- norms
+def _ref_norm(x, gamma, beta, eps, rms):
+    xf = x.float()
+    if rms:
+        rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        return (xf * rstd * gamma.float()), None, rstd
+    mean = xf.mean(-1, keepdim=True)
+    var = xf.var(-1, unbiased=False, keepdim=True)
+    rstd = torch.rsqrt(var + eps)
+    z = (xf - mean) * rstd * gamma.float()
+    if beta is not None:
+        z = z + beta.float()
+    return z, mean, rstd
+
+
+class _NormFn(torch.autograd.Function):
+    """z = norm(x0 + residual); optionally returns the sum as the new residual stream."""
+
+    @staticmethod
+    def forward(ctx, x0, residual, gamma, beta, eps, rms, prenorm):
+        ctx.rms, ctx.prenorm = rms, prenorm
+        ctx.has_res = residual is not None
+        ctx.has_beta = beta is not None
+        shp = x0.shape
+        h = shp[-1]
+        x0_2 = x0.reshape(-1, h)
+        rows = x0_2.shape[0]
+        if not use_native(x0):
+            x = x0_2.float() if residual is None else x0_2.float() + residual.reshape(-1, h).float()
+            x = x.to(x0.dtype)
+            z, mean, rstd = _ref_norm(x, gamma, beta, eps, rms)
+            z = z.to(x0.dtype)
+            mean = None if mean is None else mean.reshape(-1)
+            rstd = rstd.reshape(-1)
+        else:
+            x0_2 = x0_2.contiguous()
+            res2 = None if residual is None else residual.reshape(-1, h).contiguous()
+            z = torch.empty_like(x0_2)
+            need_x = residual is not None
+            x = torch.empty_like(x0_2) if need_x else x0_2
+            mean = None if rms else torch.empty(rows, dtype=torch.float32, device=x0.device)
+            rstd = torch.empty(rows, dtype=torch.float32, device=x0.device)
+            call("mb_norm_fwd", ptr(x0_2), ptr(res2), ptr(gamma), ptr(beta), ptr(z),
+                 ptr(x) if need_x else 0, ptr(mean), ptr(rstd), rows, h, float(eps), int(rms), stream())
+        ctx.save_for_backward(x, gamma, mean, rstd)
+        z = z.reshape(shp)
+        if prenorm:
+            return z, x.reshape(shp)
+        return z
+
+    @staticmethod
+    def backward(ctx, dz, *args):
+        x, gamma, mean, rstd = ctx.saved_tensors
+        dres_in = args[0] if (ctx.prenorm and len(args) > 0) else None
+        shp = dz.shape
+        h = shp[-1]
+        dz2 = dz.reshape(-1, h)
+        rows = dz2.shape[0]
+        if not use_native(dz):
+            xf = x.reshape(-1, h).float()
+            g = gamma.float()
+            if ctx.rms:
+                xh = xf * rstd[:, None]
+                m1 = 0.0
+            else:
+                xh = (xf - mean[:, None]) * rstd[:, None]
+            dy = dz2.float() * g
+            if not ctx.rms:
+                m1 = dy.mean(-1, keepdim=True)
+            m2 = (dy * xh).mean(-1, keepdim=True)
+            dx = rstd[:, None] * (dy - m1 - xh * m2)
+            if dres_in is not None:
+                dx = dx + dres_in.reshape(-1, h).float()
+            dx = dx.to(dz.dtype)
+            dgamma = (dz2.float() * xh).sum(0).to(gamma.dtype)
+            dbeta = dz2.float().sum(0).to(gamma.dtype) if ctx.has_beta else None
+        else:
+            dz2 = dz2.contiguous()
+            dr = None if dres_in is None else dres_in.reshape(-1, h).contiguous()
+            dx = torch.empty_like(dz2)
+            dgamma = torch.empty_like(gamma)
+            dbeta = torch.empty_like(gamma) if ctx.has_beta else None
+            nrows = native.kernels().mb_norm_bwd_scratch_rows(rows, h)
+            scratch = _get_scratch(2 * nrows * h, dz.device, "norm")
+            call("mb_norm_bwd", ptr(dz2), ptr(x), ptr(gamma), ptr(mean), ptr(rstd), ptr(dr), ptr(dx),
+                 ptr(dgamma), ptr(dbeta), ptr(scratch), rows, h, int(ctx.rms), 0, stream())
+        dx = dx.reshape(shp)
+        return dx, (dx if ctx.has_res else None), dgamma, dbeta, None, None, None
+
+
+def layer_norm(x, gamma, beta, eps=1e-5, residual=None, prenorm=False):
+    return _NormFn.apply(x, residual, gamma, beta, eps, False, prenorm)
+
+
+def rms_norm(x, gamma, eps=1e-5, residual=None, prenorm=False):
+    return _NormFn.apply(x, residual, gamma, None, eps, True, prenorm)
+
+
+# ------------------------------------------------------------------------------ rotary
+_rope_cache = {}
+
+
+def rope_tables(seq: int, rot_dim: int, base: float, device):
+    key = (seq, rot_dim, base, str(device))
+    if key not in _rope_cache:
+        inv = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float32, device=device) / rot_dim))
+        t = torch.arange(seq, dtype=torch.float32, device=device)
+        fr = torch.outer(t, inv)
+        _rope_cache[key] = (fr.cos().contiguous(), fr.sin().contiguous())
+    return _rope_cache[key]
+
+
+def _rope_apply(qkv, cos, sin, rot, conj, n_rot):
+    # qkv: [b, s, 3, nh, d] (or [b, s, n, nh, d]); rotate slots [0, n_rot)
+    b, s, n3, nh, d = qkv.shape
+    if not use_native(qkv):
+        out = qkv.clone()
+        x = qkv[:, :, :n_rot, :, :rot].float()
+        x1, x2 = x[..., : rot // 2], x[..., rot // 2:]
+        c = cos[:s].view(1, s, 1, 1, rot // 2)
+        sn = sin[:s].view(1, s, 1, 1, rot // 2)
+        if conj:
+            sn = -sn
+        out[:, :, :n_rot, :, : rot // 2] = (x1 * c - x2 * sn).to(qkv.dtype)
+        out[:, :, :n_rot, :, rot // 2: rot] = (x1 * sn + x2 * c).to(qkv.dtype)
+        return out
+    assert qkv.is_contiguous()
+    call("mb_rope", ptr(qkv), ptr(cos), ptr(sin), b * s, s, nh, d, rot, int(conj), n_rot, n3 * nh * d,
+         stream())
+    return qkv
+
+
+def apply_rotary_qkv_(qkv, cos, sin, rot_dim: int, conj: bool = False):
+    """Rotates q and k of a packed ``[b, s, 3, heads, d]`` tensor (in place on CUDA).
+    Not differentiable by itself: :func:`attention_qkvpacked` applies it inside its
+    forward and its conjugate inside its backward."""
+    return _rope_apply(qkv, cos, sin, rot_dim, conj, 2)
+
+
+# --------------------------------------------------------------------------- attention
+def _ref_attention(q, k, v, scale, causal):
+    # q: [b, sq, nh, d]; k, v: [b, sk, nh_kv, d]
+    b, sq, nh, d = q.shape
+    sk, nkv = k.shape[1], k.shape[2]
+    if nkv != nh:
+        k = k.repeat_interleave(nh // nkv, dim=2)
+        v = v.repeat_interleave(nh // nkv, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    if causal:
+        mask = torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(sk - sq)
+        s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.softmax(s, dim=-1)
+    o = torch.einsum("bhqk,bkhd->bqhd", p, v.float())
+    return o.to(q.dtype), lse
+
+
+def attn_fwd(q, k, v, scale, causal, block_n=None):
+    """Forward only: returns (o [b,sq,nh,d], lse [b,nh,sq] fp32)."""
+    if not use_native(q):
+        return _ref_attention(q, k, v, scale, causal)
+    b, sq, nh, d = q.shape
+    sk, nkv = k.shape[1], k.shape[2]
+    assert q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1
+    o = torch.empty(b, sq, nh, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(b, nh, sq, dtype=torch.float32, device=q.device)
+    call("mb_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), b, sq, sk, nh, nkv, d,
+         q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+         v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
+         float(scale), int(causal), block_n or Settings.attn_block_n, stream())
+    return o, lse
+
+
+def _attn_bwd_library(dout, q, k, v, o, lse, scale, causal):
+    """Backward through a library kernel (used until the tcgen05 backward covers the case)."""
+    qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
+    with torch.enable_grad():
+        nh, nkv = q.shape[2], k.shape[2]
+        out = F.scaled_dot_product_attention(
+            qq.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=causal, scale=scale,
+            enable_gqa=(nh != nkv))
+    return torch.autograd.grad(out, (qq, kk, vv), dout.transpose(1, 2))
+
+
+class _AttnFn(torch.autograd.Function):
+    """Attention over separate q / k / v tensors (views allowed)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, causal):
+        o, lse = attn_fwd(q, k, v, scale, causal)
+        ctx.scale, ctx.causal = scale, causal
+        ctx.save_for_backward(q, k, v, o, lse)
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, o, lse = ctx.saved_tensors
+        from . import attention_bwd
+        dq, dk, dv = attention_bwd.backward(dout, q, k, v, o, lse, ctx.scale, ctx.causal)
+        return dq, dk, dv, None, None
+
+
+def attention(q, k, v, scale: Optional[float] = None, causal: bool = True):
+    """Multi-head attention; q ``[b,sq,nh,d]``, k/v ``[b,sk,nh_kv,d]`` (views allowed)."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    return _AttnFn.apply(q, k, v, float(scale), bool(causal))
+
+
+class _PackedAttnFn(torch.autograd.Function):
+    """Rotary embedding + attention on a packed ``[b, s, 3, heads, d]`` projection output.
+
+    The rotation is applied in place on the projection output (nothing else keeps that
+    tensor: the producing linear saves its input, not its output) and the gradient is
+    produced as one packed tensor, so autograd never splits or re-concatenates q/k/v."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, rot, scale, causal):
+        if rot:
+            qkv = _rope_apply(qkv, cos, sin, rot, False, 2)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        o, lse = attn_fwd(q, k, v, scale, causal)
+        ctx.rot, ctx.scale, ctx.causal = rot, scale, causal
+        ctx.save_for_backward(qkv, o, lse, cos, sin)
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, o, lse, cos, sin = ctx.saved_tensors
+        from . import attention_bwd
+        dqkv = torch.empty_like(qkv)
+        attention_bwd.backward(dout, qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], o, lse, ctx.scale,
+                               ctx.causal, out=(dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]))
+        if ctx.rot:
+            dqkv = _rope_apply(dqkv, cos, sin, ctx.rot, True, 2)
+        return dqkv, None, None, None, None, None
+
+
+def attention_qkvpacked(qkv, scale: Optional[float] = None, causal: bool = True, rotary=None):
+    """``rotary`` is ``None`` or ``(cos, sin, rot_dim)`` from :func:`rope_tables`."""
+    if scale is None:
+        scale = 1.0 / math.sqrt(qkv.shape[-1])
+    cos, sin, rot = rotary if rotary is not None else (None, None, 0)
+    return _PackedAttnFn.apply(qkv, cos, sin, int(rot), float(scale), bool(causal))
+
+
+# ------------------------------------------------------- non-flash attention softmax
+class _CausalSoftmaxFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scale, causal):
+        ctx.scale = scale
+        sq, sk = x.shape[-2], x.shape[-1]
+        if not use_native(x):
+            s = x.float() * scale
+            if causal:
+                mask = torch.ones(sq, sk, dtype=torch.bool, device=x.device).tril(sk - sq)
+                s = s.masked_fill(~mask, float("-inf"))
+            y = torch.softmax(s, dim=-1).to(x.dtype)
+        else:
+            x = x.contiguous()
+            y = torch.empty_like(x)
+            call("mb_causal_softmax_fwd", ptr(x), ptr(y), x.numel() // sk, sq, sk, float(scale),
+                 int(causal), stream())
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        sk = y.shape[-1]
+        if not use_native(y):
+            yf, df = y.float(), dy.float()
+            dx = ctx.scale * yf * (df - (df * yf).sum(-1, keepdim=True))
+            return dx.to(y.dtype), None, None
+        dy = dy.contiguous()
+        dx = torch.empty_like(y)
+        call("mb_causal_softmax_bwd", ptr(dy), ptr(y), ptr(dx), y.numel() // sk, sk, float(ctx.scale),
+             stream())
+        return dx, None, None
+
+
+def scaled_causal_softmax(x, scale: float, causal: bool = True):
+    return _CausalSoftmaxFn.apply(x, float(scale), bool(causal))
+
+
+# ----------------------------------------------------------------------- cross entropy
+class _XentFn(torch.autograd.Function):
+    """Vocab-parallel cross entropy; logits ``[rows, v_local]`` are overwritten by the
+    gradient in the backward pass (as in the reference's in-place variant)."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, v0, group, ignore_index):
+        rows, cols = logits.shape
+        ctx.v0, ctx.ignore = v0, ignore_index
+        tp = group is not None and torch.distributed.get_world_size(group) > 1
+        if not use_native(logits):
+            lf = logits.float()
+            m = lf.max(-1).values
+            if tp:
+                torch.distributed.all_reduce(m, op=torch.distributed.ReduceOp.MAX, group=group)
+            se = torch.exp(lf - m[:, None]).sum(-1)
+            lab = labels - v0
+            inr = (lab >= 0) & (lab < cols)
+            tgt = torch.where(inr, lf.gather(1, lab.clamp(0, cols - 1)[:, None])[:, 0],
+                              torch.zeros_like(m))
+            if tp:
+                torch.distributed.all_reduce(se, group=group)
+                torch.distributed.all_reduce(tgt, group=group)
+            lse = se.log() + m
+            loss = torch.where(labels == ignore_index, torch.zeros_like(lse), lse - tgt)
+        else:
+            assert logits.stride(1) == 1
+            stats = torch.empty(rows, 3, dtype=torch.float32, device=logits.device)
+            call("mb_xent_stats", ptr(logits), ptr(labels), ptr(stats), rows, cols, logits.stride(0), v0,
+                 stream())
+            if tp:
+                gm = stats[:, 0].clone()
+                torch.distributed.all_reduce(gm, op=torch.distributed.ReduceOp.MAX, group=group)
+                rest = stats[:, 1:].clone()
+                rest[:, 0] *= torch.exp(stats[:, 0] - gm)
+                torch.distributed.all_reduce(rest, group=group)
+                stats = torch.cat([gm[:, None], rest], dim=1).contiguous()
+            loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+            lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+            call("mb_xent_loss", ptr(stats), ptr(labels), ptr(loss), ptr(lse), rows, ignore_index,
+                 stream())
+        ctx.save_for_backward(logits, labels, lse)
+        return loss
+
+    @staticmethod
+    def backward(ctx, gloss):
+        logits, labels, lse = ctx.saved_tensors
+        rows, cols = logits.shape
+        if not use_native(logits):
+            p = torch.exp(logits.float() - lse[:, None])
+            lab = labels - ctx.v0
+            inr = (lab >= 0) & (lab < cols)
+            oh = torch.zeros_like(p)
+            oh[inr, lab[inr]] = 1.0
+            g = (p - oh) * gloss.float()[:, None]
+            g = torch.where((labels == ctx.ignore)[:, None], torch.zeros_like(g), g)
+            return g.to(logits.dtype), None, None, None, None
+        gloss = gloss.contiguous().float()
+        call("mb_xent_bwd", ptr(logits), ptr(labels), ptr(lse), ptr(gloss), 1.0, rows, cols,
+             logits.stride(0), ctx.v0, ctx.ignore, 0, stream())
+        return logits, None, None, None, None
+
+
+def cross_entropy(logits, labels, vocab_start: int = 0, group=None, ignore_index: int = -100):
+    """Per-row loss (fp32) of ``[rows, v_local]`` logits against global ``labels``."""
+    return _XentFn.apply(logits, labels, int(vocab_start), group, int(ignore_index))
+
+
+# --------------------------------------------------------------------------- embedding
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, wte, wpe, v0):
+        b, s = ids.shape
+        h = wte.shape[1]
+        ctx.v0 = v0
+        ctx.has_pos = wpe is not None
+        ctx.save_for_backward(ids, wte, wpe)
+        v1 = v0 + wte.shape[0]
+        if not use_native(wte):
+            loc = ids - v0
+            inr = (loc >= 0) & (loc < wte.shape[0])
+            out = wte[loc.clamp(0, wte.shape[0] - 1)].float() * inr[..., None].float()
+            if wpe is not None:
+                out = out + wpe[:s].float()[None]
+            return out.to(wte.dtype)
+        ids = ids.contiguous()
+        out = torch.empty(b, s, h, dtype=wte.dtype, device=wte.device)
+        call("mb_embedding_fwd", ptr(ids), ptr(wte), ptr(wpe), ptr(out), b * s, s, h, v0, v1, stream())
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        ids, wte, wpe = ctx.saved_tensors
+        b, s = ids.shape
+        h = wte.shape[1]
+        v0, v1 = ctx.v0, ctx.v0 + wte.shape[0]
+        dwte = torch.zeros(wte.shape, dtype=torch.float32, device=wte.device)
+        dwpe = torch.zeros(wpe.shape, dtype=torch.float32, device=wte.device) if ctx.has_pos else None
+        if not use_native(wte):
+            loc = ids - v0
+            inr = (loc >= 0) & (loc < wte.shape[0])
+            d2 = dout.float().reshape(-1, h)
+            sel = inr.reshape(-1)
+            dwte.index_add_(0, loc.reshape(-1)[sel], d2[sel])
+            if dwpe is not None:
+                dwpe[:s] += dout.float().sum(0)
+        else:
+            dout = dout.contiguous()
+            call("mb_embedding_bwd", ptr(ids.contiguous()), ptr(dout), ptr(dwte), ptr(dwpe), b, s, h, v0,
+                 v1, stream())
+        return None, dwte.to(wte.dtype), (None if dwpe is None else dwpe.to(wpe.dtype)), None
+
+
+def embedding(ids, wte, wpe=None, vocab_start: int = 0):
+    """``wte[ids - vocab_start]`` (zero outside this rank's slice) ``+ wpe[position]``."""
+    return _EmbeddingFn.apply(ids, wte, wpe, int(vocab_start))
+
+
+# --------------------------------------------------------------------- optimizer / casts
+def adam_step(master, exp_avg, exp_avg_sq, grad, model, *, lr, beta1, beta2, eps, weight_decay, step,
+              inv_scale=1.0, adamw=True):
+    """One fused Adam(W) step on a flat shard; writes the bf16 model copy when given."""
+    if not use_native(master):
+        g = grad.float() * inv_scale
+        if not adamw and weight_decay:
+            g = g + weight_decay * master
+        exp_avg.mul_(beta1).add_(g, alpha=1 - beta1)
+        exp_avg_sq.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        mh = exp_avg / (1 - beta1 ** step)
+        vh = exp_avg_sq / (1 - beta2 ** step)
+        upd = mh / (vh.sqrt() + eps)
+        if adamw and weight_decay:
+            upd = upd + weight_decay * master
+        master.add_(upd, alpha=-lr)
+        if model is not None:
+            model.copy_(master)
+        return
+    n = master.numel()
+    call("mb_adam_step", ptr(master), ptr(exp_avg), ptr(exp_avg_sq), ptr(grad),
+         int(grad.dtype == torch.float32), ptr(model), n, float(lr), float(beta1), float(beta2),
+         float(eps), float(weight_decay), int(step), float(inv_scale), int(adamw), stream())
+
+
+def cast_to_bf16(src_f32, dst_bf16, scale: float = 1.0):
+    if not use_native(src_f32):
+        dst_bf16.copy_(src_f32 * scale)
+        return dst_bf16
+    call("mb_cast_f32_to_bf16", ptr(src_f32), ptr(dst_bf16), src_f32.numel(), float(scale), stream())
+    return dst_bf16
+
+
+def accumulate_grad(src_bf16, dst, scale: float = 1.0, accumulate: bool = True):
+    """dst (fp32 or bf16) (+)= scale * src (bf16)."""
+    if not use_native(src_bf16):
+        v = src_bf16.float() * scale
+        dst.copy_((dst.float() + v) if accumulate else v)
+        return dst
+    if dst.dtype == torch.float32:
+        call("mb_axpy_bf16_to_f32", ptr(src_bf16), ptr(dst), src_bf16.numel(), float(scale),
+             int(accumulate), stream())
+    else:
+        assert scale == 1.0 and accumulate
+        call("mb_add_bf16", ptr(src_bf16), ptr(dst), src_bf16.numel(), stream())
+    return dst

@@ -1,0 +1,76 @@
+"""tcgen05 attention forward (and the backward path in use) against fp32 references."""
+import math
+
+import pytest
+import torch
+
+from mist_b200.ops import functional as F
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("d", [128, 80, 64, 96])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("block_n", [64, 128])
+def test_attn_fwd_packed(d, causal, block_n):
+    torch.manual_seed(0)
+    b, s, nh = 2, 384, 3
+    qkv = torch.randn(b, s, 3, nh, d, device=DEV, dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    scale = 1 / math.sqrt(d)
+    o, lse = F.attn_fwd(q, k, v, scale, causal, block_n=block_n)
+    o_ref, lse_ref = F._ref_attention(q.float(), k.float(), v.float(), scale, causal)
+    assert _rel_err(o, o_ref) < 2e-2
+    assert torch.allclose(lse, lse_ref, atol=2e-2, rtol=1e-3)
+
+
+def test_attn_fwd_ragged_and_gqa():
+    torch.manual_seed(1)
+    b, sq, nh, nkv, d = 1, 200, 4, 2, 128
+    q = torch.randn(b, sq, nh, d, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(b, sq, nkv, d, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(b, sq, nkv, d, device=DEV, dtype=torch.bfloat16)
+    o, lse = F.attn_fwd(q, k, v, 0.1, True)
+    o_ref, lse_ref = F._ref_attention(q.float(), k.float(), v.float(), 0.1, True)
+    assert _rel_err(o, o_ref) < 2e-2
+    assert torch.allclose(lse, lse_ref, atol=2e-2, rtol=1e-3)
+
+
+def test_attn_fwd_long_sequence():
+    torch.manual_seed(2)
+    b, s, nh, d = 1, 2048, 2, 128
+    qkv = torch.randn(b, s, 3, nh, d, device=DEV, dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    o, lse = F.attn_fwd(q, k, v, 1 / math.sqrt(d), True)
+    o_ref = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True).transpose(1, 2)
+    assert _rel_err(o, o_ref) < 2e-2
+
+
+@pytest.mark.parametrize("d,rot", [(128, 32), (80, 0)])
+def test_attention_qkvpacked_grad(d, rot):
+    torch.manual_seed(3)
+    b, s, nh = 2, 256, 2
+    qkv = torch.randn(b, s, 3, nh, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    rotary = None
+    if rot:
+        cos, sin = F.rope_tables(s, rot, 10000.0, DEV)
+        rotary = (cos, sin, rot)
+    g = torch.randn(b, s, nh, d, device=DEV, dtype=torch.bfloat16)
+    o = F.attention_qkvpacked(qkv.clone(), rotary=rotary)
+    # gradient w.r.t. the clone's source
+    qkv2 = qkv.detach().clone().requires_grad_(True)
+    o2 = F.attention_qkvpacked(qkv2 * 1.0, rotary=rotary)
+    o2.backward(g)
+    ref_in = qkv.detach().cpu().float().requires_grad_(True)
+    rot_cpu = None if rotary is None else (rotary[0].cpu(), rotary[1].cpu(), rot)
+    o_ref = F.attention_qkvpacked(ref_in * 1.0, rotary=rot_cpu)
+    o_ref.backward(g.cpu().float())
+    assert _rel_err(o.cpu(), o_ref) < 2e-2
+    assert _rel_err(qkv2.grad.cpu(), ref_in.grad) < 3e-2

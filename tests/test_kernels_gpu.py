@@ -1,0 +1,237 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from mist_b200.ops import functional as F
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (384, 640, 192), (1000, 520, 264), (2048, 2560, 2560)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_layouts(M, N, K, a_mn, b_mn, tile_n):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operand needs a leading dimension that is a multiple of 8")
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    out = F.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn, tile_n=tile_n)
+    assert _rel_err(out, ref) < 1e-2
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 320
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t() + bias.float()
+    out = F.gemm(a, b, bias=bias)
+    assert _rel_err(out, ref) < 1e-2
+    pre = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    out = F.gemm(a, b, bias=bias, aux=pre, flags=F.EPI_GELU | F.EPI_SAVE_PRE)
+    assert _rel_err(pre, ref) < 1e-2
+    assert _rel_err(out, torch.nn.functional.gelu(ref, approximate="tanh")) < 1e-2
+    # fp32 accumulate
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    ref2 = acc + a.float() @ b.float().t()
+    F.gemm(a, b, out=acc, flags=F.EPI_ACCUM)
+    assert _rel_err(acc, ref2) < 1e-3
+    # bf16 accumulate + residual
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    out = F.gemm(a, b, aux=res, flags=F.EPI_RESIDUAL)
+    assert _rel_err(out, a.float() @ b.float().t() + res.float()) < 1e-2
+
+
+def test_linear_autograd_matches_reference():
+    torch.manual_seed(2)
+    x = torch.randn(4, 128, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(512, 256, device=DEV, dtype=torch.bfloat16) * 0.05).requires_grad_(True)
+    b = torch.randn(512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = F.linear(x, w, b, activation="gelu")
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.gelu(torch.nn.functional.linear(xr, wr, br), approximate="tanh")
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2
+    assert _rel_err(x.grad, xr.grad) < 2e-2
+    assert _rel_err(w.grad, wr.grad) < 2e-2
+    assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+@pytest.mark.parametrize("h", [256, 2048, 2560, 4096, 5120, 6144, 8192])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_fwd_bwd(h, rms):
+    torch.manual_seed(3)
+    rows = 777
+    x0 = torch.randn(rows, h, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    res = torch.randn(rows, h, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = (1 + 0.1 * torch.randn(h, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    b = (0.1 * torch.randn(h, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    if rms:
+        z, xs = F.rms_norm(x0, g, 1e-5, residual=res, prenorm=True)
+    else:
+        z, xs = F.layer_norm(x0, g, b, 1e-5, residual=res, prenorm=True)
+    dz, dxs = torch.randn_like(z), torch.randn_like(xs)
+    torch.autograd.backward([z, xs], [dz, dxs])
+
+    x0r, resr, gr, br = (t.detach().float().requires_grad_(True) for t in (x0, res, g, b))
+    xsr = (x0r + resr).to(torch.bfloat16).float()  # the kernel rounds the stream to bf16
+    xsr_leaf = (x0r + resr)
+    if rms:
+        zr = xsr_leaf * torch.rsqrt(xsr_leaf.pow(2).mean(-1, keepdim=True) + 1e-5) * gr
+    else:
+        zr = torch.nn.functional.layer_norm(xsr_leaf, (h,), gr, br, 1e-5)
+    torch.autograd.backward([zr, xsr_leaf], [dz.float(), dxs.float()])
+    assert _rel_err(z, zr) < 1e-2
+    assert _rel_err(xs, xsr) < 1e-2
+    assert _rel_err(x0.grad, x0r.grad) < 1e-2
+    assert _rel_err(res.grad, resr.grad) < 1e-2
+    assert _rel_err(g.grad, gr.grad) < 2e-2
+    if not rms:
+        assert _rel_err(b.grad, br.grad) < 2e-2
+
+
+def test_gelu_swiglu_bias_dropout_add():
+    torch.manual_seed(4)
+    x = torch.randn(333, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    bias = torch.randn(1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = F.gelu(x, bias)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, br = x.detach().float().requires_grad_(True), bias.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.gelu(xr + br, approximate="tanh")
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2 and _rel_err(bias.grad, br.grad) < 2e-2
+
+    x = torch.randn(333, 2 * 768, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = F.swiglu(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    a, u = xr.chunk(2, -1)
+    yr = torch.nn.functional.silu(a) * u
+    yr.backward(g.float())
+    assert _rel_err(y, yr) < 1e-2 and _rel_err(x.grad, xr.grad) < 1e-2
+
+    x = torch.randn(64, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(64, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = F.bias_dropout_add(x, b, r, 0.0)
+    assert _rel_err(y, x.float() + b.float() + r.float()) < 1e-2
+    y.sum().backward()
+    assert torch.allclose(x.grad.float(), torch.ones_like(x.grad).float())
+    # dropout: mask regenerated identically in backward, keep-rate close to 1-p
+    y = F.bias_dropout_add(x, None, None, 0.25, seed=1234)
+    kept = (y != 0).float().mean().item()
+    assert abs(kept - 0.75) < 0.02
+    x.grad = None
+    y.backward(torch.ones_like(y))
+    assert torch.equal(x.grad != 0, y != 0)
+
+
+@pytest.mark.parametrize("d,rot", [(128, 128), (128, 32), (80, 16), (64, 64)])
+def test_rope(d, rot):
+    torch.manual_seed(5)
+    b, s, nh = 2, 96, 6
+    qkv = torch.randn(b, s, 3, nh, d, device=DEV, dtype=torch.bfloat16)
+    cos, sin = F.rope_tables(s, rot, 10000.0, DEV)
+    ref = F._rope_apply(qkv.cpu(), cos.cpu(), sin.cpu(), rot, False, 2)
+    out = F.apply_rotary_qkv_(qkv.clone(), cos, sin, rot)
+    assert _rel_err(out.cpu(), ref) < 1e-2
+    back = F.apply_rotary_qkv_(out.clone(), cos, sin, rot, conj=True)
+    assert _rel_err(back, qkv) < 2e-2
+
+
+@pytest.mark.parametrize("cols,v0", [(50304, 0), (12576, 12576), (32000, 0), (1000, 0)])
+def test_cross_entropy(cols, v0):
+    torch.manual_seed(6)
+    rows = 300
+    logits = (torch.randn(rows, cols, device=DEV) * 3).to(torch.bfloat16).requires_grad_(True)
+    labels = torch.randint(v0, v0 + cols, (rows,), device=DEV)
+    loss = F.cross_entropy(logits, labels, vocab_start=v0)
+    ref_in = logits.detach().float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, labels - v0, reduction="none")
+    assert torch.allclose(loss, ref, atol=2e-2, rtol=1e-2)
+    w = torch.rand(rows, device=DEV)
+    (loss * w).sum().backward()
+    (ref * w).sum().backward()
+    assert _rel_err(logits.grad, ref_in.grad) < 2e-2
+
+
+def test_embedding_fwd_bwd():
+    torch.manual_seed(7)
+    b, s, h, v = 3, 64, 256, 1000
+    ids = torch.randint(0, v, (b, s), device=DEV)
+    wte = torch.randn(v, h, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    wpe = torch.randn(s, h, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = F.embedding(ids, wte, wpe)
+    ref = wte.float()[ids] + wpe.float()[None]
+    assert _rel_err(out, ref) < 1e-2
+    g = torch.randn_like(out)
+    out.backward(g)
+    wr = wte.detach().float().requires_grad_(True)
+    pr = wpe.detach().float().requires_grad_(True)
+    (wr[ids] + pr[None]).backward(g.float())
+    assert _rel_err(wte.grad, wr.grad) < 1e-2 and _rel_err(wpe.grad, pr.grad) < 1e-2
+    # vocab-parallel slice: ids outside [v0, v1) give zero rows
+    half = F.embedding(ids, wte.detach()[500:], None, vocab_start=500)
+    mask = (ids >= 500)[..., None].float()
+    assert _rel_err(half, wte.detach().float()[ids] * mask) < 1e-2
+
+
+def test_causal_softmax():
+    torch.manual_seed(8)
+    x = torch.randn(2, 4, 128, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = F.scaled_causal_softmax(x, 0.125)
+    xr = x.detach().float().requires_grad_(True)
+    mask = torch.ones(128, 128, dtype=torch.bool, device=DEV).tril()
+    yr = torch.softmax((xr * 0.125).masked_fill(~mask, float("-inf")), -1)
+    assert _rel_err(y, yr) < 1e-2
+    g = torch.randn_like(y)
+    y.backward(g)
+    yr.backward(g.float())
+    assert _rel_err(x.grad, xr.grad) < 2e-2
+
+
+def test_adam_matches_torch():
+    torch.manual_seed(9)
+    n = 100003
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV).to(torch.bfloat16)
+    ref = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    model = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    for step in range(1, 4):
+        ref.grad = g.float() * 0.5
+        opt.step()
+        F.adam_step(p, m, v, g, model, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                    step=step, inv_scale=0.5, adamw=True)
+    assert torch.allclose(p, ref.detach(), atol=1e-5, rtol=1e-4)
+    assert _rel_err(model, ref.detach()) < 1e-2
+
+
+def test_cast_and_accumulate():
+    src = torch.randn(10001, device=DEV)
+    dst = torch.empty(10001, device=DEV, dtype=torch.bfloat16)
+    F.cast_to_bf16(src, dst, 2.0)
+    assert _rel_err(dst, src * 2) < 1e-2
+    acc = torch.ones(10001, device=DEV)
+    F.accumulate_grad(dst, acc, 0.5, True)
+    assert _rel_err(acc, 1 + dst.float() * 0.5) < 1e-5
