@@ -1,0 +1,112 @@
+"""Public training API: configuration name -> a session that runs training iterations.
+
+    session = build_training("config", ["experiment=b200-gpt3-2.7b-dp8-zero2"])
+    loss = session.step(input_ids_on_host, labels_on_host)
+
+The session hides the strategy: data/tensor/pipeline layout, ZeRO level, activation
+checkpointing, offloading and the overlap schedule all come from the ``strategy`` block
+of the configuration (the file the tuner writes).  The exec entry point
+(``benchmark/mist_b200/exec/benchmark_one_case.py``) and ``bench.py`` are thin wrappers
+around it.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .config import MistConfig, StageStrategy, load_config
+from .models.provider import base_model_provider, get_inputs_provider
+from .parallel.engine import TrainEngine
+from .parallel.state import ParallelState
+
+
+def _stage_layer_range(cfg: MistConfig, stage: int):
+    parts = cfg.strategy.layer_partitions
+    start = sum(parts[:stage])
+    return start, start + parts[stage]
+
+
+class TrainingSession:
+    def __init__(self, cfg: MistConfig, comm_backend: Optional[str] = None, seed: int = 1234,
+                 device: Optional[torch.device] = None, hp: Optional[Dict] = None):
+        self.cfg = cfg
+        world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+        assert world == cfg.hardware.num_devices or world == 1, \
+            f"configuration describes {cfg.hardware.num_devices} devices, job has {world}"
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = device
+        self.ps = ParallelState.from_config(cfg) if world > 1 else ParallelState.from_config(cfg, rank=0, create_groups=False)
+        st = cfg.strategy
+        stage = self.ps.stage
+        self.strategy = st.stage(stage)
+        self.G = st.gradient_accumulation_steps
+        self.micro_batch = self.strategy.micro_batch_size
+        self.seq_len = cfg.training.max_sequence_length
+        self.sequence_parallel = bool(cfg.get("sequence_parallel", False)) and self.ps.tp_size > 1
+        self.comm_backend = comm_backend or cfg.get("comm_backend", "nccl")
+        dtype = cfg.training.params_dtype
+        # same seed on every data-parallel replica; tensor-parallel ranks draw different slices
+        torch.manual_seed(seed + 1000 * self.ps.tp_rank + 17 * stage)
+        lr = _stage_layer_range(cfg, stage)
+        multi_stage = st.num_stages > 1
+        self.model = base_model_provider(
+            cfg.model, process_groups=self.ps.tp_group, pre_post_process_group=self.ps.tp_group,
+            pre_process=self.ps.is_first_stage, post_process=self.ps.is_last_stage,
+            layer_range=lr if multi_stage else None, sequence_parallel=self.sequence_parallel,
+            device=device, dtype=dtype)
+        pre_post = StageStrategy.from_vector(st.pre_post_strategy_array) if st.pre_post_strategy == "preset" else None
+        self.engine = TrainEngine(self.model, self.ps, self.strategy, self.G, st.gradient_checkpointing[stage],
+                                  hp=hp, comm_backend=self.comm_backend, overlap=bool(cfg.get("overlap", True)),
+                                  pre_post_strategy=pre_post)
+        self.pipeline = None
+        if multi_stage:
+            from .parallel.pipeline import PipelineSchedule
+            self.pipeline = PipelineSchedule(self)
+        self._h2d_stream = torch.cuda.Stream() if device.type == "cuda" else None
+
+    # ------------------------------------------------------------------------------ steps
+    def _split_micro(self, ids, labels):
+        if self.G == 1:
+            return [{"input_ids": ids, "labels": labels}]
+        return [{"input_ids": a, "labels": b} for a, b in zip(ids.chunk(self.G), labels.chunk(self.G))]
+
+    def step_on_device(self, input_ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """One iteration on tensors already on the device; returns the loss tensor (device)."""
+        batches = self._split_micro(input_ids, labels)
+        if self.pipeline is not None:
+            return self.pipeline.train_step(batches)
+        return self.engine.train_step(batches)
+
+    def step(self, input_ids: torch.Tensor, labels: torch.Tensor) -> float:
+        """One iteration from host tensors (pinned memory recommended): copies the inputs to
+        the device, trains, and returns the loss as a Python float."""
+        if self.device.type == "cuda":
+            ids = input_ids.to(self.device, non_blocking=True)
+            lab = labels.to(self.device, non_blocking=True)
+        else:
+            ids, lab = input_ids, labels
+        loss = self.step_on_device(ids, lab)
+        return float(loss.item())
+
+    def finish(self):
+        self.engine.finish()
+
+    # -------------------------------------------------------------------------- accounting
+    def flops_per_step(self) -> float:
+        """Model FLOPs (forward + backward) of this rank's share of one iteration."""
+        c = self.cfg.model
+        b, s = self.micro_batch * self.G, self.seq_len
+        tokens = b * s
+        per_layer = 2 * tokens * (c.params_per_block()) + 2 * 2 * b * s * s * c.hidden_size * 0.5
+        total = c.num_hidden_layers * per_layer + 2 * tokens * c.hidden_size * c.vocab_size
+        return 3.0 * total / max(self.ps.tp_size * self.ps.num_stages, 1)
+
+
+def build_training(config_name: str = "config", overrides: Optional[List[str]] = None,
+                   comm_backend: Optional[str] = None, seed: int = 1234, config_dirs=(), hp=None) -> TrainingSession:
+    cfg, _ = load_config(config_name, overrides, config_dirs=config_dirs)
+    return TrainingSession(cfg, comm_backend=comm_backend, seed=seed, hp=hp)

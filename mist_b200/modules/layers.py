@@ -1,0 +1,354 @@
+"""Module library: tensor-parallel linears, norms, embeddings, attention and MLP blocks.
+
+Activations are ``[batch, seq, hidden]``.  Under sequence parallelism the regions
+between a row-parallel output and the next column-parallel input hold
+``[batch * seq / tp, hidden]`` token shards (tokens flattened, dim 0 split), the
+column-parallel linear all-gathers its input and the row-parallel linear
+reduce-scatters its output.
+
+Parity map (reference): ColumnParallelLinear / RowParallelLinear
+mist/modules/fused_dense.py:221-327; ParallelMHA mist/modules/mha.py:1028-1337;
+ParallelMLP / ParallelGatedMlp mist/modules/mlp.py:17-128; VocabParallelEmbedding /
+ParallelEmbedding mist/modules/embedding.py:17-299; LayerNorm / RMSNorm
+mist/modules/layer_norm.py:880-908, rms_norm.py:124-139; RotaryEmbedding
+mist/modules/rotary.py:348-540.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as F
+from ..parallel import dist_ops
+from ..parallel.dist_ops import group_rank, group_size
+
+
+def _empty_param(*shape, dtype, device):
+    return nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))
+
+
+# ------------------------------------------------------------------------------- norms
+class LayerNorm(nn.Module):
+    """LayerNorm with the residual add folded in: ``forward(x, residual)`` returns
+    ``(norm(x + residual), x + residual)`` when ``prenorm`` else ``norm(x + residual)``."""
+
+    def __init__(self, hidden_size, eps=1e-5, prenorm=False, sequence_parallel=False, device=None, dtype=None):
+        super().__init__()
+        self.eps, self.prenorm = eps, prenorm
+        self.weight = _empty_param(hidden_size, dtype=dtype, device=device)
+        self.bias = _empty_param(hidden_size, dtype=dtype, device=device)
+        self.weight._sequence_parallel = self.bias._sequence_parallel = sequence_parallel
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        if self.weight.device.type != "meta":
+            nn.init.ones_(self.weight)
+            nn.init.zeros_(self.bias)
+
+    def forward(self, x, residual=None):
+        return F.layer_norm(x, self.weight, self.bias, self.eps, residual=residual, prenorm=self.prenorm)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden_size, eps=1e-5, prenorm=False, sequence_parallel=False, device=None, dtype=None):
+        super().__init__()
+        self.eps, self.prenorm = eps, prenorm
+        self.weight = _empty_param(hidden_size, dtype=dtype, device=device)
+        self.weight._sequence_parallel = sequence_parallel
+        self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        if self.weight.device.type != "meta":
+            nn.init.ones_(self.weight)
+
+    def forward(self, x, residual=None):
+        return F.rms_norm(x, self.weight, self.eps, residual=residual, prenorm=self.prenorm)
+
+
+def get_norm(kind: str, hidden_size, eps, prenorm=False, sequence_parallel=False, device=None, dtype=None):
+    cls = RMSNorm if kind.lower() == "rmsnorm" else LayerNorm
+    return cls(hidden_size, eps=eps, prenorm=prenorm, sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+
+
+# ----------------------------------------------------------------------------- linears
+class FusedDense(nn.Module):
+    """``act(x W^T + b)``; all three GEMMs run on the tcgen05 kernel."""
+
+    def __init__(self, in_features, out_features, bias=True, activation=None, device=None, dtype=None):
+        super().__init__()
+        self.in_features, self.out_features, self.activation = in_features, out_features, activation
+        self.weight = _empty_param(out_features, in_features, dtype=dtype, device=device)
+        self.bias = _empty_param(out_features, dtype=dtype, device=device) if bias else None
+        self.reset_parameters()
+
+    def reset_parameters(self, std: float = 0.02):
+        if self.weight.device.type != "meta":
+            nn.init.normal_(self.weight, mean=0.0, std=std)
+            if self.bias is not None:
+                nn.init.zeros_(self.bias)
+
+    def forward(self, x, residual=None):
+        return F.linear(x, self.weight, self.bias, activation=self.activation, residual=residual)
+
+
+class ColumnParallelLinear(FusedDense):
+    """Output features split over the tensor-parallel group.  With sequence parallelism
+    the input is a token shard that is all-gathered first (and its gradient
+    reduce-scattered); without it the input is replicated and its gradient all-reduced."""
+
+    def __init__(self, in_features, out_features, process_group=None, bias=True, activation=None,
+                 sequence_parallel=False, multiple_of=1, device=None, dtype=None):
+        ws, rk = group_size(process_group), group_rank(process_group)
+        assert out_features % multiple_of == 0
+        local_out = dist_ops.dim_for_rank(out_features, ws, rk, multiple_of)
+        super().__init__(in_features, local_out, bias=bias, activation=activation, device=device, dtype=dtype)
+        self.process_group, self.sequence_parallel = process_group, sequence_parallel
+        self.global_out_features = out_features
+
+    def forward(self, x, residual=None):
+        if self.sequence_parallel:
+            x = dist_ops.all_gather(x.reshape(-1, x.shape[-1]), self.process_group)
+        else:
+            x = dist_ops.copy_to_group(x, self.process_group)
+        return F.linear(x, self.weight, self.bias, activation=self.activation, residual=residual)
+
+
+class RowParallelLinear(FusedDense):
+    """Input features split over the group; the partial outputs are summed by an
+    all-reduce, or by a reduce-scatter over tokens under sequence parallelism.  The bias
+    (if any) is applied by the first rank only so that the sum counts it once."""
+
+    def __init__(self, in_features, out_features, process_group=None, bias=True, sequence_parallel=False,
+                 multiple_of=1, device=None, dtype=None):
+        ws, rk = group_size(process_group), group_rank(process_group)
+        local_in = dist_ops.dim_for_rank(in_features, ws, rk, multiple_of)
+        super().__init__(local_in, out_features, bias=bias and rk == 0, device=device, dtype=dtype)
+        self.process_group, self.sequence_parallel = process_group, sequence_parallel
+        if self.bias is not None:
+            self.bias._sequence_parallel = sequence_parallel and ws > 1
+
+    def forward(self, x, residual=None):
+        ws = group_size(self.process_group)
+        if ws == 1:
+            return F.linear(x, self.weight, self.bias, residual=residual)
+        y = F.linear(x, self.weight, self.bias)
+        if self.sequence_parallel:
+            y = dist_ops.reduce_scatter(y.reshape(-1, y.shape[-1]), self.process_group)
+        else:
+            y = dist_ops.all_reduce(y, self.process_group)
+        if residual is not None:
+            y = y + residual.reshape(y.shape)
+        return y
+
+
+# -------------------------------------------------------------------------- embeddings
+class VocabParallelEmbedding(nn.Module):
+    """Word (+ learned position, + token type) embeddings; the vocabulary is split over the
+    tensor-parallel group and out-of-slice ids contribute zeros before the all-reduce."""
+
+    def __init__(self, vocab_size, hidden_size, max_position_embeddings=0, num_tokentypes=0,
+                 process_group=None, sequence_parallel=False, padding_idx=None, device=None, dtype=None):
+        super().__init__()
+        ws, rk = group_size(process_group), group_rank(process_group)
+        assert vocab_size % ws == 0, f"vocab {vocab_size} must divide by tp {ws}"
+        self.process_group, self.sequence_parallel = process_group, sequence_parallel
+        self.vocab_size, self.local_vocab = vocab_size, vocab_size // ws
+        self.vocab_start = rk * self.local_vocab
+        self.padding_idx = padding_idx
+        self.word_embeddings = nn.Embedding(self.local_vocab, hidden_size, device=device, dtype=dtype)
+        self.position_embeddings = (nn.Embedding(max_position_embeddings, hidden_size, device=device, dtype=dtype)
+                                    if max_position_embeddings > 0 else None)
+        self.tokentype_embeddings = (nn.Embedding(num_tokentypes, hidden_size, device=device, dtype=dtype)
+                                     if num_tokentypes > 0 else None)
+        self.reset_parameters()
+
+    def reset_parameters(self, std=0.02):
+        for emb in (self.word_embeddings, self.position_embeddings, self.tokentype_embeddings):
+            if emb is not None and emb.weight.device.type != "meta":
+                nn.init.normal_(emb.weight, mean=0.0, std=std)
+
+    def forward(self, input_ids, position_ids=None, tokentype_ids=None):
+        ws = group_size(self.process_group)
+        wpe = self.position_embeddings.weight if self.position_embeddings is not None else None
+        if position_ids is not None and wpe is not None:
+            # explicit position ids: gather rows, the fused kernel handles the arange case
+            x = F.embedding(input_ids, self.word_embeddings.weight, None, self.vocab_start)
+            pos = wpe[position_ids]
+            x = x + (pos if ws == 1 or group_rank(self.process_group) == 0 else 0)
+        else:
+            use_pos = wpe is not None and (ws == 1 or group_rank(self.process_group) == 0)
+            x = F.embedding(input_ids, self.word_embeddings.weight, wpe if use_pos else None, self.vocab_start)
+        if tokentype_ids is not None and self.tokentype_embeddings is not None:
+            tt = self.tokentype_embeddings(tokentype_ids)
+            x = x + (tt if ws == 1 or group_rank(self.process_group) == 0 else 0)
+        if ws > 1:
+            if self.sequence_parallel:
+                x = dist_ops.reduce_scatter(x.reshape(-1, x.shape[-1]), self.process_group)
+            else:
+                x = dist_ops.all_reduce(x, self.process_group)
+        return x
+
+    def state_dict_for_save_checkpoint(self, prefix="", keep_vars=False):
+        sd = {"word_embeddings": self.word_embeddings.state_dict(prefix=prefix, keep_vars=keep_vars)}
+        if self.position_embeddings is not None:
+            sd["position_embeddings"] = self.position_embeddings.state_dict(prefix=prefix, keep_vars=keep_vars)
+        if self.tokentype_embeddings is not None:
+            sd["tokentype_embeddings"] = self.tokentype_embeddings.state_dict(prefix=prefix, keep_vars=keep_vars)
+        return sd
+
+    def load_state_dict_from_checkpoint(self, sd, strict=True):
+        self.word_embeddings.load_state_dict(sd["word_embeddings"], strict=strict)
+        if self.position_embeddings is not None and "position_embeddings" in sd:
+            self.position_embeddings.load_state_dict(sd["position_embeddings"], strict=strict)
+        if self.tokentype_embeddings is not None and "tokentype_embeddings" in sd:
+            self.tokentype_embeddings.load_state_dict(sd["tokentype_embeddings"], strict=strict)
+
+
+# --------------------------------------------------------------------------- attention
+class ParallelMHA(nn.Module):
+    """Multi-head (self or cross) attention with heads split over the tensor-parallel group.
+
+    ``use_flash_attn`` selects the tcgen05 flash kernel; otherwise scores are
+    materialised and normalised by the scaled (causal) softmax kernel, which is the
+    O(s^2)-memory path the analyzer also models."""
+
+    def __init__(self, hidden_size, num_heads, num_heads_kv=None, process_group=None, qkv_proj_bias=True,
+                 out_proj_bias=True, dropout=0.0, softmax_scale=None, causal=False, cross_attn=False,
+                 rotary_emb_dim=0, rotary_emb_base=10000.0, use_flash_attn=True, sequence_parallel=False,
+                 layer_idx=None, device=None, dtype=None):
+        super().__init__()
+        ws = group_size(process_group)
+        self.hidden_size, self.causal, self.cross_attn = hidden_size, causal, cross_attn
+        self.num_heads = num_heads
+        self.num_heads_kv = num_heads_kv or num_heads
+        assert num_heads % ws == 0 and self.num_heads_kv % ws == 0, "heads must divide by tp"
+        assert hidden_size % num_heads == 0
+        self.head_dim = hidden_size // num_heads
+        self.local_heads, self.local_heads_kv = num_heads // ws, self.num_heads_kv // ws
+        self.rotary_emb_dim, self.rotary_emb_base = int(rotary_emb_dim), rotary_emb_base
+        self.use_flash_attn, self.dropout, self.layer_idx = use_flash_attn, dropout, layer_idx
+        self.softmax_scale = softmax_scale or 1.0 / math.sqrt(self.head_dim)
+        self.process_group, self.sequence_parallel = process_group, sequence_parallel
+        kv_dim = self.num_heads_kv * self.head_dim
+        fk = dict(process_group=process_group, sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+        if not cross_attn:
+            self.Wqkv = ColumnParallelLinear(hidden_size, hidden_size + 2 * kv_dim, bias=qkv_proj_bias,
+                                             multiple_of=self.head_dim * (self.num_heads // self.num_heads_kv + 2), **fk)
+        else:
+            self.Wq = ColumnParallelLinear(hidden_size, hidden_size, bias=qkv_proj_bias,
+                                           multiple_of=self.head_dim, **fk)
+            self.Wkv = ColumnParallelLinear(hidden_size, 2 * kv_dim, bias=qkv_proj_bias,
+                                            multiple_of=2 * self.head_dim, **fk)
+        self.out_proj = RowParallelLinear(hidden_size, hidden_size, bias=out_proj_bias,
+                                          multiple_of=self.head_dim, **fk)
+
+    def _attend(self, q, k, v, causal):
+        if self.use_flash_attn:
+            return F.attention(q, k, v, self.softmax_scale, causal)
+        # materialised scores: [b, h, sq, sk]
+        b, sq, nh, d = q.shape
+        if k.shape[2] != nh:
+            k = k.repeat_interleave(nh // k.shape[2], dim=2)
+            v = v.repeat_interleave(nh // v.shape[2], dim=2)
+        scores = torch.matmul(q.transpose(1, 2), k.permute(0, 2, 3, 1))
+        probs = F.scaled_causal_softmax(scores, self.softmax_scale, causal)
+        if self.dropout > 0 and self.training:
+            probs = torch.nn.functional.dropout(probs, self.dropout)
+        return torch.matmul(probs, v.transpose(1, 2)).transpose(1, 2)
+
+    def forward(self, x, x_kv=None, batch_size=None, residual=None):
+        """``x``: [b, s, h], or a [b*s/tp, h] token shard under sequence parallelism (then
+        ``batch_size`` is needed to recover the sequence length)."""
+        if not self.cross_attn:
+            qkv = self.Wqkv(x)
+            if qkv.dim() == 2:
+                qkv = qkv.view(batch_size, -1, qkv.shape[-1])
+            b, s = qkv.shape[:2]
+            if self.local_heads == self.local_heads_kv:
+                qkv = qkv.view(b, s, 3, self.local_heads, self.head_dim)
+                rotary = None
+                if self.rotary_emb_dim > 0:
+                    cos, sin = F.rope_tables(s, self.rotary_emb_dim, self.rotary_emb_base, qkv.device)
+                    rotary = (cos, sin, self.rotary_emb_dim)
+                if self.use_flash_attn:
+                    ctx = F.attention_qkvpacked(qkv, self.softmax_scale, self.causal, rotary)
+                else:
+                    if rotary is not None:
+                        qkv = _RotaryOutOfPlace.apply(qkv, *rotary)
+                    ctx = self._attend(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], self.causal)
+            else:
+                hq, hk, d = self.local_heads, self.local_heads_kv, self.head_dim
+                q = qkv[..., : hq * d].reshape(b, s, hq, d)
+                k = qkv[..., hq * d: (hq + hk) * d].reshape(b, s, hk, d)
+                v = qkv[..., (hq + hk) * d:].reshape(b, s, hk, d)
+                ctx = self._attend(q, k, v, self.causal)
+        else:
+            q = self.Wq(x)
+            kv = self.Wkv(x_kv)
+            if q.dim() == 2:
+                q = q.view(batch_size, -1, q.shape[-1])
+                kv = kv.view(batch_size, -1, kv.shape[-1])
+            b, sq = q.shape[:2]
+            q = q.view(b, sq, self.local_heads, self.head_dim)
+            kv = kv.view(b, kv.shape[1], 2, self.local_heads_kv, self.head_dim)
+            ctx = self._attend(q, kv[:, :, 0], kv[:, :, 1], False)
+        ctx = ctx.reshape(ctx.shape[0], ctx.shape[1], -1)
+        return self.out_proj(ctx, residual=residual)
+
+
+class _RotaryOutOfPlace(torch.autograd.Function):
+    """Differentiable rotary embedding for the non-flash attention path."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, rot):
+        ctx.save_for_backward(cos, sin)
+        ctx.rot = rot
+        return F.apply_rotary_qkv_(qkv.clone(), cos, sin, rot)
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        return F.apply_rotary_qkv_(g.contiguous().clone(), cos, sin, ctx.rot, conj=True), None, None, None
+
+
+# --------------------------------------------------------------------------------- MLP
+class ParallelMLP(nn.Module):
+    """fc1 (column parallel, GELU fused into the GEMM epilogue) -> fc2 (row parallel)."""
+
+    def __init__(self, hidden_size, intermediate_size, process_group=None, bias1=True, bias2=True,
+                 activation="gelu", sequence_parallel=False, device=None, dtype=None):
+        super().__init__()
+        fk = dict(process_group=process_group, sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+        self.fc1 = ColumnParallelLinear(hidden_size, intermediate_size, bias=bias1, activation="gelu", **fk)
+        self.fc2 = RowParallelLinear(intermediate_size, hidden_size, bias=bias2, **fk)
+
+    def forward(self, x, residual=None):
+        return self.fc2(self.fc1(x), residual=residual)
+
+
+class ParallelGatedMlp(nn.Module):
+    """fc1 produces ``[gate | up]`` (each rank holds matching halves), SwiGLU, then fc2."""
+
+    def __init__(self, hidden_size, intermediate_size, process_group=None, bias1=False, bias2=False,
+                 sequence_parallel=False, device=None, dtype=None):
+        super().__init__()
+        fk = dict(process_group=process_group, sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+        self.fc1 = ColumnParallelLinear(hidden_size, 2 * intermediate_size, bias=bias1, multiple_of=2, **fk)
+        self.fc2 = RowParallelLinear(intermediate_size, hidden_size, bias=bias2, **fk)
+
+    def forward(self, x, residual=None):
+        return self.fc2(F.swiglu(self.fc1(x)), residual=residual)
+
+
+# -------------------------------------------------------------------------------- loss
+def vocab_parallel_cross_entropy(logits, labels, process_group=None, ignore_index=-100):
+    """Per-token loss of ``[tokens, vocab/tp]`` logits against global labels."""
+    ws = group_size(process_group)
+    rk = group_rank(process_group)
+    group = None if (ws == 1 or isinstance(process_group, dist_ops.FakeGroup)) else process_group
+    return F.cross_entropy(logits, labels, vocab_start=rk * logits.shape[-1], group=group,
+                           ignore_index=ignore_index)

@@ -559,7 +559,28 @@ def attention_qkvpacked(qkv, scale: Optional[float] = None, causal: bool = True,
     if scale is None:
         scale = 1.0 / math.sqrt(qkv.shape[-1])
     cos, sin, rot = rotary if rotary is not None else (None, None, 0)
+    if qkv.is_cuda and Settings.attn_backend == "sdpa":
+        # library baseline for A/B runs: rotary out of place, attention by torch SDPA
+        if rot:
+            qkv = _RotaryFn.apply(qkv, cos, sin, int(rot))
+        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        return F.scaled_dot_product_attention(q, k, v, is_causal=causal, scale=scale).transpose(1, 2)
     return _PackedAttnFn.apply(qkv, cos, sin, int(rot), float(scale), bool(causal))
+
+
+class _RotaryFn(torch.autograd.Function):
+    """Out-of-place differentiable rotary embedding on packed qkv."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, rot):
+        ctx.save_for_backward(cos, sin)
+        ctx.rot = rot
+        return _rope_apply(qkv.clone(), cos, sin, rot, False, 2)
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        return _rope_apply(g.contiguous().clone(), cos, sin, ctx.rot, True, 2), None, None, None
 
 
 # ------------------------------------------------------- non-flash attention softmax

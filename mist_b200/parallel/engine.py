@@ -1,0 +1,289 @@
+"""Overlap-centric training engine for one pipeline stage.
+
+The model is cut into *units* (embedding, each transformer block, head).  Each unit owns
+a :class:`~mist_b200.parallel.flat_unit.FlatUnit`.  Instead of module hooks scattered over
+the model, two autograd markers per block tell the engine where the backward pass is:
+
+* the marker placed after a block runs its backward *before* the block's backward
+  (-> ZeRO-3: make the block's weights resident, prefetch the previous block);
+* the marker placed before a block runs its backward *after* the block's backward
+  (-> the block's gradient bucket is complete: reduce it, step the optimizer on the
+  shard and refresh the weights, all on the communication stream while the compute
+  stream continues with the previous block).
+
+The weights of a unit are only touched again by the next iteration's forward, which
+waits on the unit's ``param_ready`` event; so the optimizer step is overlapped with the
+rest of the backward pass instead of being deferred into the next forward.
+
+Parity: reference mist/re_swap_manager/manager.py:796-1338 (ModelReSwapManager),
+:1339-1790 (the four hooks), streams :944-964; mist/re_swap_manager/optimizer.py:126-602.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..config import StageStrategy, ZeroLevel
+from ..ops import functional as F
+from ..ops import native
+from .flat_unit import FlatUnit
+from .state import ParallelState
+
+DEFAULT_HP = dict(lr=1e-5, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, adamw=True)
+
+
+class _Marker(torch.autograd.Function):
+    """Identity on (hidden, residual); calls ``fn()`` when the backward pass reaches it."""
+
+    @staticmethod
+    def forward(ctx, fn, hidden, residual):
+        ctx.fn = fn
+        ctx.has_res = residual is not None
+        if residual is None:
+            return hidden.view_as(hidden)
+        return hidden.view_as(hidden), residual.view_as(residual)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.fn()
+        if ctx.has_res:
+            return None, grads[0], grads[1]
+        return None, grads[0], None
+
+
+def _mark(fn, hidden, residual):
+    if not torch.is_grad_enabled() or not hidden.requires_grad:
+        return hidden, residual
+    out = _Marker.apply(fn, hidden, residual)
+    if residual is None:
+        return out, None
+    return out
+
+
+class TrainEngine:
+    def __init__(self, model: nn.Module, pstate: Optional[ParallelState] = None,
+                 strategy: Optional[StageStrategy] = None, grad_accum_steps: int = 1,
+                 ckpt_layers: int = 0, hp: Optional[Dict] = None, comm_backend: str = "nccl",
+                 grad_dtype: Optional[torch.dtype] = None, overlap: bool = True,
+                 pre_post_strategy: Optional[StageStrategy] = None):
+        self.model = model
+        self.ps = pstate or ParallelState.single()
+        self.strategy = strategy or StageStrategy(1, 1, 1, False, False, False, 0, 0, 0, 0)
+        self.G = int(grad_accum_steps)
+        self.hp = dict(DEFAULT_HP, **(hp or {}))
+        self.comm_backend = comm_backend
+        self.overlap = overlap
+        zero = self.strategy.zero
+        pp_zero = (pre_post_strategy or self.strategy).zero
+        dp, dpr = self.ps.dp_size, self.ps.dp_rank
+        self.device = next(model.parameters()).device
+        self.cuda = self.device.type == "cuda"
+        if grad_dtype is None:
+            # bf16 buckets are enough when nothing is accumulated in them across micro steps
+            pdt = next(model.parameters()).dtype
+            grad_dtype = pdt if (self.G == 1 or zero >= ZeroLevel.OPT_GRAD) else torch.float32
+        self.grad_dtype = grad_dtype
+
+        # ----------------------------------------------------------------------- units
+        lm = getattr(model, "language_model", model)
+        self.stacks = [s for s in (getattr(lm, "encoder", None), getattr(lm, "decoder", None)) if s is not None]
+        layer_params = set()
+        self.units: List[FlatUnit] = []
+        self.layer_units: Dict[int, List[FlatUnit]] = {}
+        mk = dict(dp_size=dp, dp_rank=dpr, device=self.device, dtype=next(model.parameters()).dtype)
+        pre_params = []
+        if getattr(lm, "embedding", None) is not None:
+            pre_params = [(f"embedding.{n}", p) for n, p in lm.embedding.named_parameters()]
+        pre_ids = {id(p) for _, p in pre_params}
+        for stack in self.stacks:
+            stack.hooks = self
+            us = []
+            for i, layer in enumerate(stack.layers):
+                u = FlatUnit(f"layer{layer.layer_idx}", layer, zero=zero, **mk)
+                us.append(u)
+                layer_params.update(id(p) for p in u.params)
+            self.layer_units[id(stack)] = us
+        post_params = [(n, p) for n, p in model.named_parameters()
+                       if id(p) not in layer_params and id(p) not in pre_ids]
+        self.pre_unit = FlatUnit("pre", pre_params, zero=min(pp_zero, ZeroLevel.OPT_GRAD), **mk) if pre_params else None
+        self.post_unit = FlatUnit("post", post_params, zero=min(pp_zero, ZeroLevel.OPT_GRAD), **mk) if post_params else None
+        for stack in self.stacks:
+            self.units.extend(self.layer_units[id(stack)])
+        for u in (self.pre_unit, self.post_unit):
+            if u is not None:
+                self.units.append(u)
+        for stack in self.stacks:
+            stack.gradient_checkpointing = min(int(ckpt_layers), len(stack.layers))
+
+        # -------------------------------------------------------- buckets, state, streams
+        for u in self.units:
+            u.bind_grad_bucket(torch.zeros(u.padded, dtype=self.grad_dtype, device=self.device))
+            u.init_optimizer_state()
+        self.compute_stream = torch.cuda.current_stream() if self.cuda else None
+        self.comm_stream = torch.cuda.Stream() if (self.cuda and overlap) else self.compute_stream
+        self.param_ready: Dict[str, "torch.cuda.Event"] = {}
+        #: recorded on the comm stream once a bucket has been read by a mid-iteration reduction
+        self.bucket_free: Dict[str, "torch.cuda.Event"] = {}
+        self._micro = 0
+        self._pending_post = False
+        # ZeRO-3 ring of gathered-weight slots (two slots: current block + the prefetched one)
+        self.zero3 = zero >= ZeroLevel.FULL and dp > 1
+        if self.zero3:
+            biggest = max(u.padded for us in self.layer_units.values() for u in us)
+            self._slots = [torch.empty(biggest, dtype=mk["dtype"], device=self.device) for _ in range(2)]
+            self._slot_of: Dict[str, int] = {}
+            self._next_slot = 0
+            self._gather_done: Dict[str, "torch.cuda.Event"] = {}
+        self.fused = None
+        if comm_backend == "fused" and dp > 1:
+            from .fused_comm import FusedDPComm
+            self.fused = FusedDPComm(self)
+
+    # -------------------------------------------------------------------- stream helpers
+    def _on_comm(self):
+        if self.cuda and self.comm_stream is not self.compute_stream:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            return torch.cuda.stream(self.comm_stream)
+        import contextlib
+        return contextlib.nullcontext()
+
+    def _wait_params(self, unit: FlatUnit):
+        ev = self.param_ready.pop(unit.name, None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def _wait_bucket(self, unit: Optional[FlatUnit]):
+        if unit is None:
+            return
+        ev = self.bucket_free.pop(unit.name, None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    # ----------------------------------------------------------------- ZeRO-3 residency
+    def _gather(self, unit: FlatUnit):
+        """Starts the all-gather of ``unit``'s weights into the next ring slot (comm stream)."""
+        if not self.zero3 or unit.flat_param is not None:
+            return
+        slot = self._next_slot
+        self._next_slot ^= 1
+        self._slot_of[unit.name] = slot
+        with self._on_comm():
+            unit.unshard(self._slots[slot], self.ps.dp_ag_group)
+            if self.cuda:
+                ev = torch.cuda.Event()
+                ev.record()
+                self._gather_done[unit.name] = ev
+
+    def _ensure_resident(self, unit: FlatUnit):
+        if not self.zero3:
+            return
+        self._gather(unit)
+        ev = self._gather_done.pop(unit.name, None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def _release(self, unit: FlatUnit):
+        if self.zero3:
+            unit.reshard()
+
+    # ----------------------------------------------------------- callbacks from the stack
+    def before_layer(self, stack, i, hidden, residual):
+        units = self.layer_units[id(stack)]
+        u = units[i]
+        self._wait_params(u)
+        self._ensure_resident(u)
+        if i + 1 < len(units):
+            self._gather(units[i + 1])          # one-block look-ahead
+        return _mark(lambda: self._layer_backward_done(stack, i), hidden, residual)
+
+    def after_layer(self, stack, i, hidden, residual):
+        units = self.layer_units[id(stack)]
+        if torch.is_grad_enabled():
+            hidden, residual = _mark(lambda: self._layer_backward_start(stack, i), hidden, residual)
+        if self.zero3 and i + 1 < len(units):
+            # weights of block i are dropped once block i+1 starts (its slot is reused by i+2)
+            pass
+        if i + 1 == len(units) and self.post_unit is not None:
+            self._wait_params(self.post_unit)
+        return hidden, residual
+
+    def _layer_backward_start(self, stack, i):
+        units = self.layer_units[id(stack)]
+        self._wait_bucket(units[i])
+        if i + 1 == len(units) and self.post_unit is not None and stack is self.stacks[-1]:
+            self._unit_backward_done(self.post_unit)   # head + final norm finished before the last block
+        if self.zero3:
+            u = units[i]
+            if u.flat_param is None:
+                self._ensure_resident(u)
+            if i > 0:
+                self._gather(units[i - 1])
+
+    def _layer_backward_done(self, stack, i):
+        u = self.layer_units[id(stack)][i]
+        self._unit_backward_done(u)
+        if self.zero3:
+            self._release(u)
+
+    # --------------------------------------------------------------------- gradient path
+    def _unit_backward_done(self, unit: FlatUnit):
+        last = self._micro == self.G - 1
+        unit.collect_autograd_grads()
+        if self.fused is not None and self.fused.handles(unit):
+            self.fused.reduce_and_step(unit, last)
+            return
+        with self._on_comm():
+            grad = unit.reduce_grads(self.ps.dp_rs_group, last)
+            if grad is not None:
+                unit.optimizer_step(grad, self.hp, self.ps.dp_ag_group, grad_divisor=float(self.ps.dp_size * self.G))
+                if self.cuda:
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    self.param_ready[unit.name] = ev
+            elif self.cuda and self.comm_stream is not self.compute_stream:
+                ev = torch.cuda.Event()
+                ev.record()
+                self.bucket_free[unit.name] = ev
+
+    # ------------------------------------------------------------------------- stepping
+    def forward_backward(self, batch: Dict, micro_index: int = 0):
+        """One micro step: forward, loss, backward.  Returns the detached loss."""
+        self._micro = micro_index
+        if self.pre_unit is not None:
+            self._wait_params(self.pre_unit)
+        loss = self.model(**batch)
+        self._wait_bucket(self.pre_unit)
+        self._wait_bucket(self.post_unit)
+        loss.backward()
+        if self.pre_unit is not None:
+            self._unit_backward_done(self.pre_unit)
+        return loss.detach()
+
+    def train_step(self, batches: List[Dict]):
+        """One iteration over ``G`` micro batches; optimizer steps are issued per unit as
+        soon as the unit's last gradient is reduced."""
+        assert len(batches) == self.G, f"expected {self.G} micro batches, got {len(batches)}"
+        losses = [self.forward_backward(b, k) for k, b in enumerate(batches)]
+        return torch.stack(losses).mean()
+
+    def finish(self):
+        """Blocks the compute stream on every outstanding optimizer step."""
+        if self.cuda:
+            for ev in self.param_ready.values():
+                torch.cuda.current_stream().wait_event(ev)
+            self.param_ready.clear()
+            if self.comm_stream is not self.compute_stream:
+                torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    # ----------------------------------------------------------------------- accounting
+    def num_parameters(self) -> int:
+        return sum(u.numel for u in self.units)
+
+    def state_bytes(self) -> Dict[str, int]:
+        w = sum((u.flat_param.numel() if u.flat_param is not None else u.param_shard.numel()) * 2 for u in self.units)
+        g = sum(u.flat_grad.numel() * u.flat_grad.element_size() for u in self.units)
+        o = sum(u.master.numel() * 12 for u in self.units)
+        return {"weights": w, "grads": g, "optimizer": o}

@@ -1,0 +1,225 @@
+"""Flat parameter / gradient / optimizer-state storage of one schedulable unit
+(the embedding stage, one transformer block, or the head).
+
+All parameters of the unit are views into one contiguous bf16 buffer and all gradients
+into one contiguous bucket, so the data-parallel collectives and the optimizer run once
+per unit on flat memory.  Sharding level:
+
+==========  ======================  ==================  =========================
+level       weights                 gradients           fp32 master + Adam moments
+==========  ======================  ==================  =========================
+none        full                    all-reduce          full
+ZeRO-1      full                    reduce-scatter at   1/dp shard
+                                    the last micro step
+ZeRO-2      full                    reduce-scatter      1/dp shard
+                                    every micro step
+ZeRO-3      1/dp shard; gathered    as ZeRO-2           1/dp shard
+            into a ring slot
+==========  ======================  ==================  =========================
+
+Parity: reference mist/re_swap_manager/flat_param.py:91-108 (levels), :315-420 (handle),
+:986-1121 (ring-buffer allocation), :1283-1370 (unshard), :1459-1529 (gradient reduction).
+Unlike the reference, reduced gradients are averaged over data-parallel ranks and
+micro steps (there the division is commented out and gradients are summed).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..config import ZeroLevel
+from ..ops import functional as F
+
+ALIGN = 128  # elements: every parameter view starts 256-byte aligned (TMA needs 16)
+
+
+def _round_up(n, m):
+    return (n + m - 1) // m * m
+
+
+class FlatUnit:
+    def __init__(self, name: str, module: nn.Module, *, dp_size: int = 1, dp_rank: int = 0,
+                 zero: ZeroLevel = ZeroLevel.NONE, device=None, dtype=torch.bfloat16,
+                 allocator=None, init_params: bool = True):
+        self.name, self.module = name, module
+        self.dp_size, self.dp_rank, self.zero = dp_size, dp_rank, ZeroLevel(zero)
+        self.dtype = dtype
+        if isinstance(module, nn.Module):
+            params = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
+        else:   # an explicit list of (name, parameter)
+            params = [(n, p) for n, p in module if p.requires_grad]
+        # de-duplicate tied parameters
+        seen, self.params, self.param_names = set(), [], []
+        for n, p in params:
+            if id(p) not in seen:
+                seen.add(id(p))
+                self.params.append(p)
+                self.param_names.append(n)
+        self.device = device if device is not None else (self.params[0].device if self.params else "cpu")
+        self.offsets, off = [], 0
+        for p in self.params:
+            self.offsets.append(off)
+            off += _round_up(p.numel(), ALIGN)
+        self.numel = off
+        self.padded = _round_up(max(off, 1), ALIGN * max(dp_size, 1))
+        self.shard_numel = self.padded // dp_size
+        alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
+        self._alloc = alloc
+        # ---- weights
+        self.flat_param: Optional[torch.Tensor] = None     # full weights (None while resharded, ZeRO-3)
+        self.param_shard: Optional[torch.Tensor] = None    # persistent 1/dp shard (ZeRO-3 only)
+        full = alloc(self.padded, dtype)
+        if init_params:
+            for p, o in zip(self.params, self.offsets):
+                if p.device.type != "meta":
+                    full[o:o + p.numel()].copy_(p.detach().reshape(-1).to(dtype))
+        if self.zero >= ZeroLevel.FULL and dp_size > 1:
+            self.param_shard = full[self.shard_range()].clone()
+            self._use_views(full)     # keep shapes/devices sane until the first unshard
+            self._boot_full = full
+        else:
+            self.flat_param = full
+            self._use_views(full)
+        # ---- gradients
+        self.flat_grad: Optional[torch.Tensor] = None      # bound by the engine (own bucket or ring slot)
+        self.grad_shard_acc: Optional[torch.Tensor] = None  # fp32 accumulator of the reduced shard
+        self.micro_steps_accumulated = 0
+        # ---- optimizer state (created by init_optimizer_state)
+        self.master = self.exp_avg = self.exp_avg_sq = None
+        self.step_count = 0
+
+    # ------------------------------------------------------------------------- layout
+    def shard_range(self, rank: Optional[int] = None) -> slice:
+        r = self.dp_rank if rank is None else rank
+        return slice(r * self.shard_numel, (r + 1) * self.shard_numel)
+
+    @property
+    def sharded_state(self) -> bool:
+        return self.zero >= ZeroLevel.OPT and self.dp_size > 1
+
+    @property
+    def state_numel(self) -> int:
+        return self.shard_numel if self.sharded_state else self.padded
+
+    def _use_views(self, flat: torch.Tensor):
+        for p, o in zip(self.params, self.offsets):
+            p.data = flat[o:o + p.numel()].view(p.shape)
+
+    def bind_grad_bucket(self, bucket: torch.Tensor, fresh: bool = True):
+        """Points every parameter's gradient view into ``bucket`` (a full-size flat tensor)."""
+        assert bucket.numel() >= self.padded
+        self.flat_grad = bucket[: self.padded]
+        for p, o in zip(self.params, self.offsets):
+            p.grad_bucket = self.flat_grad[o:o + p.numel()].view(p.shape)
+            if fresh:
+                p.grad_accumulate = False
+
+    def collect_autograd_grads(self):
+        """Moves ``.grad`` tensors produced by autograd (norm weights, biases, embeddings)
+        into the bucket; linear weights were written there directly by the wgrad GEMM."""
+        for p in self.params:
+            g = p.grad
+            if g is None:
+                if not getattr(p, "grad_accumulate", False):
+                    p.grad_bucket.zero_()      # parameter did not take part in this micro step
+                    p.grad_accumulate = True
+                continue
+            if getattr(p, "grad_accumulate", False):
+                p.grad_bucket.add_(g.to(p.grad_bucket.dtype))
+            else:
+                p.grad_bucket.copy_(g)
+                p.grad_accumulate = True
+            p.grad = None
+
+    # ------------------------------------------------------------------ optimizer state
+    def init_optimizer_state(self, state_dtype=torch.float32):
+        src = self.param_shard if self.param_shard is not None else (
+            self.flat_param[self.shard_range()] if self.sharded_state else self.flat_param)
+        self.master = src.detach().to(state_dtype).clone()
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+
+    # --------------------------------------------------------------------------- ZeRO-3
+    def unshard(self, slot: torch.Tensor, group, async_op=False):
+        """All-gathers the weight shards into ``slot`` and points the parameters at it."""
+        assert self.param_shard is not None
+        full = slot[: self.padded]
+        handle = None
+        if group is not None:
+            handle = dist.all_gather_into_tensor(full, self.param_shard, group=group, async_op=async_op)
+        else:
+            full[self.shard_range()].copy_(self.param_shard)
+        self.flat_param = full
+        self._use_views(full)
+        self._boot_full = None
+        return handle
+
+    def reshard(self):
+        if self.param_shard is not None:
+            self.flat_param = None
+
+    # ---------------------------------------------------------------- gradient reduction
+    def reduce_grads(self, group, last_micro_step: bool):
+        """Reference (NCCL) path.  Returns the tensor the optimizer should consume, or None
+        when nothing is due yet."""
+        self.micro_steps_accumulated += 1
+        if self.dp_size == 1 or group is None:
+            return self.flat_grad if last_micro_step else None
+        if self.zero >= ZeroLevel.OPT_GRAD:
+            out = torch.empty(self.shard_numel, dtype=self.flat_grad.dtype, device=self.flat_grad.device)
+            dist.reduce_scatter_tensor(out, self.flat_grad, group=group)
+            if self.grad_shard_acc is None and last_micro_step and self.micro_steps_accumulated == 1:
+                return out
+            if self.grad_shard_acc is None:
+                self.grad_shard_acc = torch.zeros(self.shard_numel, dtype=torch.float32, device=out.device)
+            F.accumulate_grad(out, self.grad_shard_acc, 1.0, True)
+            for p in self.params:
+                p.grad_accumulate = False      # the bucket restarts for the next micro step
+            return self.grad_shard_acc if last_micro_step else None
+        if not last_micro_step:
+            return None
+        if self.zero == ZeroLevel.OPT:
+            out = torch.empty(self.shard_numel, dtype=self.flat_grad.dtype, device=self.flat_grad.device)
+            dist.reduce_scatter_tensor(out, self.flat_grad, group=group)
+            return out
+        dist.all_reduce(self.flat_grad, group=group)
+        return self.flat_grad
+
+    def optimizer_step(self, grad: torch.Tensor, hp: Dict, group, grad_divisor: float):
+        """Fused Adam on this rank's state, writing the bf16 weights, then (ZeRO-1/2) the
+        all-gather that refreshes the other ranks' slices."""
+        self.step_count += 1
+        if self.param_shard is not None:
+            model_out = self.param_shard
+        elif self.sharded_state:
+            model_out = self.flat_param[self.shard_range()]
+        else:
+            model_out = self.flat_param
+        g = grad if grad.numel() == self.master.numel() else grad[self.shard_range()]
+        F.adam_step(self.master, self.exp_avg, self.exp_avg_sq, g, model_out, lr=hp["lr"], beta1=hp["beta1"],
+                    beta2=hp["beta2"], eps=hp["eps"], weight_decay=hp["weight_decay"], step=self.step_count,
+                    inv_scale=1.0 / grad_divisor, adamw=hp.get("adamw", True))
+        if self.sharded_state and self.param_shard is None and group is not None:
+            dist.all_gather_into_tensor(self.flat_param, model_out, group=group)
+        self.micro_steps_accumulated = 0
+        if self.grad_shard_acc is not None:
+            self.grad_shard_acc.zero_()
+        for p in self.params:
+            p.grad_accumulate = False
+
+    # ------------------------------------------------------------------ checkpoint views
+    def state_for_checkpoint(self) -> Dict[str, torch.Tensor]:
+        return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
+                "step": torch.tensor(self.step_count)}
+
+    def load_state_from_checkpoint(self, sd: Dict[str, torch.Tensor]):
+        self.master.copy_(sd["master"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.step_count = int(sd["step"])
+        dst = self.param_shard if self.param_shard is not None else (
+            self.flat_param[self.shard_range()] if self.sharded_state else self.flat_param)
+        dst.copy_(self.master.to(dst.dtype))

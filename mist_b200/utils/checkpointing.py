@@ -1,0 +1,26 @@
+"""Activation checkpointing of a transformer block.
+
+The block's forward is re-run during the backward pass instead of keeping its
+intermediate activations (reference: mist/utils/gradient_checkpointing.py:33-48, which
+wraps ``torch.utils.checkpoint`` in re-entrant mode).  The non-re-entrant form is used
+here so that module hooks and tensors that do not require grad behave as in a normal
+forward; RNG state is preserved so dropout masks repeat.
+"""
+from __future__ import annotations
+
+import torch
+from torch.utils.checkpoint import checkpoint
+
+
+def checkpoint_block(layer, hidden, residual, encoder_output, batch_size):
+    def run(h, r, e):
+        return layer(h, r, e, batch_size)
+
+    return checkpoint(run, hidden, residual, encoder_output, use_reentrant=False, preserve_rng_state=True)
+
+
+def apply_gradient_checkpointing(stack, num_layers: int):
+    """Marks the last ``num_layers`` blocks of a ParallelTransformer for recomputation."""
+    assert 0 <= num_layers <= len(stack.layers)
+    stack.gradient_checkpointing = int(num_layers)
+    return stack
