@@ -16,6 +16,7 @@
 // warps 2..5 = epilogue (TMEM -> registers -> global).  Two accumulator stages in
 // TMEM let the epilogue of tile i overlap the main loop of tile i+1.
 #include "sm100.cuh"
+#include <string.h>
 
 using namespace sm100;
 
@@ -44,6 +45,7 @@ struct GemmParams {
   int flags;
   float alpha;
   int* status;
+  int tma_epilogue;  // 1: stage tiles in shared memory and write them with TMA stores
 };
 
 template <int BN, int STAGES>
@@ -51,7 +53,9 @@ struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kStagingBytes = BM * 128;  // one [128 rows][128 bytes] swizzled tile
+  static constexpr int kStagingOffset = STAGES * kStageBytes;
+  static constexpr int kBarOffset = kStagingOffset + 2 * kStagingBytes;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem base word
   static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
 };
@@ -63,6 +67,7 @@ __device__ __forceinline__ void report(int* status, int code) {
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_aux,
                  const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -209,6 +214,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t tcount = 0;
     bool ok = true;
     const bool out_fp32 = (p.flags & EPI_OUT_FP32) != 0;
+    uint32_t epi_units = 0;  // staging tiles handed to TMA so far (selects the buffer)
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++tcount) {
       int m0, n0;
       tile_coords(t, m0, n0);
@@ -222,6 +228,75 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.tma_epilogue) {
+        // Coalesced path: each thread writes its row's 128 bytes into a swizzled staging
+        // tile, one elected thread hands the tile to TMA (store, or reduce-add for
+        // accumulation into an fp32 gradient bucket).  Two staging tiles alternate.
+        const int r = q * 32 + lane;
+        const bool leader = (threadIdx.x == 64);
+        const int cols_per_unit = out_fp32 ? 32 : 64;
+        const int units = BN / cols_per_unit;
+        const int npass = (p.flags & EPI_SAVE_PRE) ? 2 : 1;
+        for (int u = 0; u < units; ++u) {
+          const int ucol0 = n0 + u * cols_per_unit;
+          if (ucol0 >= p.N) break;  // uniform over the CTA: nothing to store further right
+          for (int pass = 0; pass < npass; ++pass) {
+            uint8_t* stg = smem + L::kStagingOffset + (epi_units & 1) * L::kStagingBytes;
+            if (leader) tma_wait_read<1>();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int halves = out_fp32 ? 1 : 2;
+            for (int hh = 0; hh < halves; ++hh) {
+              uint32_t rr[32];
+              tmem_ld32(taddr + u * cols_per_unit + hh * 32, rr);
+              tmem_ld_wait();
+              float v[32];
+              const int col0 = ucol0 + hh * 32;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rr[i]) * p.alpha;
+              if (p.flags & EPI_BIAS) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  v[i] += __bfloat162float(p.bias[min(col0 + i, p.N - 1)]);
+              }
+              const bool act = (p.flags & EPI_GELU) && (pass == npass - 1);
+              if (act) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = mb::gelu_tanh(v[i]);
+              }
+              if (out_fp32) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                  *reinterpret_cast<float4*>(stg + r * 128 + ((g ^ (r & 7)) << 4)) =
+                      make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+              } else {
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                  *reinterpret_cast<mb::bf16x8*>(stg + r * 128 + (((hh * 4 + g) ^ (r & 7)) << 4)) =
+                      mb::pack8(v + 8 * g);
+              }
+            }
+            fence_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (leader) {
+              const CUtensorMap* dst = (npass == 2 && pass == 0) ? &tma_aux : &tma_c;
+              if ((p.flags & EPI_ACCUM) && out_fp32) {
+                asm volatile(
+                    "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group "
+                    "[%0, {%2, %3}], [%1];\n" ::"l"(reinterpret_cast<uint64_t>(dst)),
+                    "r"(smem_u32(stg)), "r"(ucol0), "r"(m0)
+                    : "memory");
+              } else {
+                tma_store_2d(dst, stg, ucol0, m0);
+              }
+              tma_commit();
+            }
+            ++epi_units;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty_bar[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -325,6 +400,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_before();
       mbar_arrive(&tempty_bar[acc]);
     }
+    if (p.tma_epilogue && threadIdx.x == 64) tma_wait_all<0>();
   }
 
   tc_fence_before();
@@ -371,11 +447,26 @@ bool make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
   return r == CUDA_SUCCESS;
 }
 
+// Output tile map: [rows][cols] of bf16 (64-column box) or fp32 (32-column box), i.e. 128-byte
+// swizzled rows matching the epilogue's staging tile.
+bool make_tmap_out(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, uint64_t ld, bool fp32) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * (fp32 ? 4u : 2u)};
+  cuuint32_t box[2] = {fp32 ? 32u : 64u, static_cast<cuuint32_t>(BM)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
+                  dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int g_num_sms = 0;
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas,
-           cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
+           const GemmParams& p, int max_ctas, cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   constexpr int smem = L::kTotal + 1024;
   static bool configured = false;
@@ -387,7 +478,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
   }
   int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   int grid = num_tiles < max_ctas ? num_tiles : max_ctas;
-  kern<<<grid, kThreads, smem, stream>>>(ta, tb, p);
+  kern<<<grid, kThreads, smem, stream>>>(ta, tb, tc, tx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -456,13 +547,30 @@ MB_API int mb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int
   p.flags = flags;
   p.alpha = alpha;
   p.status = mb_status_device_ptr();
+  // The TMA epilogue covers the hot epilogues; anything else takes the direct-store path.
+  const bool out_fp32 = (flags & EPI_OUT_FP32) != 0;
+  const int esz = out_fp32 ? 4 : 2;
+  const int fast_ok_flags = EPI_BIAS | EPI_GELU | EPI_SAVE_PRE | EPI_OUT_FP32 | (out_fp32 ? EPI_ACCUM : 0);
+  bool fast = ((flags & ~fast_ok_flags) == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0) &&
+              ((static_cast<long>(ldc) * esz) % 16 == 0) && !((flags & EPI_GELU) && out_fp32);
+  if ((flags & EPI_SAVE_PRE) &&
+      (!aux || (reinterpret_cast<uintptr_t>(aux) & 15) || !(flags & EPI_GELU)))
+    fast = false;
+  CUtensorMap tc, tx;
+  memset(&tc, 0, sizeof(tc));
+  memset(&tx, 0, sizeof(tx));
+  if (fast) {
+    if (!make_tmap_out(&tc, C, M, N, ldc, out_fp32)) fast = false;
+    if (fast && (flags & EPI_SAVE_PRE) && !make_tmap_out(&tx, aux, M, N, ldc, false)) fast = false;
+  }
+  p.tma_epilogue = fast ? 1 : 0;
 
 #define MB_DISPATCH(BN_, ST_)                                                                \
   do {                                                                                       \
-    if (!a_mn_major && !b_mn_major) return launch<BN_, ST_, false, false>(ta, tb, p, max_ctas, stream); \
-    if (!a_mn_major && b_mn_major) return launch<BN_, ST_, false, true>(ta, tb, p, max_ctas, stream);   \
-    if (a_mn_major && !b_mn_major) return launch<BN_, ST_, true, false>(ta, tb, p, max_ctas, stream);   \
-    return launch<BN_, ST_, true, true>(ta, tb, p, max_ctas, stream);                        \
+    if (!a_mn_major && !b_mn_major) return launch<BN_, ST_, false, false>(ta, tb, tc, tx, p, max_ctas, stream); \
+    if (!a_mn_major && b_mn_major) return launch<BN_, ST_, false, true>(ta, tb, tc, tx, p, max_ctas, stream);   \
+    if (a_mn_major && !b_mn_major) return launch<BN_, ST_, true, false>(ta, tb, tc, tx, p, max_ctas, stream);   \
+    return launch<BN_, ST_, true, true>(ta, tb, tc, tx, p, max_ctas, stream);                        \
   } while (0)
 
   if (bn == 256) MB_DISPATCH(256, 4);

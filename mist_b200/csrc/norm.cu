@@ -42,7 +42,7 @@ __device__ __forceinline__ void row_reduce(float (&v)[NVAL], float* red, int tpr
 }
 
 template <bool RMS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ residual,
                 const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
                 __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ x_out,
@@ -54,48 +54,34 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __res
   const int nvec = h >> 3;
   const int groups = (rows + rpc - 1) / rpc;
 
-  // gamma / beta stay in registers across the rows of the persistent loop
-  float g[VPT][8], b[VPT][8];
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    int vi = tr + i * tpr;
-    if (vi < nvec) {
-      mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(gamma + 8 * vi), g[i]);
-      if (!RMS && beta) mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(beta + 8 * vi), b[i]);
-      else {
-#pragma unroll
-        for (int k = 0; k < 8; ++k) b[i][k] = 0.f;
-      }
-    }
-  }
-
   for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
     const int row = grp * rpc + rl;
     const bool active = row < rows;
-    float x[VPT][8];
+    // The row stays in registers as packed bf16 (what later passes and the backward
+    // pass see); gamma / beta are re-read per row and hit L1.
+    mb::bf16x8 xp[VPT];
     float acc[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       int vi = tr + i * tpr;
       if (active && vi < nvec) {
         size_t off = static_cast<size_t>(row) * h + 8 * vi;
-        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(x0 + off), x[i]);
+        xp[i] = *reinterpret_cast<const mb::bf16x8*>(x0 + off);
+        float x[8];
+        mb::unpack8(xp[i], x);
         if (residual) {
           float r[8];
           mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(residual + off), r);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) x[i][k] += r[k];
+          for (int k = 0; k < 8; ++k) x[k] += r[k];
+          xp[i] = mb::pack8(x);
+          mb::unpack8(xp[i], x);
         }
-        if (x_out) {
-          mb::bf16x8 pk = mb::pack8(x[i]);
-          *reinterpret_cast<mb::bf16x8*>(x_out + off) = pk;
-          // keep what later passes will re-read: the rounded value
-          mb::unpack8(pk, x[i]);
-        }
+        if (x_out) *reinterpret_cast<mb::bf16x8*>(x_out + off) = xp[i];
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          acc[0] += x[i][k];
-          acc[1] += x[i][k] * x[i][k];
+          acc[0] += x[k];
+          acc[1] += x[k] * x[k];
         }
       }
     }
@@ -111,9 +97,18 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __res
     for (int i = 0; i < VPT; ++i) {
       int vi = tr + i * tpr;
       if (active && vi < nvec) {
-        float o[8];
+        float x[8], g[8], o[8];
+        mb::unpack8(xp[i], x);
+        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(gamma + 8 * vi), g);
+        if (!RMS && beta) {
+          float b[8];
+          mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(beta + 8 * vi), b);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o[k] = (x[i][k] - mean) * rstd * g[i][k] + b[i][k];
+          for (int k = 0; k < 8; ++k) o[k] = (x[k] - mean) * rstd * g[k] + b[k];
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] = (x[k] - mean) * rstd * g[k];
+        }
         *reinterpret_cast<mb::bf16x8*>(z + static_cast<size_t>(row) * h + 8 * vi) = mb::pack8(o);
       }
     }
@@ -121,7 +116,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __res
 }
 
 template <bool RMS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                 const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres_in,
@@ -133,11 +128,9 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __res
   const int nvec = h >> 3;
   const int groups = (rows + rpc - 1) / rpc;
 
-  float g[VPT][8], dg[VPT][8], db[VPT][8];
+  float dg[VPT][8], db[VPT][8];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    int vi = tr + i * tpr;
-    if (vi < nvec) mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(gamma + 8 * vi), g[i]);
 #pragma unroll
     for (int k = 0; k < 8; ++k) dg[i][k] = db[i][k] = 0.f;
   }
@@ -147,24 +140,27 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __res
     const bool active = row < rows;
     const float mean = (active && !RMS) ? mean_in[row] : 0.f;
     const float rstd = active ? rstd_in[row] : 0.f;
-    float xh[VPT][8], dy[VPT][8];
+    mb::bf16x8 xp[VPT], dzp[VPT];  // packed: half the registers of fp32 copies
     float acc[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       int vi = tr + i * tpr;
       if (active && vi < nvec) {
         size_t off = static_cast<size_t>(row) * h + 8 * vi;
-        float xv[8], dzv[8];
-        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(x + off), xv);
-        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(dz + off), dzv);
+        xp[i] = *reinterpret_cast<const mb::bf16x8*>(x + off);
+        dzp[i] = *reinterpret_cast<const mb::bf16x8*>(dz + off);
+        float xv[8], dzv[8], g[8];
+        mb::unpack8(xp[i], xv);
+        mb::unpack8(dzp[i], dzv);
+        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(gamma + 8 * vi), g);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          xh[i][k] = (xv[k] - mean) * rstd;
-          dy[i][k] = dzv[k] * g[i][k];
-          dg[i][k] += dzv[k] * xh[i][k];
+          float xh = (xv[k] - mean) * rstd;
+          float dy = dzv[k] * g[k];
+          dg[i][k] += dzv[k] * xh;
           db[i][k] += dzv[k];
-          acc[0] += dy[i][k];
-          acc[1] += dy[i][k] * xh[i][k];
+          acc[0] += dy;
+          acc[1] += dy * xh;
         }
       }
     }
@@ -176,9 +172,15 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __res
       int vi = tr + i * tpr;
       if (active && vi < nvec) {
         size_t off = static_cast<size_t>(row) * h + 8 * vi;
-        float o[8];
+        float xv[8], dzv[8], g[8], o[8];
+        mb::unpack8(xp[i], xv);
+        mb::unpack8(dzp[i], dzv);
+        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(gamma + 8 * vi), g);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o[k] = rstd * (dy[i][k] - m1 - xh[i][k] * m2);
+        for (int k = 0; k < 8; ++k) {
+          float xh = (xv[k] - mean) * rstd;
+          o[k] = rstd * (dzv[k] * g[k] - m1 - xh * m2);
+        }
         if (dres_in) {
           float r[8];
           mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(dres_in + off), r);
@@ -195,10 +197,13 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __res
   for (int i = 0; i < VPT; ++i) {
     int vi = tr + i * tpr;
     if (vi < nvec) {
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        part_dgamma[prow * h + 8 * vi + k] = dg[i][k];
-        if (!RMS && part_dbeta) part_dbeta[prow * h + 8 * vi + k] = db[i][k];
+      float* pg = part_dgamma + prow * h + 8 * vi;
+      *reinterpret_cast<float4*>(pg) = make_float4(dg[i][0], dg[i][1], dg[i][2], dg[i][3]);
+      *reinterpret_cast<float4*>(pg + 4) = make_float4(dg[i][4], dg[i][5], dg[i][6], dg[i][7]);
+      if (!RMS && part_dbeta) {
+        float* pb = part_dbeta + prow * h + 8 * vi;
+        *reinterpret_cast<float4*>(pb) = make_float4(db[i][0], db[i][1], db[i][2], db[i][3]);
+        *reinterpret_cast<float4*>(pb + 4) = make_float4(db[i][4], db[i][5], db[i][6], db[i][7]);
       }
     }
   }
@@ -264,7 +269,7 @@ MB_API int mb_norm_bwd_scratch_rows(int rows, int h) {
   int tpr, rpc;
   pick_shape(h, tpr, rpc);
   int groups = (rows + rpc - 1) / rpc;
-  int grid = num_sms() * 2;
+  int grid = num_sms() * 4;
   if (grid > groups) grid = groups;
   return grid * rpc;
 }
@@ -278,7 +283,7 @@ MB_API int mb_norm_fwd(const void* x0, const void* residual, const void* gamma, 
   int tpr, rpc;
   pick_shape(h, tpr, rpc);
   int groups = (rows + rpc - 1) / rpc;
-  int grid = num_sms() * 4;
+  int grid = num_sms() * 8;
   if (grid > groups) grid = groups;
   auto a = reinterpret_cast<const __nv_bfloat16*>(x0);
   auto r = reinterpret_cast<const __nv_bfloat16*>(residual);
@@ -305,7 +310,7 @@ MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const f
   int tpr, rpc;
   pick_shape(h, tpr, rpc);
   int groups = (rows + rpc - 1) / rpc;
-  int grid = num_sms() * 2;
+  int grid = num_sms() * 4;
   if (grid > groups) grid = groups;
   int nparts = grid * rpc;
   float* pg = scratch;

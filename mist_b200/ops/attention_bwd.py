@@ -67,7 +67,7 @@ def _native_backward(dout, q, k, v, o, lse, scale, causal, out):
         dq, dk, dv = out
     dout = dout.contiguous()
     delta = torch.empty(b, nh, sq, dtype=torch.float32, device=q.device)
-    dq_acc = torch.zeros(b, nh, sq, d, dtype=torch.float32, device=q.device)
+    dq_acc = torch.empty(b, nh, sq, d, dtype=torch.float32, device=q.device)   # zeroed by the launch wrapper
     call("mb_attn_bwd", ptr(dout), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(dq_acc),
          ptr(dq), ptr(dk), ptr(dv), b, sq, sk, nh, d,
          q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),

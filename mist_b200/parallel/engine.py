@@ -203,9 +203,9 @@ class TrainEngine:
         units = self.layer_units[id(stack)]
         if torch.is_grad_enabled():
             hidden, residual = _mark(lambda: self._layer_backward_start(stack, i), hidden, residual)
-        if self.zero3 and i + 1 < len(units):
-            # weights of block i are dropped once block i+1 starts (its slot is reused by i+2)
-            pass
+        if self.zero3 and (i + 1 < len(units) or not torch.is_grad_enabled()):
+            # block i's slot is reused by block i+2; the last block stays resident for the backward
+            self._release(units[i])
         if i + 1 == len(units) and self.post_unit is not None:
             self._wait_params(self.post_unit)
         return hidden, residual
