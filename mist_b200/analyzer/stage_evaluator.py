@@ -1,0 +1,310 @@
+"""Batched cost model of one pipeline stage.
+
+For a device mesh, a gradient-accumulation count and a stage shape (number of blocks,
+number of checkpointed blocks, with/without embedding and head) this evaluates *every*
+candidate strategy vector ``[b, dp, tp, wre, gre, ore, wo, go, oo, ao]`` at once with
+numpy broadcasting and returns, per candidate,
+
+* ``stable``: seconds per micro batch (forward + backward of all layers of the stage),
+* ``delta`` : seconds paid once per iteration (gradient synchronisation that only happens
+  at the last micro batch, optimizer step, weight refresh, optimizer-state swaps),
+* peak memory of the forward and of the backward pass, and a feasibility flag.
+
+Per layer and pass four channels run concurrently -- compute, GPU<->GPU collectives
+(ZeRO all-gather / reduce-scatter), host->GPU and GPU->host copies (offloading) -- and
+their combined time comes from the interference model; tensor-parallel collectives sit
+on the critical path and are added on top.  Execution latencies come from the operator
+database, memory terms from the symbolic layer analysis evaluated at ``b``.
+
+Parity: reference mist/analyzer/batched_module_analyzer.py:417-536 (search space),
+:687-3144 (batched_stage_analyze: memory :100-256, latencies :259-414, channel overlap
+:1362-1902, stable / delta split :1910-2028, state memory with ring buffers :2091-2162,
+peak memory :2755-3062, feasibility :2805-2812).  The schedule costed here is the one
+:mod:`mist_b200.parallel.engine` executes (optimizer step overlapped with the backward pass
+of the last micro batch rather than deferred into the next forward).
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass
+from functools import lru_cache
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import sympy as sp
+
+from ..config import MistConfig
+from ..node_database.database import OpDatabase
+from ..node_database.node_spec import NodeSpec
+from ..tools import comm_model
+from .layer_analyzer import LayerInfo, ModelAnalysis, get_analysis
+
+BATCH_SIZE_CANDIDATES = (1, 2, 4, 8)
+OFFLOAD_RATIOS = (0.0, 0.25, 0.375, 0.5, 0.625, 0.75, 0.875, 1.0)
+SPARSE_OFFLOAD_RATIOS = (0.0, 0.25, 0.375, 0.5, 0.75, 1.0)
+GB = float(1 << 30)
+#: allocator fragmentation allowance on top of the modelled peak
+MEMORY_FACTOR = 1.06
+ADAM_BYTES_PER_PARAM = 28.0     # fp32 master/m/v read+write (24) + bf16 grad read (2) + bf16 weight write (2)
+
+
+# ------------------------------------------------------------------------------ search space
+def create_search_space(num_nodes: int, gpus_per_node: int, global_batch: int, grad_accum: int, cfg: MistConfig,
+                        tp_size: Optional[int] = None, batch_candidates: Sequence[int] = BATCH_SIZE_CANDIDATES
+                        ) -> np.ndarray:
+    """All strategy vectors for one stage on ``num_nodes x gpus_per_node`` devices: [N, 10]."""
+    n_gpus = num_nodes * gpus_per_node
+    per_micro = global_batch // grad_accum
+    tun = cfg.tuning
+    par = []
+    for b in batch_candidates:
+        if b > per_micro or per_micro % b:
+            continue
+        dp = per_micro // b
+        if dp > n_gpus or n_gpus % dp:
+            continue
+        tp = n_gpus // dp
+        if tp_size is not None and tp != tp_size:
+            continue
+        if tp > gpus_per_node or (cfg.get("disable_tp_tuning", False) and tp > 1 and tp_size is None):
+            continue
+        if cfg.model.num_attention_heads % tp or cfg.model.vocab_size % tp:
+            continue
+        if dp == 1 or not (tun and tun.zero_2_and_3_enabled):
+            flags = [(0, 0, 1)]
+        else:
+            flags = [(0, 0, 1), (0, 1, 1), (1, 1, 1)]
+        for f in flags:
+            par.append((b, dp, tp) + f)
+    if not par:
+        return np.zeros((0, 10))
+    state_on = bool(tun and tun.state_offloading_enabled)
+    act_on = bool(tun and tun.activation_offloading_enabled)
+
+    def fixed(name, default):
+        v = cfg.get(name, None)
+        return [float(v)] if v is not None else default
+
+    wo = fixed("fixed_wo_ratio", list(SPARSE_OFFLOAD_RATIOS) if state_on and not cfg.get("disable_wo_tuning", False) else [0.0])
+    go = fixed("fixed_go_ratio", list(SPARSE_OFFLOAD_RATIOS) if state_on and not cfg.get("disable_go_tuning", False) else [0.0])
+    oo = fixed("fixed_oo_ratio", list(OFFLOAD_RATIOS) if state_on and not cfg.get("disable_oo_tuning", False) else [0.0])
+    ao = fixed("fixed_ao_ratio", list(OFFLOAD_RATIOS) if act_on else [0.0])
+    off = [o for o in itertools.product(wo, go, oo, ao) if not (o[0] > 0 and o[1] == 0)]
+    space = np.array([p + o for p in par for o in off], dtype=np.float64)
+    return space
+
+
+# ------------------------------------------------------------------ per-(tp, b) layer numbers
+@dataclass
+class LayerNumbers:
+    exec_fwd: float
+    exec_bwd: float
+    tp_fwd: float            # tensor-parallel collectives on the critical path, seconds
+    tp_bwd: float
+    fwd_peak: float          # bytes
+    bwd_peak: float
+    saved: float
+    input_bytes: float
+    output_bytes: float
+    weight_bytes: float
+    params: float
+
+
+class StageEvaluator:
+    def __init__(self, cfg: MistConfig, db: Optional[OpDatabase] = None, cache_dir: Optional[str] = None):
+        self.cfg = cfg
+        self.db = db or OpDatabase()
+        self.cache_dir = cache_dir
+        self.hw = cfg.hardware
+        self._analysis: Dict[int, ModelAnalysis] = {}
+        self._numbers: Dict[Tuple[int, int, str], LayerNumbers] = {}
+        self._b = sp.Symbol("b", integer=True, positive=True)
+
+    # ------------------------------------------------------------------------- analysis
+    def analysis(self, tp: int) -> ModelAnalysis:
+        if tp not in self._analysis:
+            self._analysis[tp] = get_analysis(self.cfg, tp, self.cache_dir)
+        return self._analysis[tp]
+
+    def _val(self, expr, b: int) -> float:
+        if isinstance(expr, sp.Basic):
+            return float(expr.subs(self._b, b))
+        return float(expr)
+
+    def layer_numbers(self, tp: int, b: int, which: str) -> LayerNumbers:
+        key = (tp, b, which)
+        if key in self._numbers:
+            return self._numbers[key]
+        info: LayerInfo = self.analysis(tp).layer(which)
+        ef = eb = 0.0
+        tpf = tpb = 0.0
+        for n in info.nodes:
+            fl_f, fl_b = self._val(n.flops_fwd, b), self._val(n.flops_bwd, b)
+            by_f, by_b = self._val(n.bytes_fwd, b), self._val(n.bytes_bwd, b)
+            if n.comm_fwd is None and n.comm_bwd is None:
+                spec = NodeSpec.from_dict(n.spec, {"b": b})
+                f, w = self.db.latency(spec, fl_f, fl_b, by_f, by_b)
+                ef += f
+                eb += w
+            for comm, fwd in ((n.comm_fwd, True), (n.comm_bwd, False)):
+                if comm is None:
+                    continue
+                t = float(comm_model.gpu_gpu_latency(comm.kind, np.array([self._val(comm.nbytes, b) / 1e9]), tp, 1,
+                                                     self.hw.gpu_gpu_comm_params)[0])
+                if fwd:
+                    tpf += t
+                else:
+                    tpb += t
+        num = LayerNumbers(ef, eb, tpf, tpb, self._val(info.fwd.peak, b), self._val(info.bwd.peak, b),
+                           self._val(info.fwd.saved, b), self._val(info.input_bytes, b), self._val(info.fwd.output, b),
+                           float(info.weight_bytes), float(info.num_params))
+        self._numbers[key] = num
+        return num
+
+    # --------------------------------------------------------------------------- helpers
+    def _coll(self, kind: str, nbytes: np.ndarray, n: np.ndarray) -> np.ndarray:
+        per_node = self.hw.num_gpus_per_node
+        intra = np.minimum(n, per_node)
+        inter = np.maximum(n // per_node, 1)
+        return comm_model.gpu_gpu_latency(kind, nbytes / 1e9, intra, inter, self.hw.gpu_gpu_comm_params)
+
+    def _h2d(self, nbytes):
+        return comm_model.host_copy_latency(np.asarray(nbytes) / 1e9, self.hw.cpu_gpu_comm_params)
+
+    def _d2h(self, nbytes):
+        return comm_model.host_copy_latency(np.asarray(nbytes) / 1e9, self.hw.gpu_cpu_comm_params)
+
+    def _interf(self, C, G2G, C2G, G2C):
+        return comm_model.interference_estimate(C, G2G, C2G, G2C, self.hw.interference_model_params)
+
+    # -------------------------------------------------------------------------- evaluate
+    def evaluate(self, space: np.ndarray, num_layers: int, num_ckpt: int, grad_accum: int, has_pre: bool,
+                 has_post: bool, inflight_extra: int = 0, pre_post_space: Optional[np.ndarray] = None) -> Dict[str, np.ndarray]:
+        """``space``: [N, 10].  ``inflight_extra``: additional micro batches whose activations are
+        alive at the memory peak (1F1B warm-up depth of this stage)."""
+        N = space.shape[0]
+        b = space[:, 0].astype(int)
+        dp = space[:, 1].astype(int)
+        tp = space[:, 2].astype(int)
+        wre, gre, ore = space[:, 3] > 0, space[:, 4] > 0, space[:, 5] > 0
+        wo, go, oo, ao = space[:, 6], space[:, 7], space[:, 8], space[:, 9]
+        L, c, G = int(num_layers), int(num_ckpt), int(grad_accum)
+
+        def gather(which: str) -> Dict[str, np.ndarray]:
+            fields = ("exec_fwd", "exec_bwd", "tp_fwd", "tp_bwd", "fwd_peak", "bwd_peak", "saved", "input_bytes",
+                      "output_bytes", "weight_bytes", "params")
+            out = {f: np.zeros(N) for f in fields}
+            for (t, bb) in set(zip(tp.tolist(), b.tolist())):
+                sel = (tp == t) & (b == bb)
+                num = self.layer_numbers(t, bb, which)
+                for f in fields:
+                    out[f][sel] = getattr(num, f)
+            return out
+
+        def layer_cost(x: Dict[str, np.ndarray], ckpt: bool, last_micro: bool):
+            """(forward seconds, backward seconds) of one layer for every candidate."""
+            W = x["weight_bytes"]
+            w_shard = np.where(wre, W / dp, W)
+            g_shard = np.where(gre, W / dp, W)
+            kept = x["input_bytes"] if ckpt else x["saved"]
+            ag_w = np.where(wre, self._coll("all_gather", W, dp), 0.0)
+            # forward
+            f_c = x["exec_fwd"]
+            f_g2g = ag_w
+            f_c2g = self._h2d(wo * w_shard)
+            f_g2c = self._d2h(ao * kept)
+            fwd = self._interf(f_c, f_g2g, f_c2g, f_g2c) + x["tp_fwd"]
+            # backward
+            b_c = x["exec_bwd"] + (x["exec_fwd"] if ckpt else 0.0)
+            rs_every = np.where(gre, self._coll("reduce_scatter", W, dp), 0.0)
+            b_g2g = ag_w + rs_every
+            b_c2g = self._h2d(wo * w_shard + ao * kept + (go * g_shard if G > 1 else 0.0))
+            b_g2c = self._d2h(go * g_shard)
+            if last_micro:
+                # gradient sync that waits for the last micro batch, optimizer, weight refresh
+                sync = np.where(gre, 0.0, np.where(ore, self._coll("reduce_scatter", W, dp),
+                                                   self._coll("all_reduce", W, dp)))
+                refresh = np.where(ore & ~wre, self._coll("all_gather", W, dp), 0.0)
+                shard_params = np.where(ore, x["params"] / dp, x["params"])
+                adam = shard_params * ADAM_BYTES_PER_PARAM / (self.db.model.hbm_gbs * 1e9)
+                opt_bytes = 12.0 * shard_params * oo
+                b_c = b_c + adam
+                b_g2g = b_g2g + sync + refresh
+                b_c2g = b_c2g + self._h2d(opt_bytes)
+                b_g2c = b_g2c + self._d2h(opt_bytes)
+            bwd = self._interf(b_c, b_g2g, b_c2g, b_g2c) + x["tp_bwd"] + (x["tp_fwd"] if ckpt else 0.0)
+            return fwd, bwd
+
+        blk = gather("block_layer")
+        f0, b0 = layer_cost(blk, False, False)
+        f1, b1 = layer_cost(blk, True, False)
+        _, b0l = layer_cost(blk, False, True)
+        _, b1l = layer_cost(blk, True, True)
+        stable = (L - c) * (f0 + b0) + c * (f1 + b1)
+        delta = (L - c) * (b0l - b0) + c * (b1l - b1)
+
+        # ---- memory of the stage
+        W = blk["weight_bytes"]
+        w_res = L * np.where(wre, W / dp, W) * (1 - wo)
+        w_ring = np.where(wre | (wo > 0), 2 * W, 0.0)
+        g_res = L * np.where(gre, W / dp, W) * (1 - go) * (2.0 if G > 1 else 1.0)   # fp32 accumulation when G > 1
+        g_ring = np.where(gre | (go > 0), 2 * W, 0.0)
+        o_res = L * 6.0 * np.where(ore, W / dp, W) * (1 - oo)
+        o_stage = np.where(oo > 0, 2 * 6.0 * np.where(ore, W / dp, W), 0.0)
+        states = w_res + w_ring + g_res + g_ring + o_res + o_stage
+        inflight = 1 + int(inflight_extra)
+        acts = inflight * ((L - c) * blk["saved"] * (1 - ao) + c * blk["input_bytes"] * (1 - ao))
+        peak_f = states + acts + blk["fwd_peak"]
+        bwd_tr = np.maximum(blk["bwd_peak"], (blk["fwd_peak"] + blk["bwd_peak"]) if c > 0 else 0.0)
+        peak_b = states + acts + bwd_tr
+
+        for present, which in ((has_pre, "pre_layer"), (has_post, "post_layer")):
+            if not present:
+                continue
+            x = gather(which)
+            f, bw = layer_cost(x, False, False)
+            _, bwl = layer_cost(x, False, True)
+            stable = stable + f + bw
+            delta = delta + (bwl - bw)
+            Wp = x["weight_bytes"]
+            st = np.where(wre, Wp / dp, Wp) + np.where(gre, Wp / dp, Wp) + 6.0 * np.where(ore, Wp / dp, Wp)
+            peak_f = peak_f + st + inflight * x["saved"]
+            peak_b = peak_b + st + inflight * x["saved"]
+            peak_f = np.maximum(peak_f, states + acts + st + x["fwd_peak"])
+            peak_b = np.maximum(peak_b, states + acts + st + x["bwd_peak"])
+
+        cap = self.hw.memory_capacity * GB
+        feasible = np.maximum(peak_f, peak_b) * MEMORY_FACTOR <= cap
+        return {"stable": stable, "delta": delta, "peak_fwd": peak_f, "peak_bwd": peak_b, "feasible": feasible}
+
+
+# ------------------------------------------------------------------------------- pipeline
+def pipeline_latency(stable: Sequence[float], delta: Sequence[float], grad_accum: int) -> float:
+    """Iteration time of a 1F1B pipeline: ``sum T + (G - 1) max T + max_s (D_s - sum_{i<s} T_i)``;
+    a single stage costs ``T * G + D``."""
+    T, D = list(stable), list(delta)
+    if len(T) == 1:
+        return T[0] * grad_accum + D[0]
+    prefix, worst = 0.0, -float("inf")
+    for t, d in zip(T, D):
+        worst = max(worst, d - prefix)
+        prefix += t
+    return sum(T) + (grad_accum - 1) * max(T) + max(worst, 0.0)
+
+
+def analyze_strategy(cfg: MistConfig, evaluator: Optional[StageEvaluator] = None) -> Dict:
+    """Predicted cost of the strategy written in ``cfg.strategy`` (the analyze entry point)."""
+    ev = evaluator or StageEvaluator(cfg)
+    st = cfg.strategy
+    S, G = st.num_stages, st.gradient_accumulation_steps
+    stables, deltas, peaks = [], [], []
+    for s in range(S):
+        vec = np.array([st.stage_strategies[s]], dtype=np.float64)
+        warm = min(S - 1 - s, max(G - 1, 0))
+        res = ev.evaluate(vec, st.layer_partitions[s], st.gradient_checkpointing[s], G, has_pre=(s == 0),
+                          has_post=(s == S - 1), inflight_extra=warm)
+        stables.append(float(res["stable"][0]))
+        deltas.append(float(res["delta"][0]))
+        peaks.append((float(res["peak_fwd"][0]), float(res["peak_bwd"][0])))
+    total = pipeline_latency(stables, deltas, G)
+    return {"total": total, "stable": stables, "delta": deltas, "peak_memories": peaks}

@@ -23,6 +23,20 @@ import torch.nn.functional as F
 from . import native
 from .native import call, ptr, stream, use_native
 
+
+def _sym(*xs):
+    """True when any argument is a shape-symbolic tensor of the analyzer (then the op is
+    recorded by its symbolic rule instead of being executed)."""
+    for x in xs:
+        if x is not None and type(x).__name__ == "SymTensor":
+            return True
+    return False
+
+
+def _rules():
+    from ..analyzer import rules
+    return rules
+
 # --------------------------------------------------------------------------- settings
 EPI_BIAS, EPI_GELU, EPI_SAVE_PRE, EPI_ACCUM, EPI_DGELU, EPI_OUT_FP32, EPI_RESIDUAL = 1, 2, 4, 8, 16, 32, 64
 
@@ -173,6 +187,8 @@ class _LinearFn(torch.autograd.Function):
 
 def linear(x, weight, bias=None, activation: Optional[str] = None, residual=None):
     """``act(x @ weight.T + bias) (+ residual)`` with the three GEMMs on tcgen05."""
+    if _sym(x):
+        return _rules().linear(x, weight, bias, activation, residual)
     return _LinearFn.apply(x, weight, bias, activation, residual)
 
 
@@ -234,6 +250,8 @@ class _GeluFn(torch.autograd.Function):
 
 
 def gelu(x, bias=None):
+    if _sym(x):
+        return _rules().gelu(x, bias)
     return _GeluFn.apply(x, bias)
 
 
@@ -270,6 +288,8 @@ class _SwigluFn(torch.autograd.Function):
 
 
 def swiglu(x):
+    if _sym(x):
+        return _rules().swiglu(x)
     return _SwigluFn.apply(x)
 
 
@@ -313,6 +333,8 @@ class _BiasDropoutAddFn(torch.autograd.Function):
 
 def bias_dropout_add(x, bias, residual, p: float = 0.0, seed: int = 0):
     """``residual + dropout(x + bias, p)``; the mask is regenerated, not stored."""
+    if _sym(x, residual):
+        return _rules().bias_dropout_add(x, bias, residual, p, seed)
     return _BiasDropoutAddFn.apply(x, bias, residual, float(p), int(seed))
 
 
@@ -407,10 +429,14 @@ class _NormFn(torch.autograd.Function):
 
 
 def layer_norm(x, gamma, beta, eps=1e-5, residual=None, prenorm=False):
+    if _sym(x):
+        return _rules().norm(x, residual, gamma, beta, eps, False, prenorm)
     return _NormFn.apply(x, residual, gamma, beta, eps, False, prenorm)
 
 
 def rms_norm(x, gamma, eps=1e-5, residual=None, prenorm=False):
+    if _sym(x):
+        return _rules().norm(x, residual, gamma, None, eps, True, prenorm)
     return _NormFn.apply(x, residual, gamma, None, eps, True, prenorm)
 
 
@@ -520,6 +546,8 @@ class _AttnFn(torch.autograd.Function):
 
 def attention(q, k, v, scale: Optional[float] = None, causal: bool = True):
     """Multi-head attention; q ``[b,sq,nh,d]``, k/v ``[b,sk,nh_kv,d]`` (views allowed)."""
+    if _sym(q):
+        return _rules().attention(q, k, v, scale, causal)
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
     return _AttnFn.apply(q, k, v, float(scale), bool(causal))
@@ -556,6 +584,8 @@ class _PackedAttnFn(torch.autograd.Function):
 
 def attention_qkvpacked(qkv, scale: Optional[float] = None, causal: bool = True, rotary=None):
     """``rotary`` is ``None`` or ``(cos, sin, rot_dim)`` from :func:`rope_tables`."""
+    if _sym(qkv):
+        return _rules().attention_qkvpacked(qkv, scale, causal, rotary)
     if scale is None:
         scale = 1.0 / math.sqrt(qkv.shape[-1])
     cos, sin, rot = rotary if rotary is not None else (None, None, 0)
@@ -619,6 +649,8 @@ class _CausalSoftmaxFn(torch.autograd.Function):
 
 
 def scaled_causal_softmax(x, scale: float, causal: bool = True):
+    if _sym(x):
+        return _rules().scaled_causal_softmax(x, scale, causal)
     return _CausalSoftmaxFn.apply(x, float(scale), bool(causal))
 
 
@@ -687,6 +719,8 @@ class _XentFn(torch.autograd.Function):
 
 def cross_entropy(logits, labels, vocab_start: int = 0, group=None, ignore_index: int = -100):
     """Per-row loss (fp32) of ``[rows, v_local]`` logits against global ``labels``."""
+    if _sym(logits):
+        return _rules().cross_entropy(logits, labels, vocab_start, group, ignore_index)
     return _XentFn.apply(logits, labels, int(vocab_start), group, int(ignore_index))
 
 
@@ -737,6 +771,8 @@ class _EmbeddingFn(torch.autograd.Function):
 
 def embedding(ids, wte, wpe=None, vocab_start: int = 0):
     """``wte[ids - vocab_start]`` (zero outside this rank's slice) ``+ wpe[position]``."""
+    if _sym(ids):
+        return _rules().embedding(ids, wte, wpe, vocab_start)
     return _EmbeddingFn.apply(ids, wte, wpe, int(vocab_start))
 
 

@@ -125,20 +125,37 @@ class _CopyToGroup(torch.autograd.Function):
         return all_reduce_raw(g.contiguous().clone(), ctx.group)[0], None
 
 
+def _symbolic(x) -> bool:
+    return type(x).__name__ == "SymTensor"
+
+
+def _rules():
+    from ..analyzer import rules
+    return rules
+
+
 def all_gather(x, group):
-    return x if _is_trivial(group) else _AllGather.apply(x, group)
+    if _is_trivial(group):
+        return x
+    return _rules().all_gather(x, group) if _symbolic(x) else _AllGather.apply(x, group)
 
 
 def reduce_scatter(x, group):
-    return x if _is_trivial(group) else _ReduceScatter.apply(x, group)
+    if _is_trivial(group):
+        return x
+    return _rules().reduce_scatter(x, group) if _symbolic(x) else _ReduceScatter.apply(x, group)
 
 
 def all_reduce(x, group):
-    return x if _is_trivial(group) else _AllReduce.apply(x, group)
+    if _is_trivial(group):
+        return x
+    return _rules().all_reduce(x, group) if _symbolic(x) else _AllReduce.apply(x, group)
 
 
 def copy_to_group(x, group):
-    return x if _is_trivial(group) else _CopyToGroup.apply(x, group)
+    if _is_trivial(group):
+        return x
+    return _rules().copy_to_group(x, group) if _symbolic(x) else _CopyToGroup.apply(x, group)
 
 
 def sync_shared_params(model: torch.nn.Module, group):
