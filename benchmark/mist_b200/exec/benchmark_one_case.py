@@ -1,0 +1,128 @@
+"""exec: run the strategy of a configuration on real GPUs and report measured latency and
+peak memory.
+
+    torchrun --nproc-per-node N benchmark/mist_b200/exec/benchmark_one_case.py --config-name X
+
+Latency is timed on the device (CUDA events around ``number`` iterations after ``warmup``)
+and the maximum over ranks is reported; peak allocated / reserved memory is gathered per
+stage (reference: benchmark/mist/exec/benchmark_one_case.py:88-621; it times non-pipelined
+runs with host timers and reports rank 0's value, summary keys :615-619).
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from common import load_from_cli, output_dir  # noqa: E402
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from mist_b200.api import TrainingSession  # noqa: E402
+from mist_b200.ops import native  # noqa: E402
+from mist_b200.utils.summary import fmt_cost, fmt_memories, update_summary  # noqa: E402
+
+
+def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cuda = torch.cuda.is_available()
+    if cuda:
+        torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        import datetime
+        dist.init_process_group("nccl" if cuda else "gloo", timeout=datetime.timedelta(seconds=cfg.nccl_timeout),
+                                **({"device_id": torch.device("cuda", local)} if cuda else {}))
+    tiny = bool(cfg.get("tiny_bench", True))
+    warmup = warmup if warmup is not None else (1 if tiny else 5)
+    number = number if number is not None else (2 if tiny else 5)
+    if cfg.get("memory_debug", False) and cuda:
+        torch.cuda.memory._record_memory_history()
+    sess = TrainingSession(cfg, comm_backend=comm_backend, seed=seed)
+    ps = sess.ps
+    mb, G, seq = sess.micro_batch, sess.G, sess.seq_len
+    vocab = cfg.model.vocab_size
+    gen = torch.Generator().manual_seed(seed + 31 * ps.dp_rank)     # same data on every tp / pp rank of a replica
+    dev = sess.device
+
+    def batch():
+        ids = torch.randint(0, vocab, (mb * G, seq), generator=gen)
+        lab = torch.randint(0, vocab, (mb * G, seq), generator=gen)
+        return ids.to(dev), lab.to(dev)
+
+    data = [batch() for _ in range(warmup + number)]
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        if cuda:
+            torch.cuda.synchronize()
+
+    prof = None
+    if cfg.get("profile", False) and cuda:
+        prof = torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA],
+                                      on_trace_ready=torch.profiler.tensorboard_trace_handler(
+                                          "./logs", worker_name=f"rank{rank}_stage{ps.stage}"))
+        prof.start()
+    for i in range(warmup):
+        sess.step_on_device(*data[i])
+    sess.finish()
+    sync()
+    if cuda:
+        torch.cuda.reset_peak_memory_stats()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+    wall = time.perf_counter()
+    loss = None
+    for i in range(number):
+        loss = sess.step_on_device(*data[warmup + i])
+    sess.finish()
+    if cuda:
+        t1.record()
+    sync()
+    latency = (t0.elapsed_time(t1) / 1e3 if cuda else time.perf_counter() - wall) / number
+    if prof is not None:
+        prof.stop()
+    native.check_status()
+    alloc = torch.cuda.max_memory_allocated() if cuda else 0
+    reserved = torch.cuda.max_memory_reserved() if cuda else 0
+    stats = torch.tensor([latency, float(alloc), float(reserved)], dtype=torch.float64, device=dev)
+    S = ps.num_stages
+    per_stage = torch.zeros(S, 2, dtype=torch.float64, device=dev)
+    per_stage[ps.stage, 0], per_stage[ps.stage, 1] = float(alloc), float(reserved)
+    if world > 1:
+        lat = stats[:1].clone()
+        dist.all_reduce(lat, op=dist.ReduceOp.MAX)
+        dist.all_reduce(per_stage, op=dist.ReduceOp.MAX)
+        latency = float(lat[0])
+    if cfg.get("memory_debug", False) and cuda:
+        torch.cuda.memory._dump_snapshot(f"memory_snapshot_rank{rank}.pickle")
+    tokens = cfg.training.global_batch_size * seq
+    return {"latency": latency, "tokens_per_s": tokens / latency, "loss": float(loss) if loss is not None else None,
+            "peak_allocated": per_stage[:, 0].tolist(), "peak_reserved": per_stage[:, 1].tolist(), "rank": rank}
+
+
+def main(argv=None):
+    cfg, node = load_from_cli(argv)
+    res = run(cfg, node, comm_backend=node.get("comm_backend"))
+    if res["rank"] == 0:
+        print(f"Total Latency: {res['latency']:.4f}")
+        print(f"Throughput: {res['tokens_per_s']:.1f} tokens/s")
+        print(f"Peak allocated memory per stage: {fmt_memories(res['peak_allocated'])}")
+        print(f"Peak reserved memory per stage: {fmt_memories(res['peak_reserved'])}")
+        update_summary(os.path.join(output_dir(node), "summary.json"), {
+            "exec_total_cost": fmt_cost(res["latency"]),
+            "exec_stage_peak_allocated_memories": fmt_memories(res["peak_allocated"]),
+            "exec_stage_peak_reserved_memories": fmt_memories(res["peak_reserved"]),
+        })
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    return res
+
+
+if __name__ == "__main__":
+    main()
