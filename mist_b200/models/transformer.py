@@ -13,6 +13,7 @@ Parity: reference mist/model/transformer.py:91-342 (ParallelTransformerLayer),
 """
 from __future__ import annotations
 
+import contextlib
 from typing import List, Optional
 
 import torch
@@ -133,11 +134,13 @@ class ParallelTransformer(nn.Module):
         for i, layer in enumerate(self.layers):
             if hooks is not None:
                 hidden, residual = hooks.before_layer(self, i, hidden, residual)
-            if i >= first_ckpt and torch.is_grad_enabled():
-                from ..utils.checkpointing import checkpoint_block
-                hidden, residual = checkpoint_block(layer, hidden, residual, encoder_output, batch_size)
-            else:
-                hidden, residual = layer(hidden, residual, encoder_output, batch_size)
+            ctx = hooks.layer_context(self, i) if hasattr(hooks, "layer_context") else contextlib.nullcontext()
+            with ctx:
+                if i >= first_ckpt and torch.is_grad_enabled():
+                    from ..utils.checkpointing import checkpoint_block
+                    hidden, residual = checkpoint_block(layer, hidden, residual, encoder_output, batch_size)
+                else:
+                    hidden, residual = layer(hidden, residual, encoder_output, batch_size)
             if hooks is not None:
                 hidden, residual = hooks.after_layer(self, i, hidden, residual)
         if self.final_norm is not None:

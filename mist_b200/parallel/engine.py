@@ -68,7 +68,7 @@ class TrainEngine:
                  strategy: Optional[StageStrategy] = None, grad_accum_steps: int = 1,
                  ckpt_layers: int = 0, hp: Optional[Dict] = None, comm_backend: str = "nccl",
                  grad_dtype: Optional[torch.dtype] = None, overlap: bool = True,
-                 pre_post_strategy: Optional[StageStrategy] = None):
+                 pre_post_strategy: Optional[StageStrategy] = None, use_grad_ring: bool = True):
         self.model = model
         self.ps = pstate or ParallelState.single()
         self.strategy = strategy or StageStrategy(1, 1, 1, False, False, False, 0, 0, 0, 0)
@@ -119,9 +119,28 @@ class TrainEngine:
             stack.gradient_checkpointing = min(int(ckpt_layers), len(stack.layers))
 
         # -------------------------------------------------------- buckets, state, streams
+        from .swap import ActivationSwapper, SwapStreams
+        self.swap_streams = SwapStreams(self.device)
+        oo, ao = float(self.strategy.opt_offload), float(self.strategy.act_offload)
+        # Gradient buckets.  With sharded gradients (ZeRO-2/3) a block's full-size bucket is only
+        # needed from its backward pass until its reduction, so the blocks share a ring of two
+        # buckets; otherwise every unit keeps its own (it accumulates over micro steps).
+        layer_units = self._all_layer_units()
+        self.use_grad_ring = bool(use_grad_ring) and zero >= ZeroLevel.OPT_GRAD and dp > 1 and len(layer_units) > 2
+        self.grad_ring, self._ring_free, self._ring_next = [], [], 0
+        if self.use_grad_ring:
+            biggest = max(u.padded for u in layer_units)
+            self.grad_ring = [torch.zeros(biggest, dtype=self.grad_dtype, device=self.device) for _ in range(2)]
+            self._ring_free = [None, None]
         for u in self.units:
-            u.bind_grad_bucket(torch.zeros(u.padded, dtype=self.grad_dtype, device=self.device))
-            u.init_optimizer_state()
+            if self.use_grad_ring and u in layer_units:
+                u.ring_slot = None
+            else:
+                u.bind_grad_bucket(torch.zeros(u.padded, dtype=self.grad_dtype, device=self.device))
+            u.init_optimizer_state(offload_ratio=oo if u in layer_units else 0.0)
+        host_n = max((u.opt_host_numel for u in self.units), default=0)
+        self.opt_staging = [torch.empty(host_n, dtype=torch.float32, device=self.device) for _ in range(3)] if host_n else None
+        self.act_swapper = ActivationSwapper(ao, self.swap_streams) if ao > 0 else None
         self.compute_stream = torch.cuda.current_stream() if self.cuda else None
         self.comm_stream = torch.cuda.Stream() if (self.cuda and overlap) else self.compute_stream
         self.param_ready: Dict[str, "torch.cuda.Event"] = {}
@@ -141,6 +160,17 @@ class TrainEngine:
         if comm_backend == "fused" and dp > 1:
             from .fused_comm import FusedDPComm
             self.fused = FusedDPComm(self)
+
+    def _all_layer_units(self):
+        return [u for us in self.layer_units.values() for u in us]
+
+    def layer_context(self, stack, i):
+        """Context the stack wraps around block ``i``'s forward (activation swapping)."""
+        import contextlib
+        if self.act_swapper is None or not torch.is_grad_enabled():
+            return contextlib.nullcontext()
+        self.act_swapper.set_scope((self._micro, id(stack), i))
+        return self.act_swapper.hooks()
 
     # -------------------------------------------------------------------- stream helpers
     def _on_comm(self):
@@ -210,9 +240,26 @@ class TrainEngine:
             self._wait_params(self.post_unit)
         return hidden, residual
 
+    def _acquire_ring_slot(self, unit: FlatUnit):
+        slot = self._ring_next
+        self._ring_next ^= 1
+        ev = self._ring_free[slot]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)     # the previous user's reduction has read it
+            self._ring_free[slot] = None
+        unit.ring_slot = slot
+        if self.fused is not None and self.fused.handles(unit):
+            self.fused.bind_ring_slot(unit, slot)
+        else:
+            unit.bind_grad_bucket(self.grad_ring[slot], fresh=True)
+
     def _layer_backward_start(self, stack, i):
         units = self.layer_units[id(stack)]
         self._wait_bucket(units[i])
+        if self.use_grad_ring:
+            self._acquire_ring_slot(units[i])
+        if self.act_swapper is not None and i > 0:
+            self.act_swapper.prefetch((self._micro, id(stack), i - 1))   # one block ahead of its backward
         if i + 1 == len(units) and self.post_unit is not None and stack is self.stacks[-1]:
             self._unit_backward_done(self.post_unit)   # head + final norm finished before the last block
         if self.zero3:
@@ -223,22 +270,36 @@ class TrainEngine:
                 self._gather(units[i - 1])
 
     def _layer_backward_done(self, stack, i):
+        if self.act_swapper is not None:
+            self.act_swapper.release((self._micro, id(stack), i))
         u = self.layer_units[id(stack)][i]
         self._unit_backward_done(u)
         if self.zero3:
             self._release(u)
 
     # --------------------------------------------------------------------- gradient path
+    def _release_ring_slot(self, unit: FlatUnit):
+        slot = getattr(unit, "ring_slot", None)
+        if slot is None:
+            return
+        if self.cuda:
+            ev = torch.cuda.Event()
+            ev.record()                       # recorded on the stream that ran the reduction
+            self._ring_free[slot] = ev
+        unit.ring_slot = None
+
     def _unit_backward_done(self, unit: FlatUnit):
         last = self._micro == self.G - 1
         unit.collect_autograd_grads()
-        if self.fused is not None and self.fused.handles(unit):
+        if self.fused is not None and self.fused.handles(unit) and not unit.opt_host_numel:
             self.fused.reduce_and_step(unit, last)
             return
         with self._on_comm():
             grad = unit.reduce_grads(self.ps.dp_rs_group, last)
             if grad is not None:
-                unit.optimizer_step(grad, self.hp, self.ps.dp_ag_group, grad_divisor=float(self.ps.dp_size * self.G))
+                swap = (self.swap_streams, self.opt_staging) if unit.opt_host_numel else None
+                unit.optimizer_step(grad, self.hp, self.ps.dp_ag_group, grad_divisor=float(self.ps.dp_size * self.G),
+                                    swap=swap)
                 if self.cuda:
                     ev = torch.cuda.Event()
                     ev.record()
@@ -247,6 +308,7 @@ class TrainEngine:
                 ev = torch.cuda.Event()
                 ev.record()
                 self.bucket_free[unit.name] = ev
+            self._release_ring_slot(unit)
 
     # ------------------------------------------------------------------------- stepping
     def forward_backward(self, batch: Dict, micro_index: int = 0):

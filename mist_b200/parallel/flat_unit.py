@@ -135,12 +135,23 @@ class FlatUnit:
             p.grad = None
 
     # ------------------------------------------------------------------ optimizer state
-    def init_optimizer_state(self, state_dtype=torch.float32):
+    def init_optimizer_state(self, state_dtype=torch.float32, offload_ratio: float = 0.0):
+        """Creates fp32 master weights and Adam moments; the trailing ``offload_ratio`` of each
+        lives in pinned host memory and is staged through device buffers around the step."""
         src = self.param_shard if self.param_shard is not None else (
             self.flat_param[self.shard_range()] if self.sharded_state else self.flat_param)
         self.master = src.detach().to(state_dtype).clone()
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
+        self.opt_split = None
+        if offload_ratio > 0:
+            from .swap import SplitTensor
+            self.opt_split = [SplitTensor(t, offload_ratio) for t in (self.master, self.exp_avg, self.exp_avg_sq)]
+            self.master, self.exp_avg, self.exp_avg_sq = (s.device_part for s in self.opt_split)
+
+    @property
+    def opt_host_numel(self) -> int:
+        return self.opt_split[0].host_numel if getattr(self, "opt_split", None) else 0
 
     # --------------------------------------------------------------------------- ZeRO-3
     def unshard(self, slot: torch.Tensor, group, async_op=False):
@@ -188,9 +199,10 @@ class FlatUnit:
         dist.all_reduce(self.flat_grad, group=group)
         return self.flat_grad
 
-    def optimizer_step(self, grad: torch.Tensor, hp: Dict, group, grad_divisor: float):
+    def optimizer_step(self, grad: torch.Tensor, hp: Dict, group, grad_divisor: float, swap=None):
         """Fused Adam on this rank's state, writing the bf16 weights, then (ZeRO-1/2) the
-        all-gather that refreshes the other ranks' slices."""
+        all-gather that refreshes the other ranks' slices.  ``swap`` = (streams, staging
+        buffers) when part of the state lives on the host."""
         self.step_count += 1
         if self.param_shard is not None:
             model_out = self.param_shard
@@ -198,10 +210,30 @@ class FlatUnit:
             model_out = self.flat_param[self.shard_range()]
         else:
             model_out = self.flat_param
-        g = grad if grad.numel() == self.master.numel() else grad[self.shard_range()]
-        F.adam_step(self.master, self.exp_avg, self.exp_avg_sq, g, model_out, lr=hp["lr"], beta1=hp["beta1"],
-                    beta2=hp["beta2"], eps=hp["eps"], weight_decay=hp["weight_decay"], step=self.step_count,
-                    inv_scale=1.0 / grad_divisor, adamw=hp.get("adamw", True))
+        n_state = self.state_numel
+        g = grad if grad.numel() == n_state else grad[self.shard_range()]
+        kw = dict(lr=hp["lr"], beta1=hp["beta1"], beta2=hp["beta2"], eps=hp["eps"], weight_decay=hp["weight_decay"],
+                  step=self.step_count, inv_scale=1.0 / grad_divisor, adamw=hp.get("adamw", True))
+        split = getattr(self, "opt_split", None)
+        if split is None:
+            F.adam_step(self.master, self.exp_avg, self.exp_avg_sq, g, model_out, **kw)
+        else:
+            streams, staging = swap
+            nd = split[0].dev_numel
+            cuda = streams.cuda
+            if cuda:
+                cur = torch.cuda.current_stream()
+                streams.h2d.wait_stream(streams.d2h)      # staging buffers free (previous unit stored back)
+            staged = [sp_.load(buf, streams) for sp_, buf in zip(split, staging)]
+            if nd:
+                F.adam_step(self.master, self.exp_avg, self.exp_avg_sq, g[:nd], model_out[:nd], **kw)
+            if cuda:
+                cur.wait_stream(streams.h2d)
+            F.adam_step(staged[0], staged[1], staged[2], g[nd:], model_out[nd:], **kw)
+            if cuda:
+                streams.d2h.wait_stream(cur)
+            for sp_, st in zip(split, staged):
+                sp_.store(st, streams)
         if self.sharded_state and self.param_shard is None and group is not None:
             dist.all_gather_into_tensor(self.flat_param, model_out, group=group)
         self.micro_steps_accumulated = 0

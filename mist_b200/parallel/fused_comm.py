@@ -33,10 +33,18 @@ class FusedDPComm:
         self.num_ctas = num_ctas
         units = [u for u in engine.units if self._eligible(u)]
         gsz = torch.empty(0, dtype=engine.grad_dtype).element_size()
-        total = sum(u.padded * (2 + gsz) + 4096 for u in units) + FLAG_SLOT_INTS * 4 * (len(units) + 1) + (1 << 20)
+        ring_units = set(id(u) for u in engine._all_layer_units()) if engine.use_grad_ring else set()
+        ring_elems = max((u.padded for u in units if id(u) in ring_units), default=0)
+        total = (sum(u.padded * (2 + (0 if id(u) in ring_units else gsz)) + 4096 for u in units)
+                 + 2 * (ring_elems * gsz + 4096) + FLAG_SLOT_INTS * 4 * (len(units) + 1) + (1 << 20))
         self.heap = SymmetricHeap(total, self.group, engine.device)
         self.tables: Dict[str, Dict] = {}
         flags, flag_off = self.heap.alloc(FLAG_SLOT_INTS * len(units), torch.int32)
+        self.ring = []
+        if ring_elems:
+            for _ in range(2):
+                buf, off = self.heap.alloc(ring_elems, engine.grad_dtype)
+                self.ring.append((buf, ptr_table(self.heap.peer_ptrs(off))))
         for k, u in enumerate(units):
             t = {}
             if u.param_shard is None:
@@ -50,9 +58,12 @@ class FusedDPComm:
                 base_bytes = self.me * u.shard_numel * 2
                 t["params"] = ptr_table([(ptr(u.param_shard) - base_bytes) if r == self.me else 0
                                          for r in range(self.R)])
-            new_g, off_g = self.heap.alloc(u.padded, engine.grad_dtype)
-            u.bind_grad_bucket(new_g)
-            t["grads"] = ptr_table(self.heap.peer_ptrs(off_g))
+            if id(u) in ring_units:
+                t["grads"] = None             # bound per backward pass to a ring slot
+            else:
+                new_g, off_g = self.heap.alloc(u.padded, engine.grad_dtype)
+                u.bind_grad_bucket(new_g)
+                t["grads"] = ptr_table(self.heap.peer_ptrs(off_g))
             t["flags"] = ptr_table([b + flag_off + 4 * FLAG_SLOT_INTS * k for b in self.heap.peer_base])
             t["epoch"] = 0
             self.tables[u.name] = t
@@ -64,6 +75,11 @@ class FusedDPComm:
 
     def handles(self, u: FlatUnit) -> bool:
         return u.name in self.tables
+
+    def bind_ring_slot(self, u: FlatUnit, slot: int):
+        buf, table = self.ring[slot]
+        u.bind_grad_bucket(buf, fresh=True)
+        self.tables[u.name]["grads"] = table
 
     def reduce_and_step(self, u: FlatUnit, last_micro_step: bool):
         eng = self.engine
@@ -94,5 +110,6 @@ class FusedDPComm:
                 u.micro_steps_accumulated = 0
             else:
                 eng.bucket_free[u.name] = ev
+            eng._release_ring_slot(u)
         for p in u.params:
             p.grad_accumulate = False
