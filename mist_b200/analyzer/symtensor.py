@@ -109,6 +109,7 @@ class _Tracer:
         self.graph = Graph()
         self.scope = "pre"
         self._ids = itertools.count(1)
+        self.param_cache: Dict[int, Any] = {}     # id(parameter) -> (parameter, SymTensor), for this trace only
 
     def new_id(self) -> int:
         return next(self._ids)
@@ -539,17 +540,15 @@ TORCH_RULES: Dict[Callable, Callable] = {
 }
 
 
-_PARAM_CACHE: Dict[int, SymTensor] = {}
-
-
 def as_sym_param(p) -> SymTensor:
-    """SymTensor standing for a real (usually meta-device) parameter; one per parameter."""
+    """SymTensor standing for a real (usually meta-device) parameter; one per parameter and trace."""
     if isinstance(p, SymTensor) or p is None:
         return p
-    key = id(p)
-    st = _PARAM_CACHE.get(key)
-    if st is None or (_TRACER is not None and st.tid not in _TRACER.graph.tensors):
-        st = SymTensor(tuple(p.shape), p.dtype, requires_grad=bool(getattr(p, "requires_grad", False)), is_param=True,
-                       label="param")
-        _PARAM_CACHE[key] = st
+    cache = _TRACER.param_cache if _TRACER is not None else {}
+    hit = cache.get(id(p))
+    if hit is not None and hit[0] is p:
+        return hit[1]
+    st = SymTensor(tuple(p.shape), p.dtype, requires_grad=bool(getattr(p, "requires_grad", False)), is_param=True,
+                   label="param")
+    cache[id(p)] = (p, st)      # keeping the parameter alive keeps its id unique within the trace
     return st

@@ -1,0 +1,563 @@
+// Tensor-parallel GEMMs fused with their sequence-parallel collective, one kernel each.
+//
+//   mode AG -> GEMM   C = allgather(A_shard) * B^T
+//       A lives in a symmetric [T][K] buffer; every rank has written its own rows.  A few
+//       CTAs of the persistent grid ("gather CTAs") pull the peers' row chunks over NVLink
+//       with bulk async copies (peer global -> shared -> local global) and publish a flag
+//       per chunk; the compute CTAs' TMA warp waits for the flag that covers its tile before
+//       loading it, and visits the locally owned rows first.  Each remote byte crosses NVLink
+//       once; afterwards the whole gathered A sits in local memory for any other consumer.
+//
+//   mode GEMM -> RS   C_shard = reduce_scatter(A * B^T)
+//       The epilogue adds every output tile into the fp32 accumulator of the rank that owns
+//       those rows with a TMA reduce-add (through NVLink for remote owners), so the
+//       reduction overlaps the main loop tile by tile.  A flag round before the first add
+//       (accumulators zeroed everywhere) and one after the last (all adds landed) bracket it.
+//
+// Both share the tcgen05 main loop of the plain GEMM (TMA-fed smem stages, accumulators in
+// TMEM).  No TMA load is multicast; peer memory is only read by plain bulk copies and only
+// written by TMA reduce / stores.  Waits on peers are bounded.
+//
+// Reference equivalents: all_gather + F.linear and F.linear + reduce_scatter in
+// mist/modules/fused_dense.py:54-75 and :320-327 (NCCL + cuBLAS, overlapped at best with a
+// weight cast), disabled in the reference's models (mist/model/transformer.py:477-479).
+#include "sm100.cuh"
+#include <string.h>
+
+using namespace sm100;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int kThreads = 192;
+constexpr int kMaxRanks = 8;
+constexpr int kCopyBufs = 8;
+constexpr int kCopyBytes = 16384;
+
+enum Mode : int { MODE_AG = 1, MODE_RS = 2 };
+
+struct CommParams {
+  int M, N, K;
+  int mode;
+  int nranks, me, epoch;
+  int rows_per_rank;
+  int n_gather;                         // gather CTAs at the end of the grid (AG mode)
+  // AG
+  const uint8_t* a_peer[kMaxRanks];     // every rank's gathered-A buffer (row-major [M][K] bf16)
+  uint8_t* a_local;
+  int* chunk_flags;                     // local: [nranks][chunks_per_rank]
+  // plain output (AG mode): bf16 C with bias
+  void* C;
+  int ldc;
+  const __nv_bfloat16* bias;
+  // flags: [0..R) ready, [R..2R) done, [2R] counter  (same layout as the p2p kernels)
+  int* flags[kMaxRanks];
+  int* status;
+  unsigned long long wait_ns;
+};
+
+struct Smem {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagingOffset = STAGES * kStageBytes;
+  static constexpr int kStagingBytes = BM * 128;
+  static constexpr int kBarOffset = kStagingOffset + 2 * kStagingBytes;
+  static constexpr int kNumBars = 2 * STAGES + 4 + kCopyBufs;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+};
+
+__device__ __forceinline__ void report(int* status, int code) {
+  if (status) atomicCAS(status, 0, code);
+}
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(int* addr, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded poll of one flag (single thread).
+__device__ bool wait_flag(const int* flag, int epoch, bool sys, unsigned long long limit_ns, int* status) {
+  const unsigned long long t0 = global_ns();
+  while ((sys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag)) < epoch) {
+    if (global_ns() - t0 > limit_ns) {
+      report(status, MB_ERR_TIMEOUT_PEER);
+      return false;
+    }
+    __nanosleep(100);
+  }
+  return true;
+}
+
+// peer global -> shared (completion on an mbarrier) and shared -> local global (bulk group)
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(gdst),
+               "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+
+template <bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap acc0,
+                 const __grid_constant__ CUtensorMap acc1, const __grid_constant__ CUtensorMap acc2,
+                 const __grid_constant__ CUtensorMap acc3, const __grid_constant__ CUtensorMap acc4,
+                 const __grid_constant__ CUtensorMap acc5, const __grid_constant__ CUtensorMap acc6,
+                 const __grid_constant__ CUtensorMap acc7, const CommParams p) {
+  using L = Smem;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint64_t* copy_bar = tempty_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(copy_bar + kCopyBufs);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int R = p.nranks;
+  int* my_flags = p.flags[p.me];
+  const int n_compute = gridDim.x - ((p.mode == MODE_AG) ? p.n_gather : 0);
+  const bool is_gather = (p.mode == MODE_AG) && (static_cast<int>(blockIdx.x) >= n_compute);
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int m_tiles_per_rank = p.rows_per_rank / BM;
+
+  // Tile order: all column tiles of one row block, row blocks starting with the locally owned
+  // ones (AG: their data is there at once) / ending with them (RS: remote adds go out first).
+  auto tile_coords = [&](int t, int& m0, int& n0) {
+    int mt = t / num_n, nt = t - mt * num_n;
+    int shift = (p.mode == MODE_AG) ? p.me : (p.me + 1) % R;
+    int mt_rot = (mt + shift * m_tiles_per_rank) % num_m;
+    m0 = mt_rot * BM;
+    n0 = nt * BN;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 128);
+    }
+    for (int b = 0; b < kCopyBufs; ++b) mbar_init(&copy_bar[b], 1);
+    fence_barrier_init();
+  }
+  if (warp == 2 && !is_gather) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = is_gather ? 0u : *tmem_slot;
+
+  // ---- phase A: announce that this rank's inputs (A rows / zeroed accumulator) are ready
+  if (blockIdx.x == 0 && threadIdx.x < R && static_cast<int>(threadIdx.x) != p.me) {
+    __threadfence_system();
+    st_release_sys(p.flags[threadIdx.x] + p.me, p.epoch);
+  }
+
+  if (is_gather) {
+    // ------------------------------------------------------------------ gather CTAs
+    if (threadIdx.x == 0) {
+      const int g = blockIdx.x - n_compute;
+      const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+      const size_t chunk_bytes = static_cast<size_t>(BM) * row_bytes;    // one flag per 128-row block
+      const int chunks_per_rank = m_tiles_per_rank;
+      uint8_t* bufs = smem;                                              // reuse the stage area
+      uint32_t issued = 0, stored = 0;
+      bool ok = true;
+      int work = 0;
+      for (int k = 0; k < R - 1 && ok; ++k) {
+        const int r = (p.me + 1 + k) % R;
+        bool peer_ready = false;
+        for (int c = 0; c < chunks_per_rank && ok; ++c, ++work) {
+          if (work % p.n_gather != g) continue;
+          if (!peer_ready) {
+            ok = wait_flag(my_flags + r, p.epoch, true, p.wait_ns, p.status);
+            peer_ready = ok;
+            if (!ok) break;
+          }
+          const size_t off = (static_cast<size_t>(r) * p.rows_per_rank + static_cast<size_t>(c) * BM) * row_bytes;
+          const uint8_t* src = p.a_peer[r] + off;
+          uint8_t* dst = p.a_local + off;
+          const int pieces = static_cast<int>((chunk_bytes + kCopyBytes - 1) / kCopyBytes);
+          int ld = 0, stp = 0;
+          while (stp < pieces && ok) {
+            // keep up to kCopyBufs loads in flight
+            while (ld < pieces && issued - stored < kCopyBufs) {
+              const uint32_t b = issued % kCopyBufs;
+              if (issued >= kCopyBufs) tma_wait_read<0>();   // the store that last used this buffer has read it
+              const uint32_t nb = static_cast<uint32_t>(min(static_cast<size_t>(kCopyBytes),
+                                                           chunk_bytes - static_cast<size_t>(ld) * kCopyBytes));
+              mbar_expect_tx(&copy_bar[b], nb);
+              bulk_load(bufs + b * kCopyBytes, src + static_cast<size_t>(ld) * kCopyBytes, nb, &copy_bar[b]);
+              ++issued;
+              ++ld;
+            }
+            const uint32_t b = stored % kCopyBufs;
+            if (!mbar_wait(&copy_bar[b], (stored / kCopyBufs) & 1)) {
+              report(p.status, MB_ERR_TIMEOUT_FULL);
+              ok = false;
+              break;
+            }
+            const uint32_t nb = static_cast<uint32_t>(min(static_cast<size_t>(kCopyBytes),
+                                                         chunk_bytes - static_cast<size_t>(stp) * kCopyBytes));
+            bulk_store(dst + static_cast<size_t>(stp) * kCopyBytes, bufs + b * kCopyBytes, nb);
+            tma_commit();
+            ++stored;
+            ++stp;
+          }
+          if (ok) {
+            tma_wait_all<0>();          // the chunk is in local memory
+            fence_proxy_async_all();
+            __threadfence();
+            st_release_gpu(p.chunk_flags + r * chunks_per_rank + c, p.epoch);
+          }
+        }
+      }
+      if (!ok) tma_wait_all<0>();
+    }
+  } else if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t armed[STAGES];
+      for (int s = 0; s < STAGES; ++s) armed[s] = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += n_compute) {
+        int m0, n0;
+        tile_coords(t, m0, n0);
+        if (p.mode == MODE_AG) {
+          const int owner = m0 / p.rows_per_rank;
+          if (owner != p.me) {
+            const int c = (m0 - owner * p.rows_per_rank) / BM;
+            ok = wait_flag(p.chunk_flags + owner * m_tiles_per_rank + c, p.epoch, false, p.wait_ns, p.status);
+            if (!ok) break;
+            fence_proxy_async_all();   // the chunk was written through the async proxy of another SM
+          }
+        }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          int s = it % STAGES;
+          uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            report(p.status, MB_ERR_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[s], L::kStageBytes);
+          armed[s]++;
+          tma_load_2d(sa, &tma_a, &full_bar[s], kb * BK, m0);
+          if (!B_MN) {
+            tma_load_2d(sb, &tma_b, &full_bar[s], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), &tma_b, &full_bar[s], n0 + 64 * j, kb * BK);
+          }
+        }
+      }
+      if (!ok)
+        for (int s = 0; s < STAGES; ++s)
+          if (armed[s]) mbar_wait(&full_bar[s], (armed[s] - 1) & 1, 50);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer
+    constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, B_MN ? 1 : 0);
+    uint32_t it = 0, tcount = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += n_compute, ++tcount) {
+      int acc = tcount & 1;
+      uint32_t acc_ph = (tcount >> 1) & 1;
+      if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1)) {
+        report(p.status, MB_ERR_TIMEOUT_TMEM);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t d_tmem = tmem_base + acc * BN;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        int s = it % STAGES;
+        uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&full_bar[s], ph, (p.mode == MODE_AG) ? 4000u : kSpinLimit)) {
+          report(p.status, MB_ERR_TIMEOUT_FULL);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          uint32_t sa = smem_u32(smem + s * L::kStageBytes);
+          uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            uint64_t ad = make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            uint64_t bd = B_MN ? make_smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
+                               : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            mma_f16_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          mma_commit(&empty_bar[s]);
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) mma_commit(&tfull_bar[acc]);
+      __syncwarp();
+    }
+  } else {
+    // --------------------------------------------------------------- epilogue
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const bool leader = (threadIdx.x == 64);
+    uint32_t tcount = 0, epi_units = 0;
+    bool ok = true;
+    const bool rs = (p.mode == MODE_RS);
+    __shared__ int peers_ok_s;
+    if (rs) {
+      // peers' accumulators are zeroed once their ready flag shows this epoch
+      if (leader) {
+        int okf = 1;
+        for (int rr = 0; rr < R && okf; ++rr)
+          if (rr != p.me) okf = wait_flag(my_flags + rr, p.epoch, true, p.wait_ns, p.status) ? 1 : 0;
+        peers_ok_s = okf;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      ok = peers_ok_s != 0;
+    }
+    const CUtensorMap* acc_maps[kMaxRanks] = {&acc0, &acc1, &acc2, &acc3, &acc4, &acc5, &acc6, &acc7};
+    for (int t = blockIdx.x; t < num_tiles && ok; t += n_compute, ++tcount) {
+      int m0, n0;
+      tile_coords(t, m0, n0);
+      int acc = tcount & 1;
+      uint32_t acc_ph = (tcount >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, (p.mode == MODE_AG) ? 4000u : kSpinLimit)) {
+        report(p.status, MB_ERR_TIMEOUT_TMEM);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const int owner = rs ? (m0 / p.rows_per_rank) : 0;
+      const int cols_per_unit = rs ? 32 : 64;     // fp32 accumulator tiles vs bf16 output tiles
+      const int units = BN / cols_per_unit;
+      for (int u = 0; u < units; ++u) {
+        const int ucol0 = n0 + u * cols_per_unit;
+        if (ucol0 >= p.N) break;
+        uint8_t* stg = smem + L::kStagingOffset + (epi_units & 1) * L::kStagingBytes;
+        if (leader) tma_wait_read<1>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int halves = rs ? 1 : 2;
+        for (int hh = 0; hh < halves; ++hh) {
+          uint32_t rr[32];
+          tmem_ld32(taddr + u * cols_per_unit + hh * 32, rr);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rr[i]);
+          if (!rs && p.bias) {
+            const int col0 = ucol0 + hh * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += __bfloat162float(p.bias[min(col0 + i, p.N - 1)]);
+          }
+          if (rs) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              *reinterpret_cast<float4*>(stg + r * 128 + ((g ^ (r & 7)) << 4)) =
+                  make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              *reinterpret_cast<mb::bf16x8*>(stg + r * 128 + (((hh * 4 + g) ^ (r & 7)) << 4)) = mb::pack8(v + 8 * g);
+          }
+        }
+        fence_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (leader) {
+          if (rs) {
+            asm volatile(
+                "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];\n" ::
+                    "l"(reinterpret_cast<uint64_t>(acc_maps[owner])),
+                "r"(smem_u32(stg)), "r"(ucol0), "r"(m0 - owner * p.rows_per_rank)
+                : "memory");
+          } else {
+            tma_store_2d(&tma_c, stg, ucol0, m0);
+          }
+          tma_commit();
+        }
+        ++epi_units;
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty_bar[acc]);
+    }
+    if (leader) tma_wait_all<0>();
+  }
+
+  // ---- phase C: whole grid done -> tell the peers; the last CTA waits for theirs
+  __threadfence_system();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2 && !is_gather) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+  __shared__ int last_s;
+  if (threadIdx.x == 0) {
+    int prev = atomicAdd(my_flags + 2 * R, 1);
+    last_s = (prev + 1 == static_cast<int>(gridDim.x) * p.epoch);
+  }
+  __syncthreads();
+  if (last_s) {
+    if (threadIdx.x < R && static_cast<int>(threadIdx.x) != p.me) {
+      __threadfence_system();
+      st_release_sys(p.flags[threadIdx.x] + R + p.me, p.epoch);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
+      for (int rr = 0; rr < R; ++rr)
+        if (rr != p.me && !wait_flag(my_flags + R + rr, p.epoch, true, p.wait_ns, p.status)) break;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_cols,
+              uint32_t box_rows, bool fp32) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * (fp32 ? 4u : 2u)};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(m, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int g_sms = 0;
+
+}  // namespace
+
+MB_API int* mb_status_device_ptr();
+
+// mode 1 (AG -> GEMM): a_ptrs[r] = rank r's symmetric [M][K] bf16 buffer (own rows valid), C [M][N] bf16.
+// mode 2 (GEMM -> RS): A = local [M][K]; acc_ptrs[r] = rank r's fp32 accumulator [M/R][N] (zeroed by its owner
+// before the launch); C unused.  B: [N][K] (b_mn = 0) or [K][N] (b_mn = 1).  chunk_flags: local int array
+// [R][M/R/128] (AG only).  flag_ptrs[r]: per-rank flag block (2R + 1 ints) reserved for this call site; `epoch`
+// counts launches on it from 1.  M/R must be a multiple of 128, K of 8.
+MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void* B, void* C, void* const* acc_ptrs,
+                        void* const* flag_ptrs, int* chunk_flags, int M, int N, int K, int ldb, int ldc, int b_mn,
+                        const void* bias, int nranks, int me, int epoch, int n_gather, int wait_ms,
+                        cudaStream_t stream) {
+  if (nranks < 1 || nranks > kMaxRanks || M % nranks) return -1;
+  const int rows_per_rank = M / nranks;
+  if (rows_per_rank % BM || (K & 7) || (ldb & 7)) return -1;
+  if (!g_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CommParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.mode = mode;
+  p.nranks = nranks; p.me = me; p.epoch = epoch;
+  p.rows_per_rank = rows_per_rank;
+  p.n_gather = (mode == MODE_AG) ? (n_gather > 0 ? n_gather : 4) : 0;
+  if (nranks == 1) p.n_gather = 0, p.mode = (mode == MODE_AG) ? MODE_AG : MODE_RS;
+  p.chunk_flags = chunk_flags;
+  p.C = C; p.ldc = ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.status = mb_status_device_ptr();
+  p.wait_ns = static_cast<unsigned long long>(wait_ms > 0 ? wait_ms : 2000) * 1000000ull;
+  for (int r = 0; r < nranks; ++r) {
+    p.flags[r] = reinterpret_cast<int*>(flag_ptrs[r]);
+    if (mode == MODE_AG) p.a_peer[r] = reinterpret_cast<const uint8_t*>(a_ptrs[r]);
+  }
+  const void* a_base = A;
+  if (mode == MODE_AG) {
+    p.a_local = reinterpret_cast<uint8_t*>(a_ptrs[me]);
+    a_base = a_ptrs[me];
+  }
+  CUtensorMap ta, tb, tc, acc[kMaxRanks];
+  memset(&tc, 0, sizeof(tc));
+  memset(acc, 0, sizeof(acc));
+  if (!make_map(&ta, a_base, M, K, K, 64, BM, false)) return -2;
+  if (!b_mn) {
+    if (!make_map(&tb, B, N, K, ldb, 64, BN, false)) return -2;
+  } else {
+    if (!make_map(&tb, B, K, N, ldb, 64, BK, false)) return -2;
+  }
+  if (mode == MODE_AG) {
+    if (!make_map(&tc, C, M, N, ldc, 64, BM, false)) return -2;
+  } else {
+    for (int r = 0; r < nranks; ++r)
+      if (!make_map(&acc[r], acc_ptrs[r], rows_per_rank, N, N, 32, BM, true)) return -2;
+  }
+  const int smem = Smem::kTotal + 1024;
+  static bool cfg0 = false, cfg1 = false;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int compute = g_sms - p.n_gather;
+  if (compute > tiles) compute = tiles;
+  const int grid = compute + p.n_gather;
+  if (!b_mn) {
+    if (!cfg0) {
+      if (cudaFuncSetAttribute(gemm_comm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return -3;
+      cfg0 = true;
+    }
+    gemm_comm_kernel<false><<<grid, kThreads, smem, stream>>>(ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4],
+                                                              acc[5], acc[6], acc[7], p);
+  } else {
+    if (!cfg1) {
+      if (cudaFuncSetAttribute(gemm_comm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return -3;
+      cfg1 = true;
+    }
+    gemm_comm_kernel<true><<<grid, kThreads, smem, stream>>>(ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4],
+                                                             acc[5], acc[6], acc[7], p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -109,7 +109,17 @@ class ColumnParallelLinear(FusedDense):
         self.process_group, self.sequence_parallel = process_group, sequence_parallel
         self.global_out_features = out_features
 
+    def _fused(self, x) -> bool:
+        return (self.sequence_parallel and F.Settings.tp_backend == "fused" and isinstance(x, torch.Tensor)
+                and x.is_cuda and group_size(self.process_group) > 1
+                and not isinstance(self.process_group, dist_ops.FakeGroup))
+
     def forward(self, x, residual=None):
+        if self._fused(x) and residual is None:
+            from ..parallel import fused_tp
+            y = fused_tp.ag_linear(x.reshape(-1, x.shape[-1]), self.weight, self.bias,
+                                   fused_tp.context_for(self.process_group))
+            return F.gelu(y) if self.activation == "gelu" else y
         if self.sequence_parallel:
             x = dist_ops.all_gather(x.reshape(-1, x.shape[-1]), self.process_group)
         else:
@@ -135,6 +145,12 @@ class RowParallelLinear(FusedDense):
         ws = group_size(self.process_group)
         if ws == 1:
             return F.linear(x, self.weight, self.bias, residual=residual)
+        if (self.sequence_parallel and F.Settings.tp_backend == "fused" and isinstance(x, torch.Tensor) and x.is_cuda
+                and not isinstance(self.process_group, dist_ops.FakeGroup)):
+            from ..parallel import fused_tp
+            y = fused_tp.linear_rs(x.reshape(-1, x.shape[-1]), self.weight, self.bias,
+                                   fused_tp.context_for(self.process_group))
+            return y if residual is None else y + residual.reshape(y.shape)
         y = F.linear(x, self.weight, self.bias)
         if self.sequence_parallel:
             y = dist_ops.reduce_scatter(y.reshape(-1, y.shape[-1]), self.process_group)

@@ -47,6 +47,7 @@ class Settings:
     attn_backend = "tcgen05"      # "tcgen05" (ours) | "sdpa" (library, A/B baseline)
     attn_block_n = 64
     gemm_max_ctas = 0             # >0 leaves SMs free for a concurrent communication kernel
+    tp_backend = "nccl"           # "nccl" | "fused": sequence-parallel linears on the GEMM+collective kernels
 
 
 _scratch = {}

@@ -1,0 +1,220 @@
+"""Symbolic analysis, cost models and the tuner (CPU only)."""
+import math
+import os
+
+import numpy as np
+import pytest
+import sympy as sp
+import torch
+
+from mist_b200.analyzer.layer_analyzer import trace_and_analyze
+from mist_b200.analyzer.stage_evaluator import (StageEvaluator, analyze_strategy, create_search_space,
+                                                pipeline_latency)
+from mist_b200.analyzer.symtensor import SymTensor, tracing
+from mist_b200.config import load_config
+from mist_b200.node_database.database import OpDatabase
+from mist_b200.node_database.node_spec import NodeSpec
+from mist_b200.symbols import SymbolManager
+from mist_b200.tools import comm_model
+from mist_b200.tuner.candidates import device_mesh_candidates, grad_accum_candidates
+from mist_b200.tuner.inter_stage import _solve_native, _solve_python, inter_stage_tune, solution_to_strategy
+from mist_b200.tuner.pareto import pareto_filter, sample_pareto_frontier
+
+B = sp.Symbol("b", integer=True, positive=True)
+
+
+def _mb(expr, b):
+    return float(sp.sympify(expr).subs(B, b)) / 2 ** 20
+
+
+def test_symbol_manager():
+    m = SymbolManager()
+    b, t = m.symbols("b tp", (2, 4))
+    assert m.map(b * 3 + t) == 10 and m.map(b * 3 + t, {"b": 5}) == 19
+    assert m.verify(sp.Eq(b * 2, t)) and not m.verify(b > t)
+    assert m.solve(sp.Eq(b * t, 8), "b") == [8 / t]
+    f = m.lambdify(b * 2 + t, ["b"])
+    assert list(f(np.array([1, 2]))) == [6, 8]
+
+
+def test_symbolic_ops_shapes_and_saved_tensors():
+    m = SymbolManager()
+    b = m.symbols("b", 2)
+    with tracing() as g:
+        x = SymTensor((b, 128, 64), torch.bfloat16, requires_grad=True)
+        w = torch.nn.Parameter(torch.empty(256, 64, dtype=torch.bfloat16, device="meta"))
+        y = torch.nn.functional.linear(x, w)
+        z = torch.tanh(y).reshape(-1, 256).transpose(0, 1)
+        s = (z * 2.0).sum()
+    assert y.shape == (b, 128, 256) and z.shape == (256, 128 * b)
+    ops = [n.op for n in g.nodes]
+    assert ops[:2] == ["linear", "tanh"] and "mul" in ops
+    lin = g.nodes[0]
+    assert sp.simplify(lin.flops_fwd - 2 * b * 128 * 64 * 256) == 0
+    assert x.tid in lin.saved                      # autograd keeps the input of a linear
+    assert g.nodes[1].saved == [g.nodes[1].outputs[0].tid]   # tanh keeps its output
+
+
+def test_layer_memory_matches_hand_count_gpt27b():
+    cfg, _ = load_config("config", check_world_size=False)
+    a = trace_and_analyze(cfg.model, 2048, tp=1)
+    unit = 16384 * 2560 * 2 / 2 ** 20                        # one [tokens, hidden] bf16 tensor at b = 8
+    # saved per block: x, ln1 out, qkv (3x), attn out, summed residual, ln2 out, fc1 pre-act (4x), gelu out (4x)
+    assert abs(_mb(a.block.fwd.saved, 8) - 16 * unit) < 0.02 * 16 * unit
+    assert abs(_mb(a.block.input_bytes, 8) - 2 * unit) < 1e-6
+    assert abs(_mb(a.block.fwd.output, 8) - 2 * unit) < 1e-6
+    assert a.block.num_params == cfg.model.params_per_block() or abs(a.block.num_params - cfg.model.params_per_block()) < 16
+    # the head keeps the logits
+    assert _mb(a.post.fwd.saved, 8) > 16384 * 50304 * 2 / 2 ** 20
+    # memory is linear in the micro batch
+    assert abs(_mb(a.block.fwd.saved, 4) * 2 - _mb(a.block.fwd.saved, 8)) < 1.0
+
+
+def test_tensor_and_sequence_parallel_trace():
+    cfg, _ = load_config("config", ["experiment=b200-llama-7b-tp2sp-dp4"], check_world_size=False)
+    a1 = trace_and_analyze(cfg.model, 4096, tp=1)
+    a2 = trace_and_analyze(cfg.model, 4096, tp=2, sequence_parallel=True)
+    assert [c.kind for c in a2.block.fwd.comms] == ["all_gather", "reduce_scatter", "all_gather", "reduce_scatter"]
+    assert [c.kind for c in a2.block.bwd.comms] == ["reduce_scatter", "all_gather", "reduce_scatter", "all_gather"]
+    assert a2.block.num_params < 0.51 * a1.block.num_params + 2 * 4096
+    assert _mb(a2.block.fwd.saved, 2) < 0.62 * _mb(a1.block.fwd.saved, 2)
+    a3 = trace_and_analyze(cfg.model, 4096, tp=2, sequence_parallel=False)
+    assert [c.kind for c in a3.block.fwd.comms] == ["all_reduce", "all_reduce"]
+
+
+def test_every_family_traces():
+    for exp, over in (("gpt2-1.3b", []), ("llama-1.3b", [])):
+        cfg, _ = load_config("config", [f"experiment={exp}"] + over, check_world_size=False)
+        a = trace_and_analyze(cfg.model, cfg.training.max_sequence_length)
+        assert a.block.nodes and a.pre.nodes and a.post.nodes
+    from mist_b200.config import ModelConfig
+    base = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                max_position_embeddings=128, vocab_size=1024, params_dtype="bfloat16", add_encoder=True, use_flash_attn=True)
+    for mc in (ModelConfig(name="falcon-t", add_decoder=False, encoder_attn_mask_type="causal", parallel_block=True,
+                           position_embedding_type="rotary", rotary_emb_fraction=1.0, **base),
+               ModelConfig(name="bert-t", add_decoder=False, encoder_attn_mask_type="padding", add_pooler=True,
+                           num_tokentypes=2, **base),
+               ModelConfig(name="t5-t", add_decoder=True, encoder_attn_mask_type="padding",
+                           decoder_attn_mask_type="causal", **base)):
+        a = trace_and_analyze(mc, 128)
+        assert a.block.num_params > 0 and a.graph_nodes > 10
+
+
+def test_comm_and_interference_models():
+    table = [4.5, 0, 100, 1e-5, 200, 1e-5, 300, 2e-5] + [4.5, 0] * 12
+    t = comm_model.gpu_gpu_latency("all_gather", np.array([0.3]), 8, 1, table)[0]
+    assert abs(t - (0.3 / 300 * 7 / 8 + 2e-5)) < 1e-12
+    assert comm_model.gpu_gpu_latency("all_reduce", np.array([0.3]), 8, 1, table)[0] == pytest.approx(2.1 * t)
+    assert comm_model.gpu_gpu_latency("all_gather", np.array([0.3]), 1, 1, table)[0] == 0.0
+    assert comm_model.host_copy_latency(np.array([0.5, 0.0]), [50.0, 1e-4]).tolist() == [0.5 / 50 + 1e-4, 0.0]
+    p = np.ones(28)
+    # with unit factors channels overlap perfectly: total = max
+    assert comm_model.interference_estimate(1.0, 0.4, 0.2, 0.7, p) == pytest.approx(1.0)
+    p[16:18] = [1.5, 1.0]              # compute stretches 1.5x while a collective runs
+    assert comm_model.interference_estimate(1.0, 0.6, 0.0, 0.0, p) == pytest.approx(0.6 + (1.5 - 0.6) / 1.5)
+    assert comm_model.interference_estimate(0.0, 0.6, 0.0, 0.0, p) == pytest.approx(0.6)
+
+
+def test_search_space_rules():
+    cfg, _ = load_config("test-small-base", check_world_size=False)
+    sp_ = create_search_space(1, 2, 32, 2, cfg)
+    assert sp_.shape[1] == 10 and len(sp_) > 100
+    assert not np.any((sp_[:, 6] > 0) & (sp_[:, 7] == 0))            # weight offload implies grad offload
+    assert np.all(sp_[:, 0] * sp_[:, 1] * 2 == 32) and np.all(sp_[:, 1] * sp_[:, 2] == 2)
+    dp1 = sp_[sp_[:, 1] == 1]
+    assert np.all(dp1[:, 3:6] == [0, 0, 1]) if len(dp1) else True     # no ZeRO choice without data parallelism
+
+
+def test_stage_evaluator_monotonic_and_feasibility(monkeypatch):
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    cfg, _ = load_config("config", check_world_size=False)
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=False))
+    vec = np.array([[8, 8, 1, 0, 1, 1, 0, 0, 0, 0], [8, 8, 1, 1, 1, 1, 0, 0, 0, 0], [8, 8, 1, 0, 0, 1, 0, 0, 0, 0]], dtype=float)
+    r0 = ev.evaluate(vec, 32, 0, 1, True, True)
+    r1 = ev.evaluate(vec, 32, 32, 1, True, True)
+    assert np.all(r1["stable"] > r0["stable"])               # recomputation costs time ...
+    assert np.all(r1["peak_bwd"] < r0["peak_bwd"])           # ... and saves memory
+    assert r0["peak_fwd"][1] < r0["peak_fwd"][0] < r0["peak_fwd"][2]    # ZeRO-3 < ZeRO-2 < ZeRO-1
+    assert np.all(r0["feasible"])
+    # a 40 GB device cannot hold it without sharding / checkpointing
+    cfg.hardware.memory_capacity = 40 * 0.88
+    assert not ev.evaluate(vec[2:], 32, 0, 1, True, True)["feasible"][0]
+
+
+def test_pipeline_latency_formula():
+    assert pipeline_latency([2.0], [0.5], 4) == pytest.approx(8.5)
+    assert pipeline_latency([1.0, 2.0], [0.5, 0.1], 4) == pytest.approx(3.0 + 3 * 2.0 + 0.5)
+    from mist_b200.ops import native
+    import ctypes as C
+    lib = native.runtime()
+    lib.rt_simulate_1f1b.restype = C.c_double
+    fwd = (C.c_double * 2)(0.4, 0.8)
+    bwd = (C.c_double * 2)(0.6, 1.2)
+    t = lib.rt_simulate_1f1b(2, 4, fwd, bwd, None, C.c_double(0.0), None)
+    # the event simulation agrees with the closed form (stage time = fwd + bwd)
+    assert t == pytest.approx(pipeline_latency([1.0, 2.0], [0.0, 0.0], 4), rel=0.08)
+
+
+def test_pareto_sampling():
+    rng = np.random.default_rng(0)
+    x, y = rng.random(200), rng.random(200)
+    feas = rng.random(200) > 0.3
+    a = sample_pareto_frontier(x, y, feas, 7, use_native=True)
+    b = sample_pareto_frontier(x, y, feas, 7, use_native=False)
+    assert a.tolist() == b.tolist() and all(feas[i] for i in a)
+    front = set(pareto_filter(np.where(feas, x, np.inf), np.where(feas, y, np.inf)).tolist())
+    assert set(a.tolist()) <= front
+    assert sample_pareto_frontier(x, y, np.zeros(200, dtype=bool), 3).tolist() == [-1, -1, -1]
+
+
+def test_inter_stage_solver_matches_exhaustive():
+    rng = np.random.default_rng(1)
+    for _ in range(10):
+        S, L, g = int(rng.integers(1, 5)), int(rng.integers(4, 9)), int(rng.integers(1, 9))
+        kinds, layers, T, D = [], [], [], []
+        for k in ([3] if S == 1 else [0, 1, 2]):
+            for l in range(1, L + 1):
+                for _ in range(3):
+                    kinds.append(k)
+                    layers.append(l)
+                    T.append(float(rng.uniform(0.5, 1.5) * l))
+                    D.append(float(rng.uniform(0, 2)))
+        a = _solve_native(S, L, g, kinds, layers, T, D)
+        b = _solve_python(S, L, g, kinds, layers, T, D)
+        assert a[0] == pytest.approx(b[0])
+        assert sum(layers[i] for i in a[1]) == L
+
+
+def test_candidates():
+    assert device_mesh_candidates(2, 8) == [(1, 1), (1, 2), (1, 4), (1, 8), (2, 8)]
+    assert grad_accum_candidates(24) == [1, 2, 4, 8]
+
+
+def test_tune_small_case_end_to_end(monkeypatch, tmp_path):
+    """GPT-1.3B on 2 devices with the L4 calibration: the tuner must return a valid strategy that
+    the analyzer prices at the tuner's own cost and that beats the hand-written base strategy."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_L4")
+    cfg, node = load_config("test-small-base", check_world_size=False)
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=False))
+    base = analyze_strategy(cfg, ev)["total"]
+    cost, sol = inter_stage_tune(cfg, ev)
+    assert sol is not None and math.isfinite(cost) and cost < base
+    strat = solution_to_strategy(cfg, sol)
+    assert sum(strat["layer_partitions"]) == 24
+    plain = node.to_dict()
+    plain["strategy"] = strat
+    from mist_b200.utils import yamlconf
+    yamlconf.dump(plain, tmp_path / "best.yaml")
+    cfg2, _ = load_config("best", config_dirs=[tmp_path], check_world_size=False)    # validates the strategy
+    again = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))["total"]
+    assert again == pytest.approx(cost, rel=1e-6)
+
+
+def test_op_database_roundtrip(tmp_path):
+    db = OpDatabase(device="TEST_GPU", root=tmp_path, allow_profile=False)
+    spec = NodeSpec.from_dict({"op": "linear", "m": 8 * B, "n": 16, "k": 32, "act": "", "bias": False}, {"b": 4})
+    assert spec.key() == "linear(act=,bias=False,k=32,m=32,n=16)"
+    est = db.latency(spec, 1e9, 2e9, 1e6, 2e6)
+    db.add(spec, 1.5e-3, 3e-3)
+    db2 = OpDatabase(device="TEST_GPU", root=tmp_path, allow_profile=False)
+    assert db2.latency(spec) == (1.5e-3, 3e-3) and est != (1.5e-3, 3e-3)
