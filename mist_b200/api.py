@@ -48,6 +48,8 @@ class TrainingSession:
         self.seq_len = cfg.training.max_sequence_length
         self.sequence_parallel = bool(cfg.get("sequence_parallel", False)) and self.ps.tp_size > 1
         self.comm_backend = comm_backend or cfg.get("comm_backend", "nccl")
+        from .ops import functional as _F
+        _F.Settings.tp_backend = cfg.get("tp_backend", _F.Settings.tp_backend)
         dtype = cfg.training.params_dtype
         # same seed on every data-parallel replica; tensor-parallel ranks draw different slices
         torch.manual_seed(seed + 1000 * self.ps.tp_rank + 17 * stage)

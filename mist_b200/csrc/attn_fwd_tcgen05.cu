@@ -48,8 +48,8 @@ struct Smem {
   static constexpr int oV = oK + kStages * kKV;
   static constexpr int oP = oV + kStages * kKV;
   static constexpr int oBar = oP + kP;
-  // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done
-  static constexpr int kNumBars = 1 + 2 + 2 + 2 + 2 + 2 + 1 + 1;
+  // q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_done, k_empty[2]
+  static constexpr int kNumBars = 1 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 2;
   static constexpr int kTotal = oBar + kNumBars * 8 + 16;
 };
 
@@ -77,6 +77,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* s_empty = bars + 9;
   uint64_t* p_full = bars + 11;
   uint64_t* pv_done = bars + 12;
+  uint64_t* k_empty = bars + 13;   // K stage free as soon as its S MMA has read it (V waits for PV)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
 
   const int warp = threadIdx.x >> 5;
@@ -108,6 +109,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&k_full[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&s_empty[s], 128);
     }
@@ -140,7 +142,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_4d(smem + L::oQ + c * chunk_q, &tm_q, q_full, 64 * c, head, q0, batch);
       for (int j = 0; j < nblocks && ok; ++j) {
         int st = j % kStages;
-        if (j >= kStages && !mbar_wait(&kv_empty[st], ((j / kStages) - 1) & 1)) {
+        if (j >= kStages && !mbar_wait(&k_empty[st], ((j / kStages) - 1) & 1)) {
           report(p.status, MB_ERR_TIMEOUT_EMPTY);
           ok = false;
           break;
@@ -150,6 +152,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_expect_tx(&k_full[st], p.nchunks * chunk_kv);
         for (int c = 0; c < p.nchunks; ++c)
           tma_load_4d(sk_ + c * chunk_kv, &tm_k, &k_full[st], 64 * c, head_kv, j * BN, batch);
+        if (j >= kStages && !mbar_wait(&kv_empty[st], ((j / kStages) - 1) & 1)) {
+          report(p.status, MB_ERR_TIMEOUT_EMPTY);
+          ok = false;
+          break;
+        }
         mbar_expect_tx(&v_full[st], p.nchunks * chunk_kv);
         for (int c = 0; c < p.nchunks; ++c)
           tma_load_4d(sv_ + c * chunk_kv, &tm_v, &v_full[st], 64 * c, head_kv, j * BN, batch);
@@ -178,6 +185,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             uint64_t bd = make_smem_desc_sw128(sk_ + ch * chunk_kv + in, 16, 1024);
             mma_f16_ss(tmem_s + b * BN, ad, bd, idesc_s, kk != 0 ? 1u : 0u);
           }
+          mma_commit(&k_empty[st]);
           mma_commit(&s_full[b]);
         }
         __syncwarp();

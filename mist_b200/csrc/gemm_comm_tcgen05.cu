@@ -45,6 +45,7 @@ struct CommParams {
   int nranks, me, epoch;
   int rows_per_rank;
   int n_gather;                         // gather CTAs at the end of the grid (AG mode)
+  int acc_bf16;                         // RS: accumulators are bf16 (two ranks: order-independent sum)
   // AG
   const uint8_t* a_peer[kMaxRanks];     // every rank's gathered-A buffer (row-major [M][K] bf16)
   uint8_t* a_local;
@@ -368,7 +369,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       const int owner = rs ? (m0 / p.rows_per_rank) : 0;
-      const int cols_per_unit = rs ? 32 : 64;     // fp32 accumulator tiles vs bf16 output tiles
+      const bool f32_units = rs && !p.acc_bf16;
+      const int cols_per_unit = f32_units ? 32 : 64;     // fp32 accumulator tiles vs bf16 tiles
       const int units = BN / cols_per_unit;
       for (int u = 0; u < units; ++u) {
         const int ucol0 = n0 + u * cols_per_unit;
@@ -376,7 +378,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         uint8_t* stg = smem + L::kStagingOffset + (epi_units & 1) * L::kStagingBytes;
         if (leader) tma_wait_read<1>();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        const int halves = rs ? 1 : 2;
+        const int halves = f32_units ? 1 : 2;
         for (int hh = 0; hh < halves; ++hh) {
           uint32_t rr[32];
           tmem_ld32(taddr + u * cols_per_unit + hh * 32, rr);
@@ -389,7 +391,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] += __bfloat162float(p.bias[min(col0 + i, p.N - 1)]);
           }
-          if (rs) {
+          if (f32_units) {
 #pragma unroll
             for (int g = 0; g < 8; ++g)
               *reinterpret_cast<float4*>(stg + r * 128 + ((g ^ (r & 7)) << 4)) =
@@ -485,12 +487,12 @@ MB_API int* mb_status_device_ptr();
 
 // mode 1 (AG -> GEMM): a_ptrs[r] = rank r's symmetric [M][K] bf16 buffer (own rows valid), C [M][N] bf16.
 // mode 2 (GEMM -> RS): A = local [M][K]; acc_ptrs[r] = rank r's fp32 accumulator [M/R][N] (zeroed by its owner
-// before the launch); C unused.  B: [N][K] (b_mn = 0) or [K][N] (b_mn = 1).  chunk_flags: local int array
+// before the launch; bf16 when acc_bf16 != 0); C unused.  B: [N][K] (b_mn = 0) or [K][N] (b_mn = 1).  chunk_flags: local int array
 // [R][M/R/128] (AG only).  flag_ptrs[r]: per-rank flag block (2R + 1 ints) reserved for this call site; `epoch`
 // counts launches on it from 1.  M/R must be a multiple of 128, K of 8.
 MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void* B, void* C, void* const* acc_ptrs,
                         void* const* flag_ptrs, int* chunk_flags, int M, int N, int K, int ldb, int ldc, int b_mn,
-                        const void* bias, int nranks, int me, int epoch, int n_gather, int wait_ms,
+                        const void* bias, int nranks, int me, int epoch, int n_gather, int wait_ms, int acc_bf16,
                         cudaStream_t stream) {
   if (nranks < 1 || nranks > kMaxRanks || M % nranks) return -1;
   const int rows_per_rank = M / nranks;
@@ -506,6 +508,7 @@ MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void
   p.nranks = nranks; p.me = me; p.epoch = epoch;
   p.rows_per_rank = rows_per_rank;
   p.n_gather = (mode == MODE_AG) ? (n_gather > 0 ? n_gather : 4) : 0;
+  p.acc_bf16 = acc_bf16;
   if (nranks == 1) p.n_gather = 0, p.mode = (mode == MODE_AG) ? MODE_AG : MODE_RS;
   p.chunk_flags = chunk_flags;
   p.C = C; p.ldc = ldc;
@@ -534,7 +537,7 @@ MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void
     if (!make_map(&tc, C, M, N, ldc, 64, BM, false)) return -2;
   } else {
     for (int r = 0; r < nranks; ++r)
-      if (!make_map(&acc[r], acc_ptrs[r], rows_per_rank, N, N, 32, BM, true)) return -2;
+      if (!make_map(&acc[r], acc_ptrs[r], rows_per_rank, N, N, acc_bf16 ? 64 : 32, BM, !acc_bf16)) return -2;
   }
   const int smem = Smem::kTotal + 1024;
   static bool cfg0 = false, cfg1 = false;

@@ -30,7 +30,7 @@ from .symm import SymmetricHeap, ptr_table
 native.register_signature(
     "mb_gemm_comm",
     [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
-     C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p])
+     C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p])
 
 MODE_AG, MODE_RS = 1, 2
 FLAG_INTS = 32
@@ -77,8 +77,8 @@ class FusedTPContext:
     def gathered(self, M, K, tag=""):
         return self._alloc(("A", M, K, tag), M * K, torch.bfloat16)
 
-    def accumulator(self, rows, N):
-        return self._alloc(("acc", rows, N), rows * N, torch.float32)
+    def accumulator(self, rows, N, dtype=torch.float32):
+        return self._alloc(("acc", rows, N, dtype), rows * N, dtype)
 
 
 def _ag_gemm(ctx: FusedTPContext, x_shard: torch.Tensor, w: torch.Tensor, bias, b_mn: bool, tag: str):
@@ -93,7 +93,7 @@ def _ag_gemm(ctx: FusedTPContext, x_shard: torch.Tensor, w: torch.Tensor, bias, 
     s = ctx.site((MODE_AG, M, N, K, b_mn, tag))
     s["epoch"] += 1
     call("mb_gemm_comm", MODE_AG, a_table, None, ptr(w), ptr(out), None, s["flags"], ptr(s["chunk"]), M, N, K,
-         w.stride(0), out.stride(0), int(b_mn), ptr(bias), ctx.R, ctx.me, s["epoch"], ctx.n_gather, 0, native.stream())
+         w.stride(0), out.stride(0), int(b_mn), ptr(bias), ctx.R, ctx.me, s["epoch"], ctx.n_gather, 0, 0, native.stream())
     return out, a2
 
 
@@ -102,12 +102,18 @@ def _gemm_rs(ctx: FusedTPContext, x: torch.Tensor, w: torch.Tensor, b_mn: bool):
     M, K = x.shape
     N = w.shape[1] if b_mn else w.shape[0]
     rows = M // ctx.R
-    acc, acc_table = ctx.accumulator(rows, N)
+    # two ranks: a + b is order independent, so the sum can be formed in bf16 directly (half the
+    # NVLink bytes, no conversion pass); more ranks accumulate in fp32 to stay order independent
+    # up to fp32 rounding
+    bf16_acc = ctx.R <= 2
+    acc, acc_table = ctx.accumulator(rows, N, torch.bfloat16 if bf16_acc else torch.float32)
     acc.zero_()
     s = ctx.site((MODE_RS, M, N, K, b_mn))
     s["epoch"] += 1
     call("mb_gemm_comm", MODE_RS, None, ptr(x), ptr(w), None, acc_table, s["flags"], None, M, N, K, w.stride(0), N,
-         int(b_mn), None, ctx.R, ctx.me, s["epoch"], 0, 0, native.stream())
+         int(b_mn), None, ctx.R, ctx.me, s["epoch"], 0, 0, int(bf16_acc), native.stream())
+    if bf16_acc:
+        return acc.view(rows, N).clone()
     out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
     F.cast_to_bf16(acc, out.view(-1))
     return out

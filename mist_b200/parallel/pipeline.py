@@ -1,11 +1,13 @@
 """Non-interleaved 1F1B pipeline schedule over NCCL point-to-point.
 
 Each stage runs ``warm-up forwards -> (forward, backward) pairs -> cool-down backwards``.
-Activations and their gradients travel with ``batch_isend_irecv``; the calls are ordered
-against the compute stream by NCCL's own events, so nothing waits on the host: receives
-for the next step are posted before the current step's compute is launched and the
-compute stream only blocks when it really needs the data (the reference follows every
-p2p call with a device-wide ``torch.cuda.synchronize()``, schedules.py:506-657).
+Activations and their gradients travel with ``batch_isend_irecv``: the send of one
+direction and the receive of the other are issued as one batch per step ("send forward,
+receive backward" / "send backward, receive forward"), in the same order on both
+neighbours, because NCCL executes a rank's p2p calls towards one peer in issue order.
+The calls are ordered against the compute stream by NCCL's own events, so the host
+never blocks (the reference follows every p2p call with a device-wide
+``torch.cuda.synchronize()``, schedules.py:506-657).
 
 Stage boundary tensor: a stage hands on ``hidden + residual`` as one ``[b, s, h]`` tensor
 (one add), and the next stage starts with ``residual = None``; this is the same math as
@@ -148,65 +150,94 @@ class PipelineSchedule:
         return None if x is None else x.grad
 
     # -------------------------------------------------------------------------- schedule
+    def _exchange(self, send_fwd=None, send_bwd=None, recv_fwd=False, recv_bwd=False):
+        """One batched p2p step.  Sends and receives that belong together are issued in a
+        single ``batch_isend_irecv`` per neighbour pair, in the same order on both sides
+        (NCCL runs a rank's p2p calls towards one peer in issue order, so un-paired calls
+        on the two sides deadlock).  Returns (received forward input, received gradient)."""
+        ps = self.ps
+        ops, keep, slots = [], [], {}
+        if send_fwd is not None and not self.last:
+            for peer, info in ps.send_next:
+                part = (send_fwd[info.slice_of(send_fwd.shape[0])] if info.is_sharded else send_fwd).contiguous()
+                self.p2p._exchange_meta_send(peer, part, "fwd")
+                ops.append(dist.P2POp(dist.isend, part, peer))
+                keep.append(part)
+        if recv_bwd and not self.last:
+            slots["bwd"] = []
+            for peer, info in ps.recv_next:
+                shape, dtype, _ = self.p2p._meta[("fwd", peer)]       # gradient has the shape of what was sent
+                buf = torch.empty(shape, dtype=dtype, device=self.device)
+                slots["bwd"].append((info, buf))
+                ops.append(dist.P2POp(dist.irecv, buf, peer))
+        if send_bwd is not None and not self.first:
+            for peer, info in ps.send_prev:
+                part = (send_bwd[info.slice_of(send_bwd.shape[0])] if info.is_sharded else send_bwd).contiguous()
+                ops.append(dist.P2POp(dist.isend, part, peer))
+                keep.append(part)
+        if recv_fwd and not self.first:
+            slots["fwd"] = []
+            for peer, info in ps.recv_prev:
+                shape, dtype, _ = self.p2p._exchange_meta_recv(peer, "fwd")
+                buf = torch.empty(shape, dtype=dtype, device=self.device)
+                slots["fwd"].append((info, buf))
+                ops.append(dist.P2POp(dist.irecv, buf, peer))
+        if ops:
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+
+        def assemble(parts):
+            if not parts:
+                return None
+            if len(parts) == 1:
+                return parts[0][1]
+            parts.sort(key=lambda x: x[0].shard_idx)
+            return torch.cat([b for _, b in parts], dim=0)
+
+        return assemble(slots.get("fwd", [])), assemble(slots.get("bwd", []))
+
     def train_step(self, batches: List[Dict]) -> torch.Tensor:
         G, W = self.G, self.num_warmup
-        ps = self.ps
-        pending_sends = []
+        remaining = G - W
         inflight: List[Tuple] = []       # (input, output, micro index)
         losses = []
-        f = b = 0
+        f = 0
 
-        def post_recv_fwd():
-            return self.p2p.recv(ps.recv_prev, "fwd") if not self.first else None
-
-        def post_recv_bwd():
-            return self.p2p.recv(ps.recv_next, "bwd") if not self.last else None
-
-        def send_fwd(t):
-            if not self.last:
-                pending_sends.append(self.p2p.send(t.detach(), ps.send_next, "fwd"))
-
-        def send_bwd(g):
-            if not self.first and g is not None:
-                pending_sends.append(self.p2p.send(g, ps.send_prev, "bwd"))
-
-        recv_f = post_recv_fwd() if G > 0 else None
-        # warm-up forwards
-        for _ in range(W):
-            x, out = self._forward(batches[f], f, recv_f)
-            recv_f = post_recv_fwd() if f + 1 < G else None
-            send_fwd(out)
+        def fwd(x_in):
+            nonlocal f
+            x, out = self._forward(batches[f], f, None if x_in is None else ([], x_in))
             inflight.append((x, out, f))
             f += 1
-        # steady state: one forward, one backward
-        recv_b = post_recv_bwd() if (f < G or inflight) else None
-        while f < G:
-            x, out = self._forward(batches[f], f, recv_f)
-            recv_f = post_recv_fwd() if f + 1 < G else None
-            send_fwd(out)
-            inflight.append((x, out, f))
-            f += 1
+            return out
+
+        def bwd(grad):
             x0, out0, k0 = inflight.pop(0)
-            grad = P2PHandler.finish(*recv_b) if recv_b is not None else None
             if self.last:
                 losses.append(out0.detach())
-            gx = self._backward(x0, out0, k0, grad)
-            b += 1
-            recv_b = post_recv_bwd() if (b < G) else None
-            send_bwd(gx)
-        # cool-down backwards
+            return self._backward(x0, out0, k0, grad)
+
+        # warm-up: receive, forward, send
+        for i in range(W):
+            x_in, _ = self._exchange(recv_fwd=True)
+            out = fwd(x_in)
+            self._exchange(send_fwd=out.detach())
+        x_in = None
+        if remaining > 0:
+            x_in, _ = self._exchange(recv_fwd=True)
+        # steady state: forward, (send forward | receive gradient), backward, (send gradient | receive next)
+        for i in range(remaining):
+            out = fwd(x_in)
+            _, grad = self._exchange(send_fwd=None if self.last else out.detach(), recv_bwd=True)
+            gx = bwd(grad)
+            if i + 1 < remaining:
+                x_in, _ = self._exchange(send_bwd=gx, recv_fwd=True)
+            else:
+                self._exchange(send_bwd=gx)
+        # cool-down
         while inflight:
-            x0, out0, k0 = inflight.pop(0)
-            grad = P2PHandler.finish(*recv_b) if recv_b is not None else None
-            if self.last:
-                losses.append(out0.detach())
-            gx = self._backward(x0, out0, k0, grad)
-            b += 1
-            recv_b = post_recv_bwd() if (b < G) else None
-            send_bwd(gx)
-        for reqs, keep in pending_sends:
-            for r in reqs:
-                r.wait()
+            _, grad = self._exchange(recv_bwd=True)
+            gx = bwd(grad)
+            self._exchange(send_bwd=gx)
         if self.last:
             return torch.stack(losses).mean()
         return torch.zeros((), device=self.device)

@@ -93,7 +93,11 @@ class SplitTensor:
         host_n = int(n * ratio) // align * align
         self.numel, self.host_numel, self.dev_numel = n, host_n, n - host_n
         self.device_part = full[: self.dev_numel].clone() if self.dev_numel < n else full
-        self.host_part = _pin(full[self.dev_numel:].detach().to("cpu")) if host_n else None
+        self.host_part = None
+        if host_n:
+            # allocate pinned memory once and copy straight into it (no pageable staging copy)
+            self.host_part = torch.empty(host_n, dtype=full.dtype, device="cpu", pin_memory=torch.cuda.is_available())
+            self.host_part.copy_(full[self.dev_numel:].detach())
         self.dtype, self.device = full.dtype, full.device
 
     def load(self, staging: torch.Tensor, streams: SwapStreams) -> Optional[torch.Tensor]:
