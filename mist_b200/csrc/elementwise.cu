@@ -493,3 +493,60 @@ MB_API int mb_add_bf16(const void* src, void* dst, size_t n, cudaStream_t s) {
   add_bf16_kernel<<<grid_for((n + 7) / 8), kBlock, 0, s>>>(BF(src), BFM(dst), n);
   return LAUNCH_OK();
 }
+
+// ------------------------------------------------------------- allocation-free variant
+// Column sums with the inter-stage partial sums in a fixed device array (see no_alloc.h).
+#include "no_alloc.h"
+#include <stdio.h>
+
+namespace {
+constexpr long kStaticScratchFloats = 1L << 20;   // 4 MiB per GPU
+constexpr int kMaxDevices = 64;
+}  // namespace
+
+// In host code this name is only a handle for the runtime; the device address is obtained
+// once per GPU with cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_colsum_scratch[kStaticScratchFloats];
+
+namespace {
+float* g_colsum_scratch_addr[kMaxDevices] = {nullptr};
+
+float* colsum_static_scratch() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (!g_colsum_scratch_addr[dev]) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_colsum_scratch) != cudaSuccess) return nullptr;
+    g_colsum_scratch_addr[dev] = p;
+  }
+  return g_colsum_scratch_addr[dev];
+}
+}  // namespace
+
+MB_API long mb_colsum_static_capacity(void) { return kStaticScratchFloats; }
+
+MB_API int mb_colsum_static(const void* x, void* out, int rows, int cols, int out_fp32, int accumulate,
+                            cudaStream_t s) {
+  if (cols <= 0 || rows < 0 || cols % 8) return -1;
+  if (!rows) return 0;
+  const int rpp = 256;
+  const int parts = (rows + rpp - 1) / rpp;
+  const long need = static_cast<long>(parts) * cols;
+  if (need > kStaticScratchFloats) {
+    fprintf(stderr,
+            "mb_colsum_static: %d x %d needs %ld scratch floats, the built-in array holds %ld; "
+            "use mb_colsum with a caller-provided buffer\n",
+            rows, cols, need, kStaticScratchFloats);
+    return -22;
+  }
+  float* scratch = colsum_static_scratch();
+  if (!scratch) return -3;
+  dim3 g1((cols / 8 + 127) / 128, parts);
+  colsum_stage1<<<g1, 128, 0, s>>>(BF(x), scratch, rows, cols, rpp);
+  if (out_fp32)
+    colsum_stage2<float><<<(cols + 255) / 256, 256, 0, s>>>(scratch, reinterpret_cast<float*>(out), parts, cols,
+                                                            accumulate);
+  else
+    colsum_stage2<__nv_bfloat16><<<(cols + 255) / 256, 256, 0, s>>>(scratch, BFM(out), parts, cols, accumulate);
+  return LAUNCH_OK();
+}
