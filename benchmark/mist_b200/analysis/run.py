@@ -6,6 +6,8 @@ Prints and records (``summary.json``) the total latency, per-stage stable / delt
 and per-stage peak forward / backward memory (reference: benchmark/mist/analysis/run.py:
 37-243; output keys :236-241).  Runs on CPU; operator latencies come from the database of
 the target GPU (``FAKE_DEVICE_NAME`` or the ``hardware.gpu_type`` of the configuration).
+With ``MIST_B200_PROFILE_OPS=1`` on a machine that has that GPU, operators the database does
+not know yet are measured and added (``MIST_B200_OP_CACHE`` chooses where).
 """
 from __future__ import annotations
 
@@ -22,9 +24,12 @@ from mist_b200.utils.summary import fmt_cost, fmt_costs, fmt_memories, update_su
 
 def analyze(cfg, cache_dir=None):
     assert cfg.strategy is not None, "analyze needs strategy.enabled=true"
-    if cfg.hardware.gpu_type and not os.environ.get("FAKE_DEVICE_NAME"):
+    # MIST_B200_PROFILE_OPS=1 (on a machine with the target GPU): operators missing from the
+    # database are timed on the device and stored, so later CPU-only runs find them.
+    profile_ops = os.environ.get("MIST_B200_PROFILE_OPS") == "1"
+    if cfg.hardware.gpu_type and not os.environ.get("FAKE_DEVICE_NAME") and not profile_ops:
         os.environ["FAKE_DEVICE_NAME"] = str(cfg.hardware.gpu_type)
-    ev = StageEvaluator(cfg, OpDatabase(allow_profile=False), cache_dir=cache_dir)
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=profile_ops), cache_dir=cache_dir)
     return analyze_strategy(cfg, ev)
 
 

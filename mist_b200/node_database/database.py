@@ -43,6 +43,20 @@ class OpDatabase:
         self.allow_profile = allow_profile and torch.cuda.is_available() and not os.environ.get("FAKE_DEVICE_NAME")
         self.model = analytic.device_model(self.device)
         self._mem: Dict[str, Dict[str, Dict]] = {}
+        # Entries are timed one operator at a time, at boost clocks.  A training step keeps the
+        # tensor cores busy for seconds and settles at the power-capped clock, so tensor-core
+        # bound operators run slower there by the ratio of the burst to the sustained GEMM
+        # rate of the device; ``_meta.json`` beside the entries holds that ratio.
+        self.sustained_scale, self.scaled_ops = 1.0, ()
+        meta = self.dir / "_meta.json"
+        if meta.exists():
+            try:
+                with open(meta) as f:
+                    m = json.load(f)
+                self.sustained_scale = float(m.get("sustained_scale", 1.0))
+                self.scaled_ops = tuple(m.get("scaled_ops", ()))
+            except (json.JSONDecodeError, OSError, ValueError):
+                pass
         self.hits = self.misses = self.profiled = 0
 
     # ---------------------------------------------------------------------------- files
@@ -92,7 +106,8 @@ class OpDatabase:
         e = entries.get(key)
         if e is not None:
             self.hits += 1
-            return float(e["fwd"]), float(e["bwd"])
+            k = self.sustained_scale if spec.op in self.scaled_ops else 1.0
+            return float(e["fwd"]) * k, float(e["bwd"]) * k
         self.misses += 1
         if self.allow_profile:
             from . import profiler
@@ -112,7 +127,8 @@ class OpDatabase:
         out = {}
         if self.dir.exists():
             for p in self.dir.glob("*.json"):
-                out.update(self._load(p.stem))
+                if not p.name.startswith("_"):
+                    out.update(self._load(p.stem))
         return out
 
     def refit_model(self):

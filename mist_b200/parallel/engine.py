@@ -122,6 +122,7 @@ class TrainEngine:
         from .swap import ActivationSwapper, SwapStreams
         self.swap_streams = SwapStreams(self.device)
         oo, ao = float(self.strategy.opt_offload), float(self.strategy.act_offload)
+        wo, go = float(self.strategy.weight_offload), float(self.strategy.grad_offload)
         # Gradient buckets.  With sharded gradients (ZeRO-2/3) a block's full-size bucket is only
         # needed from its backward pass until its reduction, so the blocks share a ring of two
         # buckets; otherwise every unit keeps its own (it accumulates over micro steps).
@@ -138,6 +139,9 @@ class TrainEngine:
             else:
                 u.bind_grad_bucket(torch.zeros(u.padded, dtype=self.grad_dtype, device=self.device))
             u.init_optimizer_state(offload_ratio=oo if u in layer_units else 0.0)
+            if u in layer_units:      # like the optimizer state, only the blocks' tensors are offloaded
+                u.enable_weight_offload(wo)
+                u.enable_grad_offload(go)
         host_n = max((u.opt_host_numel for u in self.units), default=0)
         self.opt_staging = [torch.empty(host_n, dtype=torch.float32, device=self.device) for _ in range(3)] if host_n else None
         self.act_swapper = ActivationSwapper(ao, self.swap_streams) if ao > 0 else None
@@ -148,15 +152,25 @@ class TrainEngine:
         self.bucket_free: Dict[str, "torch.cuda.Event"] = {}
         self._micro = 0
         self._pending_post = False
-        # ZeRO-3 ring of gathered-weight slots (two slots: current block + the prefetched one)
-        self.zero3 = zero >= ZeroLevel.FULL and dp > 1
+        # Ring of full-weight slots (two: current block + the prefetched one) for blocks whose
+        # full weights are not persistent on the device: ZeRO-3 shards and host-offloaded weights.
+        self.zero3 = any(u.ring_resident for u in layer_units)
+        self._step_scratch = None
         if self.zero3:
             biggest = max(u.padded for us in self.layer_units.values() for u in us)
             self._slots = [torch.empty(biggest, dtype=mk["dtype"], device=self.device) for _ in range(2)]
             self._slot_of: Dict[str, int] = {}
             self._next_slot = 0
             self._gather_done: Dict[str, "torch.cuda.Event"] = {}
+            if any(u.weight_split is not None for u in layer_units):
+                self._step_scratch = torch.empty(biggest, dtype=mk["dtype"], device=self.device)
+                for u in layer_units:      # drop the start-up copies of the full weights
+                    if u.weight_split is not None:
+                        u._use_views(self._slots[0][: u.padded])
+                        u._boot_full = None
         self.fused = None
+        if comm_backend == "fused" and dp > 1 and (wo > 0 or go > 0):
+            comm_backend = self.comm_backend = "nccl"     # offloaded weights / gradients use the library path
         if comm_backend == "fused" and dp > 1:
             from .fused_comm import FusedDPComm
             self.fused = FusedDPComm(self)
@@ -195,13 +209,14 @@ class TrainEngine:
     # ----------------------------------------------------------------- ZeRO-3 residency
     def _gather(self, unit: FlatUnit):
         """Starts the all-gather of ``unit``'s weights into the next ring slot (comm stream)."""
-        if not self.zero3 or unit.flat_param is not None:
+        if not self.zero3 or unit.flat_param is not None or not unit.ring_resident:
             return
         slot = self._next_slot
         self._next_slot ^= 1
         self._slot_of[unit.name] = slot
         with self._on_comm():
-            unit.unshard(self._slots[slot], self.ps.dp_ag_group)
+            unit.unshard(self._slots[slot], self.ps.dp_ag_group if unit.is_zero3 else None,
+                         streams=self.swap_streams)
             if self.cuda:
                 ev = torch.cuda.Event()
                 ev.record()
@@ -295,11 +310,12 @@ class TrainEngine:
             self.fused.reduce_and_step(unit, last)
             return
         with self._on_comm():
-            grad = unit.reduce_grads(self.ps.dp_rs_group, last)
+            grad = unit.reduce_grads(self.ps.dp_rs_group, last, streams=self.swap_streams)
             if grad is not None:
-                swap = (self.swap_streams, self.opt_staging) if unit.opt_host_numel else None
+                swap = ((self.swap_streams, self.opt_staging)
+                        if (unit.opt_host_numel or unit.weight_split is not None) else None)
                 unit.optimizer_step(grad, self.hp, self.ps.dp_ag_group, grad_divisor=float(self.ps.dp_size * self.G),
-                                    swap=swap)
+                                    swap=swap, step_scratch=self._step_scratch)
                 if self.cuda:
                     ev = torch.cuda.Event()
                     ev.record()
@@ -345,7 +361,11 @@ class TrainEngine:
         return sum(u.numel for u in self.units)
 
     def state_bytes(self) -> Dict[str, int]:
-        w = sum((u.flat_param.numel() if u.flat_param is not None else u.param_shard.numel()) * 2 for u in self.units)
+        def persistent(u):
+            if u.weight_split is not None:
+                return u.weight_split.dev_numel
+            return u.param_shard.numel() if u.param_shard is not None else u.flat_param.numel()
+        w = sum(persistent(u) * 2 for u in self.units)
         g = sum(u.flat_grad.numel() * u.flat_grad.element_size() for u in self.units)
         o = sum(u.master.numel() * 12 for u in self.units)
         return {"weights": w, "grads": g, "optimizer": o}

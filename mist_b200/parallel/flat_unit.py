@@ -17,6 +17,13 @@ ZeRO-3      1/dp shard; gathered    as ZeRO-2           1/dp shard
             into a ring slot
 ==========  ======================  ==================  =========================
 
+Host offloading (fractions of the strategy vector): the trailing ``weight_offload`` of the
+persistent weights (the full buffer, or the ZeRO-3 shard) and the trailing ``grad_offload``
+of the fp32 accumulator of reduced gradients live in pinned host memory.  Offloaded weights
+are assembled in a ring slot one block ahead of their use, exactly like ZeRO-3 gathered
+weights, and written back after the optimizer step (reference: mist/re_swap_manager/
+flat_param.py:1124-1250 swap-in/out of weights and gradients).
+
 Parity: reference mist/re_swap_manager/flat_param.py:91-108 (levels), :315-420 (handle),
 :986-1121 (ring-buffer allocation), :1283-1370 (unshard), :1459-1529 (gradient reduction).
 Unlike the reference, reduced gradients are averaged over data-parallel ranks and
@@ -90,6 +97,9 @@ class FlatUnit:
         # ---- optimizer state (created by init_optimizer_state)
         self.master = self.exp_avg = self.exp_avg_sq = None
         self.step_count = 0
+        # ---- host offloading (enable_weight_offload / enable_grad_offload)
+        self.weight_split = None       # SplitTensor of the persistent weights
+        self.grad_split = None         # SplitTensor of the fp32 accumulator of the reduced shard
 
     # ------------------------------------------------------------------------- layout
     def shard_range(self, rank: Optional[int] = None) -> slice:
@@ -103,6 +113,48 @@ class FlatUnit:
     @property
     def state_numel(self) -> int:
         return self.shard_numel if self.sharded_state else self.padded
+
+    @property
+    def is_zero3(self) -> bool:
+        return self.zero >= ZeroLevel.FULL and self.dp_size > 1
+
+    @property
+    def ring_resident(self) -> bool:
+        """True when the full weights only exist while the block is in use (ring slot)."""
+        return self.param_shard is not None or self.weight_split is not None
+
+    @property
+    def persistent_numel(self) -> int:
+        return self.shard_numel if self.is_zero3 else self.padded
+
+    def persistent_region(self, full: torch.Tensor) -> torch.Tensor:
+        """The part of a full-size buffer that this rank stores persistently."""
+        return full[self.shard_range()] if self.is_zero3 else full[: self.padded]
+
+    def enable_weight_offload(self, ratio: float):
+        """Moves the trailing ``ratio`` of the persistent weights to pinned host memory.  Call
+        after ``init_optimizer_state`` (the master weights are cut from the device copy)."""
+        from .swap import SplitTensor
+        if ratio <= 0:
+            return
+        src = self.param_shard if self.param_shard is not None else self.flat_param
+        split = SplitTensor(src, ratio)
+        if not split.host_numel:
+            return
+        self.weight_split = split
+        self.param_shard = None
+        self.flat_param = None
+
+    def enable_grad_offload(self, ratio: float):
+        """Keeps the trailing ``ratio`` of the reduced-gradient accumulator on the host between
+        micro steps.  Only sharded gradients (ZeRO-2/3) accumulate outside the bucket."""
+        from .swap import SplitTensor
+        if ratio <= 0 or not (self.zero >= ZeroLevel.OPT_GRAD and self.dp_size > 1):
+            return
+        acc = torch.zeros(self.shard_numel, dtype=torch.float32, device=self.device)
+        split = SplitTensor(acc, ratio)
+        if split.host_numel:
+            self.grad_split = split
 
     def _use_views(self, flat: torch.Tensor):
         for p, o in zip(self.params, self.offsets):
@@ -154,12 +206,19 @@ class FlatUnit:
         return self.opt_split[0].host_numel if getattr(self, "opt_split", None) else 0
 
     # --------------------------------------------------------------------------- ZeRO-3
-    def unshard(self, slot: torch.Tensor, group, async_op=False):
-        """All-gathers the weight shards into ``slot`` and points the parameters at it."""
-        assert self.param_shard is not None
+    def unshard(self, slot: torch.Tensor, group, async_op=False, streams=None):
+        """Builds the full weights in ``slot`` and points the parameters at it: offloaded
+        weights are assembled from their device and host parts, ZeRO-3 shards all-gathered
+        (in place when the shard was assembled inside the slot)."""
+        assert self.ring_resident
         full = slot[: self.padded]
         handle = None
-        if group is not None:
+        if self.weight_split is not None:
+            mine = self.persistent_region(full)
+            self.weight_split.load_into(mine, streams)
+            if self.is_zero3 and group is not None:
+                handle = dist.all_gather_into_tensor(full, mine, group=group, async_op=async_op)
+        elif group is not None:
             handle = dist.all_gather_into_tensor(full, self.param_shard, group=group, async_op=async_op)
         else:
             full[self.shard_range()].copy_(self.param_shard)
@@ -169,11 +228,30 @@ class FlatUnit:
         return handle
 
     def reshard(self):
-        if self.param_shard is not None:
+        if self.ring_resident:
             self.flat_param = None
 
     # ---------------------------------------------------------------- gradient reduction
-    def reduce_grads(self, group, last_micro_step: bool):
+    def _accumulate_offloaded(self, out: torch.Tensor, last_micro_step: bool, streams):
+        """Adds one micro step's reduced shard to the accumulator whose tail lives on the host.
+        The first micro step writes (nothing to load), the others load-add-store; on the last
+        one the full sum is returned in a temporary for the optimizer."""
+        sp = self.grad_split
+        first = self.micro_steps_accumulated == 1
+        full = torch.empty(self.shard_numel, dtype=torch.float32, device=out.device)
+        if first:
+            F.accumulate_grad(out, full, 1.0, False)
+        else:
+            sp.load_into(full, streams)
+            F.accumulate_grad(out, full, 1.0, True)
+        if last_micro_step:
+            return full
+        sp.store_from(full, streams)
+        if streams.cuda:
+            full.record_stream(streams.d2h)
+        return None
+
+    def reduce_grads(self, group, last_micro_step: bool, streams=None):
         """Reference (NCCL) path.  Returns the tensor the optimizer should consume, or None
         when nothing is due yet."""
         self.micro_steps_accumulated += 1
@@ -184,11 +262,13 @@ class FlatUnit:
             dist.reduce_scatter_tensor(out, self.flat_grad, group=group)
             if self.grad_shard_acc is None and last_micro_step and self.micro_steps_accumulated == 1:
                 return out
+            for p in self.params:
+                p.grad_accumulate = False      # the bucket restarts for the next micro step
+            if self.grad_split is not None:
+                return self._accumulate_offloaded(out, last_micro_step, streams)
             if self.grad_shard_acc is None:
                 self.grad_shard_acc = torch.zeros(self.shard_numel, dtype=torch.float32, device=out.device)
             F.accumulate_grad(out, self.grad_shard_acc, 1.0, True)
-            for p in self.params:
-                p.grad_accumulate = False      # the bucket restarts for the next micro step
             return self.grad_shard_acc if last_micro_step else None
         if not last_micro_step:
             return None
@@ -199,12 +279,20 @@ class FlatUnit:
         dist.all_reduce(self.flat_grad, group=group)
         return self.flat_grad
 
-    def optimizer_step(self, grad: torch.Tensor, hp: Dict, group, grad_divisor: float, swap=None):
+    def optimizer_step(self, grad: torch.Tensor, hp: Dict, group, grad_divisor: float, swap=None,
+                       step_scratch: Optional[torch.Tensor] = None):
         """Fused Adam on this rank's state, writing the bf16 weights, then (ZeRO-1/2) the
         all-gather that refreshes the other ranks' slices.  ``swap`` = (streams, staging
         buffers) when part of the state lives on the host."""
         self.step_count += 1
-        if self.param_shard is not None:
+        if self.weight_split is not None:
+            # offloaded weights: the step writes into a scratch copy that is then split again
+            streams = swap[0]
+            if streams.cuda:
+                torch.cuda.current_stream().wait_stream(streams.d2h)   # scratch free again
+            scratch = step_scratch[: self.padded]
+            model_out = scratch[self.shard_range()] if self.sharded_state else scratch
+        elif self.param_shard is not None:
             model_out = self.param_shard
         elif self.sharded_state:
             model_out = self.flat_param[self.shard_range()]
@@ -234,7 +322,11 @@ class FlatUnit:
                 streams.d2h.wait_stream(cur)
             for sp_, st in zip(split, staged):
                 sp_.store(st, streams)
-        if self.sharded_state and self.param_shard is None and group is not None:
+        if self.weight_split is not None:
+            if self.sharded_state and not self.is_zero3 and group is not None:
+                dist.all_gather_into_tensor(scratch, model_out, group=group)
+            self.weight_split.store_from(self.persistent_region(scratch), swap[0])
+        elif self.sharded_state and self.param_shard is None and group is not None:
             dist.all_gather_into_tensor(self.flat_param, model_out, group=group)
         self.micro_steps_accumulated = 0
         if self.grad_shard_acc is not None:
@@ -252,6 +344,9 @@ class FlatUnit:
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])
         self.step_count = int(sd["step"])
+        if self.weight_split is not None:
+            raise NotImplementedError("loading a checkpoint into host-offloaded weights: load first, "
+                                      "then enable the offload")
         dst = self.param_shard if self.param_shard is not None else (
             self.flat_param[self.shard_range()] if self.sharded_state else self.flat_param)
         dst.copy_(self.master.to(dst.dtype))

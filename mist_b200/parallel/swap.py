@@ -120,6 +120,40 @@ class SplitTensor:
         else:
             self.host_part.copy_(staged[: self.host_numel])
 
+    def load_into(self, dst: torch.Tensor, streams: SwapStreams):
+        """Assembles the whole tensor in ``dst`` (device): the device part with a copy on the
+        current stream, the host part over the host->device stream, which the current stream
+        then waits for.  The host->device stream first waits for the current stream (``dst``
+        may still be read by earlier work) and for pending stores of this tensor."""
+        dst[: self.dev_numel].copy_(self.device_part)
+        if not self.host_numel:
+            return
+        tail = dst[self.dev_numel: self.numel]
+        if streams.cuda:
+            cur = torch.cuda.current_stream()
+            streams.h2d.wait_stream(cur)
+            streams.h2d.wait_stream(streams.d2h)
+            with torch.cuda.stream(streams.h2d):
+                tail.copy_(self.host_part, non_blocking=True)
+            cur.wait_stream(streams.h2d)
+        else:
+            tail.copy_(self.host_part)
+
+    def store_from(self, src: torch.Tensor, streams: SwapStreams):
+        """Writes a whole device tensor back: leading part to the device part, the rest to the
+        host over the device->host stream (ordered after the current stream).  The caller must
+        not overwrite ``src`` before the device->host stream has passed this point."""
+        self.device_part.copy_(src[: self.dev_numel])
+        if not self.host_numel:
+            return
+        tail = src[self.dev_numel: self.numel]
+        if streams.cuda:
+            streams.d2h.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(streams.d2h):
+                self.host_part.copy_(tail, non_blocking=True)
+        else:
+            self.host_part.copy_(tail)
+
     def full(self) -> torch.Tensor:
         """Materialises the whole tensor on the device (checkpointing, tests)."""
         if not self.host_numel:

@@ -47,14 +47,14 @@ def test_single_rank_matches_adamw(exp, G, ckpt):
     assert diff < 1e-4
 
 
-def _dp_worker(rank, world, port, zero_flags, G, ret):
+def _dp_worker(rank, world, port, zero_flags, G, ret, offload=(0, 0, 0, 0)):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         cfg, model = _tiny_model()
         plan = build_plan([(1, world)], [(2, world, 1)], (1, world))
         ps = ParallelState(plan, rank)
-        strat = StageStrategy(2, world, 1, *zero_flags, 0, 0, 0, 0)
+        strat = StageStrategy(2, world, 1, *zero_flags, *offload)
         eng = TrainEngine(model, ps, strat, grad_accum_steps=G, hp=dict(lr=1e-3))
         prov = get_inputs_provider(cfg.model.name)
         losses = []
@@ -63,8 +63,12 @@ def _dp_worker(rank, world, port, zero_flags, G, ret):
             losses.append(eng.train_step(batches).item())
         if eng.zero3:
             for u in eng.units:
-                if u.param_shard is not None and u.flat_param is None:
-                    u.unshard(torch.empty(u.padded), ps.dp_ag_group)
+                if u.ring_resident and u.flat_param is None:
+                    u.unshard(torch.empty(u.padded), ps.dp_ag_group if u.is_zero3 else None,
+                              streams=eng.swap_streams)
+            if any(offload[:2]):
+                ret["offloaded"] = (sum(u.weight_split.host_numel for u in eng.units if u.weight_split is not None),
+                                    sum(u.grad_split.host_numel for u in eng.units if u.grad_split is not None))
         flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
         if rank == 0:
             ret["flat"] = flat.clone()
@@ -94,6 +98,53 @@ def test_data_parallel_gloo_matches_single_process(zero_flags, G):
         opt.step()
     flat_ref = torch.cat([p.detach().reshape(-1) for p in ref.parameters()])
     assert (ret["flat"] - flat_ref).abs().max().item() < 2e-4
+
+
+@pytest.mark.parametrize("zero_flags", [(False, False, True), (False, True, True), (True, True, True)])
+def test_weight_grad_optimizer_offload_gloo_matches_single_process(zero_flags):
+    """Half of the weights, of the accumulated gradient shard and of the optimizer state on the
+    host must not change the training result."""
+    world, G = 2, 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 31500 + (os.getpid() + hash(zero_flags)) % 2000
+    mp.spawn(_dp_worker, args=(world, port, zero_flags, G, ret, (0.5, 0.5, 0.5, 0)), nprocs=world, join=True)
+    assert ret["offloaded"][0] > 0
+    if zero_flags[1]:
+        assert ret["offloaded"][1] > 0
+    cfg, ref = _tiny_model()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(3):
+        opt.zero_grad()
+        for k in range(G):
+            for r in range(world):
+                (ref(**prov(2, 32, 256, "cpu", seed=1000 * it + 10 * k + r)) / (G * world)).backward()
+        opt.step()
+    flat_ref = torch.cat([p.detach().reshape(-1) for p in ref.parameters()])
+    assert (ret["flat"] - flat_ref).abs().max().item() < 2e-4
+
+
+def test_single_rank_weight_offload_matches_adamw():
+    cfg, model = _tiny_model()
+    ref = copy.deepcopy(model)
+    eng = TrainEngine(model, strategy=StageStrategy(2, 1, 1, False, False, False, 0.5, 0, 0, 0), hp=dict(lr=1e-3))
+    assert eng.zero3 and all(u.weight_split is not None for u in eng._all_layer_units())
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(3):
+        b = prov(2, 32, 256, "cpu", seed=it)
+        loss = eng.train_step([b])
+        opt.zero_grad()
+        l = ref(**b)
+        l.backward()
+        opt.step()
+        assert abs(loss.item() - l.item()) < 1e-4
+    for u in eng._all_layer_units():
+        if u.flat_param is None:
+            u.unshard(torch.empty(u.padded), None, streams=eng.swap_streams)
+    diff = max((a - b).abs().max().item() for a, b in zip(model.parameters(), ref.parameters()))
+    assert diff < 1e-4
 
 
 def _pp_worker(rank, world, port, ret):
