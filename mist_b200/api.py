@@ -63,6 +63,7 @@ class TrainingSession:
         pre_post = StageStrategy.from_vector(st.pre_post_strategy_array) if st.pre_post_strategy == "preset" else None
         self.engine = TrainEngine(self.model, self.ps, self.strategy, self.G, st.gradient_checkpointing[stage],
                                   hp=hp, comm_backend=self.comm_backend, overlap=bool(cfg.get("overlap", True)),
+                                  zero3_gather=str(cfg.get("zero3_gather", "nccl")),
                                   pre_post_strategy=pre_post)
         self.pipeline = None
         if multi_stage:

@@ -14,7 +14,15 @@
 //       reduction overlaps the main loop tile by tile.  A flag round before the first add
 //       (accumulators zeroed everywhere) and one after the last (all adds landed) bracket it.
 //
-// Both share the tcgen05 main loop of the plain GEMM (TMA-fed smem stages, accumulators in
+//   mode weight-AG -> GEMM   C = A * W^T + bias, W inside a flat parameter buffer sharded over ranks
+//       ZeRO-3 keeps 1/R of a block's flat bf16 parameters per rank.  Every rank holds its
+//       shard at its place in a symmetric full-size buffer; the gather CTAs pull all remote
+//       shards in pieces ("chunks", one flag each), starting with the pieces that hold the
+//       weight matrix of this GEMM, and the TMA warp of a compute CTA waits for the chunks
+//       under its B tile.  When the kernel ends the whole block's parameters are local for
+//       the block's other operators.
+//
+// All share the tcgen05 main loop of the plain GEMM (TMA-fed smem stages, accumulators in
 // TMEM).  No TMA load is multicast; peer memory is only read by plain bulk copies and only
 // written by TMA reduce / stores.  Waits on peers are bounded.
 //
@@ -34,10 +42,10 @@ constexpr int BK = 64;
 constexpr int STAGES = 4;
 constexpr int kThreads = 192;
 constexpr int kMaxRanks = 8;
-constexpr int kCopyBufs = 8;
+constexpr int kCopyBufs = 11;   // 11 x 16 KB of the 192 KB stage area in flight per gather CTA
 constexpr int kCopyBytes = 16384;
 
-enum Mode : int { MODE_AG = 1, MODE_RS = 2 };
+enum Mode : int { MODE_AG = 1, MODE_RS = 2, MODE_AGW = 3 };
 
 struct CommParams {
   int M, N, K;
@@ -46,10 +54,14 @@ struct CommParams {
   int rows_per_rank;
   int n_gather;                         // gather CTAs at the end of the grid (AG mode)
   int acc_bf16;                         // RS: accumulators are bf16 (two ranks: order-independent sum)
-  // AG
-  const uint8_t* a_peer[kMaxRanks];     // every rank's gathered-A buffer (row-major [M][K] bf16)
+  // AG: every rank's gathered-A buffer (row-major [M][K] bf16); weight-AG: every rank's flat buffer
+  const uint8_t* a_peer[kMaxRanks];
   uint8_t* a_local;
   int* chunk_flags;                     // local: [nranks][chunks_per_rank]
+  // weight-AG: layout of the flat parameter buffer (bytes)
+  unsigned long long shard_bytes, chunk_bytes, b_off, bias_off;
+  int chunks_per_rank;
+  int n_shift;                          // first column tile whose weights are local (tile order starts there)
   // plain output (AG mode): bf16 C with bias
   void* C;
   int ldc;
@@ -119,6 +131,23 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uin
                : "memory");
 }
 
+// Weight-AG: waits (single thread) for every remote chunk that overlaps bytes [lo, hi) of the flat buffer.
+__device__ bool wait_range(const CommParams& p, unsigned long long lo, unsigned long long hi) {
+  unsigned long long x = lo;
+  while (x < hi) {
+    const int r = static_cast<int>(x / p.shard_bytes);
+    const unsigned long long base = static_cast<unsigned long long>(r) * p.shard_bytes;
+    const int c = static_cast<int>((x - base) / p.chunk_bytes);
+    if (r != p.me &&
+        !wait_flag(p.chunk_flags + r * p.chunks_per_rank + c, p.epoch, false, p.wait_ns, p.status))
+      return false;
+    unsigned long long next = base + static_cast<unsigned long long>(c + 1) * p.chunk_bytes;
+    if (next > base + p.shard_bytes) next = base + p.shard_bytes;
+    x = next;
+  }
+  return true;
+}
+
 template <bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -142,8 +171,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   const int R = p.nranks;
   int* my_flags = p.flags[p.me];
-  const int n_compute = gridDim.x - ((p.mode == MODE_AG) ? p.n_gather : 0);
-  const bool is_gather = (p.mode == MODE_AG) && (static_cast<int>(blockIdx.x) >= n_compute);
+  const bool gathers = (p.mode == MODE_AG) || (p.mode == MODE_AGW);
+  const int n_compute = gridDim.x - (gathers ? p.n_gather : 0);
+  const bool is_gather = gathers && (static_cast<int>(blockIdx.x) >= n_compute);
 
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
@@ -154,6 +184,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   // Tile order: all column tiles of one row block, row blocks starting with the locally owned
   // ones (AG: their data is there at once) / ending with them (RS: remote adds go out first).
   auto tile_coords = [&](int t, int& m0, int& n0) {
+    if (p.mode == MODE_AGW) {
+      // all row tiles of one column tile, column tiles in the order their weights arrive
+      int nt = t / num_m, mt = t - nt * num_m;
+      m0 = mt * BM;
+      n0 = ((nt + p.n_shift) % num_n) * BN;
+      return;
+    }
     int mt = t / num_n, nt = t - mt * num_n;
     int shift = (p.mode == MODE_AG) ? p.me : (p.me + 1) % R;
     int mt_rot = (mt + shift * m_tiles_per_rank) % num_m;
@@ -192,59 +229,84 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // ------------------------------------------------------------------ gather CTAs
     if (threadIdx.x == 0) {
       const int g = blockIdx.x - n_compute;
-      const size_t row_bytes = static_cast<size_t>(p.K) * 2;
-      const size_t chunk_bytes = static_cast<size_t>(BM) * row_bytes;    // one flag per 128-row block
-      const int chunks_per_rank = m_tiles_per_rank;
       uint8_t* bufs = smem;                                              // reuse the stage area
       uint32_t issued = 0, stored = 0;
       bool ok = true;
-      int work = 0;
-      for (int k = 0; k < R - 1 && ok; ++k) {
-        const int r = (p.me + 1 + k) % R;
-        bool peer_ready = false;
-        for (int c = 0; c < chunks_per_rank && ok; ++c, ++work) {
-          if (work % p.n_gather != g) continue;
-          if (!peer_ready) {
-            ok = wait_flag(my_flags + r, p.epoch, true, p.wait_ns, p.status);
-            peer_ready = ok;
-            if (!ok) break;
-          }
-          const size_t off = (static_cast<size_t>(r) * p.rows_per_rank + static_cast<size_t>(c) * BM) * row_bytes;
-          const uint8_t* src = p.a_peer[r] + off;
-          uint8_t* dst = p.a_local + off;
-          const int pieces = static_cast<int>((chunk_bytes + kCopyBytes - 1) / kCopyBytes);
-          int ld = 0, stp = 0;
-          while (stp < pieces && ok) {
-            // keep up to kCopyBufs loads in flight
-            while (ld < pieces && issued - stored < kCopyBufs) {
-              const uint32_t b = issued % kCopyBufs;
-              if (issued >= kCopyBufs) tma_wait_read<0>();   // the store that last used this buffer has read it
-              const uint32_t nb = static_cast<uint32_t>(min(static_cast<size_t>(kCopyBytes),
-                                                           chunk_bytes - static_cast<size_t>(ld) * kCopyBytes));
-              mbar_expect_tx(&copy_bar[b], nb);
-              bulk_load(bufs + b * kCopyBytes, src + static_cast<size_t>(ld) * kCopyBytes, nb, &copy_bar[b]);
-              ++issued;
-              ++ld;
-            }
-            const uint32_t b = stored % kCopyBufs;
-            if (!mbar_wait(&copy_bar[b], (stored / kCopyBufs) & 1)) {
-              report(p.status, MB_ERR_TIMEOUT_FULL);
-              ok = false;
-              break;
-            }
+      unsigned ready_mask = 0;
+
+      // Copies `bytes` from a peer to local memory through the shared-memory ring, keeping up to
+      // kCopyBufs loads in flight, then publishes `flag`.
+      auto copy_chunk = [&](int r, const uint8_t* src, uint8_t* dst, size_t bytes, int* flag) {
+        if (!(ready_mask >> r & 1u)) {
+          ok = wait_flag(my_flags + r, p.epoch, true, p.wait_ns, p.status);
+          if (!ok) return;
+          ready_mask |= 1u << r;
+        }
+        const int pieces = static_cast<int>((bytes + kCopyBytes - 1) / kCopyBytes);
+        int ld = 0, stp = 0;
+        while (stp < pieces && ok) {
+          while (ld < pieces && issued - stored < kCopyBufs) {
+            const uint32_t b = issued % kCopyBufs;
+            if (issued >= kCopyBufs) tma_wait_read<0>();   // the store that last used this buffer has read it
             const uint32_t nb = static_cast<uint32_t>(min(static_cast<size_t>(kCopyBytes),
-                                                         chunk_bytes - static_cast<size_t>(stp) * kCopyBytes));
-            bulk_store(dst + static_cast<size_t>(stp) * kCopyBytes, bufs + b * kCopyBytes, nb);
-            tma_commit();
-            ++stored;
-            ++stp;
+                                                         bytes - static_cast<size_t>(ld) * kCopyBytes));
+            mbar_expect_tx(&copy_bar[b], nb);
+            bulk_load(bufs + b * kCopyBytes, src + static_cast<size_t>(ld) * kCopyBytes, nb, &copy_bar[b]);
+            ++issued;
+            ++ld;
           }
-          if (ok) {
-            tma_wait_all<0>();          // the chunk is in local memory
-            fence_proxy_async_all();
-            __threadfence();
-            st_release_gpu(p.chunk_flags + r * chunks_per_rank + c, p.epoch);
+          const uint32_t b = stored % kCopyBufs;
+          if (!mbar_wait(&copy_bar[b], (stored / kCopyBufs) & 1)) {
+            report(p.status, MB_ERR_TIMEOUT_FULL);
+            ok = false;
+            break;
           }
+          const uint32_t nb = static_cast<uint32_t>(min(static_cast<size_t>(kCopyBytes),
+                                                       bytes - static_cast<size_t>(stp) * kCopyBytes));
+          bulk_store(dst + static_cast<size_t>(stp) * kCopyBytes, bufs + b * kCopyBytes, nb);
+          tma_commit();
+          ++stored;
+          ++stp;
+        }
+        if (ok) {
+          tma_wait_all<0>();          // the chunk is in local memory
+          fence_proxy_async_all();
+          __threadfence();
+          st_release_gpu(flag, p.epoch);
+        }
+      };
+
+      if (p.mode == MODE_AG) {
+        const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+        const size_t chunk_bytes = static_cast<size_t>(BM) * row_bytes;    // one flag per 128-row block
+        const int chunks_per_rank = m_tiles_per_rank;
+        int work = 0;
+        for (int k = 0; k < R - 1 && ok; ++k) {
+          const int r = (p.me + 1 + k) % R;
+          for (int c = 0; c < chunks_per_rank && ok; ++c, ++work) {
+            if (work % p.n_gather != g) continue;
+            const size_t off = (static_cast<size_t>(r) * p.rows_per_rank + static_cast<size_t>(c) * BM) * row_bytes;
+            copy_chunk(r, p.a_peer[r] + off, p.a_local + off, chunk_bytes, p.chunk_flags + r * chunks_per_rank + c);
+          }
+        }
+      } else {
+        // flat parameter buffer: chunks in address order starting at the one that holds the first
+        // weights this GEMM needs, wrapping around; the local shard is skipped
+        const int cpr = p.chunks_per_rank;
+        const int total = R * cpr;
+        const unsigned long long first = p.b_off + static_cast<unsigned long long>(p.n_shift) * BN * p.K * 2;
+        const int r0 = static_cast<int>(first / p.shard_bytes);
+        const int g0 = r0 * cpr + static_cast<int>((first - r0 * p.shard_bytes) / p.chunk_bytes);
+        int work = 0;
+        for (int i = 0; i < total && ok; ++i) {
+          const int gi = (g0 + i) % total;
+          const int r = gi / cpr, c = gi - r * cpr;
+          if (r == p.me) continue;
+          if ((work++) % p.n_gather != g) continue;
+          const unsigned long long in_shard = static_cast<unsigned long long>(c) * p.chunk_bytes;
+          const size_t bytes = static_cast<size_t>(min(p.chunk_bytes, p.shard_bytes - in_shard));
+          const size_t off = static_cast<size_t>(r * p.shard_bytes + in_shard);
+          copy_chunk(r, p.a_peer[r] + off, p.a_local + off, bytes, p.chunk_flags + gi);
         }
       }
       if (!ok) tma_wait_all<0>();
@@ -267,6 +329,12 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             if (!ok) break;
             fence_proxy_async_all();   // the chunk was written through the async proxy of another SM
           }
+        } else if (p.mode == MODE_AGW) {
+          const unsigned long long lo = p.b_off + static_cast<unsigned long long>(n0) * p.K * 2;
+          const unsigned long long hi = p.b_off + static_cast<unsigned long long>(min(n0 + BN, p.N)) * p.K * 2;
+          ok = wait_range(p, lo, hi);
+          if (!ok) break;
+          fence_proxy_async_all();
         }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           int s = it % STAGES;
@@ -312,7 +380,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         int s = it % STAGES;
         uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait(&full_bar[s], ph, (p.mode == MODE_AG) ? 4000u : kSpinLimit)) {
+        if (!mbar_wait(&full_bar[s], ph, (p.mode != MODE_RS) ? 4000u : kSpinLimit)) {
           report(p.status, MB_ERR_TIMEOUT_FULL);
           ok = false;
           break;
@@ -355,13 +423,19 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       asm volatile("bar.sync 1, 128;" ::: "memory");
       ok = peers_ok_s != 0;
     }
+    if (p.mode == MODE_AGW && p.bias) {
+      // the bias vector is part of the flat buffer and may still be on its way
+      if (leader) peers_ok_s = wait_range(p, p.bias_off, p.bias_off + static_cast<unsigned long long>(p.N) * 2) ? 1 : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      ok = peers_ok_s != 0;
+    }
     const CUtensorMap* acc_maps[kMaxRanks] = {&acc0, &acc1, &acc2, &acc3, &acc4, &acc5, &acc6, &acc7};
     for (int t = blockIdx.x; t < num_tiles && ok; t += n_compute, ++tcount) {
       int m0, n0;
       tile_coords(t, m0, n0);
       int acc = tcount & 1;
       uint32_t acc_ph = (tcount >> 1) & 1;
-      if (!mbar_wait(&tfull_bar[acc], acc_ph, (p.mode == MODE_AG) ? 4000u : kSpinLimit)) {
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, (p.mode != MODE_RS) ? 4000u : kSpinLimit)) {
         report(p.status, MB_ERR_TIMEOUT_TMEM);
         ok = false;
         break;
@@ -480,6 +554,25 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, ui
 }
 
 int g_sms = 0;
+bool g_cfg[2] = {false, false};
+
+int launch(bool b_mn, int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb,
+           const CUtensorMap& tc, const CUtensorMap* acc, const CommParams& p) {
+  const int smem = Smem::kTotal + 1024;
+  if (!g_cfg[b_mn]) {
+    cudaError_t e = b_mn ? cudaFuncSetAttribute(gemm_comm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
+                         : cudaFuncSetAttribute(gemm_comm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return -3;
+    g_cfg[b_mn] = true;
+  }
+  if (b_mn)
+    gemm_comm_kernel<true><<<grid, kThreads, smem, stream>>>(ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4],
+                                                             acc[5], acc[6], acc[7], p);
+  else
+    gemm_comm_kernel<false><<<grid, kThreads, smem, stream>>>(ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4],
+                                                              acc[5], acc[6], acc[7], p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 }  // namespace
 
@@ -507,7 +600,7 @@ MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void
   p.M = M; p.N = N; p.K = K; p.mode = mode;
   p.nranks = nranks; p.me = me; p.epoch = epoch;
   p.rows_per_rank = rows_per_rank;
-  p.n_gather = (mode == MODE_AG) ? (n_gather > 0 ? n_gather : 4) : 0;
+  p.n_gather = (mode == MODE_AG) ? (n_gather > 0 ? n_gather : 8) : 0;
   p.acc_bf16 = acc_bf16;
   if (nranks == 1) p.n_gather = 0, p.mode = (mode == MODE_AG) ? MODE_AG : MODE_RS;
   p.chunk_flags = chunk_flags;
@@ -539,28 +632,74 @@ MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void
     for (int r = 0; r < nranks; ++r)
       if (!make_map(&acc[r], acc_ptrs[r], rows_per_rank, N, N, acc_bf16 ? 64 : 32, BM, !acc_bf16)) return -2;
   }
-  const int smem = Smem::kTotal + 1024;
-  static bool cfg0 = false, cfg1 = false;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int compute = g_sms - p.n_gather;
   if (compute > tiles) compute = tiles;
-  const int grid = compute + p.n_gather;
-  if (!b_mn) {
-    if (!cfg0) {
-      if (cudaFuncSetAttribute(gemm_comm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return -3;
-      cfg0 = true;
-    }
-    gemm_comm_kernel<false><<<grid, kThreads, smem, stream>>>(ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4],
-                                                              acc[5], acc[6], acc[7], p);
-  } else {
-    if (!cfg1) {
-      if (cudaFuncSetAttribute(gemm_comm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-        return -3;
-      cfg1 = true;
-    }
-    gemm_comm_kernel<true><<<grid, kThreads, smem, stream>>>(ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4],
-                                                             acc[5], acc[6], acc[7], p);
+  return launch(b_mn != 0, compute + p.n_gather, stream, ta, tb, tc, acc, p);
+}
+
+// Weight all-gather fused into the GEMM that consumes the first weights of a ZeRO-3 block.
+//   w_ptrs[r]: rank r's symmetric flat bf16 parameter buffer of R * shard_elems elements; rank r's own
+//              shard [r * shard_elems, (r + 1) * shard_elems) must be valid there before the launch.
+//   C[M][N] = A[M][K] * W^T (+ bias), W = [N][K] row-major at element b_off of the flat buffer, bias (N
+//   elements) at bias_off or none when bias_off < 0.  On return of the kernel the local flat buffer holds
+//   every rank's shard.  chunk_flags: local int array [R][ceil(shard_bytes / chunk_bytes)], zero before the
+//   first launch.  shard_elems % 8 == 0, chunk_bytes % 16 == 0, b_off % 8 == 0, K % 8 == 0.
+MB_API int mb_gemm_param_gather(void* const* w_ptrs, const void* A, void* C, void* const* flag_ptrs,
+                                int* chunk_flags, int M, int N, int K, int ldc, long long b_off, long long bias_off,
+                                long long shard_elems, long long chunk_bytes, int nranks, int me, int epoch,
+                                int n_gather, int wait_ms, cudaStream_t stream) {
+  if (nranks < 1 || nranks > kMaxRanks || (K & 7) || (b_off & 7) || (shard_elems & 7) || chunk_bytes <= 0 ||
+      (chunk_bytes & 15) || b_off < 0 || (bias_off >= 0 && (bias_off & 7)))
+    return -1;
+  if (b_off + static_cast<long long>(N) * K > shard_elems * nranks) return -1;
+  if (!g_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  CommParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.mode = MODE_AGW;
+  p.nranks = nranks; p.me = me; p.epoch = epoch;
+  p.rows_per_rank = M;
+  p.n_gather = nranks > 1 ? (n_gather > 0 ? n_gather : 24) : 0;
+  p.chunk_flags = chunk_flags;
+  p.C = C; p.ldc = ldc;
+  p.status = mb_status_device_ptr();
+  p.wait_ns = static_cast<unsigned long long>(wait_ms > 0 ? wait_ms : 2000) * 1000000ull;
+  p.shard_bytes = static_cast<unsigned long long>(shard_elems) * 2;
+  p.chunk_bytes = static_cast<unsigned long long>(chunk_bytes);
+  p.chunks_per_rank = static_cast<int>((p.shard_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
+  p.b_off = static_cast<unsigned long long>(b_off) * 2;
+  for (int r = 0; r < nranks; ++r) {
+    p.flags[r] = reinterpret_cast<int*>(flag_ptrs[r]);
+    p.a_peer[r] = reinterpret_cast<const uint8_t*>(w_ptrs[r]);
+  }
+  p.a_local = reinterpret_cast<uint8_t*>(w_ptrs[me]);
+  if (bias_off >= 0) {
+    p.bias_off = static_cast<unsigned long long>(bias_off) * 2;
+    p.bias = reinterpret_cast<const __nv_bfloat16*>(p.a_local + p.bias_off);
+  }
+  // start with the first column tile whose weights are entirely in the local shard, if there is one
+  const int num_n = (N + BN - 1) / BN;
+  const unsigned long long tile_bytes = static_cast<unsigned long long>(BN) * K * 2;
+  const unsigned long long my_lo = static_cast<unsigned long long>(me) * p.shard_bytes, my_hi = my_lo + p.shard_bytes;
+  for (int nt = 0; nt < num_n; ++nt) {
+    const unsigned long long lo = p.b_off + nt * tile_bytes;
+    const unsigned long long hi = p.b_off + static_cast<unsigned long long>(min(N, (nt + 1) * BN)) * K * 2;
+    if (lo >= my_lo && hi <= my_hi) {
+      p.n_shift = nt;
+      break;
+    }
+  }
+  CUtensorMap ta, tb, tc, acc[kMaxRanks];
+  memset(acc, 0, sizeof(acc));
+  if (!make_map(&ta, A, M, K, K, 64, BM, false)) return -2;
+  if (!make_map(&tb, p.a_local + p.b_off, N, K, K, 64, BN, false)) return -2;
+  if (!make_map(&tc, C, M, N, ldc, 64, BM, false)) return -2;
+  const int tiles = ((M + BM - 1) / BM) * num_n;
+  int compute = g_sms - p.n_gather;
+  if (compute > tiles) compute = tiles;
+  return launch(false, compute + p.n_gather, stream, ta, tb, tc, acc, p);
 }

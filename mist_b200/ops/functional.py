@@ -47,6 +47,7 @@ class Settings:
     attn_backend = "tcgen05"      # "tcgen05" (ours) | "sdpa" (library, A/B baseline)
     attn_block_n = 64
     gemm_max_ctas = 0             # >0 leaves SMs free for a concurrent communication kernel
+    gemm_pair = True              # large GEMMs on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2)
     tp_backend = "nccl"           # "nccl" | "fused": sequence-parallel linears on the GEMM+collective kernels
 
 
@@ -84,6 +85,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         flags |= EPI_OUT_FP32
     if bias is not None:
         flags |= EPI_BIAS
+    if Settings.gemm_pair and tile_n == 0:
+        # returns 1 (nothing launched) when the shape or epilogue needs the single-CTA kernel
+        rc = native.kernels().mb_gemm_pair_bf16(ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0),
+                                                out.stride(0), int(a_mn), int(b_mn), flags, ptr(bias), ptr(aux),
+                                                float(alpha), Settings.gemm_max_ctas, stream())
+        if rc == 0:
+            native.launch_count += 1
+            return out
+        if rc != 1:
+            raise RuntimeError(f"mb_gemm_pair_bf16 failed with code {rc}")
     call("mb_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
          int(a_mn), int(b_mn), flags, ptr(bias), ptr(aux), float(alpha), tile_n,
          Settings.gemm_max_ctas, stream())
@@ -135,7 +146,15 @@ class _LinearFn(torch.autograd.Function):
                 aux = residual.reshape(-1, weight.shape[0])
                 assert aux.is_contiguous()
                 flags |= EPI_RESIDUAL
-            y = gemm(x2, weight, bias=bias, aux=aux, flags=flags)
+            fused_gather = getattr(weight, "param_gather", None)
+            if fused_gather is not None and flags != 0:
+                raise RuntimeError("the weight-gathering GEMM has no activation / residual epilogue")
+            if fused_gather is not None:
+                # ZeRO-3: this GEMM also brings in the block's remote weight shards
+                weight.param_gather = None
+                y = fused_gather(x2)
+            else:
+                y = gemm(x2, weight, bias=bias, aux=aux, flags=flags)
         ctx.save_for_backward(x2, weight, pre)
         return y.reshape(*xs[:-1], weight.shape[0])
 
@@ -202,6 +221,7 @@ def colsum(x2: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: boo
             return s.to(x2.dtype)
         out.copy_(out.float() + s if accumulate else s)
         return out
+    x2 = x2.contiguous()      # gradients of reductions arrive as stride-0 expansions
     if out is None:
         out = torch.empty(cols, dtype=x2.dtype, device=x2.device)
     parts = (rows + 255) // 256

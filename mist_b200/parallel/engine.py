@@ -63,12 +63,35 @@ def _mark(fn, hidden, residual):
     return out
 
 
+def _round_up_to(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+def _first_matrix(unit: FlatUnit):
+    """(weight, element offset, bias offset or None) of the first 2-D parameter in a unit's flat
+    layout -- the weight of the block's first GEMM -- when it is a plain ``[N, K]`` matrix."""
+    for k, p in enumerate(unit.params):
+        if p.dim() == 2:
+            if p.shape[1] % 8:
+                return None
+            bias_off = None
+            if k + 1 < len(unit.params) and unit.params[k + 1].dim() == 1 and \
+                    unit.params[k + 1].numel() == p.shape[0] and unit.param_names[k + 1].endswith("bias") and \
+                    unit.param_names[k + 1].rsplit(".", 1)[0] == unit.param_names[k].rsplit(".", 1)[0]:
+                bias_off = unit.offsets[k + 1]
+            return p, unit.offsets[k], bias_off
+        if p.dim() > 2:
+            return None
+    return None
+
+
 class TrainEngine:
     def __init__(self, model: nn.Module, pstate: Optional[ParallelState] = None,
                  strategy: Optional[StageStrategy] = None, grad_accum_steps: int = 1,
                  ckpt_layers: int = 0, hp: Optional[Dict] = None, comm_backend: str = "nccl",
                  grad_dtype: Optional[torch.dtype] = None, overlap: bool = True,
-                 pre_post_strategy: Optional[StageStrategy] = None, use_grad_ring: bool = True):
+                 pre_post_strategy: Optional[StageStrategy] = None, use_grad_ring: bool = True,
+                 zero3_gather: str = "nccl"):
         self.model = model
         self.ps = pstate or ParallelState.single()
         self.strategy = strategy or StageStrategy(1, 1, 1, False, False, False, 0, 0, 0, 0)
@@ -168,6 +191,20 @@ class TrainEngine:
                     if u.weight_split is not None:
                         u._use_views(self._slots[0][: u.padded])
                         u._boot_full = None
+        # "fused": in the forward pass a block's remote weight shards are pulled in by the block's
+        # first GEMM itself (one kernel) instead of a prefetched all-gather; the backward pass keeps
+        # the prefetch.  Needs plain ZeRO-3 shards (no host-offloaded weights) on CUDA.
+        self.param_gather = None
+        if (zero3_gather == "fused" and self.zero3 and self.cuda and dp > 1
+                and F.Settings.gemm_backend == "tcgen05" and not (F.Settings.tp_backend == "fused" and self.ps.tp_size > 1)
+                and all(u.param_shard is not None for u in layer_units)):
+            from .fused_zero3 import ParamGatherContext
+            biggest = max(u.padded for u in layer_units)
+            self.param_gather = ParamGatherContext(self.ps.dp_group, _round_up_to(biggest, 128 * dp), self.device)
+            self._slots = [self.param_gather.slot_tensor(0), self.param_gather.slot_tensor(1)]
+            self._dp_root = dist.get_global_rank(self.ps.dp_group, 0)
+            for u in layer_units:
+                u.first_weight = _first_matrix(u)
         self.fused = None
         if comm_backend == "fused" and dp > 1 and (wo > 0 or go > 0):
             comm_backend = self.comm_backend = "nccl"     # offloaded weights / gradients use the library path
@@ -222,6 +259,31 @@ class TrainEngine:
                 ev.record()
                 self._gather_done[unit.name] = ev
 
+    def _gather_in_first_gemm(self, unit: FlatUnit) -> bool:
+        """Forward pass of a block whose weights are not resident: stages this rank's shard in a
+        symmetric slot, fetches the few parameters used before the first GEMM (the input norm)
+        with a small broadcast, and arms the first linear layer to run the weight-gathering GEMM.
+        Returns False when the block has to take the all-gather path."""
+        pg, fw = self.param_gather, getattr(unit, "first_weight", None)
+        if pg is None or fw is None or unit.flat_param is not None or unit.padded != pg.padded:
+            return False
+        weight, b_off, bias_off = fw
+        if b_off > unit.shard_numel:
+            return False
+        slot = self._next_slot
+        self._next_slot ^= 1
+        self._slot_of[unit.name] = slot
+        full = self._slots[slot][: unit.padded]
+        pg.stage_shard(slot, unit.param_shard)
+        if b_off:
+            dist.broadcast(full[:b_off], src=self._dp_root, group=self.ps.dp_ag_group)
+        unit.flat_param = full
+        unit._use_views(full)
+        unit._boot_full = None
+        N, K = weight.shape
+        weight.param_gather = lambda x2: pg.gather_linear(slot, x2, b_off, N, K, bias_off)
+        return True
+
     def _ensure_resident(self, unit: FlatUnit):
         if not self.zero3:
             return
@@ -239,9 +301,12 @@ class TrainEngine:
         units = self.layer_units[id(stack)]
         u = units[i]
         self._wait_params(u)
-        self._ensure_resident(u)
-        if i + 1 < len(units):
-            self._gather(units[i + 1])          # one-block look-ahead
+        if self._gather_in_first_gemm(u):
+            pass                                  # the next block gathers inside its own first GEMM
+        else:
+            self._ensure_resident(u)
+            if i + 1 < len(units) and self.param_gather is None:
+                self._gather(units[i + 1])          # one-block look-ahead
         return _mark(lambda: self._layer_backward_done(stack, i), hidden, residual)
 
     def after_layer(self, stack, i, hidden, residual):

@@ -1,0 +1,131 @@
+"""Checkpoint save / resume (with a change of ZeRO level in between) and host-side failure
+detection, on CPU with gloo ranks.  No GPU is involved: a "failed" rank is one that stops
+beating or exits between steps."""
+import os
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mist_b200.config import load_config
+from mist_b200.models.provider import get_inputs_provider
+
+TINY = ["model.num_hidden_layers=3", "model.hidden_size=64", "model.intermediate_size=128",
+        "model.num_attention_heads=4", "training.max_sequence_length=32", "model.vocab_size=256",
+        "strategy.layer_partitions=[3]", "training.params_dtype=float32", "hardware.num_gpus_per_node=2",
+        "training.global_batch_size=8", "strategy.device_assignment=[[1,2]]", "strategy.gradient_checkpointing=[0]",
+        "strategy.gradient_accumulation_steps=2"]
+
+
+def _cfg(zero):
+    vec = f"[2,2,1,{zero[0]},{zero[1]},{zero[2]},0,0,0,0]"
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + [
+        f"strategy.stage_strategies=[{vec}]", f"strategy.pre_post_strategy_array={vec}"], check_world_size=False)
+    return cfg
+
+
+def _ckpt_worker(rank, world, port, path, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        from mist_b200.utils import checkpoint
+        prov = get_inputs_provider("gpt2")
+
+        def batch(it):
+            b = prov(4, 32, 256, "cpu", seed=1000 * it + rank)
+            return b["input_ids"], b["labels"]
+
+        # run A: ZeRO-2 for two steps, save, one more step
+        a = TrainingSession(_cfg((0, 1, 1)), seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        for it in range(2):
+            a.step_on_device(*batch(it))
+        a.finish()
+        checkpoint.save(a, path, step=2)
+        loss_a = float(a.step_on_device(*batch(2)))
+        a.finish()
+        # run B: ZeRO-3 from another seed, resume, same third step
+        b = TrainingSession(_cfg((1, 1, 1)), seed=123, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        step = checkpoint.load(b, path)
+        loss_b = float(b.step_on_device(*batch(2)))
+        b.finish()
+
+        def full_weights(sess):
+            out = []
+            for u in sess.engine.units:
+                if u.ring_resident and u.flat_param is None:
+                    u.unshard(torch.empty(u.padded), sess.ps.dp_ag_group if u.is_zero3 else None,
+                              streams=sess.engine.swap_streams)
+                out.append(u.flat_param[: u.numel].detach().clone())
+            return torch.cat(out)
+
+        wa, wb = full_weights(a), full_weights(b)
+        if rank == 0:
+            ret["step"] = step
+            ret["losses"] = (loss_a, loss_b)
+            ret["diff"] = (wa - wb).abs().max().item()
+            ret["files"] = sorted(os.listdir(path))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_checkpoint_resume_under_another_zero_level(tmp_path):
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 33500 + os.getpid() % 2000
+    mp.spawn(_ckpt_worker, args=(world, port, str(tmp_path / "ckpt"), ret), nprocs=world, join=True)
+    assert ret["step"] == 2
+    assert "meta.json" in ret["files"] and "strategy.yaml" in ret["files"]
+    assert any(f.startswith("model_stage0") for f in ret["files"])
+    assert abs(ret["losses"][0] - ret["losses"][1]) < 1e-5
+    assert ret["diff"] < 1e-5
+
+
+def _hb_worker(rank, world, port, ret):
+    from mist_b200.utils.watchdog import Heartbeat
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=__import__("datetime").timedelta(seconds=30))
+    hb = Heartbeat(store, rank, world)
+    store.set(f"ready/{rank}", "1")
+    for r in range(world):
+        store.wait([f"ready/{r}"])
+    if rank == 1:
+        # this rank "fails" between steps: it stops beating and leaves
+        store.set("left/1", "1")
+        store.wait(["done/0"])
+        return
+    store.wait(["left/1"])
+    for _ in range(3):
+        hb.beat()
+        time.sleep(0.3)
+    stale = hb.stale_ranks(max_age_s=0.5)
+    raised = False
+    try:
+        hb.check(max_age_s=0.5)
+    except RuntimeError:
+        raised = True
+    ret["stale"] = stale
+    ret["raised"] = raised
+    ret["pids"] = hb.pids()
+    store.set("done/0", "1")
+
+
+def test_heartbeat_reports_a_rank_that_stopped():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 35500 + os.getpid() % 2000
+    mp.spawn(_hb_worker, args=(world, port, ret), nprocs=world, join=True)
+    assert ret["stale"] == [1]
+    assert ret["raised"]
+    assert set(ret["pids"].keys()) == {0, 1}
+
+
+def test_bounded_wait_status_names():
+    """The host side of the device status word: codes map to messages (the device side is
+    covered by the GPU tests, where every wait has a time limit)."""
+    from mist_b200.ops import native
+    assert native._STATUS_NAMES[4].startswith("peer flag")
+    assert set(native._STATUS_NAMES) == {1, 2, 3, 4, 5}

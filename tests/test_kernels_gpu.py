@@ -56,6 +56,43 @@ def test_gemm_epilogues():
     assert _rel_err(out, a.float() @ b.float().t() + res.float()) < 1e-2
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+@pytest.mark.parametrize("K", [320, 1088])
+def test_gemm_cta_pair_layouts_and_epilogues(a_mn, b_mn, K):
+    """256 x 256 tiles on CTA pairs: ragged bottom edge (the second CTA of the last pair has no
+    live rows), ragged right edge, fewer and more k-blocks than pipeline stages."""
+    from mist_b200.ops import native
+    from mist_b200.ops.native import ptr, stream
+    torch.manual_seed(3)
+    M, N = 2176, 2624
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    a_in = a.t().contiguous() if a_mn else a
+    b_in = b.t().contiguous() if b_mn else b
+    ref = a.float() @ b.float().t()
+    lib = native.kernels()
+
+    def run(out, flags, bias_t=None, aux=None):
+        rc = lib.mb_gemm_pair_bf16(ptr(a_in), ptr(b_in), ptr(out), M, N, K, a_in.stride(0), b_in.stride(0),
+                                   out.stride(0), int(a_mn), int(b_mn), flags, ptr(bias_t), ptr(aux), 1.0, 0, stream())
+        assert rc == 0, rc           # 1 would mean "use the single-CTA kernel": the pair kernel must take these
+        torch.cuda.synchronize()
+        native.check_status()
+
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    run(out, 0)
+    assert _rel_err(out, ref) < 1e-2
+    pre = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    run(out, F.EPI_BIAS | F.EPI_GELU | F.EPI_SAVE_PRE, bias, pre)
+    assert _rel_err(pre, ref + bias.float()) < 1e-2
+    assert _rel_err(out, torch.nn.functional.gelu(ref + bias.float(), approximate="tanh")) < 1e-2
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    ref2 = acc + ref
+    run(acc, F.EPI_OUT_FP32 | F.EPI_ACCUM)
+    assert _rel_err(acc, ref2) < 1e-3
+
+
 def test_linear_autograd_matches_reference():
     torch.manual_seed(2)
     x = torch.randn(4, 128, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
@@ -135,6 +172,8 @@ def test_gelu_swiglu_bias_dropout_add():
     assert _rel_err(y, x.float() + b.float() + r.float()) < 1e-2
     y.sum().backward()
     assert torch.allclose(x.grad.float(), torch.ones_like(x.grad).float())
+    # the incoming gradient is a stride-0 expansion here; the bias gradient must still sum 64 rows
+    assert torch.allclose(b.grad.float(), torch.full_like(b.grad, 64.0).float())
     # dropout: mask regenerated identically in backward, keep-rate close to 1-p
     y = F.bias_dropout_add(x, None, None, 0.25, seed=1234)
     kept = (y != 0).float().mean().item()
