@@ -276,9 +276,45 @@ class ParallelMHA(nn.Module):
             probs = torch.nn.functional.dropout(probs, self.dropout)
         return torch.matmul(probs, v.transpose(1, 2)).transpose(1, 2)
 
+    def _forward_cached(self, x, residual=None):
+        """Inference with a key/value cache (``self.inference_params`` set by
+        :mod:`mist_b200.inference`): the new keys and values are appended to this layer's cache;
+        a multi-token call (the prompt) attends causally inside itself, a single-token call
+        runs the single-query kernel over the cache (reference: the ``inference_params``
+        branches of mist/modules/mha.py:531-575,1110-1170)."""
+        ip = self.inference_params
+        assert not self.cross_attn and not self.sequence_parallel and x.dim() == 3
+        qkv = self.Wqkv(x)
+        b, s = qkv.shape[:2]
+        hq, hk, d = self.local_heads, self.local_heads_kv, self.head_dim
+        off = ip.seqlen_offset
+        if hq == hk:
+            qkv = qkv.view(b, s, 3, hq, d)
+            if self.rotary_emb_dim > 0:
+                cos, sin = F.rope_tables(ip.max_seqlen, self.rotary_emb_dim, self.rotary_emb_base, qkv.device)
+                qkv = F.apply_rotary_qkv_(qkv.contiguous(), cos[off:off + s], sin[off:off + s], self.rotary_emb_dim)
+            q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        else:
+            q = qkv[..., : hq * d].reshape(b, s, hq, d)
+            k = qkv[..., hq * d: (hq + hk) * d].reshape(b, s, hk, d)
+            v = qkv[..., (hq + hk) * d:].reshape(b, s, hk, d)
+        cache = ip.cache_for(self.layer_idx, b, hk, d, qkv.dtype, qkv.device)      # [b, max_seq, 2, hk, d]
+        cache[:b, off:off + s, 0].copy_(k)
+        cache[:b, off:off + s, 1].copy_(v)
+        if s == 1:
+            ctx = F.decode_attention(q[:, 0], cache[:b, :, 0], cache[:b, :, 1], off + 1, self.softmax_scale)
+            ctx = ctx.unsqueeze(1)
+        else:
+            assert off == 0, "a multi-token call must start the sequence (prompt processing)"
+            ctx = self._attend(q, k, v, self.causal)
+        ctx = ctx.reshape(b, s, -1)
+        return self.out_proj(ctx, residual=residual)
+
     def forward(self, x, x_kv=None, batch_size=None, residual=None):
         """``x``: [b, s, h], or a [b*s/tp, h] token shard under sequence parallelism (then
         ``batch_size`` is needed to recover the sequence length)."""
+        if getattr(self, "inference_params", None) is not None:
+            return self._forward_cached(x, residual)
         if not self.cross_attn:
             qkv = self.Wqkv(x)
             if qkv.dim() == 2:

@@ -503,6 +503,32 @@ def apply_rotary_qkv_(qkv, cos, sin, rot_dim: int, conj: bool = False):
 
 
 # --------------------------------------------------------------------------- attention
+def decode_attention(q, k_cache, v_cache, seq_len: int, scale: Optional[float] = None):
+    """One new query per sequence against the first ``seq_len`` cached positions (no autograd).
+
+    ``q``: ``[b, nh, d]``; ``k_cache`` / ``v_cache``: ``[b, max_seq, nh_kv, d]`` (views with unit
+    stride along ``d`` are fine).  Returns ``[b, nh, d]``."""
+    b, nh, d = q.shape
+    nkv = k_cache.shape[2]
+    scale = float(scale if scale is not None else 1.0 / math.sqrt(d))
+    if not (use_native(q) and q.dtype == torch.bfloat16 and d % 8 == 0 and d <= 256
+            and k_cache.stride(3) == 1 and v_cache.stride(3) == 1
+            and all(st % 8 == 0 for st in k_cache.stride()[:3] + v_cache.stride()[:3])):
+        k = k_cache[:, :seq_len].float()
+        v = v_cache[:, :seq_len].float()
+        if nkv != nh:
+            k = k.repeat_interleave(nh // nkv, dim=2)
+            v = v.repeat_interleave(nh // nkv, dim=2)
+        s = torch.einsum("bhd,bkhd->bhk", q.float(), k) * scale
+        return torch.einsum("bhk,bkhd->bhd", torch.softmax(s, dim=-1), v).to(q.dtype)
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    ks, vs = k_cache.stride(), v_cache.stride()
+    call("mb_decode_attn", ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), b, nh, nkv, d, int(seq_len),
+         ks[0], ks[1], ks[2], vs[0], vs[1], vs[2], scale, stream())
+    return out
+
+
 def _ref_attention(q, k, v, scale, causal):
     # q: [b, sq, nh, d]; k, v: [b, sk, nh_kv, d]
     b, sq, nh, d = q.shape

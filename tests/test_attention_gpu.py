@@ -74,3 +74,22 @@ def test_attention_qkvpacked_grad(d, rot):
     o_ref.backward(g.cpu().float())
     assert _rel_err(o.cpu(), o_ref) < 2e-2
     assert _rel_err(qkv2.grad.cpu(), ref_in.grad) < 3e-2
+
+
+@pytest.mark.parametrize("nh,nkv,d,seq_len", [(8, 8, 128, 300), (8, 2, 64, 5), (4, 4, 80, 1), (16, 4, 256, 1031)])
+def test_single_query_attention_over_kv_cache(nh, nkv, d, seq_len):
+    """Decode step: one query per sequence against the first ``seq_len`` positions of a cache
+    that is a strided view ([b, max_seq, 2, heads, d]), vs fp32 softmax(q K^T) V."""
+    from mist_b200.ops import functional as F
+    torch.manual_seed(5)
+    b, max_seq = 3, 1100
+    cache = torch.randn(b, max_seq, 2, nkv, d, device="cuda", dtype=torch.bfloat16)
+    q = torch.randn(b, nh, d, device="cuda", dtype=torch.bfloat16)
+    scale = d ** -0.5
+    out = F.decode_attention(q, cache[:, :, 0], cache[:, :, 1], seq_len, scale)
+    k = cache[:, :seq_len, 0].float().repeat_interleave(nh // nkv, dim=2)
+    v = cache[:, :seq_len, 1].float().repeat_interleave(nh // nkv, dim=2)
+    s = torch.einsum("bhd,bkhd->bhk", q.float(), k) * scale
+    ref = torch.einsum("bhk,bkhd->bhd", torch.softmax(s, dim=-1), v)
+    err = ((out.float() - ref).norm() / ref.norm()).item()
+    assert err < 1e-2, err
