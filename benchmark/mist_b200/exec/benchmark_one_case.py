@@ -63,6 +63,9 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
             torch.cuda.synchronize()
 
     prof = None
+    if cfg.get("profile", False):
+        from mist_b200.utils.logging import enable_ranges
+        enable_ranges(True)       # label scheduler actions (unshard / grad reduce / optimizer step / swaps)
     if cfg.get("profile", False) and cuda:
         prof = torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA],
                                       on_trace_ready=torch.profiler.tensorboard_trace_handler(

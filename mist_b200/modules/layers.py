@@ -295,8 +295,13 @@ class ParallelMHA(nn.Module):
                 qkv = F.apply_rotary_qkv_(qkv.contiguous(), cos[off:off + s], sin[off:off + s], self.rotary_emb_dim)
             q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
         else:
-            q = qkv[..., : hq * d].reshape(b, s, hq, d)
-            k = qkv[..., hq * d: (hq + hk) * d].reshape(b, s, hk, d)
+            qk = qkv[..., : (hq + hk) * d].reshape(b, s, 1, hq + hk, d)
+            if self.rotary_emb_dim > 0:
+                cos, sin = F.rope_tables(ip.max_seqlen, self.rotary_emb_dim, self.rotary_emb_base, qkv.device)
+                qk = F._rope_apply(qk.contiguous().clone(), cos[off:off + s], sin[off:off + s], self.rotary_emb_dim,
+                                   False, 1)
+            qk = qk.reshape(b, s, hq + hk, d)
+            q, k = qk[:, :, :hq], qk[:, :, hq:]
             v = qkv[..., (hq + hk) * d:].reshape(b, s, hk, d)
         cache = ip.cache_for(self.layer_idx, b, hk, d, qkv.dtype, qkv.device)      # [b, max_seq, 2, hk, d]
         cache[:b, off:off + s, 0].copy_(k)
@@ -334,8 +339,15 @@ class ParallelMHA(nn.Module):
                     ctx = self._attend(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], self.causal)
             else:
                 hq, hk, d = self.local_heads, self.local_heads_kv, self.head_dim
-                q = qkv[..., : hq * d].reshape(b, s, hq, d)
-                k = qkv[..., hq * d: (hq + hk) * d].reshape(b, s, hk, d)
+                if self.rotary_emb_dim > 0:
+                    # grouped-query layout [q heads | k heads | v heads]: rotate the q and k heads together
+                    cos, sin = F.rope_tables(s, self.rotary_emb_dim, self.rotary_emb_base, qkv.device)
+                    qk = qkv[..., : (hq + hk) * d].reshape(b, s, 1, hq + hk, d)
+                    qk = _RotaryOutOfPlace.apply(qk, cos, sin, self.rotary_emb_dim, 1).reshape(b, s, hq + hk, d)
+                    q, k = qk[:, :, :hq], qk[:, :, hq:]
+                else:
+                    q = qkv[..., : hq * d].reshape(b, s, hq, d)
+                    k = qkv[..., hq * d: (hq + hk) * d].reshape(b, s, hk, d)
                 v = qkv[..., (hq + hk) * d:].reshape(b, s, hk, d)
                 ctx = self._attend(q, k, v, self.causal)
         else:
@@ -356,15 +368,16 @@ class _RotaryOutOfPlace(torch.autograd.Function):
     """Differentiable rotary embedding for the non-flash attention path."""
 
     @staticmethod
-    def forward(ctx, qkv, cos, sin, rot):
+    def forward(ctx, qkv, cos, sin, rot, n_rot=2):
+        """``qkv``: ``[b, s, n, heads, d]``; the first ``n_rot`` of the ``n`` slots are rotated."""
         ctx.save_for_backward(cos, sin)
-        ctx.rot = rot
-        return F.apply_rotary_qkv_(qkv.clone(), cos, sin, rot)
+        ctx.rot, ctx.n_rot = rot, n_rot
+        return F._rope_apply(qkv.contiguous().clone(), cos, sin, rot, False, n_rot)
 
     @staticmethod
     def backward(ctx, g):
         cos, sin = ctx.saved_tensors
-        return F.apply_rotary_qkv_(g.contiguous().clone(), cos, sin, ctx.rot, conj=True), None, None, None
+        return F._rope_apply(g.contiguous().clone(), cos, sin, ctx.rot, True, ctx.n_rot), None, None, None, None
 
 
 # --------------------------------------------------------------------------------- MLP

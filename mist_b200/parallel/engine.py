@@ -29,6 +29,7 @@ import torch.nn as nn
 from ..config import StageStrategy, ZeroLevel
 from ..ops import functional as F
 from ..ops import native
+from ..utils.logging import record
 from .flat_unit import FlatUnit
 from .state import ParallelState
 
@@ -251,7 +252,7 @@ class TrainEngine:
         slot = self._next_slot
         self._next_slot ^= 1
         self._slot_of[unit.name] = slot
-        with self._on_comm():
+        with self._on_comm(), record(f"{unit.name}.unshard"):
             unit.unshard(self._slots[slot], self.ps.dp_ag_group if unit.is_zero3 else None,
                          streams=self.swap_streams)
             if self.cuda:
@@ -274,7 +275,8 @@ class TrainEngine:
         self._next_slot ^= 1
         self._slot_of[unit.name] = slot
         full = self._slots[slot][: unit.padded]
-        pg.stage_shard(slot, unit.param_shard)
+        with record(f"{unit.name}.unshard_in_first_gemm"):
+            pg.stage_shard(slot, unit.param_shard)
         if b_off:
             dist.broadcast(full[:b_off], src=self._dp_root, group=self.ps.dp_ag_group)
         unit.flat_param = full
@@ -294,7 +296,8 @@ class TrainEngine:
 
     def _release(self, unit: FlatUnit):
         if self.zero3:
-            unit.reshard()
+            with record(f"{unit.name}.reshard"):
+                unit.reshard()
 
     # ----------------------------------------------------------- callbacks from the stack
     def before_layer(self, stack, i, hidden, residual):
@@ -375,12 +378,15 @@ class TrainEngine:
             self.fused.reduce_and_step(unit, last)
             return
         with self._on_comm():
-            grad = unit.reduce_grads(self.ps.dp_rs_group, last, streams=self.swap_streams)
+            with record(f"{unit.name}.post_backward_grad_reduce"):
+                grad = unit.reduce_grads(self.ps.dp_rs_group, last, streams=self.swap_streams)
             if grad is not None:
                 swap = ((self.swap_streams, self.opt_staging)
                         if (unit.opt_host_numel or unit.weight_split is not None) else None)
-                unit.optimizer_step(grad, self.hp, self.ps.dp_ag_group, grad_divisor=float(self.ps.dp_size * self.G),
-                                    swap=swap, step_scratch=self._step_scratch)
+                with record(f"OPT-{unit.name}.step"):
+                    unit.optimizer_step(grad, self.hp, self.ps.dp_ag_group,
+                                        grad_divisor=float(self.ps.dp_size * self.G), swap=swap,
+                                        step_scratch=self._step_scratch)
                 if self.cuda:
                     ev = torch.cuda.Event()
                     ev.record()

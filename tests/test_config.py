@@ -77,3 +77,18 @@ def test_yaml_roundtrip(tmp_path):
     cfg2, _ = load_config("out", config_dirs=[tmp_path], check_world_size=False)
     assert cfg2.strategy.stage_strategies == cfg.strategy.stage_strategies
     assert cfg2.strategy.num_stages == 2
+
+
+def test_memory_snapshot_summary():
+    from mist_b200.tools.parse_memory_snapshot import summarise
+    snap = {"segments": [
+        {"segment_type": "large", "total_size": 100, "allocated_size": 60, "active_size": 60, "blocks": [
+            {"state": "active_allocated", "size": 60, "requested_size": 50,
+             "frames": [{"filename": "/x/engine.py", "line": 12, "name": "alloc"}]},
+            {"state": "inactive", "size": 40}]},
+        {"segment_type": "small", "total_size": 10, "allocated_size": 10, "active_size": 10, "blocks": [
+            {"state": "active_allocated", "size": 10}]}]}
+    r = summarise(snap, top=1)
+    assert r["reserved"] == 110 and r["allocated"] == 70 and r["largest_free_block"] == 40
+    assert r["by_kind"]["large"] == (1, 100, 60)
+    assert r["top_blocks"][0][0] == 60 and "engine.py:12" in r["top_blocks"][0][2]

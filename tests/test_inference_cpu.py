@@ -13,9 +13,12 @@ TINY = ["model.num_hidden_layers=2", "model.hidden_size=64", "model.intermediate
         "strategy.layer_partitions=[2]", "training.params_dtype=float32"]
 
 
-@pytest.mark.parametrize("exp", ["gpt2-1.3b", "llama-350m"])
-def test_cached_generation_matches_full_recompute(exp):
-    cfg, _ = load_config("config", [f"experiment={exp}"] + TINY, check_world_size=False)
+@pytest.mark.parametrize("exp,extra", [("gpt2-1.3b", []), ("llama-350m", []),
+                                       ("llama-350m", ["+model.num_heads_kv=2"])])     # grouped-query + rotary
+def test_cached_generation_matches_full_recompute(exp, extra):
+    cfg, _ = load_config("config", [f"experiment={exp}"] + TINY + extra, check_world_size=False)
+    if extra:
+        assert cfg.model.num_heads_kv == 2
     torch.manual_seed(0)
     model = base_model_provider(cfg.model, device="cpu", dtype=torch.float32).eval()
     prompt = torch.randint(0, 128, (2, 7))
