@@ -243,6 +243,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int half = threadIdx.x >> 7; // which 32 query columns
     const int c0 = half * 32;
     const int kv_idx = kv0 + r;
+    const int kv_last = kv0 + BKV - 1;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const bool leader = (threadIdx.x == 0);
     uint8_t* sp_ = smem + L::oP;
@@ -282,12 +283,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t sr[32];
         tmem_ld32(t_s + c0 + lane_off, sr);
         tmem_ld_wait();
+        // Only blocks on the diagonal or at the end of the queries / keys need the mask (the test
+        // is uniform over the CTA): the others take the shorter loop.
+        const bool need_mask = (q0 + BQ > p.sq) || (kv_last >= p.sk) || (p.causal && kv_last > q0 + coff);
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int qi = q0 + c0 + c;
-          const bool valid = (qi < p.sq) && (kv_idx < p.sk) && (!p.causal || kv_idx <= qi + coff);
-          const float e = mb::fast_exp2(__uint_as_float(sr[c]) * p.scale_log2 - s_lse[vb * BQ + c0 + c]);
-          pf[c] = valid ? e : 0.f;
+          for (int c = 0; c < 32; ++c) {
+            const int qi = q0 + c0 + c;
+            const bool valid = (qi < p.sq) && (kv_idx < p.sk) && (!p.causal || kv_idx <= qi + coff);
+            const float e = mb::fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -s_lse[vb * BQ + c0 + c]));
+            pf[c] = valid ? e : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            pf[c] = mb::fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -s_lse[vb * BQ + c0 + c]));
         }
 #pragma unroll
         for (int c = 0; c < 32; c += 2) pk[c >> 1] = pack2(pf[c], pf[c + 1]);

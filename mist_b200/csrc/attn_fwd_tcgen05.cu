@@ -249,29 +249,49 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       const int kv0 = j * BN;
       const int vis = p.causal ? min(p.sk - 1, qi + coff) : p.sk - 1;  // last visible key
-      float mx = -INFINITY;
+      // Only tiles that touch the diagonal or the end of the keys need the mask; the test is the
+      // same for every thread of the CTA (first row of the tile has the smallest horizon).
+      const int vis_tile = p.causal ? min(p.sk - 1, q0 + coff) : p.sk - 1;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      if (kv0 + BN - 1 > vis_tile) {
 #pragma unroll
-      for (int i = 0; i < BN; ++i) {
-        float v = __uint_as_float(sr[i]) * p.scale_log2;
-        v = (kv0 + i <= vis) ? v : -INFINITY;
-        sr[i] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+        for (int i = 0; i < BN; i += 4) {
+          float v0 = (kv0 + i <= vis) ? __uint_as_float(sr[i]) : -INFINITY;
+          float v1 = (kv0 + i + 1 <= vis) ? __uint_as_float(sr[i + 1]) : -INFINITY;
+          float v2 = (kv0 + i + 2 <= vis) ? __uint_as_float(sr[i + 2]) : -INFINITY;
+          float v3 = (kv0 + i + 3 <= vis) ? __uint_as_float(sr[i + 3]) : -INFINITY;
+          sr[i] = __float_as_uint(v0); sr[i + 1] = __float_as_uint(v1);
+          sr[i + 2] = __float_as_uint(v2); sr[i + 3] = __float_as_uint(v3);
+          mx0 = fmaxf(mx0, v0); mx1 = fmaxf(mx1, v1); mx2 = fmaxf(mx2, v2); mx3 = fmaxf(mx3, v3);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+        }
       }
+      // raw scores; the softmax scale (> 0, so maxima commute with it) is folded into the FFMA below
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
       // Lazy rescaling: keep the old reference maximum unless the new one is much
       // larger; probabilities then stay below 2^8, harmless in fp32 / bf16.
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new - m_run > 8.f || m_run == -INFINITY) ? m_new : m_run;
       const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
-      const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
-      float sum = 0.f;
+      const float m_neg = (m_use == -INFINITY) ? 0.f : -m_use;
+      float sum0 = 0.f, sum1 = 0.f;
       uint32_t pk[BN / 2];
 #pragma unroll
       for (int i = 0; i < BN; i += 2) {
-        float a = mb::fast_exp2(__uint_as_float(sr[i]) - m_safe);
-        float c = mb::fast_exp2(__uint_as_float(sr[i + 1]) - m_safe);
-        sum += a + c;
+        float a = mb::fast_exp2(fmaf(__uint_as_float(sr[i]), p.scale_log2, m_neg));
+        float c = mb::fast_exp2(fmaf(__uint_as_float(sr[i + 1]), p.scale_log2, m_neg));
+        sum0 += a;
+        sum1 += c;
         pk[i >> 1] = pack_bf16x2(a, c);
       }
+      const float sum = sum0 + sum1;
       l_run = l_run * alpha + sum;
       m_run = m_use;
 

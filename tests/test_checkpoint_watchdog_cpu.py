@@ -129,3 +129,49 @@ def test_bounded_wait_status_names():
     from mist_b200.ops import native
     assert native._STATUS_NAMES[4].startswith("peer flag")
     assert set(native._STATUS_NAMES) == {1, 2, 3, 4, 5}
+
+
+def test_p2p_metadata_roundtrip_and_limits():
+    from mist_b200.parallel.pipeline import META_LEN, decode_meta, encode_meta
+    t = torch.zeros(2, 3, 5, dtype=torch.bfloat16, requires_grad=True)
+    vec = encode_meta(t)
+    assert len(vec) == META_LEN
+    shape, dtype, rg = decode_meta(vec)
+    assert shape == (2, 3, 5) and dtype == torch.bfloat16 and rg
+    with pytest.raises(AssertionError):
+        encode_meta(torch.zeros(1, 1, 1, 1, 1, 1, 1))         # more than 6 dimensions
+    with pytest.raises(KeyError):
+        encode_meta(torch.zeros(2, dtype=torch.float64))      # dtype without a wire code
+
+
+def _leaver_worker(rank, world, port, ret):
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    x = torch.ones(4)
+    dist.all_reduce(x)              # step 1: everybody is there
+    if rank == 1:
+        os._exit(0)                 # leaves between steps, nothing in flight
+    t0 = time.time()
+    try:
+        dist.all_reduce(x)          # step 2: the peer is gone
+        ret["outcome"] = "completed"
+    except Exception as e:          # noqa: BLE001 - the point is that it raises instead of hanging
+        ret["outcome"] = type(e).__name__
+    ret["seconds"] = time.time() - t0
+    os._exit(0)
+
+
+def test_collective_after_a_rank_left_raises_within_the_timeout():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 36500 + os.getpid() % 2000
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaver_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive()
+    assert ret["outcome"] != "completed"
+    assert ret["seconds"] < 30
