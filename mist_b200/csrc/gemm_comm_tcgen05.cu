@@ -663,7 +663,11 @@ MB_API int mb_gemm_param_gather(void* const* w_ptrs, const void* A, void* C, voi
   p.M = M; p.N = N; p.K = K; p.mode = MODE_AGW;
   p.nranks = nranks; p.me = me; p.epoch = epoch;
   p.rows_per_rank = M;
-  p.n_gather = nranks > 1 ? (n_gather > 0 ? n_gather : 24) : 0;
+  // Gather CTAs pull ~15 GB/s each (measured); 32 of them when fetching the remote shards takes longer than
+  // the GEMM itself, 16 when the GEMM dominates and needs the SMs more.
+  const double gather_s = static_cast<double>(shard_elems) * 2.0 * (nranks - 1) / 450e9;
+  const double gemm_s = 2.0 * M * static_cast<double>(N) * K / 1.4e15;
+  p.n_gather = nranks > 1 ? (n_gather > 0 ? n_gather : (gather_s > gemm_s ? 32 : 16)) : 0;
   p.chunk_flags = chunk_flags;
   p.C = C; p.ldc = ldc;
   p.status = mb_status_device_ptr();

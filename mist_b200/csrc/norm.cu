@@ -13,6 +13,7 @@
 // row and several rows share a CTA, the grid is persistent over row groups.
 // The kernels are bandwidth bound; they touch each element once per pass.
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace {
 
@@ -215,21 +216,39 @@ __global__ void norm_bwd_finalize_kernel(const float* __restrict__ part_dgamma,
                                          __nv_bfloat16* __restrict__ dgamma,
                                          __nv_bfloat16* __restrict__ dbeta, int nparts, int h,
                                          int accumulate) {
-  __shared__ float sg[8][33], sb[8][33];
+  // 32 x 32 threads: 32 columns per CTA, the partial rows dealt round-robin to the 32 row threads, four
+  // independent running sums per thread so the loads of a column do not serialise on one add chain.
+  __shared__ float sg[32][33], sb[32][33];
   const int col = blockIdx.x * 32 + threadIdx.x;
   float ag = 0.f, ab = 0.f;
   if (col < h) {
-    for (int r = threadIdx.y; r < nparts; r += 8) {
-      ag += part_dgamma[static_cast<size_t>(r) * h + col];
-      if (part_dbeta) ab += part_dbeta[static_cast<size_t>(r) * h + col];
+    float g0 = 0.f, g1 = 0.f, g2 = 0.f, g3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+    const int step = blockDim.y;
+    int r = threadIdx.y;
+    for (; r + 3 * step < nparts; r += 4 * step) {
+      g0 += part_dgamma[static_cast<size_t>(r) * h + col];
+      g1 += part_dgamma[static_cast<size_t>(r + step) * h + col];
+      g2 += part_dgamma[static_cast<size_t>(r + 2 * step) * h + col];
+      g3 += part_dgamma[static_cast<size_t>(r + 3 * step) * h + col];
+      if (part_dbeta) {
+        b0 += part_dbeta[static_cast<size_t>(r) * h + col];
+        b1 += part_dbeta[static_cast<size_t>(r + step) * h + col];
+        b2 += part_dbeta[static_cast<size_t>(r + 2 * step) * h + col];
+        b3 += part_dbeta[static_cast<size_t>(r + 3 * step) * h + col];
+      }
     }
+    for (; r < nparts; r += step) {
+      g0 += part_dgamma[static_cast<size_t>(r) * h + col];
+      if (part_dbeta) b0 += part_dbeta[static_cast<size_t>(r) * h + col];
+    }
+    ag = (g0 + g1) + (g2 + g3);
+    ab = (b0 + b1) + (b2 + b3);
   }
   sg[threadIdx.y][threadIdx.x] = ag;
   sb[threadIdx.y][threadIdx.x] = ab;
   __syncthreads();
   if (threadIdx.y == 0 && col < h) {
-#pragma unroll
-    for (int r = 1; r < 8; ++r) {
+    for (int r = 1; r < static_cast<int>(blockDim.y); ++r) {
       ag += sg[r][threadIdx.x];
       ab += sb[r][threadIdx.x];
     }
@@ -252,6 +271,23 @@ int num_sms() {
   return g_sms;
 }
 
+// CTAs per SM of the persistent grids; MB_NORM_FWD_CTAS_PER_SM / MB_NORM_BWD_CTAS_PER_SM override the
+// defaults for tuning runs (read once per process).
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  if (!v || !*v) return dflt;
+  int x = atoi(v);
+  return x > 0 ? x : dflt;
+}
+int fwd_ctas_per_sm() {
+  static int v = env_int("MB_NORM_FWD_CTAS_PER_SM", 8);
+  return v;
+}
+int bwd_ctas_per_sm() {
+  static int v = env_int("MB_NORM_BWD_CTAS_PER_SM", 4);
+  return v;
+}
+
 void pick_shape(int h, int& tpr, int& rpc) {
   int nvec = h / 8;
   tpr = ((nvec + VPT - 1) / VPT + 31) / 32 * 32;
@@ -269,7 +305,7 @@ MB_API int mb_norm_bwd_scratch_rows(int rows, int h) {
   int tpr, rpc;
   pick_shape(h, tpr, rpc);
   int groups = (rows + rpc - 1) / rpc;
-  int grid = num_sms() * 4;
+  int grid = num_sms() * bwd_ctas_per_sm();
   if (grid > groups) grid = groups;
   return grid * rpc;
 }
@@ -283,7 +319,7 @@ MB_API int mb_norm_fwd(const void* x0, const void* residual, const void* gamma, 
   int tpr, rpc;
   pick_shape(h, tpr, rpc);
   int groups = (rows + rpc - 1) / rpc;
-  int grid = num_sms() * 8;
+  int grid = num_sms() * fwd_ctas_per_sm();
   if (grid > groups) grid = groups;
   auto a = reinterpret_cast<const __nv_bfloat16*>(x0);
   auto r = reinterpret_cast<const __nv_bfloat16*>(residual);
@@ -310,7 +346,7 @@ MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const f
   int tpr, rpc;
   pick_shape(h, tpr, rpc);
   int groups = (rows + rpc - 1) / rpc;
-  int grid = num_sms() * 4;
+  int grid = num_sms() * bwd_ctas_per_sm();
   if (grid > groups) grid = groups;
   int nparts = grid * rpc;
   float* pg = scratch;
@@ -326,7 +362,7 @@ MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const f
   else
     norm_bwd_kernel<false><<<grid, tpr * rpc, 0, stream>>>(dzz, xx, g, mean, rstd, dr, dxx, pg, pb,
                                                            rows, h, tpr, rpc);
-  dim3 fb(32, 8);
+  dim3 fb(32, 32);
   norm_bwd_finalize_kernel<<<(h + 31) / 32, fb, 0, stream>>>(
       pg, pb, reinterpret_cast<__nv_bfloat16*>(dgamma), reinterpret_cast<__nv_bfloat16*>(dbeta),
       nparts, h, accumulate);

@@ -33,9 +33,10 @@ FLAG_INTS = 32
 
 
 class ParamGatherContext:
-    """Symmetric weight slots, flag blocks and chunk flags of one data-parallel group."""
+    """Symmetric weight slots, flag blocks and chunk flags of one data-parallel group.
+    ``n_gather = 0`` lets the kernel wrapper choose the number of gather CTAs (16 or 32)."""
 
-    def __init__(self, group, padded_numel: int, device=None, n_slots: int = 2, n_gather: int = 16,
+    def __init__(self, group, padded_numel: int, device=None, n_slots: int = 2, n_gather: int = 0,
                  chunk_bytes: int = 1 << 20, emulate_ranks: int = 0, max_sites: int = 64):
         self.group, self.n_gather, self.chunk_bytes = group, int(n_gather), int(chunk_bytes)
         self.padded = int(padded_numel)
