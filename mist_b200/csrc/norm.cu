@@ -17,7 +17,7 @@
 
 namespace {
 
-constexpr int VPT = 4;  // 16-byte vectors per thread (covers hidden <= 8 * VPT * tpr)
+constexpr int kMaxVPT = 4;  // 16-byte vectors per thread (covers hidden <= 8 * VPT * tpr)
 
 // Sum over the `tpr` threads that share a row.  `red` holds [rows_per_cta][8] floats.
 template <int NVAL>
@@ -42,7 +42,7 @@ __device__ __forceinline__ void row_reduce(float (&v)[NVAL], float* red, int tpr
   }
 }
 
-template <bool RMS>
+template <bool RMS, int VPT>
 __global__ void __launch_bounds__(256, 4)
 norm_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ residual,
                 const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
@@ -116,7 +116,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __res
   }
 }
 
-template <bool RMS>
+template <bool RMS, int VPT>
 __global__ void __launch_bounds__(256, 2)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
@@ -288,7 +288,18 @@ int bwd_ctas_per_sm() {
   return v;
 }
 
+// Two vectors per thread when a row then still fits 256 threads (more, lighter warps hide the
+// memory latency better), else four.  MB_NORM_VPT forces a choice for tuning runs.
+int pick_vpt(int h) {
+  static int forced = env_int("MB_NORM_VPT", 0);
+  int nvec = h / 8;
+  if (forced == 2 && nvec <= 2 * 256) return 2;
+  if (forced == 4) return 4;
+  return (nvec <= 2 * 256) ? 2 : 4;
+}
+
 void pick_shape(int h, int& tpr, int& rpc) {
+  const int VPT = pick_vpt(h);
   int nvec = h / 8;
   tpr = ((nvec + VPT - 1) / VPT + 31) / 32 * 32;
   if (tpr > 256) tpr = 256;
@@ -314,7 +325,7 @@ MB_API int mb_norm_bwd_scratch_rows(int rows, int h) {
 MB_API int mb_norm_fwd(const void* x0, const void* residual, const void* gamma, const void* beta,
                        void* z, void* x_out, float* mean, float* rstd, int rows, int h, float eps,
                        int rms, cudaStream_t stream) {
-  if (h % 8 != 0 || h > 8 * VPT * 256) return -1;
+  if (h % 8 != 0 || h > 8 * kMaxVPT * 256) return -1;
   if (rows == 0) return 0;
   int tpr, rpc;
   pick_shape(h, tpr, rpc);
@@ -327,12 +338,11 @@ MB_API int mb_norm_fwd(const void* x0, const void* residual, const void* gamma, 
   auto b = reinterpret_cast<const __nv_bfloat16*>(beta);
   auto zz = reinterpret_cast<__nv_bfloat16*>(z);
   auto xo = reinterpret_cast<__nv_bfloat16*>(x_out);
-  if (rms)
-    norm_fwd_kernel<true><<<grid, tpr * rpc, 0, stream>>>(a, r, g, b, zz, xo, mean, rstd, rows, h,
-                                                          eps, tpr, rpc);
-  else
-    norm_fwd_kernel<false><<<grid, tpr * rpc, 0, stream>>>(a, r, g, b, zz, xo, mean, rstd, rows, h,
-                                                           eps, tpr, rpc);
+  const bool v2 = pick_vpt(h) == 2;
+#define MB_FWD(R_, V_) norm_fwd_kernel<R_, V_><<<grid, tpr * rpc, 0, stream>>>(a, r, g, b, zz, xo, mean, rstd, rows, h, eps, tpr, rpc)
+  if (rms) { if (v2) MB_FWD(true, 2); else MB_FWD(true, 4); }
+  else { if (v2) MB_FWD(false, 2); else MB_FWD(false, 4); }
+#undef MB_FWD
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -341,7 +351,7 @@ MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const f
                        const float* rstd, const void* dres_in, void* dx, void* dgamma, void* dbeta,
                        float* scratch, int rows, int h, int rms, int accumulate,
                        cudaStream_t stream) {
-  if (h % 8 != 0 || h > 8 * VPT * 256) return -1;
+  if (h % 8 != 0 || h > 8 * kMaxVPT * 256) return -1;
   if (rows == 0) return 0;
   int tpr, rpc;
   pick_shape(h, tpr, rpc);
@@ -356,12 +366,11 @@ MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const f
   auto g = reinterpret_cast<const __nv_bfloat16*>(gamma);
   auto dr = reinterpret_cast<const __nv_bfloat16*>(dres_in);
   auto dxx = reinterpret_cast<__nv_bfloat16*>(dx);
-  if (rms)
-    norm_bwd_kernel<true><<<grid, tpr * rpc, 0, stream>>>(dzz, xx, g, mean, rstd, dr, dxx, pg, pb,
-                                                          rows, h, tpr, rpc);
-  else
-    norm_bwd_kernel<false><<<grid, tpr * rpc, 0, stream>>>(dzz, xx, g, mean, rstd, dr, dxx, pg, pb,
-                                                           rows, h, tpr, rpc);
+  const bool v2 = pick_vpt(h) == 2;
+#define MB_BWD(R_, V_) norm_bwd_kernel<R_, V_><<<grid, tpr * rpc, 0, stream>>>(dzz, xx, g, mean, rstd, dr, dxx, pg, pb, rows, h, tpr, rpc)
+  if (rms) { if (v2) MB_BWD(true, 2); else MB_BWD(true, 4); }
+  else { if (v2) MB_BWD(false, 2); else MB_BWD(false, 4); }
+#undef MB_BWD
   dim3 fb(32, 32);
   norm_bwd_finalize_kernel<<<(h + 31) / 32, fb, 0, stream>>>(
       pg, pb, reinterpret_cast<__nv_bfloat16*>(dgamma), reinterpret_cast<__nv_bfloat16*>(dbeta),
