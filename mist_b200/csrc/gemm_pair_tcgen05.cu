@@ -23,38 +23,51 @@ constexpr int BM = 128;       // rows per CTA (256 per pair)
 constexpr int BN = 256;       // columns per pair; each CTA stages BN / 2 rows of B
 constexpr int BNH = BN / 2;
 constexpr int BK = 64;
-constexpr int STAGES = 6;
+// Six pipeline stages; the kernels whose epilogue reads a second operand (gelu' or residual) give one
+// stage up for two staging tiles that TMA fills with that operand ahead of the epilogue.
+constexpr int kStagesPlain = 6;
+constexpr int kStagesAux = 5;
 constexpr int kThreads = 192;
 
-enum EpiFlags : int { EPI_BIAS = 1, EPI_GELU = 2, EPI_SAVE_PRE = 4, EPI_ACCUM = 8, EPI_OUT_FP32 = 32 };
+enum EpiFlags : int {
+  EPI_BIAS = 1, EPI_GELU = 2, EPI_SAVE_PRE = 4, EPI_ACCUM = 8, EPI_DGELU = 16, EPI_OUT_FP32 = 32, EPI_RESIDUAL = 64
+};
 
 struct PairParams {
   int M, N, K;
   const __nv_bfloat16* bias;
+  const __nv_bfloat16* aux;   // DGELU: pre-activation, RESIDUAL: tensor to add; [M][N] bf16 with row stride ldc
+  int ldc;
   int flags;
   float alpha;
   int* status;
 };
 
-struct L {
+template <bool AUX>
+struct Layout {
+  static constexpr int kStages = AUX ? kStagesAux : kStagesPlain;
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BNH * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStagingBytes = BM * 128;
-  static constexpr int kStagingOffset = STAGES * kStageBytes;
-  static constexpr int kBarOffset = kStagingOffset + 2 * kStagingBytes;
-  static constexpr int kTotal = kBarOffset + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int kStagingOffset = kStages * kStageBytes;
+  static constexpr int kAuxOffset = kStagingOffset + 2 * kStagingBytes;          // two tiles, AUX only
+  static constexpr int kBarOffset = kAuxOffset + (AUX ? 2 * kStagingBytes : 0);
+  // full[S], empty[S], tmem_full[2], tmem_empty[2], aux_full[2], tmem base word
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 6) * 8 + 16;
 };
 
 __device__ __forceinline__ void report(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool AUX>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap tma_aux,
                  const PairParams p) {
+  using L = Layout<AUX>;
+  constexpr int STAGES = L::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // Both CTAs of the pair must use the same offsets: the dynamic segment starts at the same
   // shared-memory address in every CTA of a launch, so the same rounding applies.
@@ -64,7 +77,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* aux_full = tempty_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_full + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -97,6 +111,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);   // one MMA commit, broadcast to both CTAs
       mbar_init(&tempty_bar[a], 8);  // leader's: 4 epilogue warps of each CTA
+      mbar_init(&aux_full[a], 1);    // second epilogue operand staged by TMA (AUX kernels)
     }
     fence_barrier_init();
     prefetch_tmap(&tma_a);
@@ -211,13 +226,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int cols_per_unit = out_fp32 ? 32 : 64;
     const int units = BN / cols_per_unit;
     const int npass = (p.flags & EPI_SAVE_PRE) ? 2 : 1;
-    uint32_t tcount = 0, epi_units = 0;
+    uint32_t tcount = 0, epi_units = 0, aux_units = 0;
     bool ok = true;
     for (int t = pair; t < num_tiles && ok; t += num_pairs, ++tcount) {
       int m0, n0;
       tile_coords(t, m0, n0);
       int acc = tcount & 1;
       uint32_t acc_ph = (tcount >> 1) & 1;
+      if (AUX && leader && m0 < p.M) {
+        // the first two operand tiles of this output tile travel while the main loop still runs
+        const int live = min(units, (p.N - n0 + cols_per_unit - 1) / cols_per_unit);
+        for (int u = 0; u < 2 && u < live; ++u) {
+          const uint32_t au = aux_units + u;
+          mbar_expect_tx(&aux_full[au & 1], L::kStagingBytes);
+          tma_load_2d(smem + L::kAuxOffset + (au & 1) * L::kStagingBytes, &tma_aux, &aux_full[au & 1],
+                      n0 + u * cols_per_unit, m0);
+        }
+      }
       if (!mbar_wait(&tfull_bar[acc], acc_ph)) {
         report(p.status, MB_ERR_TIMEOUT_TMEM);
         ok = false;
@@ -226,9 +251,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       const bool rows_live = m0 < p.M;   // the second CTA of a pair can hang over the bottom edge
+      int units_live = 0;
+      if (rows_live) units_live = min(units, (p.N - n0 + cols_per_unit - 1) / cols_per_unit);
       for (int u = 0; u < units && rows_live; ++u) {
         const int ucol0 = n0 + u * cols_per_unit;
         if (ucol0 >= p.N) break;
+        if (AUX) {
+          const uint32_t au = aux_units + u;
+          if (!mbar_wait(&aux_full[au & 1], (au >> 1) & 1)) {
+            report(p.status, MB_ERR_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+        }
         for (int pass = 0; pass < npass; ++pass) {
           uint8_t* stg = smem + L::kStagingOffset + (epi_units & 1) * L::kStagingBytes;
           if (leader) tma_wait_read<1>();
@@ -245,6 +280,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             if (p.flags & EPI_BIAS) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] += __bfloat162float(p.bias[min(col0 + i, p.N - 1)]);
+            }
+            if (AUX) {
+              // second operand from the tile TMA staged for this unit (same swizzle as the output tile)
+              const uint8_t* at = smem + L::kAuxOffset + ((aux_units + u) & 1) * L::kStagingBytes;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f[8];
+                mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(at + r * 128 + (((hh * 4 + j) ^ (r & 7)) << 4)), f);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  if (p.flags & EPI_DGELU) v[8 * j + i] *= mb::gelu_tanh_grad(f[i]);
+                  else v[8 * j + i] += f[i];
+                }
+              }
             }
             if ((p.flags & EPI_GELU) && (pass == npass - 1)) {
 #pragma unroll
@@ -263,6 +312,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
           fence_async_smem();
           asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (AUX && leader && u + 2 < units_live) {
+            // every thread has read this unit's operand tile: refill the buffer for the unit after next
+            const uint32_t au = aux_units + u + 2;
+            mbar_expect_tx(&aux_full[au & 1], L::kStagingBytes);
+            tma_load_2d(smem + L::kAuxOffset + (au & 1) * L::kStagingBytes, &tma_aux, &aux_full[au & 1],
+                        n0 + (u + 2) * cols_per_unit, m0);
+          }
           if (leader) {
             const CUtensorMap* dst = (npass == 2 && pass == 0) ? &tma_aux : &tma_c;
             if ((p.flags & EPI_ACCUM) && out_fp32) {
@@ -279,6 +335,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           ++epi_units;
         }
       }
+      aux_units += units_live;
       // accumulator stage read: tell the leader's MMA warp (one arrival per warp)
       tc_fence_before();
       __syncwarp();
@@ -329,12 +386,12 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, ui
 
 int g_sms = 0;
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool AUX>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& tx,
            const PairParams& p, int max_ctas, cudaStream_t stream) {
-  constexpr int smem = L::kTotal + 1024;
+  constexpr int smem = Layout<AUX>::kTotal + 1024;
   static bool configured = false;
-  auto kern = gemm_pair_kernel<A_MN, B_MN>;
+  auto kern = gemm_pair_kernel<A_MN, B_MN, AUX>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
     configured = true;
@@ -359,12 +416,22 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
   return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, tx, p) == cudaSuccess ? 0 : -4;
 }
 
+template <bool AUX>
+int dispatch(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+             const CUtensorMap& tx, const PairParams& p, int max_ctas, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch<false, false, AUX>(ta, tb, tc, tx, p, max_ctas, stream);
+  if (!a_mn && b_mn) return launch<false, true, AUX>(ta, tb, tc, tx, p, max_ctas, stream);
+  if (a_mn && !b_mn) return launch<true, false, AUX>(ta, tb, tc, tx, p, max_ctas, stream);
+  return launch<true, true, AUX>(ta, tb, tc, tx, p, max_ctas, stream);
+}
+
 }  // namespace
 
 MB_API int* mb_status_device_ptr();
 
 // Same contract as mb_gemm_bf16 for the epilogues the TMA-store path covers (bias, GELU with
-// optional pre-activation copy, bf16 or fp32 output, fp32 accumulation).  Returns 1 without
+// optional pre-activation copy, bf16 or fp32 output, fp32 accumulation, and for bf16 output
+// multiplication by gelu'(aux) or addition of aux).  Returns 1 without
 // launching when the arguments need the single-CTA kernel (other epilogue flags, unaligned C,
 // fewer than two 256 x 256 tiles); the caller then uses mb_gemm_bf16.
 MB_API int mb_gemm_pair_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
@@ -375,11 +442,18 @@ MB_API int mb_gemm_pair_bf16(const void* A, const void* B, void* C, int M, int N
     return -1;
   const bool out_fp32 = (flags & EPI_OUT_FP32) != 0;
   const int esz = out_fp32 ? 4 : 2;
-  const int ok_flags = EPI_BIAS | EPI_GELU | EPI_SAVE_PRE | EPI_OUT_FP32 | (out_fp32 ? EPI_ACCUM : 0);
+  const int ok_flags = EPI_BIAS | EPI_GELU | EPI_SAVE_PRE | EPI_OUT_FP32 | (out_fp32 ? EPI_ACCUM : 0) |
+                       (out_fp32 ? 0 : (EPI_DGELU | EPI_RESIDUAL));
   if ((flags & ~ok_flags) || (reinterpret_cast<uintptr_t>(C) & 15) || ((static_cast<long>(ldc) * esz) % 16) ||
       ((flags & EPI_GELU) && out_fp32))
     return 1;
   if ((flags & EPI_SAVE_PRE) && (!aux || (reinterpret_cast<uintptr_t>(aux) & 15) || !(flags & EPI_GELU))) return 1;
+  if (flags & (EPI_DGELU | EPI_RESIDUAL)) {
+    // one second operand only, read with 16-byte loads at row stride ldc
+    if (!aux || (reinterpret_cast<uintptr_t>(aux) & 15) || (ldc & 7) || (flags & (EPI_GELU | EPI_SAVE_PRE)) ||
+        ((flags & EPI_DGELU) && (flags & EPI_RESIDUAL)))
+      return 1;
+  }
   if (!g_sms) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -394,16 +468,17 @@ MB_API int mb_gemm_pair_bf16(const void* A, const void* B, void* C, int M, int N
   ok = ok && (b_mn_major ? make_map(&tb, B, K, N, ldb, 64, BK, false, true)
                          : make_map(&tb, B, N, K, ldb, 64, BNH, false, true));
   ok = ok && make_map(&tc, C, M, N, ldc, out_fp32 ? 32 : 64, BM, out_fp32, false);
-  if (ok && (flags & EPI_SAVE_PRE)) ok = make_map(&tx, aux, M, N, ldc, 64, BM, false, false);
+  const bool has_aux = (flags & (EPI_DGELU | EPI_RESIDUAL)) != 0;
+  if (ok && ((flags & EPI_SAVE_PRE) || has_aux)) ok = make_map(&tx, aux, M, N, ldc, 64, BM, false, false);
   if (!ok) return -2;
   PairParams p;
   p.M = M; p.N = N; p.K = K;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.aux = reinterpret_cast<const __nv_bfloat16*>(aux);
+  p.ldc = ldc;
   p.flags = flags;
   p.alpha = alpha;
   p.status = mb_status_device_ptr();
-  if (!a_mn_major && !b_mn_major) return launch<false, false>(ta, tb, tc, tx, p, max_ctas, stream);
-  if (!a_mn_major && b_mn_major) return launch<false, true>(ta, tb, tc, tx, p, max_ctas, stream);
-  if (a_mn_major && !b_mn_major) return launch<true, false>(ta, tb, tc, tx, p, max_ctas, stream);
-  return launch<true, true>(ta, tb, tc, tx, p, max_ctas, stream);
+  if (has_aux) return dispatch<true>(a_mn_major != 0, b_mn_major != 0, ta, tb, tc, tx, p, max_ctas, stream);
+  return dispatch<false>(a_mn_major != 0, b_mn_major != 0, ta, tb, tc, tx, p, max_ctas, stream);
 }

@@ -392,6 +392,23 @@ class ParallelMLP(nn.Module):
         self.fc2 = RowParallelLinear(intermediate_size, hidden_size, bias=bias2, **fk)
 
     def forward(self, x, residual=None):
+        fc1, fc2 = self.fc1, self.fc2
+        if (residual is None and isinstance(x, torch.Tensor) and F.mlp_gelu_fused_available(x)
+                and not fc1._fused(x) and x.dtype == fc1.weight.dtype):
+            # local compute as one autograd node (GELU's derivative rides on a GEMM epilogue in the
+            # backward pass); the tensor-parallel collectives stay around it
+            pg, ws = fc1.process_group, group_size(fc1.process_group)
+            if fc1.sequence_parallel:
+                x = dist_ops.all_gather(x.reshape(-1, x.shape[-1]), pg)
+            else:
+                x = dist_ops.copy_to_group(x, pg)
+            y = F.mlp_gelu(x, fc1.weight, fc1.bias, fc2.weight, fc2.bias)
+            if ws > 1:
+                if fc2.sequence_parallel:
+                    y = dist_ops.reduce_scatter(y.reshape(-1, y.shape[-1]), pg)
+                else:
+                    y = dist_ops.all_reduce(y, pg)
+            return y
         return self.fc2(self.fc1(x), residual=residual)
 
 

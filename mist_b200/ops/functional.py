@@ -48,6 +48,7 @@ class Settings:
     attn_block_n = 64
     gemm_max_ctas = 0             # >0 leaves SMs free for a concurrent communication kernel
     gemm_pair = True              # large GEMMs on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2)
+    fuse_mlp_gelu = True          # GELU MLP as one autograd node (gelu' folded into a dgrad GEMM epilogue)
     tp_backend = "nccl"           # "nccl" | "fused": sequence-parallel linears on the GEMM+collective kernels
 
 
@@ -210,6 +211,66 @@ def linear(x, weight, bias=None, activation: Optional[str] = None, residual=None
     if _sym(x):
         return _rules().linear(x, weight, bias, activation, residual)
     return _LinearFn.apply(x, weight, bias, activation, residual)
+
+
+class _MlpGeluFn(torch.autograd.Function):
+    """``gelu(x W1^T + b1) W2^T + b2`` as one autograd node, so the backward pass can fold
+    GELU's derivative into the epilogue of the GEMM that produces the gradient of the
+    activations: ``dpre = (dy W2) * gelu'(pre)`` in one kernel instead of a GEMM followed by an
+    elementwise pass over the ``[tokens, ffn]`` tensor (reference: the cuBLASLt ``DGELU_BGRAD``
+    epilogue behind ``bias_act_linear_dgrad_bgrad``, csrc/fused_dense_lib/fused_dense_cuda.cu:
+    407-520, used by mist/modules/fused_dense.py:386-480 ``FusedMLPFunc``)."""
+
+    @staticmethod
+    def forward(ctx, x, w1, b1, w2, b2):
+        xs = x.shape
+        x2 = x.reshape(-1, xs[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        pre = torch.empty(x2.shape[0], w1.shape[0], dtype=x.dtype, device=x.device)
+        act = gemm(x2, w1, bias=b1, aux=pre, flags=EPI_GELU | EPI_SAVE_PRE)
+        y = gemm(act, w2, bias=b2)
+        ctx.save_for_backward(x2, w1, w2, pre, act)
+        ctx.has_b1, ctx.has_b2 = b1 is not None, b2 is not None
+        return y.reshape(*xs[:-1], w2.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w1, w2, pre, act = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+
+        def wgrad(g, inp, weight):
+            bucket = getattr(weight, "grad_bucket", None)
+            if bucket is None:
+                return gemm(g, inp, a_mn=True, b_mn=True)
+            gemm(g, inp, a_mn=True, b_mn=True, out=bucket,
+                 flags=EPI_ACCUM if getattr(weight, "grad_accumulate", False) else 0)
+            weight.grad_accumulate = True
+            return None
+
+        db2 = colsum(dy2) if (ctx.has_b2 and ctx.needs_input_grad[4]) else None
+        dw2 = wgrad(dy2, act, w2) if ctx.needs_input_grad[3] else None
+        dpre = gemm(dy2, w2, b_mn=True, aux=pre, flags=EPI_DGELU)      # (dy W2) * gelu'(pre)
+        db1 = colsum(dpre) if (ctx.has_b1 and ctx.needs_input_grad[2]) else None
+        dw1 = wgrad(dpre, x2, w1) if ctx.needs_input_grad[1] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dpre, w1, b_mn=True).reshape(*dy.shape[:-1], w1.shape[1])
+        return dx, dw1, db1, dw2, db2
+
+
+def mlp_gelu_fused_available(x) -> bool:
+    return (Settings.fuse_mlp_gelu and (not _sym(x)) and use_native(x) and Settings.gemm_backend == "tcgen05"
+            and x.dtype == torch.bfloat16)
+
+
+def mlp_gelu(x, w1, b1, w2, b2):
+    """Two-layer GELU MLP; one fused autograd node on the tcgen05 path, two linears otherwise."""
+    if mlp_gelu_fused_available(x):
+        return _MlpGeluFn.apply(x, w1, b1, w2, b2)
+    return linear(linear(x, w1, b1, activation="gelu"), w2, b2)
 
 
 # ---------------------------------------------------------------- column sum (bias grad)

@@ -93,6 +93,45 @@ def test_gemm_cta_pair_layouts_and_epilogues(a_mn, b_mn, K):
     assert _rel_err(acc, ref2) < 1e-3
 
 
+@pytest.mark.parametrize("M,h,f", [(2304, 2560, 2304), (300, 256, 520)])
+def test_fused_gelu_mlp_matches_reference(M, h, f):
+    """One autograd node for fc1 -> GELU -> fc2; the backward pass multiplies by gelu'(pre) in the
+    epilogue of the dgrad GEMM (CTA-pair kernel for the large case, single-CTA for the small one)."""
+    torch.manual_seed(6)
+    x = (torch.randn(M, h, device=DEV, dtype=torch.bfloat16)).requires_grad_(True)
+    w1 = (torch.randn(f, h, device=DEV, dtype=torch.bfloat16) * 0.03).requires_grad_(True)
+    b1 = (torch.randn(f, device=DEV, dtype=torch.bfloat16) * 0.1).requires_grad_(True)
+    w2 = (torch.randn(h, f, device=DEV, dtype=torch.bfloat16) * 0.03).requires_grad_(True)
+    b2 = (torch.randn(h, device=DEV, dtype=torch.bfloat16) * 0.1).requires_grad_(True)
+    y = F.mlp_gelu(x, w1, b1, w2, b2)
+    g = torch.randn_like(y)
+    grads = torch.autograd.grad(y, (x, w1, b1, w2, b2), g)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (x, w1, b1, w2, b2)]
+    xr, w1r, b1r, w2r, b2r = ref_in
+    yr = torch.nn.functional.gelu(xr @ w1r.t() + b1r, approximate="tanh") @ w2r.t() + b2r
+    grads_r = torch.autograd.grad(yr, ref_in, g.float())
+    assert _rel_err(y, yr) < 1e-2
+    for name, a, b in zip(("dx", "dw1", "db1", "dw2", "db2"), grads, grads_r):
+        assert _rel_err(a, b) < 2e-2, name
+
+
+def test_gemm_cta_pair_residual_epilogue():
+    from mist_b200.ops import native
+    from mist_b200.ops.native import ptr, stream
+    torch.manual_seed(7)
+    M, N, K = 2176, 2624, 320
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    rc = native.kernels().mb_gemm_pair_bf16(ptr(a), ptr(b), ptr(out), M, N, K, K, K, N, 0, 0, F.EPI_RESIDUAL, None,
+                                            ptr(res), 1.0, 0, stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    native.check_status()
+    assert _rel_err(out, a.float() @ b.float().t() + res.float()) < 1e-2
+
+
 def test_linear_autograd_matches_reference():
     torch.manual_seed(2)
     x = torch.randn(4, 128, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
