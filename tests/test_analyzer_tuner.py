@@ -218,3 +218,39 @@ def test_op_database_roundtrip(tmp_path):
     db.add(spec, 1.5e-3, 3e-3)
     db2 = OpDatabase(device="TEST_GPU", root=tmp_path, allow_profile=False)
     assert db2.latency(spec) == (1.5e-3, 3e-3) and est != (1.5e-3, 3e-3)
+
+
+def test_experiment_orchestration_tune_then_analyze(tmp_path):
+    """tune -> analyze for two search spaces without GPUs; the analyzer must reproduce the cost
+    the tuner reported for its best strategy, and an identical solution is not run twice."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "exp"
+    r = subprocess.run([sys.executable, os.path.join(root, "benchmark/mist_b200/experiment/run.py"), "--model",
+                        "gpt2/1.3b", "-m", "2", "--global-batch-size", "8", "--spaces", "mist", "zero1-only",
+                        "--skip-exec", "--out", str(out)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    s = json.load(open(out / "mist" / "summary.json"))
+    assert abs(float(s["tuning_best_cost"]) - float(s["analyzed_total_cost"])) <= 0.02 * float(s["tuning_best_cost"])
+    assert (out / "mist" / "best_config.yaml").exists()
+
+
+def test_prediction_accuracy_report(tmp_path, capsys):
+    import importlib.util
+    import json
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(
+        "acc", os.path.join(root, "benchmark/mist_b200/prediction-accuracy/get_mem_and_latency_accuracy.py"))
+    acc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(acc)
+    for name, pred, meas in (("a", 1.10, 1.00), ("b", 1.98, 2.00)):
+        d = tmp_path / name
+        d.mkdir()
+        json.dump({"analyzed_total_cost": str(pred), "exec_total_cost": str(meas),
+                   "analyzed_stage_peak_memories": "[1100 MB]", "exec_stage_peak_allocated_memories": "[1000 MB]"},
+                  open(d / "summary.json", "w"))
+    acc.main([str(tmp_path)])
+    text = capsys.readouterr().out
+    assert "2 cases" in text and "mean abs rel err 5.50 %" in text and "memory : mean abs rel err 10.00 %" in text
