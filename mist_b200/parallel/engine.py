@@ -33,7 +33,7 @@ from ..utils.logging import record
 from .flat_unit import FlatUnit
 from .state import ParallelState
 
-DEFAULT_HP = dict(lr=1e-5, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, adamw=True)
+DEFAULT_HP = dict(lr=1e-5, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, adamw=True, loss_scale=1.0)
 
 
 class _Marker(torch.autograd.Function):
@@ -98,6 +98,10 @@ class TrainEngine:
         self.strategy = strategy or StageStrategy(1, 1, 1, False, False, False, 0, 0, 0, 0)
         self.G = int(grad_accum_steps)
         self.hp = dict(DEFAULT_HP, **(hp or {}))
+        from ..utils.grad_scaler import ConstantGradScaler
+        # constant loss scale (fp16 runs): the loss is multiplied before the backward pass and the
+        # optimizer kernels divide by it together with the data-parallel / micro-step average
+        self.scaler = ConstantGradScaler(float(self.hp.get("loss_scale", 1.0)))
         self.comm_backend = comm_backend
         self.overlap = overlap
         zero = self.strategy.zero
@@ -385,7 +389,7 @@ class TrainEngine:
                         if (unit.opt_host_numel or unit.weight_split is not None) else None)
                 with record(f"OPT-{unit.name}.step"):
                     unit.optimizer_step(grad, self.hp, self.ps.dp_ag_group,
-                                        grad_divisor=float(self.ps.dp_size * self.G), swap=swap,
+                                        grad_divisor=float(self.ps.dp_size * self.G) * self.scaler.loss_scale, swap=swap,
                                         step_scratch=self._step_scratch)
                 if self.cuda:
                     ev = torch.cuda.Event()
@@ -406,7 +410,7 @@ class TrainEngine:
         loss = self.model(**batch)
         self._wait_bucket(self.pre_unit)
         self._wait_bucket(self.post_unit)
-        loss.backward()
+        self.scaler.scale(loss).backward()
         if self.pre_unit is not None:
             self._unit_backward_done(self.pre_unit)
         return loss.detach()

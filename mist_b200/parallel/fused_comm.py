@@ -102,7 +102,7 @@ class FusedDPComm:
                  ptr(u.exp_avg_sq), ptr(acc), u.shard_numel, self.R, self.me, t["epoch"],
                  int(u.flat_grad.dtype == torch.float32), int(last_micro_step), float(hp["lr"]), float(hp["beta1"]),
                  float(hp["beta2"]), float(hp["eps"]), float(hp["weight_decay"]), max(u.step_count, 1),
-                 1.0 / float(self.R * eng.G), int(hp.get("adamw", True)), self.num_ctas, native.stream())
+                 1.0 / (float(self.R * eng.G) * eng.scaler.loss_scale), int(hp.get("adamw", True)), self.num_ctas, native.stream())
             ev = torch.cuda.Event()
             ev.record()
             if last_micro_step:

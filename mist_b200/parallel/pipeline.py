@@ -142,7 +142,7 @@ class PipelineSchedule:
         self.engine._wait_bucket(self.engine.pre_unit)
         self.engine._wait_bucket(self.engine.post_unit)
         if self.last:
-            out.backward()
+            self.engine.scaler.scale(out).backward()
         else:
             torch.autograd.backward(out, grad)
         if self.engine.pre_unit is not None:

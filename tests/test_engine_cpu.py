@@ -224,3 +224,22 @@ def test_pipeline_1f1b_matches_single_process():
                 idx, tail = rest.split(".", 1)
                 n2 = f"{head}.layers.{int(idx) + 2 * stage}.{tail}"
             assert (final[n2] - p).abs().max().item() < 2e-4, n2
+
+
+def test_constant_loss_scale_does_not_change_the_update():
+    from mist_b200.utils.grad_scaler import ConstantGradScaler
+    cfg, model = _tiny_model()
+    ref = copy.deepcopy(model)
+    a = TrainEngine(model, grad_accum_steps=2, hp=dict(lr=1e-3, loss_scale=256.0))
+    b = TrainEngine(ref, grad_accum_steps=2, hp=dict(lr=1e-3))
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        batches = [prov(2, 32, 256, "cpu", seed=7 * it + k) for k in range(2)]
+        la, lb = a.train_step(batches), b.train_step(batches)
+        assert abs(la.item() - lb.item()) < 1e-5            # reported loss is the unscaled one
+    diff = max((p - q).abs().max().item() for p, q in zip(model.parameters(), ref.parameters()))
+    assert diff < 1e-5
+    s = ConstantGradScaler(4.0)
+    g = [torch.full((3,), 8.0), torch.tensor([float("inf")])]
+    assert s.unscale_(g[:1]) is False and torch.allclose(g[0], torch.full((3,), 2.0))
+    assert s.unscale_(g[1:]) is True
