@@ -92,3 +92,14 @@ def test_memory_snapshot_summary():
     assert r["reserved"] == 110 and r["allocated"] == 70 and r["largest_free_block"] == 40
     assert r["by_kind"]["large"] == (1, 100, 60)
     assert r["top_blocks"][0][0] == 60 and "engine.py:12" in r["top_blocks"][0][2]
+
+
+def test_merge_calibration_records(tmp_path):
+    import json
+    from mist_b200.tools.merge_json_results import main
+    a = [{"intra": 2, "inter": 1, "g2g_gbytes": 0.5, "c2g_gbytes": 0.0, "g2c_gbytes": 0.0, "C": 0.0, "latency": 1.0}]
+    b = [dict(a[0], latency=2.0), dict(a[0], intra=8)]
+    for name, recs in (("a.json", a), ("b.json", b)):
+        json.dump(recs, open(tmp_path / name, "w"))
+    out = main([str(tmp_path / "a.json"), str(tmp_path / "b.json"), "-o", str(tmp_path / "m.json")])
+    assert len(out) == 2 and sorted(r["latency"] for r in out) == [2.0, 2.0]
