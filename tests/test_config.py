@@ -102,4 +102,4 @@ def test_merge_calibration_records(tmp_path):
     for name, recs in (("a.json", a), ("b.json", b)):
         json.dump(recs, open(tmp_path / name, "w"))
     out = main([str(tmp_path / "a.json"), str(tmp_path / "b.json"), "-o", str(tmp_path / "m.json")])
-    assert len(out) == 2 and sorted(r["latency"] for r in out) == [2.0, 2.0]
+    assert len(out) == 2 and {(r["intra"], r["latency"]) for r in out} == {(2, 2.0), (8, 1.0)}
