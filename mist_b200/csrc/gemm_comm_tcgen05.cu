@@ -29,7 +29,7 @@
 // Reference equivalents: all_gather + F.linear and F.linear + reduce_scatter in
 // mist/modules/fused_dense.py:54-75 and :320-327 (NCCL + cuBLAS, overlapped at best with a
 // weight cast), disabled in the reference's models (mist/model/transformer.py:477-479).
-#include "sm100.cuh"
+#include "sm100_pair.cuh"
 #include <string.h>
 
 using namespace sm100;
@@ -39,7 +39,6 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
 constexpr int kThreads = 192;
 constexpr int kMaxRanks = 8;
 constexpr int kCopyBufs = 11;   // 11 x 16 KB of the 192 KB stage area in flight per gather CTA
@@ -72,14 +71,20 @@ struct CommParams {
   unsigned long long wait_ns;
 };
 
+// PAIR: two CTAs of a cluster share each 256 x 256 tile (tcgen05 cta_group::2): a CTA stages its own
+// 128 rows of A and 128 of the 256 rows of B, so a stage is 32 KB and six fit where the single-CTA
+// kernel has four of 48 KB.
+template <bool PAIR>
 struct Smem {
+  static constexpr int kStages = PAIR ? 6 : 4;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;
   static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBBytes = kBRows * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStagingOffset = STAGES * kStageBytes;
+  static constexpr int kStagingOffset = kStages * kStageBytes;
   static constexpr int kStagingBytes = BM * 128;
   static constexpr int kBarOffset = kStagingOffset + 2 * kStagingBytes;
-  static constexpr int kNumBars = 2 * STAGES + 4 + kCopyBufs;
+  static constexpr int kNumBars = 2 * kStages + 4 + kCopyBufs;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
 };
 
@@ -148,7 +153,7 @@ __device__ bool wait_range(const CommParams& p, unsigned long long lo, unsigned 
   return true;
 }
 
-template <bool B_MN>
+template <bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ CUtensorMap acc0,
@@ -156,7 +161,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                  const __grid_constant__ CUtensorMap acc3, const __grid_constant__ CUtensorMap acc4,
                  const __grid_constant__ CUtensorMap acc5, const __grid_constant__ CUtensorMap acc6,
                  const __grid_constant__ CUtensorMap acc7, const CommParams p) {
-  using L = Smem;
+  using L = Smem<PAIR>;
+  constexpr int STAGES = L::kStages;
+  constexpr int TM = PAIR ? 2 * BM : BM;          // rows of an output tile (per CTA always BM)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -172,14 +179,19 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int R = p.nranks;
   int* my_flags = p.flags[p.me];
   const bool gathers = (p.mode == MODE_AG) || (p.mode == MODE_AGW);
-  const int n_compute = gridDim.x - (gathers ? p.n_gather : 0);
+  const int n_compute = gridDim.x - (gathers ? p.n_gather : 0);   // CTAs; even when PAIR
   const bool is_gather = gathers && (static_cast<int>(blockIdx.x) >= n_compute);
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;            // CTA of the pair; 0 leads
+  const bool leader_cta = (rank == 0);
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);   // tile loop index
+  const int n_workers = PAIR ? (n_compute >> 1) : n_compute;
 
-  const int num_m = (p.M + BM - 1) / BM;
+  const int num_m = (p.M + TM - 1) / TM;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int m_tiles_per_rank = p.rows_per_rank / BM;
+  const int m_tiles_per_rank = p.rows_per_rank / TM;
+  const int ag_chunks_per_rank = p.rows_per_rank / BM;   // all-gather flags: one per 128-row block
 
   // Tile order: all column tiles of one row block, row blocks starting with the locally owned
   // ones (AG: their data is there at once) / ending with them (RS: remote adds go out first).
@@ -187,14 +199,14 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (p.mode == MODE_AGW) {
       // all row tiles of one column tile, column tiles in the order their weights arrive
       int nt = t / num_m, mt = t - nt * num_m;
-      m0 = mt * BM;
+      m0 = mt * TM + static_cast<int>(rank) * BM;
       n0 = ((nt + p.n_shift) % num_n) * BN;
       return;
     }
     int mt = t / num_n, nt = t - mt * num_n;
     int shift = (p.mode == MODE_AG) ? p.me : (p.me + 1) % R;
     int mt_rot = (mt + shift * m_tiles_per_rank) % num_m;
-    m0 = mt_rot * BM;
+    m0 = mt_rot * TM + static_cast<int>(rank) * BM;      // this CTA's rows
     n0 = nt * BN;
   };
 
@@ -205,17 +217,23 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 128);
+      mbar_init(&tempty_bar[a], PAIR ? 8 : 128);   // PAIR: one arrival per epilogue warp of both CTAs
     }
     for (int b = 0; b < kCopyBufs; ++b) mbar_init(&copy_bar[b], 1);
     fence_barrier_init();
   }
   if (warp == 2 && !is_gather) {
-    tmem_alloc(tmem_slot, 2 * BN);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, 2 * BN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 2 * BN);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything is signalled on them
   tc_fence_after();
   const uint32_t tmem_base = is_gather ? 0u : *tmem_slot;
 
@@ -279,7 +297,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       if (p.mode == MODE_AG) {
         const size_t row_bytes = static_cast<size_t>(p.K) * 2;
         const size_t chunk_bytes = static_cast<size_t>(BM) * row_bytes;    // one flag per 128-row block
-        const int chunks_per_rank = m_tiles_per_rank;
+        const int chunks_per_rank = ag_chunks_per_rank;
         int work = 0;
         for (int k = 0; k < R - 1 && ok; ++k) {
           const int r = (p.me + 1 + k) % R;
@@ -318,20 +336,22 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t armed[STAGES];
       for (int s = 0; s < STAGES; ++s) armed[s] = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += n_compute) {
+      for (int t = worker; t < num_tiles && ok; t += n_workers) {
         int m0, n0;
         tile_coords(t, m0, n0);
         if (p.mode == MODE_AG) {
           const int owner = m0 / p.rows_per_rank;
           if (owner != p.me) {
             const int c = (m0 - owner * p.rows_per_rank) / BM;
-            ok = wait_flag(p.chunk_flags + owner * m_tiles_per_rank + c, p.epoch, false, p.wait_ns, p.status);
+            ok = wait_flag(p.chunk_flags + owner * ag_chunks_per_rank + c, p.epoch, false, p.wait_ns, p.status);
             if (!ok) break;
             fence_proxy_async_all();   // the chunk was written through the async proxy of another SM
           }
         } else if (p.mode == MODE_AGW) {
-          const unsigned long long lo = p.b_off + static_cast<unsigned long long>(n0) * p.K * 2;
-          const unsigned long long hi = p.b_off + static_cast<unsigned long long>(min(n0 + BN, p.N)) * p.K * 2;
+          const int nlo = PAIR ? n0 + static_cast<int>(rank) * (BN / 2) : n0;       // this CTA's rows of W
+          const int nhi = min(PAIR ? nlo + BN / 2 : n0 + BN, p.N);
+          const unsigned long long lo = p.b_off + static_cast<unsigned long long>(min(nlo, p.N)) * p.K * 2;
+          const unsigned long long hi = p.b_off + static_cast<unsigned long long>(nhi) * p.K * 2;
           ok = wait_range(p, lo, hi);
           if (!ok) break;
           fence_proxy_async_all();
@@ -346,15 +366,32 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
           uint8_t* sa = smem + s * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
-          mbar_expect_tx(&full_bar[s], L::kStageBytes);
-          armed[s]++;
-          tma_load_2d(sa, &tma_a, &full_bar[s], kb * BK, m0);
-          if (!B_MN) {
-            tma_load_2d(sb, &tma_b, &full_bar[s], kb * BK, n0);
-          } else {
+          if (PAIR) {
+            // both CTAs' bytes are counted on the leader's barrier; each CTA loads its own halves
+            if (leader_cta) {
+              mbar_expect_tx(&full_bar[s], 2 * L::kStageBytes);
+              armed[s]++;
+            }
+            const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
+            const int nb0 = n0 + static_cast<int>(rank) * (BN / 2);
+            tma_load_2d_pair(sa, &tma_a, bar, kb * BK, m0);
+            if (!B_MN) {
+              tma_load_2d_pair(sb, &tma_b, bar, kb * BK, nb0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (BK * 128), &tma_b, &full_bar[s], n0 + 64 * j, kb * BK);
+              for (int j = 0; j < BN / 128; ++j) tma_load_2d_pair(sb + j * (BK * 128), &tma_b, bar, nb0 + 64 * j, kb * BK);
+            }
+          } else {
+            mbar_expect_tx(&full_bar[s], L::kStageBytes);
+            armed[s]++;
+            tma_load_2d(sa, &tma_a, &full_bar[s], kb * BK, m0);
+            if (!B_MN) {
+              tma_load_2d(sb, &tma_b, &full_bar[s], kb * BK, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * (BK * 128), &tma_b, &full_bar[s], n0 + 64 * j, kb * BK);
+            }
           }
         }
       }
@@ -364,10 +401,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    constexpr uint32_t idesc = make_idesc_bf16(BM, BN, 0, B_MN ? 1 : 0);
+    constexpr uint32_t idesc = make_idesc_bf16(TM, BN, 0, B_MN ? 1 : 0);
     uint32_t it = 0, tcount = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += n_compute, ++tcount) {
+    bool ok = leader_cta;          // PAIR: only the leader CTA issues MMAs (for both CTAs' accumulators)
+    for (int t = worker; t < num_tiles && ok; t += n_workers, ++tcount) {
       int acc = tcount & 1;
       uint32_t acc_ph = (tcount >> 1) & 1;
       if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1)) {
@@ -394,13 +431,18 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             uint64_t ad = make_smem_desc_sw128(sa + k * 32, 16, 1024);
             uint64_t bd = B_MN ? make_smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
                                : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            mma_f16_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR) mma_f16_ss_pair(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            else mma_f16_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          mma_commit(&empty_bar[s]);
+          if (PAIR) mma_commit_pair(&empty_bar[s]);   // frees the stage in both CTAs
+          else mma_commit(&empty_bar[s]);
         }
         __syncwarp();
       }
-      if (ok && lane == 0) mma_commit(&tfull_bar[acc]);
+      if (ok && lane == 0) {
+        if (PAIR) mma_commit_pair(&tfull_bar[acc]);
+        else mma_commit(&tfull_bar[acc]);
+      }
       __syncwarp();
     }
   } else {
@@ -430,7 +472,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       ok = peers_ok_s != 0;
     }
     const CUtensorMap* acc_maps[kMaxRanks] = {&acc0, &acc1, &acc2, &acc3, &acc4, &acc5, &acc6, &acc7};
-    for (int t = blockIdx.x; t < num_tiles && ok; t += n_compute, ++tcount) {
+    for (int t = worker; t < num_tiles && ok; t += n_workers, ++tcount) {
       int m0, n0;
       tile_coords(t, m0, n0);
       int acc = tcount & 1;
@@ -493,7 +535,12 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         ++epi_units;
       }
       tc_fence_before();
-      mbar_arrive(&tempty_bar[acc]);
+      if (PAIR) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      } else {
+        mbar_arrive(&tempty_bar[acc]);
+      }
     }
     if (leader) tma_wait_all<0>();
   }
@@ -502,9 +549,11 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   __threadfence_system();
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA leaves while the other may still use its memory or barriers
   if (warp == 2 && !is_gather) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
   }
   __shared__ int last_s;
   if (threadIdx.x == 0) {
@@ -554,24 +603,57 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, ui
 }
 
 int g_sms = 0;
-bool g_cfg[2] = {false, false};
 
-int launch(bool b_mn, int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb,
-           const CUtensorMap& tc, const CUtensorMap* acc, const CommParams& p) {
-  const int smem = Smem::kTotal + 1024;
-  if (!g_cfg[b_mn]) {
-    cudaError_t e = b_mn ? cudaFuncSetAttribute(gemm_comm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)
-                         : cudaFuncSetAttribute(gemm_comm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return -3;
-    g_cfg[b_mn] = true;
+int g_pair = 1;   // CTA pairs (cta_group::2) when the shape allows; mb_gemm_comm_set_pair switches it
+int g_last_pair = 0;   // whether the most recent launch ran on pairs (tests ask)
+
+template <bool B_MN, bool PAIR>
+int launch_t(int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+             const CUtensorMap* acc, const CommParams& p) {
+  constexpr int smem = Smem<PAIR>::kTotal + 1024;
+  static bool configured = false;
+  auto kern = gemm_comm_kernel<B_MN, PAIR>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
+    configured = true;
   }
-  if (b_mn)
-    gemm_comm_kernel<true><<<grid, kThreads, smem, stream>>>(ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4],
-                                                             acc[5], acc[6], acc[7], p);
-  else
-    gemm_comm_kernel<false><<<grid, kThreads, smem, stream>>>(ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4],
-                                                              acc[5], acc[6], acc[7], p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, acc[0], acc[1], acc[2], acc[3], acc[4], acc[5], acc[6], acc[7],
+                            p) == cudaSuccess ? 0 : -4;
+}
+
+int launch(bool b_mn, bool pair, int grid, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb,
+           const CUtensorMap& tc, const CUtensorMap* acc, const CommParams& p) {
+  g_last_pair = pair ? 1 : 0;
+  if (pair) return b_mn ? launch_t<true, true>(grid, stream, ta, tb, tc, acc, p)
+                        : launch_t<false, true>(grid, stream, ta, tb, tc, acc, p);
+  return b_mn ? launch_t<true, false>(grid, stream, ta, tb, tc, acc, p)
+              : launch_t<false, false>(grid, stream, ta, tb, tc, acc, p);
+}
+
+// Grid for one launch: `n_gather` gather CTAs after the compute CTAs; with pairs both counts are even.
+int plan_grid(bool pair, long tiles, int& n_gather) {
+  if (pair) {
+    n_gather = (n_gather + 1) & ~1;
+    int compute = (g_sms - n_gather) & ~1;
+    if (compute > 2 * tiles) compute = static_cast<int>(2 * tiles);
+    return compute;
+  }
+  int compute = g_sms - n_gather;
+  if (compute > tiles) compute = static_cast<int>(tiles);
+  return compute;
 }
 
 }  // namespace
@@ -620,9 +702,12 @@ MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void
   CUtensorMap ta, tb, tc, acc[kMaxRanks];
   memset(&tc, 0, sizeof(tc));
   memset(acc, 0, sizeof(acc));
+  // pairs need whole 256-row tiles per rank and enough of them to occupy the machine
+  const bool pair = g_pair && (rows_per_rank % (2 * BM) == 0) &&
+                    (static_cast<long>(M / (2 * BM)) * ((N + BN - 1) / BN) >= (g_sms - p.n_gather) / 2);
   if (!make_map(&ta, a_base, M, K, K, 64, BM, false)) return -2;
   if (!b_mn) {
-    if (!make_map(&tb, B, N, K, ldb, 64, BN, false)) return -2;
+    if (!make_map(&tb, B, N, K, ldb, 64, pair ? BN / 2 : BN, false)) return -2;
   } else {
     if (!make_map(&tb, B, K, N, ldb, 64, BK, false)) return -2;
   }
@@ -632,11 +717,14 @@ MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void
     for (int r = 0; r < nranks; ++r)
       if (!make_map(&acc[r], acc_ptrs[r], rows_per_rank, N, N, acc_bf16 ? 64 : 32, BM, !acc_bf16)) return -2;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  int compute = g_sms - p.n_gather;
-  if (compute > tiles) compute = tiles;
-  return launch(b_mn != 0, compute + p.n_gather, stream, ta, tb, tc, acc, p);
+  const long tiles = static_cast<long>((M + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM)) * ((N + BN - 1) / BN);
+  const int compute = plan_grid(pair, tiles, p.n_gather);
+  return launch(b_mn != 0, pair, compute + p.n_gather, stream, ta, tb, tc, acc, p);
 }
+
+// 1 (default): the fused kernels run on CTA pairs when the shape allows; 0: always single CTAs.
+MB_API void mb_gemm_comm_set_pair(int on) { g_pair = on ? 1 : 0; }
+MB_API int mb_gemm_comm_last_pair(void) { return g_last_pair; }
 
 // Weight all-gather fused into the GEMM that consumes the first weights of a ZeRO-3 block.
 //   w_ptrs[r]: rank r's symmetric flat bf16 parameter buffer of R * shard_elems elements; rank r's own
@@ -699,11 +787,11 @@ MB_API int mb_gemm_param_gather(void* const* w_ptrs, const void* A, void* C, voi
   }
   CUtensorMap ta, tb, tc, acc[kMaxRanks];
   memset(acc, 0, sizeof(acc));
+  const bool pair = g_pair && (static_cast<long>((M + 2 * BM - 1) / (2 * BM)) * num_n >= (g_sms - p.n_gather) / 2);
   if (!make_map(&ta, A, M, K, K, 64, BM, false)) return -2;
-  if (!make_map(&tb, p.a_local + p.b_off, N, K, K, 64, BN, false)) return -2;
+  if (!make_map(&tb, p.a_local + p.b_off, N, K, K, 64, pair ? BN / 2 : BN, false)) return -2;
   if (!make_map(&tc, C, M, N, ldc, 64, BM, false)) return -2;
-  const int tiles = ((M + BM - 1) / BM) * num_n;
-  int compute = g_sms - p.n_gather;
-  if (compute > tiles) compute = tiles;
-  return launch(false, compute + p.n_gather, stream, ta, tb, tc, acc, p);
+  const long tiles = static_cast<long>((M + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM)) * num_n;
+  const int compute = plan_grid(pair, tiles, p.n_gather);
+  return launch(false, pair, compute + p.n_gather, stream, ta, tb, tc, acc, p);
 }

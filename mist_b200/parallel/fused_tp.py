@@ -32,6 +32,9 @@ native.register_signature(
     [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
      C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p])
 
+native.register_signature("mb_gemm_comm_set_pair", [C.c_int], None)
+native.register_signature("mb_gemm_comm_last_pair", [], C.c_int)
+
 MODE_AG, MODE_RS = 1, 2
 FLAG_INTS = 32
 

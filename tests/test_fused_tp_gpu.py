@@ -46,6 +46,48 @@ def test_emulated_two_ranks_one_gpu(b_mn):
     assert _rel(out, ref[:rows]) < 1e-2
 
 
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("pair", [1, 0])
+def test_emulated_two_ranks_large_tiles(b_mn, pair):
+    """Shapes big enough for the CTA-pair variant (256 x 256 tiles, two CTAs per tile); with
+    ``pair = 0`` the same shapes run on single CTAs."""
+    from mist_b200.ops import native
+    from mist_b200.parallel import fused_tp
+    lib = native.kernels()
+    lib.mb_gemm_comm_set_pair(pair)
+    try:
+        torch.manual_seed(1)
+        ctx = fused_tp.FusedTPContext(None, 0, emulate_ranks=2)
+        rows, K, N = 2048, 320, 1280
+        x_shard = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16)
+        peer_rows = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16)
+        w = (torch.randn(K, N, device="cuda", dtype=torch.bfloat16) if b_mn
+             else torch.randn(N, K, device="cuda", dtype=torch.bfloat16)) * 0.05
+        bias = None if b_mn else torch.randn(N, device="cuda", dtype=torch.bfloat16)
+        ctx.gathered(2 * rows, K, "p")
+        ctx._keep[-1].view(2 * rows, K)[rows:].copy_(peer_rows)
+        for _ in range(2):                      # second launch: epochs advance
+            y, gathered = fused_tp._ag_gemm(ctx, x_shard, w, bias, b_mn, "p")
+            torch.cuda.synchronize()
+            native.check_status()
+            assert lib.mb_gemm_comm_last_pair() == pair
+            full = torch.cat([x_shard, peer_rows])
+            ref = full.float() @ (w.float() if b_mn else w.float().t())
+            if bias is not None:
+                ref = ref + bias.float()
+            assert _rel(gathered, full) == 0.0
+            assert _rel(y, ref) < 1e-2
+        x = torch.randn(2 * rows, K, device="cuda", dtype=torch.bfloat16)
+        out = fused_tp._gemm_rs(ctx, x, w, b_mn)
+        torch.cuda.synchronize()
+        native.check_status()
+        assert lib.mb_gemm_comm_last_pair() == pair
+        ref = x.float() @ (w.float() if b_mn else w.float().t())
+        assert _rel(out, ref[:rows]) < 1e-2
+    finally:
+        lib.mb_gemm_comm_set_pair(1)
+
+
 def _worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")

@@ -52,6 +52,32 @@ def test_emulated_ranks_one_gpu(ranks, use_bias):
         assert _rel(y, ref) < 1e-2
 
 
+def test_emulated_ranks_large_tiles_on_cta_pairs():
+    """A block big enough for the CTA-pair variant of the weight-gathering GEMM."""
+    from mist_b200.ops import native
+    from mist_b200.parallel import fused_tp   # noqa: F401  (declares the pair switch symbols)
+    from mist_b200.parallel.fused_zero3 import ParamGatherContext
+    torch.manual_seed(3)
+    ranks, h, ffn, M = 2, 768, 1024, 2048
+    offs, numel = _layout(h, ffn)
+    padded = (numel + 128 * ranks - 1) // (128 * ranks) * (128 * ranks)
+    full = torch.randn(padded, device="cuda", dtype=torch.bfloat16) * 0.05
+    ctx = ParamGatherContext(None, padded, emulate_ranks=ranks, n_gather=4, chunk_bytes=256 << 10)
+    sh = ctx.shard_numel
+    for r, t in enumerate(ctx.slots[0][2]):
+        t.fill_(float("nan"))
+        t[r * sh:(r + 1) * sh].copy_(full[r * sh:(r + 1) * sh])
+    x = torch.randn(M, h, device="cuda", dtype=torch.bfloat16)
+    y = ctx.gather_linear(0, x, offs["w_qkv"], 3 * h, h, offs["b_qkv"])
+    torch.cuda.synchronize()
+    native.check_status()
+    assert native.kernels().mb_gemm_comm_last_pair() == 1
+    w = full[offs["w_qkv"]: offs["w_qkv"] + 3 * h * h].view(3 * h, h)
+    ref = x.float() @ w.float().t() + full[offs["b_qkv"]: offs["b_qkv"] + 3 * h].float()
+    assert torch.equal(ctx.slot_tensor(0), full)
+    assert _rel(y, ref) < 1e-2
+
+
 def _worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
