@@ -146,7 +146,10 @@ def main():
     ]
     if args.layers:
         overrides += [f"model.num_hidden_layers={layers}", f"strategy.layer_partitions=[{layers}]"]
-    session = build_training("config", overrides, comm_backend=args.comm_backend, seed=1234)
+    # data-parallel gradient path: the hand-written NVLink kernel (reduce-scatter + Adam + weight write-back
+    # in one launch per block) unless --comm-backend nccl asks for the library collectives
+    comm_backend = args.comm_backend or ("fused" if world > 1 else "nccl")
+    session = build_training("config", overrides, comm_backend=comm_backend, seed=1234)
     seq, vocab = MODEL["seq"], MODEL["vocab"]
     tokens_per_step = mb * seq * world
 
