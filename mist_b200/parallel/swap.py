@@ -10,6 +10,7 @@ buffer pools mist/re_swap_manager/mem_buffer_pool.py:60-195).
 """
 from __future__ import annotations
 
+import weakref
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -240,6 +241,13 @@ class ActivationSwapper:
         if not (isinstance(obj, tuple) and len(obj) == 2 and obj[0] == "swapped"):
             return obj
         h = obj[1]
+        if h["host"] is None and h["gpu"] is None:
+            # unpacked before (e.g. a second backward through a retained graph): hand out the same
+            # tensor while it is alive
+            prev = h["weak"]() if h.get("weak") is not None else None
+            if prev is None:
+                raise RuntimeError("a swapped activation was requested again after its buffers were recycled")
+            return prev
         self._fetch(h)
         if h["event"] is not None:
             torch.cuda.current_stream().wait_event(h["event"])
@@ -249,6 +257,7 @@ class ActivationSwapper:
         if h["host"] is not None:     # the pinned buffer returns to the pool with the event that frees it
             self._pool.setdefault((tuple(h["shape"]), h["dtype"]), []).append((h["host"], h["event"]))
             h["host"] = None
+        h["weak"] = weakref.ref(out)
         return out
 
     def prefetch(self, scope):
