@@ -138,8 +138,9 @@ class RowParallelLinear(FusedDense):
         local_in = dist_ops.dim_for_rank(in_features, ws, rk, multiple_of)
         super().__init__(local_in, out_features, bias=bias and rk == 0, device=device, dtype=dtype)
         self.process_group, self.sequence_parallel = process_group, sequence_parallel
-        if self.bias is not None:
-            self.bias._sequence_parallel = sequence_parallel and ws > 1
+        # the bias lives on the first rank only and its gradient there is already complete (the
+        # backward pass of the reduce-scatter gathers the full output gradient), so it takes no
+        # part in the tensor-parallel gradient sum
 
     def forward(self, x, residual=None):
         ws = group_size(self.process_group)
@@ -180,6 +181,12 @@ class VocabParallelEmbedding(nn.Module):
                                     if max_position_embeddings > 0 else None)
         self.tokentype_embeddings = (nn.Embedding(num_tokentypes, hidden_size, device=device, dtype=dtype)
                                      if num_tokentypes > 0 else None)
+        # position / token-type tables are replicated but only the first rank adds them (before the
+        # all-reduce or reduce-scatter), so only it sees their gradient: the engine sums these
+        # gradients over the tensor-parallel group to keep the replicas identical
+        for emb in (self.position_embeddings, self.tokentype_embeddings):
+            if emb is not None and ws > 1:
+                emb.weight._tp_partial_grad = True
         self.reset_parameters()
 
     def reset_parameters(self, std=0.02):

@@ -145,6 +145,18 @@ class TrainEngine:
                 self.units.append(u)
         for stack in self.stacks:
             stack.gradient_checkpointing = min(int(ckpt_layers), len(stack.layers))
+        # Parameters that are replicated over the tensor-parallel group but whose gradient each rank
+        # only computes in part: norm weights inside the sequence-sharded region (a rank sees its
+        # tokens only) and the position / token-type tables (only the first rank adds them).  Their
+        # bucket slices are summed over the group before the data-parallel reduction
+        # (reference: allreduce_sequence_parallel_grad, mist/distributed/op.py:162-172).
+        sp_on = bool(getattr(lm, "sequence_parallel", False))
+        for u in self.units:
+            u.tp_sum_slices = []
+            if self.ps.tp_size > 1:
+                for p, o in zip(u.params, u.offsets):
+                    if getattr(p, "_tp_partial_grad", False) or (sp_on and getattr(p, "_sequence_parallel", False)):
+                        u.tp_sum_slices.append((o, p.numel()))
 
         # -------------------------------------------------------- buckets, state, streams
         from .swap import ActivationSwapper, SwapStreams
@@ -375,9 +387,23 @@ class TrainEngine:
             self._ring_free[slot] = ev
         unit.ring_slot = None
 
+    def _tp_sum_partial_grads(self, unit: FlatUnit):
+        """Sums the bucket slices of tensor-parallel-replicated parameters with partial gradients."""
+        g = unit.flat_grad
+        parts = [g[o:o + n] for o, n in unit.tp_sum_slices]
+        flat = torch.cat([t.float() for t in parts]) if len(parts) > 1 else parts[0].float()
+        dist.all_reduce(flat, group=self.ps.tp_group)
+        off = 0
+        for t in parts:
+            t.copy_(flat[off:off + t.numel()])
+            off += t.numel()
+
     def _unit_backward_done(self, unit: FlatUnit):
         last = self._micro == self.G - 1
         unit.collect_autograd_grads()
+        if unit.tp_sum_slices and (last or unit.zero >= ZeroLevel.OPT_GRAD):
+            with self._on_comm():
+                self._tp_sum_partial_grads(unit)
         if self.fused is not None and self.fused.handles(unit) and not unit.opt_host_numel:
             self.fused.reduce_and_step(unit, last)
             return

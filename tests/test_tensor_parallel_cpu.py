@@ -1,0 +1,96 @@
+"""Tensor parallelism (with and without sequence parallelism) on two gloo ranks against a
+single-process model with the same weights: losses of two training steps and the updated
+weights must agree.  The single-process weights are cut into each rank's slices the way the
+modules shard them (heads for the fused QKV projection, matching gate / up halves for the gated
+MLP, rows or columns for the other linears, vocabulary rows for embedding and head)."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mist_b200.config import load_config
+from mist_b200.models.provider import base_model_provider, get_inputs_provider
+
+TINY = ["model.num_hidden_layers=2", "model.hidden_size=64", "model.intermediate_size=128",
+        "model.num_attention_heads=4", "training.max_sequence_length=32", "model.vocab_size=256",
+        "strategy.layer_partitions=[2]", "training.params_dtype=float32", "hardware.num_gpus_per_node=2",
+        "training.global_batch_size=4", "strategy.device_assignment=[[1,2]]", "strategy.gradient_checkpointing=[1]",
+        "strategy.gradient_accumulation_steps=2", "strategy.stage_strategies=[[2,1,2,0,0,0,0,0,0,0]]",
+        "strategy.pre_post_strategy_array=[2,1,2,0,0,0,0,0,0,0]"]
+
+
+def shard_like(name: str, full: torch.Tensor, rank: int, world: int, heads: int) -> torch.Tensor:
+    """The slice of a single-process parameter that tensor-parallel rank ``rank`` holds."""
+    if "Wqkv" in name:
+        d = full.shape[0] // (3 * heads)
+        lh = heads // world
+        v = full.view(3, heads, d, *full.shape[1:])[:, rank * lh:(rank + 1) * lh]
+        return v.reshape(3 * lh * d, *full.shape[1:])
+    if "mlp.fc1" in name and full.shape[0] == 256:            # gated MLP: [gate | up]
+        f = full.shape[0] // 2
+        lf = f // world
+        return full.view(2, f, *full.shape[1:])[:, rank * lf:(rank + 1) * lf].reshape(2 * lf, *full.shape[1:])
+    if any(k in name for k in ("mlp.fc1", "word_embeddings", "lm_head.proj")):
+        return full.chunk(world, dim=0)[rank]
+    if any(k in name for k in ("out_proj.weight", "mlp.fc2.weight")):
+        return full.chunk(world, dim=1)[rank]
+    return full                                                # norms, position embeddings, row-parallel biases
+
+
+def _worker(rank, world, port, exp, sp, ref_state, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        cfg, _ = load_config("config", [f"experiment={exp}"] + TINY + [f"sequence_parallel={'true' if sp else 'false'}"],
+                             check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        assert sess.ps.tp_size == 2
+        with torch.no_grad():
+            for n, p in sess.model.named_parameters():
+                p.copy_(shard_like(n, ref_state[n], rank, world, 4))
+        for u in sess.engine.units:                             # optimizer state follows the new weights
+            u.master.copy_(u.flat_param.float())
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            b = prov(4, 32, 256, "cpu", seed=50 + it)
+            losses.append(float(sess.step_on_device(b["input_ids"], b["labels"])))
+        sess.finish()
+        ret[rank] = (losses, {n: p.detach().clone() for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("exp", ["gpt2-1.3b", "llama-350m"])
+@pytest.mark.parametrize("sp", [False, True])
+def test_tp2_matches_single_process(exp, sp):
+    cfg, _ = load_config("config", [f"experiment={exp}"] + TINY[:8], check_world_size=False)
+    torch.manual_seed(3)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+    ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 37500 + (os.getpid() + hash((exp, sp))) % 2000
+    mp.spawn(_worker, args=(2, port, exp, sp, ref_state, ret), nprocs=2, join=True)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=50 + it)
+        opt.zero_grad()
+        tot = 0.0
+        for k in range(2):                                       # two micro batches of two sequences
+            mbatch = {key: v[2 * k: 2 * k + 2] for key, v in b.items()}
+            l = ref(**mbatch) / 2
+            l.backward()
+            tot += l.item()
+        opt.step()
+        for r in range(2):
+            assert abs(ret[r][0][it] - tot) < 2e-4, (r, it, ret[r][0], tot)
+    new_state = dict(ref.named_parameters())
+    for r in range(2):
+        for n, p in ret[r][1].items():
+            want = shard_like(n, new_state[n].detach(), r, 2, 4)
+            assert (p - want).abs().max().item() < 2e-4, (r, n)
