@@ -187,12 +187,17 @@ class PipelineSchedule:
                 r.wait()
 
         def assemble(parts):
+            """Concatenates batch slices in slice order.  Several peers may return the same slice
+            (the tensor-parallel ranks of the next stage all hold the gradient of what this rank
+            sent them): one copy per slice is kept."""
             if not parts:
                 return None
-            if len(parts) == 1:
-                return parts[0][1]
-            parts.sort(key=lambda x: x[0].shard_idx)
-            return torch.cat([b for _, b in parts], dim=0)
+            by_slice = {}
+            for info, buf in parts:
+                by_slice.setdefault(info.shard_idx if info.is_sharded else 0, buf)
+            if len(by_slice) == 1:
+                return next(iter(by_slice.values()))
+            return torch.cat([by_slice[k] for k in sorted(by_slice)], dim=0)
 
         return assemble(slots.get("fwd", [])), assemble(slots.get("bwd", []))
 

@@ -94,3 +94,78 @@ def test_tp2_matches_single_process(exp, sp):
         for n, p in ret[r][1].items():
             want = shard_like(n, new_state[n].detach(), r, 2, 4)
             assert (p - want).abs().max().item() < 2e-4, (r, n)
+
+
+def _hetero_worker(rank, world, port, ref_state, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY[:8] + [
+            "hardware.num_gpus_per_node=4", "training.global_batch_size=4", "strategy.layer_partitions=[1,1]",
+            "strategy.device_assignment=[[1,2],[1,2]]", "strategy.gradient_checkpointing=[0,1]",
+            "strategy.gradient_accumulation_steps=2",
+            "strategy.stage_strategies=[[1,2,1,0,0,1,0,0,0,0],[2,1,2,0,0,0,0,0,0,0]]",
+            "strategy.pre_post_strategy_array=[1,2,1,0,0,1,0,0,0,0]"], check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        ps = sess.ps
+        with torch.no_grad():
+            for n, p in sess.model.named_parameters():
+                gname = n.replace("layers.0.", f"layers.{ps.stage}.")
+                p.copy_(shard_like(n, ref_state[gname], ps.tp_rank, ps.tp_size, 4))
+        for u in sess.engine.units:
+            src = u.flat_param[u.shard_range()] if u.sharded_state else u.flat_param
+            u.master.copy_(src.float())
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            # stage 0 is data parallel over two ranks with micro batch 1: rank r of the stage feeds
+            # sequences r, 2 + r (micro step k takes sequence 2 k + r); stage 1 sees both per micro step
+            b = prov(4, 32, 256, "cpu", seed=70 + it)
+            if ps.stage == 0:
+                idx = torch.tensor([ps.dp_rank, 2 + ps.dp_rank])
+            else:
+                idx = torch.arange(4)
+            losses.append(float(sess.step_on_device(b["input_ids"][idx], b["labels"][idx])))
+        sess.finish()
+        ret[rank] = (ps.stage, ps.tp_rank, ps.tp_size, losses,
+                     {n.replace("layers.0.", f"layers.{ps.stage}."): p.detach().clone()
+                      for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+def test_heterogeneous_pipeline_dp2_then_tp2_matches_single_process():
+    """Two pipeline stages with different layouts on four ranks: stage 0 is data parallel (two
+    ranks, micro batch 1, ZeRO-1), stage 1 tensor parallel (two ranks, micro batch 2); the
+    activations are re-sharded along the batch between them."""
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY[:8], check_world_size=False)
+    torch.manual_seed(4)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+    ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 39500 + os.getpid() % 2000
+    mp.spawn(_hetero_worker, args=(4, port, ref_state, ret), nprocs=4, join=True)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=70 + it)
+        opt.zero_grad()
+        tot = 0.0
+        for k in range(2):
+            mbatch = {key: v[2 * k: 2 * k + 2] for key, v in b.items()}
+            l = ref(**mbatch) / 2
+            l.backward()
+            tot += l.item()
+        opt.step()
+        for r in range(4):
+            stage, _, _, losses, _ = ret[r]
+            if stage == 1:
+                assert abs(losses[it] - tot) < 2e-4, (r, it, losses, tot)
+    new_state = dict(ref.named_parameters())
+    for r in range(4):
+        stage, tpr, tps, _, params = ret[r]
+        for n, p in params.items():
+            want = shard_like(n, new_state[n].detach(), tpr, tps, 4)
+            assert (p - want).abs().max().item() < 2e-4, (r, n)
