@@ -169,3 +169,147 @@ def test_heterogeneous_pipeline_dp2_then_tp2_matches_single_process():
         for n, p in params.items():
             want = shard_like(n, new_state[n].detach(), tpr, tps, 4)
             assert (p - want).abs().max().item() < 2e-4, (r, n)
+
+
+def _pptp_worker(rank, world, port, sp, ref_state, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        cfg, _ = load_config("config", ["experiment=llama-350m"] + TINY[:8] + [
+            "hardware.num_gpus_per_node=4", "training.global_batch_size=4", "strategy.layer_partitions=[1,1]",
+            "strategy.device_assignment=[[1,2],[1,2]]", "strategy.gradient_checkpointing=[1,0]",
+            "strategy.gradient_accumulation_steps=2",
+            "strategy.stage_strategies=[[2,1,2,0,0,0,0,0,0,0],[2,1,2,0,0,0,0,0,0,0]]",
+            "strategy.pre_post_strategy_array=[2,1,2,0,0,0,0,0,0,0]",
+            f"sequence_parallel={'true' if sp else 'false'}"], check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        ps = sess.ps
+        with torch.no_grad():
+            for n, p in sess.model.named_parameters():
+                gname = n.replace("layers.0.", f"layers.{ps.stage}.")
+                p.copy_(shard_like(n, ref_state[gname], ps.tp_rank, ps.tp_size, 4))
+        for u in sess.engine.units:
+            u.master.copy_(u.flat_param.float())
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            b = prov(4, 32, 256, "cpu", seed=90 + it)
+            losses.append(float(sess.step_on_device(b["input_ids"], b["labels"])))
+        sess.finish()
+        ret[rank] = (ps.stage, ps.tp_rank, ps.tp_size, losses,
+                     {n.replace("layers.0.", f"layers.{ps.stage}."): p.detach().clone()
+                      for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_pipeline_of_tensor_parallel_stages_matches_single_process(sp):
+    cfg, _ = load_config("config", ["experiment=llama-350m"] + TINY[:8], check_world_size=False)
+    torch.manual_seed(5)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+    ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 41500 + (os.getpid() + int(sp)) % 2000
+    mp.spawn(_pptp_worker, args=(4, port, sp, ref_state, ret), nprocs=4, join=True)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=90 + it)
+        opt.zero_grad()
+        tot = 0.0
+        for k in range(2):
+            mbatch = {key: v[2 * k: 2 * k + 2] for key, v in b.items()}
+            l = ref(**mbatch) / 2
+            l.backward()
+            tot += l.item()
+        opt.step()
+        for r in range(4):
+            if ret[r][0] == 1:
+                assert abs(ret[r][3][it] - tot) < 2e-4, (r, it, ret[r][3], tot)
+    new_state = dict(ref.named_parameters())
+    for r in range(4):
+        _, tpr, tps, _, params = ret[r]
+        for n, p in params.items():
+            want = shard_like(n, new_state[n].detach(), tpr, tps, 4)
+            assert (p - want).abs().max().item() < 2e-4, (r, n)
+
+
+def _dptp_worker(rank, world, port, zero, ref_state, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        vec = f"[1,2,2,{zero[0]},{zero[1]},{zero[2]},0,0,0,0]"
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY[:8] + [
+            "hardware.num_gpus_per_node=4", "training.global_batch_size=4", "strategy.layer_partitions=[2]",
+            "strategy.device_assignment=[[1,4]]", "strategy.gradient_checkpointing=[0]",
+            "strategy.gradient_accumulation_steps=2", f"strategy.stage_strategies=[{vec}]",
+            f"strategy.pre_post_strategy_array={vec}", "sequence_parallel=true"], check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        ps = sess.ps
+        with torch.no_grad():
+            for u in sess.engine.units:          # ZeRO-3 units: fill the persistent shard from the full weights
+                full = torch.zeros(u.padded)
+                for p, o, n in zip(u.params, u.offsets, u.param_names):
+                    name = n if u.name in ("pre", "post") else f"language_model.encoder.layers.{u.name[5:]}.{n}"
+                    name = name.replace("embedding.", "language_model.embedding.") if u.name == "pre" else name
+                    full[o:o + p.numel()] = shard_like(name, ref_state[name], ps.tp_rank, 2, 4).reshape(-1)
+                if u.param_shard is not None:
+                    u.param_shard.copy_(full[u.shard_range()])
+                    if u.flat_param is not None:
+                        u.flat_param.copy_(full)
+                else:
+                    u.flat_param.copy_(full)
+                u.master.copy_(full[u.shard_range()] if u.sharded_state else full)
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            b = prov(4, 32, 256, "cpu", seed=110 + it)
+            idx = torch.tensor([ps.dp_rank, 2 + ps.dp_rank])       # micro step k of dp rank d: sequence 2 k + d
+            losses.append(float(sess.step_on_device(b["input_ids"][idx], b["labels"][idx])))
+        sess.finish()
+        out = {}
+        for u in sess.engine.units:
+            if u.ring_resident and u.flat_param is None:
+                u.unshard(torch.empty(u.padded), ps.dp_ag_group)
+            for p, o, n in zip(u.params, u.offsets, u.param_names):
+                name = n if u.name in ("pre", "post") else f"language_model.encoder.layers.{u.name[5:]}.{n}"
+                name = name.replace("embedding.", "language_model.embedding.") if u.name == "pre" else name
+                out[name] = u.flat_param[o:o + p.numel()].detach().clone().view(p.shape)
+        ret[rank] = (ps.tp_rank, ps.dp_rank, losses, out)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("zero", [(0, 0, 1), (0, 1, 1), (1, 1, 1)])
+def test_dp2_x_tp2_sequence_parallel_with_zero_matches_single_process(zero):
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY[:8], check_world_size=False)
+    torch.manual_seed(6)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+    ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 43500 + (os.getpid() + hash(zero)) % 2000
+    mp.spawn(_dptp_worker, args=(4, port, zero, ref_state, ret), nprocs=4, join=True)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=110 + it)
+        opt.zero_grad()
+        per_rank = {0: 0.0, 1: 0.0}
+        for s in range(4):
+            l = ref(**{k: v[s:s + 1] for k, v in b.items()}) / 4
+            l.backward()
+            per_rank[s % 2] += l.item() * 2                       # a dp rank reports the mean over its own two
+        opt.step()
+        for r in range(4):
+            assert abs(ret[r][2][it] - per_rank[ret[r][1]]) < 2e-4, (r, it, ret[r][2], per_rank)
+    new_state = dict(ref.named_parameters())
+    for r in range(4):
+        tpr = ret[r][0]
+        for n, p in ret[r][3].items():
+            want = shard_like(n, new_state[n].detach(), tpr, 2, 4)
+            assert (p - want).abs().max().item() < 2e-4, (r, n)
