@@ -49,10 +49,18 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
     gen = torch.Generator().manual_seed(seed + 31 * ps.dp_rank)     # same data on every tp / pp rank of a replica
     dev = sess.device
 
+    from mist_b200.models.provider import family_of, get_inputs_provider
+    decoder_only = family_of(cfg.model.name) in ("gpt", "llama", "falcon")
+    provider = get_inputs_provider(cfg.model.name)
+
     def batch():
-        ids = torch.randint(0, vocab, (mb * G, seq), generator=gen)
-        lab = torch.randint(0, vocab, (mb * G, seq), generator=gen)
-        return ids.to(dev), lab.to(dev)
+        if decoder_only:
+            ids = torch.randint(0, vocab, (mb * G, seq), generator=gen)
+            lab = torch.randint(0, vocab, (mb * G, seq), generator=gen)
+            return ids.to(dev), lab.to(dev)
+        # encoder-only / encoder-decoder families: the family's own synthetic inputs (token types,
+        # decoder ids, sentence-order labels ...), seeded per data-parallel rank
+        return (provider(mb * G, seq, vocab, dev, seed=int(torch.randint(0, 2 ** 31 - 1, (1,), generator=gen))),)
 
     data = [batch() for _ in range(warmup + number)]
 
@@ -72,7 +80,7 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
                                           "./logs", worker_name=f"rank{rank}_stage{ps.stage}"))
         prof.start()
     for i in range(warmup):
-        sess.step_on_device(*data[i])
+        (sess.step_on_device if decoder_only else sess.step_on_device_batch)(*data[i])
     sess.finish()
     sync()
     if cuda:
@@ -82,7 +90,7 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
     wall = time.perf_counter()
     loss = None
     for i in range(number):
-        loss = sess.step_on_device(*data[warmup + i])
+        loss = (sess.step_on_device if decoder_only else sess.step_on_device_batch)(*data[warmup + i])
     sess.finish()
     if cuda:
         t1.record()

@@ -84,6 +84,22 @@ class TrainingSession:
             return self.pipeline.train_step(batches)
         return self.engine.train_step(batches)
 
+    def step_on_device_batch(self, batch: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """One iteration on a dictionary of model inputs (what the family's inputs provider
+        returns: token ids, token types, decoder ids, labels ...), each with this rank's
+        ``micro_batch * G`` samples along dimension 0; used for the encoder-only and
+        encoder-decoder families whose forward takes more than ids and labels."""
+        if self.G == 1:
+            batches = [dict(batch)]
+        else:
+            parts = {k: v.chunk(self.G) for k, v in batch.items()}
+            batches = [{k: parts[k][i] for k in batch} for i in range(self.G)]
+        if self.pipeline is not None:
+            assert set(batch) <= {"input_ids", "labels", "position_ids"}, \
+                "pipeline stages exchange one hidden-state tensor: decoder-only families only"
+            return self.pipeline.train_step(batches)
+        return self.engine.train_step(batches)
+
     def step(self, input_ids: torch.Tensor, labels: torch.Tensor) -> float:
         """One iteration from host tensors (pinned memory recommended): copies the inputs to
         the device, trains, and returns the loss as a Python float."""

@@ -1,4 +1,7 @@
 """Model zoo on CPU: every family trains a step; checkpoint layout round-trips."""
+import os
+
+import pytest
 import torch
 
 from mist_b200.config import ModelConfig
@@ -76,3 +79,25 @@ def test_gradient_checkpointing_same_grads():
     m.language_model.encoder.gradient_checkpointing = 2
     m(**batch).backward()
     assert all(torch.allclose(a, p.grad, atol=1e-6) for a, p in zip(g0, m.parameters()))
+
+
+@pytest.mark.parametrize("fam", ["bert/1.3b", "t5/1.7b", "falcon/1.3b", "gpt2/1.3b"])
+def test_exec_entry_point_runs_every_family_on_cpu(fam, tmp_path):
+    """The exec driver end to end (session, family input provider, timing, summary) on one CPU rank."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "benchmark/mist_b200/exec/benchmark_one_case.py"), "experiment=gpt2-1.3b",
+           f"model={fam}", "model.num_hidden_layers=2", "model.hidden_size=64", "model.intermediate_size=128",
+           "model.num_attention_heads=4", "training.max_sequence_length=32", "model.vocab_size=256",
+           "strategy.layer_partitions=[2]", "training.params_dtype=float32", "hardware.num_gpus_per_node=1",
+           "training.global_batch_size=4", "strategy.device_assignment=[[1,1]]", "strategy.gradient_checkpointing=[1]",
+           "strategy.gradient_accumulation_steps=2", "strategy.stage_strategies=[[2,1,1,0,0,0,0,0,0,0]]",
+           "strategy.pre_post_strategy_array=[2,1,1,0,0,0,0,0,0,0]", f"output_dir={tmp_path}"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert "Throughput:" in r.stdout
+    s = json.load(open(tmp_path / "summary.json"))
+    assert float(s["exec_total_cost"]) > 0
