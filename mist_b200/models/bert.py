@@ -72,7 +72,11 @@ class BertModel(nn.Module):
             hidden = out
         if self.language_model.sequence_parallel:
             grp = self.language_model.pre_post_process_group
-            hidden = dist_ops.all_gather(hidden, grp).view(input_ids.shape[0], -1, hidden.shape[-1])
+            # the head's dense + norm run on the full sequence on every rank and the vocabulary
+            # projection behind them sums its input gradient over the group, so the gradient that
+            # comes back here is complete on every rank
+            hidden = dist_ops.all_gather(hidden, grp, replicated_consumer=True).view(
+                input_ids.shape[0], -1, hidden.shape[-1])
         wte = (self.language_model.embedding.word_embeddings.weight if self.pre_process
                else self.word_embeddings.weight)
         logits = self.lm_head(hidden, wte)

@@ -96,7 +96,8 @@ class TransformerLanguageModel(nn.Module):
             if self.pooler is not None:
                 full = enc_out
                 if self.sequence_parallel:
-                    full = dist_ops.all_gather(enc_out, self.pre_post_process_group).view(bs, -1, enc_out.shape[-1])
+                    full = dist_ops.all_gather(enc_out, self.pre_post_process_group, replicated_consumer=True).view(
+                        bs, -1, enc_out.shape[-1])
                 return enc_out, self.pooler(full, pooling_sequence_index)
             return enc_out
         dec_hidden = self.embedding(dec_input_ids, dec_position_ids, None)

@@ -89,6 +89,23 @@ class _AllGather(torch.autograd.Function):
         return reduce_scatter_raw(g, ctx.group)[0], None
 
 
+class _AllGatherSliceGrad(torch.autograd.Function):
+    """All-gather whose consumers compute the same thing on every rank (a replicated head after
+    the sequence-sharded region): the incoming gradient is already complete and identical on all
+    ranks, so the backward pass keeps this rank's slice instead of summing the copies."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return all_gather_raw(x, group)[0]
+
+    @staticmethod
+    def backward(ctx, g):
+        n, r = group_size(ctx.group), group_rank(ctx.group)
+        per = g.shape[0] // n
+        return g[r * per:(r + 1) * per].contiguous(), None
+
+
 class _ReduceScatter(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
@@ -134,10 +151,15 @@ def _rules():
     return rules
 
 
-def all_gather(x, group):
+def all_gather(x, group, replicated_consumer: bool = False):
+    """Gathers dim 0 over the group.  ``replicated_consumer``: what follows is computed
+    identically on every rank, so the backward pass slices the gradient instead of
+    reduce-scattering it."""
     if _is_trivial(group):
         return x
-    return _rules().all_gather(x, group) if _symbolic(x) else _AllGather.apply(x, group)
+    if _symbolic(x):
+        return _rules().all_gather(x, group)
+    return (_AllGatherSliceGrad if replicated_consumer else _AllGather).apply(x, group)
 
 
 def reduce_scatter(x, group):

@@ -134,6 +134,15 @@ class TrainEngine:
                 us.append(u)
                 layer_params.update(id(p) for p in u.params)
             self.layer_units[id(stack)] = us
+        # A stack that is not the last one (the encoder of an encoder-decoder model) finishes its
+        # backward pass after every block of the later stacks: its own non-block parameters (the
+        # final norm) get their gradient late, so they go with the embedding unit, which is reduced
+        # at the very end of the backward pass, not with the head unit, which is reduced first.
+        for stack in self.stacks[:-1]:
+            for n, p in stack.named_parameters():
+                if id(p) not in layer_params and id(p) not in pre_ids:
+                    pre_params.append((f"stack{self.stacks.index(stack)}.{n}", p))
+                    pre_ids.add(id(p))
         post_params = [(n, p) for n, p in model.named_parameters()
                        if id(p) not in layer_params and id(p) not in pre_ids]
         self.pre_unit = FlatUnit("pre", pre_params, zero=min(pp_zero, ZeroLevel.OPT_GRAD), **mk) if pre_params else None

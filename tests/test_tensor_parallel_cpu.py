@@ -23,6 +23,12 @@ TINY = ["model.num_hidden_layers=2", "model.hidden_size=64", "model.intermediate
 
 def shard_like(name: str, full: torch.Tensor, rank: int, world: int, heads: int) -> torch.Tensor:
     """The slice of a single-process parameter that tensor-parallel rank ``rank`` holds."""
+    if "cross_attn.Wkv" in name:                               # [k | v], each split by heads
+        d = full.shape[0] // (2 * heads)
+        lh = heads // world
+        return full.view(2, heads, d, *full.shape[1:])[:, rank * lh:(rank + 1) * lh].reshape(2 * lh * d, *full.shape[1:])
+    if "cross_attn.Wq" in name or name == "lm_head.bias":     # heads / vocabulary rows are contiguous
+        return full.chunk(world, dim=0)[rank]
     if "Wqkv" in name:
         d = full.shape[0] // (3 * heads)
         lh = heads // world
@@ -312,4 +318,60 @@ def test_dp2_x_tp2_sequence_parallel_with_zero_matches_single_process(zero):
         tpr = ret[r][0]
         for n, p in ret[r][3].items():
             want = shard_like(n, new_state[n].detach(), tpr, 2, 4)
+            assert (p - want).abs().max().item() < 2e-4, (r, n)
+
+
+def _family_worker(rank, world, port, fam, sp, ref_state, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b", f"model={fam}"] + TINY +
+                             [f"sequence_parallel={'true' if sp else 'false'}"], check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        with torch.no_grad():
+            for n, p in sess.model.named_parameters():
+                p.copy_(shard_like(n, ref_state[n], rank, world, 4))
+        for u in sess.engine.units:
+            u.master.copy_(u.flat_param.float())
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            losses.append(float(sess.step_on_device_batch(prov(4, 32, 256, "cpu", seed=130 + it))))
+        sess.finish()
+        ret[rank] = (losses, {n: p.detach().clone() for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fam", ["bert/1.3b", "t5/1.7b", "falcon/1.3b"])
+@pytest.mark.parametrize("sp", [False, True])
+def test_tp2_other_families_match_single_process(fam, sp):
+    if sp and fam.startswith("t5"):
+        pytest.skip("sequence parallelism is not wired through cross attention (the model asserts)")
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b", f"model={fam}"] + TINY[:8], check_world_size=False)
+    torch.manual_seed(7)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+    ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 45500 + (os.getpid() + hash((fam, sp))) % 2000
+    mp.spawn(_family_worker, args=(2, port, fam, sp, ref_state, ret), nprocs=2, join=True)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=130 + it)
+        opt.zero_grad()
+        tot = 0.0
+        for k in range(2):
+            l = ref(**{key: v[2 * k: 2 * k + 2] for key, v in b.items()}) / 2
+            l.backward()
+            tot += l.item()
+        opt.step()
+        for r in range(2):
+            assert abs(ret[r][0][it] - tot) < 2e-4, (r, it, ret[r][0], tot)
+    new_state = dict(ref.named_parameters())
+    for r in range(2):
+        for n, p in ret[r][1].items():
+            want = shard_like(n, new_state[n].detach(), r, 2, 4)
             assert (p - want).abs().max().item() < 2e-4, (r, n)
