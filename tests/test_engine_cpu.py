@@ -47,7 +47,7 @@ def test_single_rank_matches_adamw(exp, G, ckpt):
     assert diff < 1e-4
 
 
-def _dp_worker(rank, world, port, zero_flags, G, ret, offload=(0, 0, 0, 0)):
+def _dp_worker(rank, world, port, zero_flags, G, ret, offload=(0, 0, 0, 0), ckpt=0):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -55,7 +55,7 @@ def _dp_worker(rank, world, port, zero_flags, G, ret, offload=(0, 0, 0, 0)):
         plan = build_plan([(1, world)], [(2, world, 1)], (1, world))
         ps = ParallelState(plan, rank)
         strat = StageStrategy(2, world, 1, *zero_flags, *offload)
-        eng = TrainEngine(model, ps, strat, grad_accum_steps=G, hp=dict(lr=1e-3))
+        eng = TrainEngine(model, ps, strat, grad_accum_steps=G, ckpt_layers=ckpt, hp=dict(lr=1e-3))
         prov = get_inputs_provider(cfg.model.name)
         losses = []
         for it in range(3):
@@ -112,6 +112,29 @@ def test_weight_grad_optimizer_offload_gloo_matches_single_process(zero_flags):
     assert ret["offloaded"][0] > 0
     if zero_flags[1]:
         assert ret["offloaded"][1] > 0
+    cfg, ref = _tiny_model()
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(3):
+        opt.zero_grad()
+        for k in range(G):
+            for r in range(world):
+                (ref(**prov(2, 32, 256, "cpu", seed=1000 * it + 10 * k + r)) / (G * world)).backward()
+        opt.step()
+    flat_ref = torch.cat([p.detach().reshape(-1) for p in ref.parameters()])
+    assert (ret["flat"] - flat_ref).abs().max().item() < 2e-4
+
+
+@pytest.mark.parametrize("zero_flags", [(False, True, True), (True, True, True)])
+def test_zero_with_activation_checkpointing_and_offload_gloo(zero_flags):
+    """Sharded gradients / weights with every block checkpointed (the blocks are re-run in the
+    backward pass, so their weights must be resident a second time), two micro steps, and part of
+    the saved activations on the host."""
+    world, G = 2, 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 32500 + (os.getpid() + hash(zero_flags)) % 2000
+    mp.spawn(_dp_worker, args=(world, port, zero_flags, G, ret, (0, 0, 0, 0.5), 3), nprocs=world, join=True)
     cfg, ref = _tiny_model()
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
     prov = get_inputs_provider(cfg.model.name)
