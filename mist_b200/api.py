@@ -64,6 +64,7 @@ class TrainingSession:
         self.engine = TrainEngine(self.model, self.ps, self.strategy, self.G, st.gradient_checkpointing[stage],
                                   hp=hp, comm_backend=self.comm_backend, overlap=bool(cfg.get("overlap", True)),
                                   zero3_gather=str(cfg.get("zero3_gather", "nccl")),
+                                  use_grad_ring=bool(cfg.get("use_memory_buffer", True)),
                                   pre_post_strategy=pre_post)
         self.pipeline = None
         if multi_stage:
