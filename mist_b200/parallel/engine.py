@@ -221,6 +221,12 @@ class TrainEngine:
         # first GEMM itself (one kernel) instead of a prefetched all-gather; the backward pass keeps
         # the prefetch.  Needs plain ZeRO-3 shards (no host-offloaded weights) on CUDA.
         self.param_gather = None
+        if (comm_backend == "fused" or zero3_gather == "fused") and dp > 1 and self.cuda:
+            from .symm import group_on_one_node
+            if not group_on_one_node(self.ps.dp_group):
+                # peer-memory kernels need every data-parallel rank on this node
+                comm_backend = self.comm_backend = "nccl"
+                zero3_gather = "nccl"
         if (zero3_gather == "fused" and self.zero3 and self.cuda and dp > 1
                 and F.Settings.gemm_backend == "tcgen05" and not (F.Settings.tp_backend == "fused" and self.ps.tp_size > 1)
                 and all(u.param_shard is not None for u in layer_units)):

@@ -202,5 +202,9 @@ _CONTEXTS: Dict[int, FusedTPContext] = {}
 def context_for(group, heap_bytes: int = 2 << 30) -> FusedTPContext:
     key = id(group)
     if key not in _CONTEXTS:
+        from .symm import group_on_one_node
+        if not group_on_one_node(group):
+            raise RuntimeError("tp_backend=fused needs the tensor-parallel group on one node (peer memory); "
+                               "use tp_backend=nccl for groups that span nodes")
         _CONTEXTS[key] = FusedTPContext(group, heap_bytes)
     return _CONTEXTS[key]

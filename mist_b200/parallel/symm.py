@@ -62,6 +62,17 @@ def ptr_table(ptrs: List[int]):
     return arr
 
 
+def group_on_one_node(group) -> bool:
+    """True when every rank of ``group`` runs on this host (peer memory over NVLink / CUDA IPC
+    needs that; groups that span nodes stay on the NCCL paths)."""
+    import socket
+    if group is None or not dist.is_initialized():
+        return True
+    names: List[Optional[str]] = [None] * dist.get_world_size(group)
+    dist.all_gather_object(names, socket.gethostname(), group=group)
+    return len(set(names)) == 1
+
+
 class SymmetricHeap:
     ALIGN = 1024
 
