@@ -19,6 +19,11 @@ class GPTModel(nn.Module):
         super().__init__()
         self.cfg, self.pre_process, self.post_process = cfg, pre_process, post_process
         self._verify_config(cfg)
+        if cfg.tie_word_embeddings and not (pre_process and post_process):
+            raise NotImplementedError(
+                "tie_word_embeddings with the embedding and the head on different pipeline stages: the two "
+                "copies would need a gradient all-reduce between the first and the last stage, which the "
+                "pipeline schedule does not issue; untie them (the packaged configurations do) or keep one stage")
         self.language_model = TransformerLanguageModel(
             cfg, pre_process, post_process, process_groups, pre_post_process_group, layer_range,
             sequence_parallel, device, dtype)
