@@ -127,6 +127,7 @@ def main(argv=None):
         print(f"Peak reserved memory per stage: {fmt_memories(res['peak_reserved'])}")
         update_summary(os.path.join(output_dir(node), "summary.json"), {
             "exec_total_cost": fmt_cost(res["latency"]),
+            "exec_throughput": f"{res['tokens_per_s']:.1f}",
             "exec_stage_peak_allocated_memories": fmt_memories(res["peak_allocated"]),
             "exec_stage_peak_reserved_memories": fmt_memories(res["peak_reserved"]),
         })

@@ -103,3 +103,19 @@ def test_merge_calibration_records(tmp_path):
         json.dump(recs, open(tmp_path / name, "w"))
     out = main([str(tmp_path / "a.json"), str(tmp_path / "b.json"), "-o", str(tmp_path / "m.json")])
     assert len(out) == 2 and {(r["intra"], r["latency"]) for r in out} == {(2, 2.0), (8, 1.0)}
+
+
+def test_collect_results_table(tmp_path):
+    import importlib.util
+    import json
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("collect", os.path.join(root, "benchmark/scripts/collect_single_node_results.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    (tmp_path / "a").mkdir()
+    json.dump({"analyzed_total_cost": "1.10", "exec_total_cost": "1.00", "exec_throughput": "10.0"}, open(tmp_path / "a" / "summary.json", "w"))
+    (tmp_path / "b").mkdir()
+    json.dump({"mist": {"tuning_best_cost": "2.0", "analyzed_total_cost": "2.0"}}, open(tmp_path / "b" / "summary.json", "w"))
+    rows = mod.main([str(tmp_path), "--csv", str(tmp_path / "out.csv")])
+    assert len(rows) == 2 and rows[0]["prediction_error_pct"] == "+10.0" and rows[1]["run"].endswith("mist")
+    assert (tmp_path / "out.csv").read_text().startswith("run,")
