@@ -60,9 +60,13 @@ def kv_cache(model: nn.Module, max_batch_size: int, max_seqlen: int):
 
 @torch.no_grad()
 def generate(model: nn.Module, input_ids: torch.Tensor, max_new_tokens: int, eos_token_id: Optional[int] = None,
-             temperature: float = 0.0, top_k: int = 0, generator: Optional[torch.Generator] = None) -> torch.Tensor:
+             temperature: float = 0.0, top_k: int = 0, generator: Optional[torch.Generator] = None,
+             tp_group=None) -> torch.Tensor:
     """Greedy (``temperature == 0``) or sampled continuation of ``input_ids`` ``[batch, prompt]``.
-    Returns ``[batch, prompt + generated]``; sequences that hit ``eos_token_id`` keep emitting it."""
+    Returns ``[batch, prompt + generated]``; sequences that hit ``eos_token_id`` keep emitting it.
+    With a tensor-parallel model pass its group as ``tp_group``: the vocabulary-parallel logits of
+    the last position are gathered so every rank picks the same token (sampling then needs the
+    same ``generator`` state on every rank)."""
     was_training = model.training
     model.eval()
     b, s0 = input_ids.shape
@@ -77,6 +81,10 @@ def generate(model: nn.Module, input_ids: torch.Tensor, max_new_tokens: int, eos
                 logits = model(step_ids, position_ids=pos.unsqueeze(0).expand(b, -1))
                 ip.seqlen_offset += step_ids.shape[1]
                 last = logits.reshape(b, step_ids.shape[1], -1)[:, -1].float()
+                if tp_group is not None and torch.distributed.get_world_size(tp_group) > 1:
+                    parts = [torch.empty_like(last) for _ in range(torch.distributed.get_world_size(tp_group))]
+                    torch.distributed.all_gather(parts, last.contiguous(), group=tp_group)
+                    last = torch.cat(parts, dim=-1)
                 if temperature > 0:
                     last = last / temperature
                     if top_k > 0:

@@ -375,3 +375,38 @@ def test_tp2_other_families_match_single_process(fam, sp):
         for n, p in ret[r][1].items():
             want = shard_like(n, new_state[n].detach(), r, 2, 4)
             assert (p - want).abs().max().item() < 2e-4, (r, n)
+
+
+def _gen_worker(rank, world, port, ref_state, prompt, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.inference import generate
+        cfg, _ = load_config("config", ["experiment=llama-350m"] + TINY[:8] + ["model.rotary_emb_fraction=1.0"],
+                             check_world_size=False)
+        group = dist.new_group([0, 1])
+        torch.manual_seed(0)
+        model = base_model_provider(cfg.model, process_groups=group, pre_post_process_group=group, device="cpu",
+                                    dtype=torch.float32)
+        with torch.no_grad():
+            for n, p in model.named_parameters():
+                p.copy_(shard_like(n, ref_state[n], rank, world, 4))
+        ret[rank] = generate(model, prompt, max_new_tokens=5, tp_group=group)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp2_cached_generation_matches_single_process():
+    from mist_b200.inference import generate
+    cfg, _ = load_config("config", ["experiment=llama-350m"] + TINY[:8] + ["model.rotary_emb_fraction=1.0"],
+                         check_world_size=False)
+    torch.manual_seed(8)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32).eval()
+    ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    prompt = torch.randint(0, 256, (2, 6))
+    want = generate(ref, prompt, max_new_tokens=5)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 47500 + os.getpid() % 2000
+    mp.spawn(_gen_worker, args=(2, port, ref_state, prompt, ret), nprocs=2, join=True)
+    assert torch.equal(ret[0], want) and torch.equal(ret[1], want)
