@@ -19,6 +19,7 @@ import contextlib
 from typing import Dict, Optional
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 
 from .modules.layers import ParallelMHA
@@ -81,9 +82,9 @@ def generate(model: nn.Module, input_ids: torch.Tensor, max_new_tokens: int, eos
                 logits = model(step_ids, position_ids=pos.unsqueeze(0).expand(b, -1))
                 ip.seqlen_offset += step_ids.shape[1]
                 last = logits.reshape(b, step_ids.shape[1], -1)[:, -1].float()
-                if tp_group is not None and torch.distributed.get_world_size(tp_group) > 1:
-                    parts = [torch.empty_like(last) for _ in range(torch.distributed.get_world_size(tp_group))]
-                    torch.distributed.all_gather(parts, last.contiguous(), group=tp_group)
+                if tp_group is not None and dist.get_world_size(tp_group) > 1:
+                    parts = [torch.empty_like(last) for _ in range(dist.get_world_size(tp_group))]
+                    dist.all_gather(parts, last.contiguous(), group=tp_group)
                     last = torch.cat(parts, dim=-1)
                 if temperature > 0:
                     last = last / temperature
