@@ -129,8 +129,11 @@ class TrainEngine:
         for stack in self.stacks:
             stack.hooks = self
             us = []
+            # unit names key the events, ring slots and checkpoint entries: the blocks of a second
+            # stack (decoder of an encoder-decoder model) restart at index 0, so they get a prefix
+            prefix = "layer" if stack is self.stacks[0] else f"stack{self.stacks.index(stack)}_layer"
             for i, layer in enumerate(stack.layers):
-                u = FlatUnit(f"layer{layer.layer_idx}", layer, zero=zero, **mk)
+                u = FlatUnit(f"{prefix}{layer.layer_idx}", layer, zero=zero, **mk)
                 us.append(u)
                 layer_params.update(id(p) for p in u.params)
             self.layer_units[id(stack)] = us
