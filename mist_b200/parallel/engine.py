@@ -350,8 +350,10 @@ class TrainEngine:
         units = self.layer_units[id(stack)]
         if torch.is_grad_enabled():
             hidden, residual = _mark(lambda: self._layer_backward_start(stack, i), hidden, residual)
-        if self.zero3 and (i + 1 < len(units) or not torch.is_grad_enabled()):
-            # block i's slot is reused by block i+2; the last block stays resident for the backward
+        keep = i + 1 == len(units) and stack is self.stacks[-1] and torch.is_grad_enabled()
+        if self.zero3 and not keep:
+            # block i's slot is reused by block i+2; only the very last block (of the last stack) stays
+            # resident, because the backward pass starts with it
             self._release(units[i])
         if i + 1 == len(units) and self.post_unit is not None:
             self._wait_params(self.post_unit)

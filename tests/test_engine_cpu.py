@@ -266,3 +266,49 @@ def test_constant_loss_scale_does_not_change_the_update():
     g = [torch.full((3,), 8.0), torch.tensor([float("inf")])]
     assert s.unscale_(g[:1]) is False and torch.allclose(g[0], torch.full((3,), 2.0))
     assert s.unscale_(g[1:]) is True
+
+
+def _t5_dp_worker(rank, world, port, zero_flags, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=t5/1.7b"] + TINY, check_world_size=False)
+        torch.manual_seed(0)
+        model = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+        plan = build_plan([(1, world)], [(2, world, 1)], (1, world))
+        ps = ParallelState(plan, rank)
+        eng = TrainEngine(model, ps, StageStrategy(2, world, 1, *zero_flags, 0, 0, 0, 0), grad_accum_steps=2,
+                          ckpt_layers=1, hp=dict(lr=1e-3))
+        prov = get_inputs_provider(cfg.model.name)
+        for it in range(2):
+            eng.train_step([prov(2, 32, 256, "cpu", seed=1000 * it + 10 * k + rank) for k in range(2)])
+        for u in eng.units:
+            if u.ring_resident and u.flat_param is None:
+                u.unshard(torch.empty(u.padded), ps.dp_ag_group if u.is_zero3 else None, streams=eng.swap_streams)
+        if rank == 0:
+            ret["flat"] = torch.cat([p.detach().reshape(-1) for p in model.parameters()]).clone()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("zero_flags", [(False, True, True), (True, True, True)])
+def test_encoder_decoder_model_data_parallel_zero(zero_flags):
+    """T5 (two stacks) on two data-parallel ranks with sharded gradients / weights."""
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 34100 + (os.getpid() + hash(zero_flags)) % 1000
+    mp.spawn(_t5_dp_worker, args=(world, port, zero_flags, ret), nprocs=world, join=True)
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=t5/1.7b"] + TINY, check_world_size=False)
+    torch.manual_seed(0)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        opt.zero_grad()
+        for k in range(2):
+            for r in range(world):
+                (ref(**prov(2, 32, 256, "cpu", seed=1000 * it + 10 * k + r)) / (2 * world)).backward()
+        opt.step()
+    flat_ref = torch.cat([p.detach().reshape(-1) for p in ref.parameters()])
+    assert (ret["flat"] - flat_ref).abs().max().item() < 2e-4
