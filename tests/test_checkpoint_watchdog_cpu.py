@@ -175,3 +175,53 @@ def test_collective_after_a_rank_left_raises_within_the_timeout():
         assert not p.is_alive()
     assert ret["outcome"] != "completed"
     assert ret["seconds"] < 30
+
+
+def _ckpt_pptp_worker(rank, world, port, path, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        from mist_b200.utils import checkpoint
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY[:8] + [
+            "model.num_hidden_layers=2", "hardware.num_gpus_per_node=4", "training.global_batch_size=4",
+            "strategy.layer_partitions=[1,1]", "strategy.device_assignment=[[1,2],[1,2]]",
+            "strategy.gradient_checkpointing=[0,0]", "strategy.gradient_accumulation_steps=2",
+            "strategy.stage_strategies=[[2,1,2,0,0,0,0,0,0,0],[2,1,2,0,0,0,0,0,0,0]]",
+            "strategy.pre_post_strategy_array=[2,1,2,0,0,0,0,0,0,0]"], check_world_size=False)
+        prov = get_inputs_provider("gpt2")
+
+        def batch(it):
+            b = prov(4, 32, 256, "cpu", seed=500 + it)
+            return b["input_ids"], b["labels"]
+
+        a = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        a.step_on_device(*batch(0))
+        a.finish()
+        checkpoint.save(a, path, step=1)
+        loss_a = float(a.step_on_device(*batch(1)))
+        b = TrainingSession(cfg, seed=99, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        step = checkpoint.load(b, path)
+        loss_b = float(b.step_on_device(*batch(1)))
+        ret[rank] = (step, loss_a, loss_b, a.ps.stage)
+        if rank == 0:
+            ret["files"] = sorted(os.listdir(path))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_checkpoint_roundtrip_pipeline_of_tensor_parallel_stages(tmp_path):
+    """Two pipeline stages of two tensor-parallel ranks: one model / optimizer file per (stage, tp
+    rank), and a fresh session resumed from them continues with the same loss."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 38500 + os.getpid() % 1000
+    mp.spawn(_ckpt_pptp_worker, args=(4, port, str(tmp_path / "ck"), ret), nprocs=4, join=True)
+    for s in range(2):
+        for t in range(2):
+            assert f"model_stage{s}_tp{t}.pt" in ret["files"] and f"optim_stage{s}_tp{t}.pt" in ret["files"]
+    for r in range(4):
+        step, la, lb, stage = ret[r]
+        assert step == 1
+        if stage == 1:
+            assert abs(la - lb) < 1e-5, (r, la, lb)
