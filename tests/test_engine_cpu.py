@@ -312,3 +312,64 @@ def test_encoder_decoder_model_data_parallel_zero(zero_flags):
         opt.step()
     flat_ref = torch.cat([p.detach().reshape(-1) for p in ref.parameters()])
     assert (ret["flat"] - flat_ref).abs().max().item() < 2e-4
+
+
+def _pp3_worker(rank, world, port, G, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + [
+            "hardware.num_gpus_per_node=3", f"training.global_batch_size={G}", "strategy.layer_partitions=[1,1,1]",
+            "strategy.device_assignment=[[1,1],[1,1],[1,1]]", "strategy.gradient_checkpointing=[0,1,0]",
+            f"strategy.gradient_accumulation_steps={G}",
+            "strategy.stage_strategies=[[1,1,1,0,0,0,0,0,0,0],[1,1,1,0,0,0,0,0,0,0],[1,1,1,0,0,0,0,0,0,0]]",
+            "strategy.pre_post_strategy_array=[1,1,1,0,0,0,0,0,0,0]"], check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            b = prov(G, 32, 256, "cpu", seed=300 + it)
+            losses.append(float(sess.step_on_device(b["input_ids"], b["labels"])))
+        ret[rank] = (losses, {n: p.detach().clone() for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("G", [1, 2, 5])
+def test_three_stage_pipeline_with_fewer_or_more_micro_batches_than_stages(G):
+    """1F1B with fewer micro batches than warm-up slots (G = 1), exactly the warm-up depth (G = 2)
+    and a steady state (G = 5); losses against one process holding the three stages' weights."""
+    world = 3
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 30500 + (os.getpid() + 13 * G) % 2000
+    mp.spawn(_pp3_worker, args=(world, port, G, ret), nprocs=world, join=True)
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY, check_world_size=False)
+    torch.manual_seed(0)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+    sd = ref.state_dict()
+    for stage in range(3):
+        for n, p in ret[stage][1].items():
+            sd[n.replace("layers.0.", f"layers.{stage}.")] = p      # the stages' *final* weights, to learn the names
+    # rebuild the stages' initial weights exactly as the session does (seed + 17 * stage)
+    from mist_b200.models.provider import base_model_provider as bmp
+    for stage in range(3):
+        torch.manual_seed(0 + 17 * stage)
+        m = bmp(cfg.model, pre_process=stage == 0, post_process=stage == 2, layer_range=(stage, stage + 1),
+                device="cpu", dtype=torch.float32)
+        for n, p in m.state_dict().items():
+            sd[n.replace("layers.0.", f"layers.{stage}.")] = p.clone()
+    ref.load_state_dict(sd)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(G, 32, 256, "cpu", seed=300 + it)
+        opt.zero_grad()
+        tot = 0.0
+        for k in range(G):
+            l = ref(**{key: v[k:k + 1] for key, v in b.items()}) / G
+            l.backward()
+            tot += l.item()
+        opt.step()
+        assert abs(ret[2][0][it] - tot) < 2e-4, (it, ret[2][0], tot)
