@@ -134,6 +134,7 @@ class TrainEngine:
             prefix = "layer" if stack is self.stacks[0] else f"stack{self.stacks.index(stack)}_layer"
             for i, layer in enumerate(stack.layers):
                 u = FlatUnit(f"{prefix}{layer.layer_idx}", layer, zero=zero, **mk)
+                u.ring_index = i          # position in its stack: decides the weight ring slot
                 us.append(u)
                 layer_params.update(id(p) for p in u.params)
             self.layer_units[id(stack)] = us
@@ -279,13 +280,20 @@ class TrainEngine:
             torch.cuda.current_stream().wait_event(ev)
 
     # ----------------------------------------------------------------- ZeRO-3 residency
+    def _slot_for(self, unit: FlatUnit) -> int:
+        """Blocks alternate between the two weight slots by their position in the stack, always the
+        same slot for the same block: tensors that autograd saved in a forward pass are views into
+        the slot, so the block must come back to the same memory for its backward pass, also when
+        several forward passes are in flight (pipeline warm-up) before the first backward."""
+        slot = unit.ring_index & 1
+        self._slot_of[unit.name] = slot
+        return slot
+
     def _gather(self, unit: FlatUnit):
         """Starts the all-gather of ``unit``'s weights into the next ring slot (comm stream)."""
         if not self.zero3 or unit.flat_param is not None or not unit.ring_resident:
             return
-        slot = self._next_slot
-        self._next_slot ^= 1
-        self._slot_of[unit.name] = slot
+        slot = self._slot_for(unit)
         with self._on_comm(), record(f"{unit.name}.unshard"):
             unit.unshard(self._slots[slot], self.ps.dp_ag_group if unit.is_zero3 else None,
                          streams=self.swap_streams)
@@ -305,9 +313,7 @@ class TrainEngine:
         weight, b_off, bias_off = fw
         if b_off > unit.shard_numel:
             return False
-        slot = self._next_slot
-        self._next_slot ^= 1
-        self._slot_of[unit.name] = slot
+        slot = self._slot_for(unit)
         full = self._slots[slot][: unit.padded]
         with record(f"{unit.name}.unshard_in_first_gemm"):
             pg.stage_shard(slot, unit.param_shard)
@@ -350,7 +356,10 @@ class TrainEngine:
         units = self.layer_units[id(stack)]
         if torch.is_grad_enabled():
             hidden, residual = _mark(lambda: self._layer_backward_start(stack, i), hidden, residual)
-        keep = i + 1 == len(units) and stack is self.stacks[-1] and torch.is_grad_enabled()
+        # (not under pipeline parallelism: there further forward passes may come before the
+        # backward pass and would reuse the slot)
+        keep = (i + 1 == len(units) and stack is self.stacks[-1] and torch.is_grad_enabled()
+                and self.ps.num_stages == 1)
         if self.zero3 and not keep:
             # block i's slot is reused by block i+2; only the very last block (of the last stack) stays
             # resident, because the backward pass starts with it

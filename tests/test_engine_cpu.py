@@ -373,3 +373,84 @@ def test_three_stage_pipeline_with_fewer_or_more_micro_batches_than_stages(G):
             tot += l.item()
         opt.step()
         assert abs(ret[2][0][it] - tot) < 2e-4, (it, ret[2][0], tot)
+
+
+def _ppdp_worker(rank, world, port, zero, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        vec = f"[1,2,1,{zero[0]},{zero[1]},{zero[2]},0,0,0,0]"
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + [
+            "model.num_hidden_layers=4", "hardware.num_gpus_per_node=4", "training.global_batch_size=4",
+            "strategy.layer_partitions=[2,2]", "strategy.device_assignment=[[1,2],[1,2]]",
+            "strategy.gradient_checkpointing=[1,0]", "strategy.gradient_accumulation_steps=2",
+            f"strategy.stage_strategies=[{vec},{vec}]", f"strategy.pre_post_strategy_array={vec}"],
+            check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        ps = sess.ps
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            b = prov(4, 32, 256, "cpu", seed=400 + it)
+            idx = torch.tensor([ps.dp_rank, 2 + ps.dp_rank])
+            losses.append(float(sess.step_on_device(b["input_ids"][idx], b["labels"][idx])))
+        sess.finish()
+        eng = sess.engine
+        for u in eng.units:
+            if u.ring_resident and u.flat_param is None:
+                u.unshard(torch.empty(u.padded), ps.dp_ag_group if u.is_zero3 else None, streams=eng.swap_streams)
+        ret[rank] = (ps.stage, ps.dp_rank, losses, {n: p.detach().clone() for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("zero", [(0, 0, 1), (0, 1, 1), (1, 1, 1)])
+def test_pipeline_with_data_parallel_stages_and_zero(zero):
+    world = 4
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 28500 + (os.getpid() + hash(zero)) % 1500
+    mp.spawn(_ppdp_worker, args=(world, port, zero, ret), nprocs=world, join=True)
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + ["model.num_hidden_layers=4",
+                                                                    "strategy.layer_partitions=[4]"],
+                         check_world_size=False)
+    from mist_b200.models.provider import base_model_provider as bmp
+    torch.manual_seed(0)
+    ref = bmp(cfg.model, device="cpu", dtype=torch.float32)
+    sd = ref.state_dict()
+    for stage in range(2):
+        torch.manual_seed(0 + 17 * stage)
+        m = bmp(cfg.model, pre_process=stage == 0, post_process=stage == 1, layer_range=(2 * stage, 2 * stage + 2),
+                device="cpu", dtype=torch.float32)
+        for n, p in m.state_dict().items():
+            if ".layers." in n:
+                head, rest = n.split(".layers.")
+                idx, tail = rest.split(".", 1)
+                n = f"{head}.layers.{int(idx) + 2 * stage}.{tail}"
+            sd[n] = p.clone()
+    ref.load_state_dict(sd)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=400 + it)
+        opt.zero_grad()
+        per_dp = {0: 0.0, 1: 0.0}
+        for s in range(4):
+            l = ref(**{k: v[s:s + 1] for k, v in b.items()}) / 4
+            l.backward()
+            per_dp[s % 2] += 2 * l.item()
+        opt.step()
+        for r in range(4):
+            stage, d, losses, _ = ret[r]
+            if stage == 1:
+                assert abs(losses[it] - per_dp[d]) < 2e-4, (r, it, losses, per_dp)
+    new_state = dict(ref.named_parameters())
+    for r in range(4):
+        stage, _, _, params = ret[r]
+        for n, p in params.items():
+            if ".layers." in n:
+                head, rest = n.split(".layers.")
+                idx, tail = rest.split(".", 1)
+                n = f"{head}.layers.{int(idx) + 2 * stage}.{tail}"
+            assert (p - new_state[n].detach()).abs().max().item() < 2e-4, (r, n)
