@@ -410,3 +410,68 @@ def test_tp2_cached_generation_matches_single_process():
     port = 47500 + os.getpid() % 2000
     mp.spawn(_gen_worker, args=(2, port, ref_state, prompt, ret), nprocs=2, join=True)
     assert torch.equal(ret[0], want) and torch.equal(ret[1], want)
+
+
+def _hetero2_worker(rank, world, port, ref_state, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY[:8] + [
+            "hardware.num_gpus_per_node=3", "training.global_batch_size=4", "strategy.layer_partitions=[1,1]",
+            "strategy.device_assignment=[[1,1],[1,2]]", "strategy.gradient_checkpointing=[0,0]",
+            "strategy.gradient_accumulation_steps=2",
+            "strategy.stage_strategies=[[2,1,1,0,0,0,0,0,0,0],[1,2,1,0,1,1,0,0,0,0]]",
+            "strategy.pre_post_strategy=heuristic"], check_world_size=False)   # first and last stage differ in size
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        ps = sess.ps
+        with torch.no_grad():
+            for n, p in sess.model.named_parameters():
+                p.copy_(ref_state[n.replace("layers.0.", f"layers.{ps.stage}.")])
+        for u in sess.engine.units:
+            src = u.flat_param[u.shard_range()] if u.sharded_state else u.flat_param
+            u.master.copy_(src.float())
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            b = prov(4, 32, 256, "cpu", seed=170 + it)
+            idx = torch.arange(4) if ps.stage == 0 else torch.tensor([ps.dp_rank, 2 + ps.dp_rank])
+            losses.append(float(sess.step_on_device(b["input_ids"][idx], b["labels"][idx])))
+        sess.finish()
+        ret[rank] = (ps.stage, ps.dp_rank, losses,
+                     {n.replace("layers.0.", f"layers.{ps.stage}."): p.detach().clone()
+                      for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+def test_heterogeneous_pipeline_wide_stage_feeds_two_data_parallel_ranks():
+    """Stage 0 runs micro batches of two sequences on one rank and splits each between the two
+    data-parallel ranks of stage 1 (micro batch 1, ZeRO-2); gradients come back as two halves."""
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY[:8], check_world_size=False)
+    torch.manual_seed(9)
+    ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
+    ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 49500 + os.getpid() % 1500
+    mp.spawn(_hetero2_worker, args=(3, port, ref_state, ret), nprocs=3, join=True)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=170 + it)
+        opt.zero_grad()
+        per_dp = {0: 0.0, 1: 0.0}
+        for s in range(4):
+            l = ref(**{k: v[s:s + 1] for k, v in b.items()}) / 4
+            l.backward()
+            per_dp[s % 2] += 2 * l.item()
+        opt.step()
+        for r in range(3):
+            stage, d, losses, _ = ret[r]
+            if stage == 1:
+                assert abs(losses[it] - per_dp[d]) < 2e-4, (r, it, losses, per_dp)
+    new_state = dict(ref.named_parameters())
+    for r in range(3):
+        for n, p in ret[r][3].items():
+            assert (p - new_state[n].detach()).abs().max().item() < 2e-4, (r, n)
