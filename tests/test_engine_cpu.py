@@ -375,12 +375,12 @@ def test_three_stage_pipeline_with_fewer_or_more_micro_batches_than_stages(G):
         assert abs(ret[2][0][it] - tot) < 2e-4, (it, ret[2][0], tot)
 
 
-def _ppdp_worker(rank, world, port, zero, ret):
+def _ppdp_worker(rank, world, port, zero, ret, offload="0,0,0,0"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from mist_b200.api import TrainingSession
-        vec = f"[1,2,1,{zero[0]},{zero[1]},{zero[2]},0,0,0,0]"
+        vec = f"[1,2,1,{zero[0]},{zero[1]},{zero[2]},{offload}]"
         cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + [
             "model.num_hidden_layers=4", "hardware.num_gpus_per_node=4", "training.global_batch_size=4",
             "strategy.layer_partitions=[2,2]", "strategy.device_assignment=[[1,2],[1,2]]",
@@ -405,13 +405,14 @@ def _ppdp_worker(rank, world, port, zero, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("zero", [(0, 0, 1), (0, 1, 1), (1, 1, 1)])
-def test_pipeline_with_data_parallel_stages_and_zero(zero):
+@pytest.mark.parametrize("zero,offload", [((0, 0, 1), "0,0,0,0"), ((0, 1, 1), "0,0,0,0"), ((1, 1, 1), "0,0,0,0"),
+                                          ((0, 1, 1), "0.5,0.5,0.5,0"), ((1, 1, 1), "0.5,0.5,0.5,0")])
+def test_pipeline_with_data_parallel_stages_and_zero(zero, offload):
     world = 4
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 28500 + (os.getpid() + hash(zero)) % 1500
-    mp.spawn(_ppdp_worker, args=(world, port, zero, ret), nprocs=world, join=True)
+    port = 28500 + (os.getpid() + hash((zero, offload))) % 1500
+    mp.spawn(_ppdp_worker, args=(world, port, zero, ret, offload), nprocs=world, join=True)
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + ["model.num_hidden_layers=4",
                                                                     "strategy.layer_partitions=[4]"],
                          check_world_size=False)
