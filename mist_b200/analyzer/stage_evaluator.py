@@ -306,5 +306,11 @@ def analyze_strategy(cfg: MistConfig, evaluator: Optional[StageEvaluator] = None
         stables.append(float(res["stable"][0]))
         deltas.append(float(res["delta"][0]))
         peaks.append((float(res["peak_fwd"][0]), float(res["peak_bwd"][0])))
+    if S > 1 and bool(getattr(cfg, "disable_non_uniform_pp_micro_batch_analysis", False)):
+        # Uniform micro batches: each stage is charged its average time per micro batch (the
+        # once-per-iteration part spread over the G micro batches) and no stage has a delta
+        # (benchmark/mist/analysis/run.py:126-148).
+        stables = [t + d / G for t, d in zip(stables, deltas)]
+        deltas = [0.0] * S
     total = pipeline_latency(stables, deltas, G)
     return {"total": total, "stable": stables, "delta": deltas, "peak_memories": peaks}

@@ -155,6 +155,26 @@ def test_pipeline_latency_formula():
     assert t == pytest.approx(pipeline_latency([1.0, 2.0], [0.0, 0.0], 4), rel=0.08)
 
 
+def test_uniform_micro_batch_analysis_flag(monkeypatch):
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    over = ["hardware.num_gpus_per_node=8", "strategy.enabled=true", "strategy.layer_partitions=[16,16]",
+            "strategy.device_assignment=[[1,4],[1,4]]", "strategy.gradient_checkpointing=[0,0]",
+            "strategy.gradient_accumulation_steps=4", "training.global_batch_size=32",
+            "strategy.stage_strategies=[[2,4,1,0,1,1,0,0,0,0],[2,4,1,0,1,1,0,0,0,0]]",
+            "strategy.pre_post_strategy=heuristic"]
+    cfg, _ = load_config("config", over, check_world_size=False)
+    from mist_b200.analyzer.stage_evaluator import analyze_strategy
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=False))
+    a = analyze_strategy(cfg, ev)
+    cfg2, _ = load_config("config", over + ["+disable_non_uniform_pp_micro_batch_analysis=true"], check_world_size=False)
+    b = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))
+    assert any(d > 0 for d in a["delta"]) and all(d == 0 for d in b["delta"])
+    for s in range(2):
+        assert b["stable"][s] == pytest.approx(a["stable"][s] + a["delta"][s] / 4)
+    assert b["total"] == pytest.approx(sum(b["stable"]) + 3 * max(b["stable"]))
+    assert b["peak_memories"] == a["peak_memories"]
+
+
 def test_pareto_sampling():
     rng = np.random.default_rng(0)
     x, y = rng.random(200), rng.random(200)
@@ -208,6 +228,29 @@ def test_tune_small_case_end_to_end(monkeypatch, tmp_path):
     cfg2, _ = load_config("best", config_dirs=[tmp_path], check_world_size=False)    # validates the strategy
     again = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))["total"]
     assert again == pytest.approx(cost, rel=1e-6)
+
+
+def test_every_tuning_granularity_returns_a_valid_strategy(monkeypatch):
+    """Wider search spaces can only find cheaper strategies: no-pp >= uniform-pp >= uniform-device-pp-mip
+    >= inter-stage (up to the Pareto sampling), and each result passes the strategy validation."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_L4")
+    costs = {}
+    for gran in ("no-pp", "uniform-pp", "uniform-device-pp-mip", "inter-stage"):
+        cfg, node = load_config("test-small-base", ["model.num_hidden_layers=8", "training.global_batch_size=8",
+                                                    "strategy.enabled=false", f"tuning.tuning_granularity={gran}"],
+                                check_world_size=False)
+        cost, sol = inter_stage_tune(cfg, StageEvaluator(cfg, OpDatabase(allow_profile=False)))
+        assert sol is not None and math.isfinite(cost)
+        strat = solution_to_strategy(cfg, sol)
+        assert sum(strat["layer_partitions"]) == 8
+        assert sum(n * m for n, m in strat["device_assignment"]) == 2
+        if gran == "no-pp":
+            assert len(strat["layer_partitions"]) == 1
+        costs[gran] = cost
+    tol = 1.02
+    assert costs["uniform-pp"] <= costs["no-pp"] * tol
+    assert costs["uniform-device-pp-mip"] <= costs["uniform-pp"] * tol
+    assert costs["inter-stage"] <= costs["uniform-device-pp-mip"] * tol
 
 
 def test_op_database_roundtrip(tmp_path):
