@@ -409,6 +409,409 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Pipelined variant (head size <= 96).  Same math, tiles and shared-memory layouts as the kernel
+// above; what changes is who waits for whom:
+//
+//   * S^T and dP^T are double buffered in tensor memory and the MMA warp issues the two products
+//     of query block it+1 before it waits for the probabilities of block it, so the tensor cores
+//     work on the next block while the softmax warps are busy with the current one;
+//   * Q / dO arrive through three stages, so the early S^T / dP^T issue never waits for a load
+//     that was only just requested;
+//   * the dQ^T read-out (tensor memory -> transposed staging -> TMA reduce-add) has its own four
+//     warps, so the softmax warps go straight from one block to the next.
+//
+// Tensor memory (512 columns): S^T[2] 0..127, dP^T[2] 128..255, dQ^T 256..319, dV 320..415,
+// dK 416..511.  Warps 0-7 softmax / dS (and the dK, dV epilogue), warps 8-11 dQ, 12 TMA, 13 MMA.
+//
+// Barriers and the iteration `it` they belong to (b = it & 1, st = it % 3):
+//   q_full[st]   producer -> MMA      Q, dO of block it are in stage st
+//   q_empty[st]  MMA commit -> producer  the dV / dK / dQ products of block it have read stage st
+//   sdp_full[b]  MMA commit -> softmax   S^T[b], dP^T[b] of block it are complete
+//   pds_full     softmax (256) -> MMA    P^T, dS^T of block it are in shared memory (and S^T[b],
+//                                        dP^T[b] are in registers: block it+2 may overwrite them; the
+//                                        MMA warp has always waited for pds_full of block it by then)
+//   pds_empty    MMA commit -> softmax   the products of block it have read P^T, dS^T
+//   dq_full      MMA commit -> dQ warps  dQ^T of block it is complete
+//   dq_empty     dQ warps (128) -> MMA   dQ^T of block it is in registers
+// A thread can arrive on pds_full / dq_empty for block it+1 only after a wait that itself needs the
+// phase of block it to have completed, so no phase is entered twice.
+constexpr int kThreadsPipe = 448;
+constexpr int kQStages = 3;
+constexpr int kDQWarp0 = 8;       // first dQ warp; 8 % 4 == 0, so warp w owns TMEM lanes 32 * (w - 8) ...
+constexpr int kTmaWarp = 12, kMmaWarp = 13;
+
+struct SmemPipe {
+  static constexpr int kKV = 2 * BKV * 128;
+  static constexpr int kQ = 2 * BQ * 128;
+  static constexpr int kP = BKV * 128;
+  static constexpr int kDQ = 3 * BQ * 128;      // head size <= 96: three chunks of [64 q][32 fp32]
+  static constexpr int oK = 0;
+  static constexpr int oV = oK + kKV;
+  static constexpr int oQ = oV + kKV;           // kQStages stages of (Q, dO)
+  static constexpr int oP = oQ + kQStages * 2 * kQ;
+  static constexpr int oDS = oP + kP;
+  static constexpr int oDQ = oDS + kP;
+  static constexpr int oBar = oDQ + kDQ;
+  // kv_full, q_full[3], q_empty[3], sdp_full[2], pds_full, pds_empty, dq_full, dq_empty, final_full
+  static constexpr int kNumBars = 14;
+  static constexpr int oVec = oBar + kNumBars * 8 + 16;
+  static constexpr int kTotal = oVec + 2 * 2 * BQ * 4;
+};
+static_assert(SmemPipe::kTotal <= 232448, "pipelined attention backward: shared memory over the per-CTA limit");
+
+__global__ void __launch_bounds__(kThreadsPipe, 1)
+attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                     const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
+  using L = SmemPipe;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::oBar);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;
+  uint64_t* q_empty = bars + 4;
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* pds_full = bars + 9;
+  uint64_t* pds_empty = bars + 10;
+  uint64_t* dq_full = bars + 11;
+  uint64_t* dq_empty = bars + 12;
+  uint64_t* final_full = bars + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int jb = blockIdx.x;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv0 = jb * BKV;
+  const int coff = p.sk - p.sq;
+  const int nq_blocks = (p.sq + BQ - 1) / BQ;
+  int i_start = 0;
+  if (p.causal) {
+    int first_q = kv0 - coff;
+    i_start = first_q <= 0 ? 0 : first_q / BQ;
+  }
+  const int n_iter = max(0, nq_blocks - i_start);
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) report(p.status, MB_ERR_BAD_ARG);
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < kQStages; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) mbar_init(&sdp_full[s], 1);
+    mbar_init(pds_full, kWG);
+    mbar_init(pds_empty, 1);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 128);
+    mbar_init(final_full, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+    prefetch_tmap(&tm_do);
+    prefetch_tmap(&tm_dq);
+  }
+  if (warp == kTmaWarp) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128;   // + 64 * (it & 1)
+  const uint32_t t_dq = tmem_base + 256, t_dv = tmem_base + 320, t_dk = tmem_base + 416;
+
+  const uint32_t ck = BKV * 128;
+  const uint32_t cq = BQ * 128;
+
+  if (warp == kTmaWarp) {
+    // ----------------------------------------------------------- TMA producer
+    if (lane == 0 && n_iter > 0) {
+      mbar_expect_tx(kv_full, 2 * p.nchunks * ck);
+      for (int c = 0; c < p.nchunks; ++c) {
+        tma_load_4d(smem + L::oK + c * ck, &tm_k, kv_full, 64 * c, head, kv0, batch);
+        tma_load_4d(smem + L::oV + c * ck, &tm_v, kv_full, 64 * c, head, kv0, batch);
+      }
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it % kQStages;
+        if (it >= kQStages && !mbar_wait(&q_empty[st], ((it / kQStages) - 1) & 1)) {
+          report(p.status, MB_ERR_TIMEOUT_EMPTY);
+          break;
+        }
+        uint8_t* sq_ = smem + L::oQ + st * 2 * L::kQ;
+        uint8_t* sdo_ = sq_ + L::kQ;
+        const int q0 = (i_start + it) * BQ;
+        mbar_expect_tx(&q_full[st], 2 * p.nchunks * cq);
+        for (int c = 0; c < p.nchunks; ++c) {
+          tma_load_4d(sq_ + c * cq, &tm_q, &q_full[st], 64 * c, head, q0, batch);
+          tma_load_4d(sdo_ + c * cq, &tm_do, &q_full[st], 64 * c, head, q0, batch);
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------------------------------------- MMA issuer
+    if (n_iter > 0) {
+      const uint32_t idesc_sq = make_idesc_bf16(128, BQ, 0, 0);        // S^T, dP^T
+      const uint32_t idesc_dkv = make_idesc_bf16(128, p.d, 0, 1);      // dV, dK
+      const uint32_t idesc_dq = make_idesc_bf16(128, BQ, 1, 1);        // dQ^T
+      const uint32_t sk_ = smem_u32(smem + L::oK), sv_ = smem_u32(smem + L::oV);
+      const uint32_t sp_ = smem_u32(smem + L::oP), sds_ = smem_u32(smem + L::oDS);
+      const int ksteps = p.d / 16;
+      bool ok = mbar_wait(kv_full, 0);
+      if (!ok) report(p.status, MB_ERR_TIMEOUT_FULL);
+
+      // S^T[b] = K Q^T, dP^T[b] = V dO^T of block `it`
+      auto issue_sdp = [&](int it) -> bool {
+        const int st = it % kQStages, b = it & 1;
+        if (!mbar_wait(&q_full[st], (it / kQStages) & 1)) return false;
+        // S^T[b], dP^T[b] of block it-2 are free: the caller waited for pds_full of that block
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sq_ = smem_u32(smem + L::oQ + st * 2 * L::kQ), sdo_ = sq_ + L::kQ;
+          for (int kk = 0; kk < ksteps; ++kk) {
+            const uint32_t ch = kk >> 2, in = (kk & 3) * 32;
+            mma_f16_ss(t_s + b * BQ, make_smem_desc_sw128(sk_ + ch * ck + in, 16, 1024),
+                       make_smem_desc_sw128(sq_ + ch * cq + in, 16, 1024), idesc_sq, kk != 0);
+          }
+          for (int kk = 0; kk < ksteps; ++kk) {
+            const uint32_t ch = kk >> 2, in = (kk & 3) * 32;
+            mma_f16_ss(t_dp + b * BQ, make_smem_desc_sw128(sv_ + ch * ck + in, 16, 1024),
+                       make_smem_desc_sw128(sdo_ + ch * cq + in, 16, 1024), idesc_sq, kk != 0);
+          }
+          mma_commit(&sdp_full[b]);
+        }
+        __syncwarp();
+        return true;
+      };
+
+      if (ok && !issue_sdp(0)) { report(p.status, MB_ERR_TIMEOUT_FULL); ok = false; }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it % kQStages;
+        // next block's products first: they run while the softmax warps work on this block
+        if (it + 1 < n_iter && !issue_sdp(it + 1)) {
+          report(p.status, MB_ERR_TIMEOUT_FULL);
+          ok = false;
+          break;
+        }
+        if (!mbar_wait(pds_full, it & 1) || (it > 0 && !mbar_wait(dq_empty, (it - 1) & 1))) {
+          report(p.status, MB_ERR_TIMEOUT_TMEM);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sq_ = smem_u32(smem + L::oQ + st * 2 * L::kQ), sdo_ = sq_ + L::kQ;
+#pragma unroll
+          for (int kk = 0; kk < BQ / 16; ++kk) {
+            mma_f16_ss(t_dv, make_smem_desc_sw128(sp_ + kk * 32, 16, 1024),
+                       make_smem_desc_sw128(sdo_ + kk * 2048, cq, 1024), idesc_dkv, (it | kk) != 0);
+          }
+#pragma unroll
+          for (int kk = 0; kk < BQ / 16; ++kk) {
+            mma_f16_ss(t_dk, make_smem_desc_sw128(sds_ + kk * 32, 16, 1024),
+                       make_smem_desc_sw128(sq_ + kk * 2048, cq, 1024), idesc_dkv, (it | kk) != 0);
+          }
+#pragma unroll
+          for (int kk = 0; kk < BKV / 16; ++kk) {
+            mma_f16_ss(t_dq, make_smem_desc_sw128(sk_ + kk * 2048, ck, 1024),
+                       make_smem_desc_sw128(sds_ + kk * 2048, ck, 1024), idesc_dq, kk != 0);
+          }
+          mma_commit(&q_empty[st]);
+          mma_commit(pds_empty);
+          mma_commit(dq_full);
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) mma_commit(final_full);
+      __syncwarp();
+    }
+  } else if (warp >= kDQWarp0) {
+    // --------------------------------- dQ^T: TMEM -> transposed staging -> TMA reduce-add
+    const int r = threadIdx.x - kDQWarp0 * 32;     // d index == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const bool leader = (r == 0);
+    uint8_t* sdq_ = smem + L::oDQ;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int q0 = (i_start + it) * BQ;
+      if (!mbar_wait(dq_full, it & 1)) {
+        report(p.status, MB_ERR_TIMEOUT_TMEM);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t qr[BQ];
+      tmem_ld32(t_dq + lane_off, qr);
+      tmem_ld32(t_dq + 32 + lane_off, qr + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+      if (leader) tma_wait_read<0>();            // the previous reduce has read the staging tile
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (r < 96) {
+        // thread holds dQ[q0 + c][d = r]; staging chunk r / 32 is [64 q][32 d] fp32, 128-byte swizzled
+        uint8_t* chunk = sdq_ + (r >> 5) * cq;
+        const int dl = r & 31;
+#pragma unroll
+        for (int c = 0; c < BQ; ++c)
+          *reinterpret_cast<uint32_t*>(chunk + c * 128 + ((((dl >> 2) ^ (c & 7)) << 4) | ((dl & 3) << 2))) = qr[c];
+      }
+      fence_async_smem();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (leader) {
+        for (int w = 0; w * 32 < p.d; ++w) {
+          asm volatile(
+              "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group "
+              "[%0, {%2, %3, %4}], [%1];\n" ::"l"(reinterpret_cast<uint64_t>(&tm_dq)),
+              "r"(smem_u32(sdq_ + w * cq)), "r"(32 * w), "r"(q0), "r"(batch * p.nh + head)
+              : "memory");
+        }
+        tma_commit();
+      }
+    }
+    if (leader) tma_wait_all<0>();
+  } else {
+    // ------------------------------------------------------ softmax / dS / dK, dV epilogue
+    const int r = threadIdx.x & 127;
+    const int half = threadIdx.x >> 7;
+    const int c0 = half * 32;
+    const int kv_idx = kv0 + r;
+    const int kv_last = kv0 + BKV - 1;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    uint8_t* sp_ = smem + L::oP;
+    uint8_t* sds_ = smem + L::oDS;
+    float* s_lse = reinterpret_cast<float*>(smem + L::oVec);
+    float* s_delta = s_lse + 2 * BQ;
+    const long row_base = (static_cast<long>(batch) * p.nh + head) * p.sq;
+    bool ok = true;
+
+    auto fetch_vec = [&](int it) -> float {
+      const int q = (i_start + it) * BQ + (threadIdx.x & 63);
+      if (threadIdx.x >= 128 || q >= p.sq) return 0.f;
+      return threadIdx.x < 64 ? p.lse[row_base + q] * 1.4426950408889634f : p.delta[row_base + q];
+    };
+    auto stash_vec = [&](int buf, float v) {
+      if (threadIdx.x < 64) s_lse[buf * BQ + threadIdx.x] = v;
+      else if (threadIdx.x < 128) s_delta[buf * BQ + threadIdx.x - 64] = v;
+    };
+    if (n_iter > 0) stash_vec(0, fetch_vec(0));
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int q0 = (i_start + it) * BQ;
+      const int vb = it & 1;
+      const float nxt = (it + 1 < n_iter) ? fetch_vec(it + 1) : 0.f;
+      if (!mbar_wait(&sdp_full[vb], (it >> 1) & 1)) {
+        report(p.status, MB_ERR_TIMEOUT_TMEM);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float pf[32];
+      uint32_t pk[16], dk_[16];
+      {
+        uint32_t sr[32];
+        tmem_ld32(t_s + vb * BQ + c0 + lane_off, sr);
+        tmem_ld_wait();
+        const bool need_mask = (q0 + BQ > p.sq) || (kv_last >= p.sk) || (p.causal && kv_last > q0 + coff);
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int qi = q0 + c0 + c;
+            const bool valid = (qi < p.sq) && (kv_idx < p.sk) && (!p.causal || kv_idx <= qi + coff);
+            const float e = mb::fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -s_lse[vb * BQ + c0 + c]));
+            pf[c] = valid ? e : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            pf[c] = mb::fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -s_lse[vb * BQ + c0 + c]));
+        }
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) pk[c >> 1] = pack2(pf[c], pf[c + 1]);
+      }
+      {
+        uint32_t dr[32];
+        tmem_ld32(t_dp + vb * BQ + c0 + lane_off, dr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const float a = p.scale * pf[c] * (__uint_as_float(dr[c]) - s_delta[vb * BQ + c0 + c]);
+          const float b = p.scale * pf[c + 1] * (__uint_as_float(dr[c + 1]) - s_delta[vb * BQ + c0 + c + 1]);
+          dk_[c >> 1] = pack2(a, b);
+        }
+      }
+      // the previous block's products must be done with the P^T / dS^T tiles before they are rewritten
+      if (it > 0) {
+        if (!mbar_wait(pds_empty, (it - 1) & 1)) {
+          report(p.status, MB_ERR_TIMEOUT_TMEM);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint32_t off = r * 128 + (((half * 4 + g) ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(sp_ + off) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+        *reinterpret_cast<uint4*>(sds_ + off) = make_uint4(dk_[4 * g], dk_[4 * g + 1], dk_[4 * g + 2], dk_[4 * g + 3]);
+      }
+      fence_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+      stash_vec(vb ^ 1, nxt);
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // next block's lse / delta visible to all 256
+    }
+
+    if (ok && n_iter > 0 && !mbar_wait(final_full, 0)) {
+      report(p.status, MB_ERR_TIMEOUT_TMEM);
+      ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dkrow = p.dk + batch * p.dk_bs + static_cast<long>(kv_idx) * p.dk_ts + head * p.dk_hs;
+      __nv_bfloat16* dvrow = p.dv + batch * p.dv_bs + static_cast<long>(kv_idx) * p.dv_ts + head * p.dv_hs;
+      for (int c = half; c < p.d / 16; c += 2) {
+        uint32_t a[16], b[16];
+        if (n_iter > 0) {
+          tmem_ld16(t_dv + c * 16 + lane_off, a);
+          tmem_ld16(t_dk + c * 16 + lane_off, b);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) a[i] = b[i] = 0;
+        }
+        if (kv_idx < p.sk) {
+          float fa[16], fb[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            fa[i] = __uint_as_float(a[i]);
+            fb[i] = __uint_as_float(b[i]);
+          }
+          *reinterpret_cast<mb::bf16x8*>(dvrow + c * 16) = mb::pack8(fa);
+          *reinterpret_cast<mb::bf16x8*>(dvrow + c * 16 + 8) = mb::pack8(fa + 8);
+          *reinterpret_cast<mb::bf16x8*>(dkrow + c * 16) = mb::pack8(fb);
+          *reinterpret_cast<mb::bf16x8*>(dkrow + c * 16 + 8) = mb::pack8(fb + 8);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kTmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // delta[b][h][q] = sum_d dO[b][q][h][d] * O[b][q][h][d]; one warp per (b, q, h)
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ o,
                                   float* __restrict__ delta, int batch, int sq, int nh, int d, long do_bs,
@@ -500,9 +903,18 @@ bool make_map_dq(CUtensorMap* m, float* base, int bh, int sq, int d) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int g_bwd_variant = 0;        // 0: one block at a time; 1: pipelined (head size <= 96)
+int g_bwd_last_variant = 0;
+
 }  // namespace
 
 MB_API int* mb_status_device_ptr();
+
+// Chooses the main backward kernel for later calls: 0 = the kernel that finishes one query block
+// before it starts the next (default), 1 = the pipelined kernel where it applies (head size <= 96).
+MB_API void mb_attn_bwd_set_variant(int v) { g_bwd_variant = (v == 1) ? 1 : 0; }
+// Variant the last call of mb_attn_bwd launched.
+MB_API int mb_attn_bwd_last_variant() { return g_bwd_last_variant; }
 
 // dout, o: [b][sq][nh][d] with the given element strides for dout (o is contiguous);
 // delta: [b][nh][sq] fp32 scratch; dq_acc: [b][nh][sq][d] fp32 scratch, zeroed by this call.
@@ -546,15 +958,28 @@ MB_API int mb_attn_bwd(const void* dout, const void* q, const void* k, const voi
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
   p.status = mb_status_device_ptr();
-  static bool cfg = false;
-  if (!cfg) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal) !=
-        cudaSuccess)
-      return -3;
-    cfg = true;
-  }
   dim3 grid((sk + BKV - 1) / BKV, nh, batch);
-  attn_bwd_kernel<<<grid, kThreads, Smem::kTotal, stream>>>(tq, tk, tv, tdo, tdq, p);
+  if (g_bwd_variant == 1 && d <= 96) {
+    static bool cfg_pipe = false;
+    if (!cfg_pipe) {
+      if (cudaFuncSetAttribute(attn_bwd_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               SmemPipe::kTotal) != cudaSuccess)
+        return -3;
+      cfg_pipe = true;
+    }
+    attn_bwd_pipe_kernel<<<grid, kThreadsPipe, SmemPipe::kTotal, stream>>>(tq, tk, tv, tdo, tdq, p);
+    g_bwd_last_variant = 1;
+  } else {
+    static bool cfg = false;
+    if (!cfg) {
+      if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kTotal) !=
+          cudaSuccess)
+        return -3;
+      cfg = true;
+    }
+    attn_bwd_kernel<<<grid, kThreads, Smem::kTotal, stream>>>(tq, tk, tv, tdo, tdq, p);
+    g_bwd_last_variant = 0;
+  }
   {
     long nvec = static_cast<long>(batch) * nh * sq * (d / 8);
     long blocks = (nvec + 255) / 256;

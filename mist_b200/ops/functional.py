@@ -15,6 +15,7 @@ The ops mirror the fused operators the reference's module library is built on
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -46,6 +47,10 @@ class Settings:
     gemm_backend = "tcgen05"      # "tcgen05" (ours) | "cublas" (library, A/B baseline)
     attn_backend = "tcgen05"      # "tcgen05" (ours) | "sdpa" (library, A/B baseline)
     attn_block_n = 64
+    # Backward kernel that overlaps the next block's S / dP products with the current block's softmax
+    # (head size <= 96).  Its barrier protocol is model-checked on the CPU; its numerics have not been
+    # checked on a device yet, so it is opt-in (also MIST_B200_ATTN_BWD_PIPELINED=1).
+    attn_bwd_pipelined = os.environ.get("MIST_B200_ATTN_BWD_PIPELINED") == "1"
     gemm_max_ctas = 0             # >0 leaves SMs free for a concurrent communication kernel
     gemm_pair = True              # large GEMMs on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2)
     fuse_mlp_gelu = True          # GELU MLP as one autograd node (gelu' folded into a dgrad GEMM epilogue)

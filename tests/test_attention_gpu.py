@@ -1,5 +1,6 @@
 """tcgen05 attention forward (and the backward path in use) against fp32 references."""
 import math
+import os
 
 import pytest
 import torch
@@ -74,6 +75,31 @@ def test_attention_qkvpacked_grad(d, rot):
     o_ref.backward(g.cpu().float())
     assert _rel_err(o.cpu(), o_ref) < 2e-2
     assert _rel_err(qkv2.grad.cpu(), ref_in.grad) < 3e-2
+
+
+@pytest.mark.skipif(os.environ.get("MIST_B200_UNVALIDATED_KERNELS") != "1",
+                    reason="pipelined backward kernel: opt-in until its numerics have been checked on a device")
+@pytest.mark.parametrize("d", [80, 64, 96])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("s", [64, 256, 1000])
+def test_attn_bwd_pipelined_matches_reference(d, causal, s):
+    from mist_b200.ops import attention_bwd, native
+    torch.manual_seed(4)
+    b, nh = 2, 3
+    scale = 1 / math.sqrt(d)
+    q, k, v, g = (torch.randn(b, s, nh, d, device=DEV, dtype=torch.bfloat16) for _ in range(4))
+    o, lse = F.attn_fwd(q, k, v, scale, causal)
+    F.Settings.attn_bwd_pipelined = True
+    try:
+        dq, dk, dv = attention_bwd.backward(g, q, k, v, o, lse, scale, causal)
+        torch.cuda.synchronize()
+        assert native.kernels().mb_attn_bwd_last_variant() == 1
+    finally:
+        F.Settings.attn_bwd_pipelined = False
+    native.check_status()
+    rq, rk, rv = attention_bwd._reference(g, q, k, v, scale, causal)
+    for a, r in ((dq, rq), (dk, rk), (dv, rv)):
+        assert _rel_err(a, r) < 3e-2
 
 
 @pytest.mark.parametrize("nh,nkv,d,seq_len", [(8, 8, 128, 300), (8, 2, 64, 5), (4, 4, 80, 1), (16, 4, 256, 1031)])
