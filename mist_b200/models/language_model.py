@@ -12,7 +12,7 @@ import torch
 import torch.nn as nn
 
 from ..config import AttnMaskType, ModelConfig, PositionEmbeddingType
-from ..modules.layers import ColumnParallelLinear, VocabParallelEmbedding, vocab_parallel_cross_entropy
+from ..modules.layers import ColumnParallelLinear, PaddingMask, VocabParallelEmbedding, vocab_parallel_cross_entropy
 from ..ops import functional as F
 from ..parallel import dist_ops
 from .transformer import ParallelTransformer
@@ -78,15 +78,22 @@ class TransformerLanguageModel(nn.Module):
         return 3.0 * (L * per_layer + 2 * batch_size * seq_len * h * v)
 
     def forward(self, enc_input_ids, enc_position_ids=None, enc_attn_mask=None, dec_input_ids=None,
-                dec_position_ids=None, tokentype_ids=None, pooling_sequence_index=0, enc_hidden_states=None):
+                dec_position_ids=None, tokentype_ids=None, pooling_sequence_index=0, enc_hidden_states=None,
+                dec_attn_mask=None, enc_dec_attn_mask=None):
+        """``enc_attn_mask`` / ``dec_attn_mask``: ``[batch, seq]`` key-padding masks (non-zero = real
+        token) of the encoder / decoder tokens; ``enc_dec_attn_mask``: mask of the encoder tokens as
+        cross attention sees them (defaults to ``enc_attn_mask``).  Masks without padding are dropped."""
         bs = enc_input_ids.shape[0] if enc_input_ids is not None else None
+        enc_mask = PaddingMask.prepare(enc_attn_mask)
+        dec_mask = PaddingMask.prepare(dec_attn_mask)
+        cross_mask = PaddingMask.prepare(enc_dec_attn_mask) if enc_dec_attn_mask is not None else enc_mask
         if self.pre_process:
             hidden = self.embedding(enc_input_ids, enc_position_ids, tokentype_ids)
         else:
             hidden = None
         residual = None
         if self.encoder is not None and enc_hidden_states is None:
-            out = self.encoder(hidden, residual, batch_size=bs)
+            out = self.encoder(hidden, residual, batch_size=bs, attn_mask=enc_mask)
             if not (self.post_process or self.cfg.add_decoder):
                 return out      # (hidden, residual) handed to the next pipeline stage
             enc_out = out
@@ -101,7 +108,8 @@ class TransformerLanguageModel(nn.Module):
                 return enc_out, self.pooler(full, pooling_sequence_index)
             return enc_out
         dec_hidden = self.embedding(dec_input_ids, dec_position_ids, None)
-        dec_out = self.decoder(dec_hidden, None, encoder_output=enc_out, batch_size=dec_input_ids.shape[0])
+        dec_out = self.decoder(dec_hidden, None, encoder_output=enc_out, batch_size=dec_input_ids.shape[0],
+                               attn_mask=dec_mask, enc_mask=cross_mask)
         return dec_out, enc_out
 
     # ------------------------------------------------------------------ checkpoint layout

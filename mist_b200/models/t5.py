@@ -50,7 +50,8 @@ class T5Model(nn.Module):
         lm_labels = lm_labels if lm_labels is not None else labels
         dec_out, enc_out = self.language_model(
             encoder_input_ids, dec_input_ids=decoder_input_ids, tokentype_ids=tokentype_ids,
-            enc_hidden_states=enc_hidden_states)
+            enc_hidden_states=enc_hidden_states, enc_attn_mask=encoder_attn_mask, dec_attn_mask=decoder_attn_mask,
+            enc_dec_attn_mask=encoder_decoder_attn_mask)
         if not self.post_process:
             return dec_out, enc_out
         logits = self.lm_head(dec_out, self.language_model.embedding.word_embeddings.weight)

@@ -71,24 +71,28 @@ class ParallelTransformerLayer(nn.Module):
             return F.bias_dropout_add(x, None, None, self.hidden_dropout, seed)
         return x
 
-    def forward(self, hidden, residual=None, encoder_output=None, batch_size: Optional[int] = None):
-        """Returns ``(hidden, residual)``; the caller's next norm adds them."""
+    def forward(self, hidden, residual=None, encoder_output=None, batch_size: Optional[int] = None,
+                attn_mask=None, enc_mask=None):
+        """Returns ``(hidden, residual)``; the caller's next norm adds them.  ``attn_mask`` /
+        ``enc_mask``: prepared padding masks (:class:`~mist_b200.modules.layers.PaddingMask`) of this
+        stack's tokens and of the encoder output that cross attention reads."""
         bs = batch_size if batch_size is not None else hidden.shape[0]
         if not self.parallel_block:
             x, residual = self.norm1(hidden, residual)
-            hidden = self._drop(self.attn(x, batch_size=bs))
+            hidden = self._drop(self.attn(x, batch_size=bs, attention_mask=attn_mask))
             if hidden.shape != residual.shape:
                 hidden = hidden.reshape(residual.shape)
             if self.is_decoder:
                 x, residual = self.norm_cross(hidden, residual)
-                hidden = self._drop(self.cross_attn(x, x_kv=encoder_output, batch_size=bs)).reshape(residual.shape)
+                hidden = self._drop(self.cross_attn(x, x_kv=encoder_output, batch_size=bs, attention_mask=attn_mask,
+                                                    kv_mask=enc_mask)).reshape(residual.shape)
             x, residual = self.norm2(hidden, residual)
             hidden = self._drop(self.mlp(x)).reshape(residual.shape)
             return hidden, residual
         # parallel block: attention and MLP read the same stream
         x1, residual = self.norm1(hidden, residual)
         x2 = x1 if self.tied_norm else self.norm2(residual, None)[0]
-        a = self._drop(self.attn(x1, batch_size=bs)).reshape(residual.shape)
+        a = self._drop(self.attn(x1, batch_size=bs, attention_mask=attn_mask)).reshape(residual.shape)
         m = self._drop(self.mlp(x2)).reshape(residual.shape)
         return a + m, residual
 
@@ -125,7 +129,7 @@ class ParallelTransformer(nn.Module):
         """Pipeline stages other than the first take their input from the previous stage."""
         self.input_tensor = t
 
-    def forward(self, hidden, residual=None, encoder_output=None, batch_size=None):
+    def forward(self, hidden, residual=None, encoder_output=None, batch_size=None, attn_mask=None, enc_mask=None):
         if self.input_tensor is not None:
             hidden = self.input_tensor
         n = len(self.layers)
@@ -138,9 +142,10 @@ class ParallelTransformer(nn.Module):
             with ctx:
                 if i >= first_ckpt and torch.is_grad_enabled():
                     from ..utils.checkpointing import checkpoint_block
-                    hidden, residual = checkpoint_block(layer, hidden, residual, encoder_output, batch_size)
+                    hidden, residual = checkpoint_block(layer, hidden, residual, encoder_output, batch_size,
+                                                        attn_mask, enc_mask)
                 else:
-                    hidden, residual = layer(hidden, residual, encoder_output, batch_size)
+                    hidden, residual = layer(hidden, residual, encoder_output, batch_size, attn_mask, enc_mask)
             if hooks is not None:
                 hidden, residual = hooks.after_layer(self, i, hidden, residual)
         if self.final_norm is not None:

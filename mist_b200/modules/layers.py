@@ -232,6 +232,55 @@ class VocabParallelEmbedding(nn.Module):
 
 
 # --------------------------------------------------------------------------- attention
+class PaddingMask:
+    """Key-padding mask of a batch, prepared once per forward pass and shared by every layer.
+
+    ``mask``: ``[batch, seq]``, non-zero = real token.  Attention then runs per sample over its real
+    tokens only (the tokens are sliced out when the padding is on the right, gathered otherwise) and
+    the rows of padded positions come back as zeros -- the same result as removing the padding,
+    running variable-length attention and padding the output again (reference:
+    ``unpad_input`` / ``pad_input`` around the attention core, mist/modules/mha.py:1233-1243,1332-1334).
+    Preparing the mask reads it back to the host once; a mask without padding costs nothing after that.
+    """
+
+    def __init__(self, mask: torch.Tensor):
+        assert mask.dim() == 2, "padding mask: [batch, seq] expected"
+        valid = mask != 0
+        b, s = valid.shape
+        lens = valid.sum(1)
+        prefix = (valid == (torch.arange(s, device=valid.device)[None, :] < lens[:, None])).all(1)
+        host = torch.stack([lens, prefix.long()], 1).tolist()
+        self.valid = valid
+        self.seq_len = s
+        self.lengths = [int(n) for n, _ in host]
+        self.is_prefix = [bool(p) for _, p in host]
+        self.indices = [None if self.is_prefix[i] else valid[i].nonzero().squeeze(1) for i in range(b)]
+        self.all_valid = all(n == s for n in self.lengths)
+
+    @staticmethod
+    def prepare(mask) -> Optional["PaddingMask"]:
+        """``None`` for no mask or a mask without padding; masks already prepared pass through."""
+        if mask is None:
+            return None
+        pm = mask if isinstance(mask, PaddingMask) else PaddingMask(mask)
+        return None if pm.all_valid else pm
+
+    def select(self, x: torch.Tensor, i: int) -> torch.Tensor:
+        """Real tokens of sample ``i`` of ``x`` ``[batch, seq, ...]`` as ``[1, n_i, ...]``."""
+        if self.is_prefix[i]:
+            return x[i:i + 1, :self.lengths[i]]
+        return x[i:i + 1].index_select(1, self.indices[i])
+
+    def restore(self, part: torch.Tensor, i: int) -> torch.Tensor:
+        """``[1, n_i, ...]`` back to ``[1, seq, ...]`` with zeros at the padded positions."""
+        n, s = self.lengths[i], self.seq_len
+        if n == s:
+            return part
+        if self.is_prefix[i]:
+            return torch.cat([part, part.new_zeros(1, s - n, *part.shape[2:])], 1)
+        return part.new_zeros(1, s, *part.shape[2:]).index_copy(1, self.indices[i], part)
+
+
 class ParallelMHA(nn.Module):
     """Multi-head (self or cross) attention with heads split over the tensor-parallel group.
 
@@ -283,6 +332,20 @@ class ParallelMHA(nn.Module):
             probs = torch.nn.functional.dropout(probs, self.dropout)
         return torch.matmul(probs, v.transpose(1, 2)).transpose(1, 2)
 
+    def _attend_masked(self, q, k, v, causal, q_mask: Optional[PaddingMask], k_mask: Optional[PaddingMask]):
+        """Attention per sample over its real tokens; rows of padded queries are zero."""
+        outs = []
+        for i in range(q.shape[0]):
+            qi = q_mask.select(q, i) if q_mask is not None else q[i:i + 1]
+            ki = k_mask.select(k, i) if k_mask is not None else k[i:i + 1]
+            vi = k_mask.select(v, i) if k_mask is not None else v[i:i + 1]
+            if qi.shape[1] == 0 or ki.shape[1] == 0:
+                oi = qi.new_zeros(1, qi.shape[1], q.shape[2], q.shape[3])
+            else:
+                oi = self._attend(qi, ki, vi, causal)
+            outs.append(q_mask.restore(oi, i) if q_mask is not None else oi)
+        return torch.cat(outs, 0)
+
     def _forward_cached(self, x, residual=None):
         """Inference with a key/value cache (``self.inference_params`` set by
         :mod:`mist_b200.inference`): the new keys and values are appended to this layer's cache;
@@ -322,11 +385,14 @@ class ParallelMHA(nn.Module):
         ctx = ctx.reshape(b, s, -1)
         return self.out_proj(ctx, residual=residual)
 
-    def forward(self, x, x_kv=None, batch_size=None, residual=None):
+    def forward(self, x, x_kv=None, batch_size=None, residual=None, attention_mask: Optional[PaddingMask] = None,
+                kv_mask: Optional[PaddingMask] = None):
         """``x``: [b, s, h], or a [b*s/tp, h] token shard under sequence parallelism (then
-        ``batch_size`` is needed to recover the sequence length)."""
+        ``batch_size`` is needed to recover the sequence length).  ``attention_mask`` marks the
+        real tokens of ``x`` (queries, and keys too in self attention); ``kv_mask`` those of ``x_kv``."""
         if getattr(self, "inference_params", None) is not None:
             return self._forward_cached(x, residual)
+        masked = attention_mask is not None or kv_mask is not None
         if not self.cross_attn:
             qkv = self.Wqkv(x)
             if qkv.dim() == 2:
@@ -338,7 +404,12 @@ class ParallelMHA(nn.Module):
                 if self.rotary_emb_dim > 0:
                     cos, sin = F.rope_tables(s, self.rotary_emb_dim, self.rotary_emb_base, qkv.device)
                     rotary = (cos, sin, self.rotary_emb_dim)
-                if self.use_flash_attn:
+                if masked:
+                    if rotary is not None:      # positions are those of the padded layout
+                        qkv = _RotaryOutOfPlace.apply(qkv, *rotary)
+                    ctx = self._attend_masked(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], self.causal,
+                                              attention_mask, attention_mask)
+                elif self.use_flash_attn:
                     ctx = F.attention_qkvpacked(qkv, self.softmax_scale, self.causal, rotary)
                 else:
                     if rotary is not None:
@@ -356,7 +427,10 @@ class ParallelMHA(nn.Module):
                     q = qkv[..., : hq * d].reshape(b, s, hq, d)
                     k = qkv[..., hq * d: (hq + hk) * d].reshape(b, s, hk, d)
                 v = qkv[..., (hq + hk) * d:].reshape(b, s, hk, d)
-                ctx = self._attend(q, k, v, self.causal)
+                if masked:
+                    ctx = self._attend_masked(q, k, v, self.causal, attention_mask, attention_mask)
+                else:
+                    ctx = self._attend(q, k, v, self.causal)
         else:
             q = self.Wq(x)
             kv = self.Wkv(x_kv)
@@ -366,7 +440,10 @@ class ParallelMHA(nn.Module):
             b, sq = q.shape[:2]
             q = q.view(b, sq, self.local_heads, self.head_dim)
             kv = kv.view(b, kv.shape[1], 2, self.local_heads_kv, self.head_dim)
-            ctx = self._attend(q, kv[:, :, 0], kv[:, :, 1], False)
+            if masked:
+                ctx = self._attend_masked(q, kv[:, :, 0], kv[:, :, 1], False, attention_mask, kv_mask)
+            else:
+                ctx = self._attend(q, kv[:, :, 0], kv[:, :, 1], False)
         ctx = ctx.reshape(ctx.shape[0], ctx.shape[1], -1)
         return self.out_proj(ctx, residual=residual)
 

@@ -12,9 +12,11 @@ import torch
 from torch.utils.checkpoint import checkpoint
 
 
-def checkpoint_block(layer, hidden, residual, encoder_output, batch_size):
+def checkpoint_block(layer, hidden, residual, encoder_output, batch_size, attn_mask=None, enc_mask=None):
+    # the padding masks travel in the closure: the recomputation must see this call's masks even when
+    # later micro batches have run their forward in between
     def run(h, r, e):
-        return layer(h, r, e, batch_size)
+        return layer(h, r, e, batch_size, attn_mask, enc_mask)
 
     return checkpoint(run, hidden, residual, encoder_output, use_reentrant=False, preserve_rng_state=True)
 

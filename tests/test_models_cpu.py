@@ -101,3 +101,76 @@ def test_exec_entry_point_runs_every_family_on_cpu(fam, tmp_path):
     assert "Throughput:" in r.stdout
     s = json.load(open(tmp_path / "summary.json"))
     assert float(s["exec_total_cost"]) > 0
+
+
+# ------------------------------------------------------------------------------ padding masks
+def _masks(b, s):
+    """One right-padded sample, one sample with holes, one without padding."""
+    m = torch.ones(b, s, dtype=torch.bool)
+    m[0, s - 5:] = False
+    m[1, 3] = m[1, 10] = m[1, s - 1] = False
+    return m
+
+
+@pytest.mark.parametrize("flash", [True, False])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_with_padding_mask_equals_attention_over_the_real_tokens(flash, causal):
+    from mist_b200.modules.layers import PaddingMask, ParallelMHA
+    torch.manual_seed(0)
+    b, s, h = 3, 16, 32
+    mha = ParallelMHA(h, 4, causal=causal, use_flash_attn=flash, device="cpu", dtype=torch.float32)
+    x = torch.randn(b, s, h, requires_grad=True)
+    mask = _masks(b, s)
+    out = mha(x, attention_mask=PaddingMask.prepare(mask))
+    g = torch.randn_like(out) * mask[..., None]
+    out.backward(g)
+    bias = mha.out_proj.bias.detach()
+    for i in range(b):
+        xi = x.detach()[i:i + 1, mask[i]].clone().requires_grad_(True)
+        oi = mha(xi)
+        assert torch.allclose(out[i, mask[i]], oi[0], atol=1e-5)
+        assert torch.allclose(out[i, ~mask[i]], bias.expand(int((~mask[i]).sum()), h), atol=1e-6)   # zero context
+        oi.backward(g[i:i + 1, mask[i]])
+        assert torch.allclose(x.grad[i, mask[i]], xi.grad[0], atol=1e-5)
+        assert x.grad[i, ~mask[i]].abs().max() == 0 if (~mask[i]).any() else True
+    assert PaddingMask.prepare(torch.ones(b, s)) is None      # no padding: the plain path is taken
+
+
+def test_bert_with_padding_mask_matches_the_unpadded_sample():
+    torch.manual_seed(0)
+    cfg = _cfg("bert")
+    m = base_model_provider(cfg, device="cpu", dtype=torch.float32)
+    m.language_model.encoder.gradient_checkpointing = 1
+    b, s = 2, 32
+    batch = get_inputs_provider("bert")(b, s, 256, "cpu", seed=3)
+    mask = torch.ones(b, s, dtype=torch.bool)
+    mask[0, 20:] = False
+    logits, _ = m(batch["input_ids"], attention_mask=mask, tokentype_ids=batch["tokentype_ids"])
+    alone, _ = m(batch["input_ids"][:1, :20], tokentype_ids=batch["tokentype_ids"][:1, :20])
+    assert torch.allclose(logits[0, :20], alone[0], atol=1e-4)
+    full, _ = m(batch["input_ids"][1:], tokentype_ids=batch["tokentype_ids"][1:])
+    assert torch.allclose(logits[1], full[0], atol=1e-4)
+    # the loss is differentiable through the masked path with recomputation
+    loss = m(batch["input_ids"], attention_mask=mask, tokentype_ids=batch["tokentype_ids"], lm_labels=batch["lm_labels"])
+    loss.backward()
+    enc_params = list(m.language_model.encoder.parameters())
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in enc_params)
+
+
+def test_t5_cross_attention_ignores_padded_encoder_tokens():
+    torch.manual_seed(0)
+    cfg = _cfg("t5")
+    m = base_model_provider(cfg, device="cpu", dtype=torch.float32)
+    batch = get_inputs_provider("t5")(2, 32, 256, "cpu", seed=4)
+    enc, dec = batch["encoder_input_ids"], batch["decoder_input_ids"]
+    mask = torch.ones_like(enc, dtype=torch.bool)
+    mask[0, 24:] = False
+    logits = m(enc, dec, encoder_attn_mask=mask)
+    alone = m(enc[:1, :24], dec[:1])
+    assert torch.allclose(logits[0], alone[0], atol=1e-4)
+    other = m(enc[1:], dec[1:])
+    assert torch.allclose(logits[1], other[0], atol=1e-4)
+    # changing a padded encoder token changes nothing
+    enc2 = enc.clone()
+    enc2[0, 30] = (enc2[0, 30] + 7) % 256
+    assert torch.allclose(m(enc2, dec, encoder_attn_mask=mask), logits, atol=1e-6)
