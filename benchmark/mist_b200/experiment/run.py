@@ -48,6 +48,8 @@ def main(argv=None):
     ap.add_argument("--out", default="experiment_results")
     ap.add_argument("--skip-exec", action="store_true", help="tune + analyze only (no GPUs needed)")
     ap.add_argument("--hosts", default=None, help="comma separated worker hosts for multi-node exec (pdsh)")
+    ap.add_argument("--master-addr", default=None, help="rendezvous address (default: the first host, or 127.0.0.1)")
+    ap.add_argument("--master-port", type=int, default=29533)
     args = ap.parse_args(argv)
     base = [f"experiment={args.experiment}", f"model={args.model}", f"hardware.num_nodes={args.nnodes}",
             f"hardware.num_gpus_per_node={args.nproc_per_node}", f"training.global_batch_size={args.global_batch_size}",
@@ -71,12 +73,19 @@ def main(argv=None):
         seen[sol] = space
         if args.skip_exec:
             continue
+        multi = args.nnodes > 1 and args.hosts
+        master = args.master_addr or (args.hosts.split(",")[0] if multi else "127.0.0.1")
         launcher = [sys.executable, "-m", "torch.distributed.run", f"--nnodes={args.nnodes}",
-                    f"--nproc-per-node={args.nproc_per_node}", "--master-addr", "127.0.0.1", "--master-port", "29533"]
+                    f"--nproc-per-node={args.nproc_per_node}", "--master-addr", master,
+                    "--master-port", str(args.master_port)]
+        if multi:
+            launcher.append("--node-rank=%n")      # pdsh replaces %n by the host's position in the list
         cmd = launcher + [os.path.join(BENCH, "exec", "benchmark_one_case.py"), "--config-name", "best_config", "-cd", out,
                           f"output_dir={out}"]
-        if args.nnodes > 1 and args.hosts:
-            sh(["pdsh", "-w", args.hosts, " ".join(cmd)])
+        if multi:
+            # the output directory must be on storage every host sees (the tuned configuration is read
+            # there); one ssh fan-out runs the same launcher on every host
+            sh(["pdsh", "-S", "-R", "ssh", "-w", args.hosts, f"cd {os.getcwd()} && NCCL_ASYNC_ERROR_HANDLING=1 " + " ".join(cmd)])
         else:
             sh(cmd)
     merged = {}

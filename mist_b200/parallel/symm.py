@@ -65,8 +65,14 @@ def ptr_table(ptrs: List[int]):
 def group_on_one_node(group) -> bool:
     """True when every rank of ``group`` runs on this host (peer memory over NVLink / CUDA IPC
     needs that; groups that span nodes stay on the NCCL paths)."""
+    import os
     import socket
     if group is None or not dist.is_initialized():
+        return True
+    # a launcher that reports as many local ranks as ranks in the job runs on one node: no
+    # collective is needed to know it (the same answer on every rank)
+    lw, w = os.environ.get("LOCAL_WORLD_SIZE"), os.environ.get("WORLD_SIZE")
+    if lw is not None and w is not None and lw == w:
         return True
     names: List[Optional[str]] = [None] * dist.get_world_size(group)
     dist.all_gather_object(names, socket.gethostname(), group=group)
