@@ -60,12 +60,19 @@ class TrainingSession:
             pre_process=self.ps.is_first_stage, post_process=self.ps.is_last_stage,
             layer_range=lr if multi_stage else None, sequence_parallel=self.sequence_parallel,
             device=device, dtype=dtype)
+        # a table tied across the first and the last stage: pair the ranks and copy it over once
+        tied_group = None
+        if bool(getattr(cfg.model, "tie_word_embeddings", False)) and multi_stage and world > 1:
+            tied_group = self.ps.create_embedding_group(getattr(cfg, "nccl_timeout", 120))
+            tied = self.model.tied_parameter() if hasattr(self.model, "tied_parameter") else None
+            if tied is not None:
+                dist.broadcast(tied.data, src=self.ps.embedding_src, group=tied_group)
         pre_post = StageStrategy.from_vector(st.pre_post_strategy_array) if st.pre_post_strategy == "preset" else None
         self.engine = TrainEngine(self.model, self.ps, self.strategy, self.G, st.gradient_checkpointing[stage],
                                   hp=hp, comm_backend=self.comm_backend, overlap=bool(cfg.get("overlap", True)),
                                   zero3_gather=str(cfg.get("zero3_gather", "nccl")),
                                   use_grad_ring=bool(cfg.get("use_memory_buffer", True)),
-                                  pre_post_strategy=pre_post)
+                                  pre_post_strategy=pre_post, tied_group=tied_group)
         self.pipeline = None
         if multi_stage:
             from .parallel.pipeline import PipelineSchedule

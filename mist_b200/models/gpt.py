@@ -19,11 +19,6 @@ class GPTModel(nn.Module):
         super().__init__()
         self.cfg, self.pre_process, self.post_process = cfg, pre_process, post_process
         self._verify_config(cfg)
-        if cfg.tie_word_embeddings and not (pre_process and post_process):
-            raise NotImplementedError(
-                "tie_word_embeddings with the embedding and the head on different pipeline stages: the two "
-                "copies would need a gradient all-reduce between the first and the last stage, which the "
-                "pipeline schedule does not issue; untie them (the packaged configurations do) or keep one stage")
         self.language_model = TransformerLanguageModel(
             cfg, pre_process, post_process, process_groups, pre_post_process_group, layer_range,
             sequence_parallel, device, dtype)
@@ -31,6 +26,16 @@ class GPTModel(nn.Module):
         if post_process:
             self.lm_head = LMHead(cfg, self.language_model.pre_post_process_group, sequence_parallel,
                                   device, dtype)
+        # Tied embeddings with the embedding and the head on different pipeline stages: the first
+        # stage keeps the table, the last stage a copy of it as its projection weight.  The training
+        # session copies the table into the copy once and the engine sums the two gradients over
+        # the (first stage, last stage) rank pairs before each optimizer step, so the two stay equal.
+        self.tied_across_stages = bool(cfg.tie_word_embeddings) and not (pre_process and post_process)
+        if self.tied_across_stages:
+            if pre_process:
+                self.language_model.embedding.word_embeddings.weight._tied_across_stages = True
+            if post_process:
+                self.lm_head.proj.weight._tied_across_stages = True
 
     def _verify_config(self, cfg: ModelConfig):
         assert cfg.add_encoder and not cfg.add_decoder and not cfg.add_pooler, \
@@ -47,13 +52,21 @@ class GPTModel(nn.Module):
         if not self.post_process:
             return out
         tied = None
-        if self.cfg.tie_word_embeddings:
+        if self.cfg.tie_word_embeddings and not self.tied_across_stages:
             tied = self.language_model.embedding.word_embeddings.weight
         return self.lm_head(out, labels, tied)
 
+    def tied_parameter(self):
+        """This stage's copy of the table tied across pipeline stages (``None`` on other stages)."""
+        if not self.tied_across_stages:
+            return None
+        if self.pre_process:
+            return self.language_model.embedding.word_embeddings.weight
+        return self.lm_head.proj.weight if self.post_process else None
+
     def state_dict_for_save_checkpoint(self, prefix="", keep_vars=False):
         sd = {"language_model": self.language_model.state_dict_for_save_checkpoint(prefix, keep_vars)}
-        if self.lm_head is not None and not self.cfg.tie_word_embeddings:
+        if self.lm_head is not None and (not self.cfg.tie_word_embeddings or self.tied_across_stages):
             sd["lm_head"] = self.lm_head.state_dict(prefix=prefix, keep_vars=keep_vars)
         return sd
 

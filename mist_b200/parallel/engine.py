@@ -91,7 +91,7 @@ class TrainEngine:
                  strategy: Optional[StageStrategy] = None, grad_accum_steps: int = 1,
                  ckpt_layers: int = 0, hp: Optional[Dict] = None, comm_backend: str = "nccl",
                  grad_dtype: Optional[torch.dtype] = None, overlap: bool = True,
-                 pre_post_strategy: Optional[StageStrategy] = None, use_grad_ring: bool = True,
+                 pre_post_strategy: Optional[StageStrategy] = None, use_grad_ring: bool = True, tied_group=None,
                  zero3_gather: str = "nccl"):
         self.model = model
         self.ps = pstate or ParallelState.single()
@@ -149,8 +149,16 @@ class TrainEngine:
                     pre_ids.add(id(p))
         post_params = [(n, p) for n, p in model.named_parameters()
                        if id(p) not in layer_params and id(p) not in pre_ids]
-        self.pre_unit = FlatUnit("pre", pre_params, zero=min(pp_zero, ZeroLevel.OPT_GRAD), **mk) if pre_params else None
-        self.post_unit = FlatUnit("post", post_params, zero=min(pp_zero, ZeroLevel.OPT_GRAD), **mk) if post_params else None
+        # A table tied across pipeline stages (the embedding here, the output projection on the last
+        # stage, or the other way round): its gradient is summed with the other stage's once per
+        # iteration, on the full gradient, so the unit that holds it keeps unsharded gradients and
+        # reduces them after the last micro step only (at most ZeRO-1).
+        self.tied_group = tied_group
+        self._deferred_tied: List[FlatUnit] = []
+        has_tied = tied_group is not None and any(getattr(p, "_tied_across_stages", False) for p in model.parameters())
+        pp_cap = ZeroLevel.OPT if has_tied else ZeroLevel.OPT_GRAD
+        self.pre_unit = FlatUnit("pre", pre_params, zero=min(pp_zero, pp_cap), **mk) if pre_params else None
+        self.post_unit = FlatUnit("post", post_params, zero=min(pp_zero, pp_cap), **mk) if post_params else None
         for stack in self.stacks:
             self.units.extend(self.layer_units[id(stack)])
         for u in (self.pre_unit, self.post_unit):
@@ -170,6 +178,8 @@ class TrainEngine:
                 for p, o in zip(u.params, u.offsets):
                     if getattr(p, "_tp_partial_grad", False) or (sp_on and getattr(p, "_sequence_parallel", False)):
                         u.tp_sum_slices.append((o, p.numel()))
+            u.tied_slices = [(o, p.numel()) for p, o in zip(u.params, u.offsets)
+                             if has_tied and getattr(p, "_tied_across_stages", False)]
 
         # -------------------------------------------------------- buckets, state, streams
         from .swap import ActivationSwapper, SwapStreams
@@ -190,7 +200,10 @@ class TrainEngine:
             if self.use_grad_ring and u in layer_units:
                 u.ring_slot = None
             else:
-                u.bind_grad_bucket(torch.zeros(u.padded, dtype=self.grad_dtype, device=self.device))
+                # a unit that accumulates over micro steps although the stage shards its gradients
+                # (the tied table's unit) accumulates in fp32 like every other accumulating bucket
+                gdt = torch.float32 if (u.tied_slices and self.G > 1) else self.grad_dtype
+                u.bind_grad_bucket(torch.zeros(u.padded, dtype=gdt, device=self.device))
             u.init_optimizer_state(offload_ratio=oo if u in layer_units else 0.0)
             if u in layer_units:      # like the optimizer state, only the blocks' tensors are offloaded
                 u.enable_weight_offload(wo)
@@ -427,12 +440,36 @@ class TrainEngine:
             t.copy_(flat[off:off + t.numel()])
             off += t.numel()
 
+    def _sum_tied_grads(self, unit: FlatUnit):
+        """Sums the gradient of the table tied across pipeline stages with the other stage's copy."""
+        for o, n in unit.tied_slices:
+            dist.all_reduce(unit.flat_grad[o:o + n], group=self.tied_group)
+
+    def flush_tied(self):
+        """End of the pipeline schedule: the units that hold a table tied across stages sum its
+        gradient with the other stage's copy, reduce and step.  This cannot happen where the unit's
+        backward pass ends: the last stage reaches that point at the start of its last backward pass,
+        the first stage at the very end of the iteration, and the first stage needs the last stage to
+        keep going in between."""
+        units, self._deferred_tied = self._deferred_tied, []
+        for unit in units:
+            with self._on_comm():
+                self._sum_tied_grads(unit)
+            self._reduce_and_step(unit, True)
+
     def _unit_backward_done(self, unit: FlatUnit):
         last = self._micro == self.G - 1
         unit.collect_autograd_grads()
         if unit.tp_sum_slices and (last or unit.zero >= ZeroLevel.OPT_GRAD):
             with self._on_comm():
                 self._tp_sum_partial_grads(unit)
+        if unit.tied_slices:
+            if last:
+                self._deferred_tied.append(unit)
+            return          # gradients accumulate in the unit's bucket until the end of the iteration
+        self._reduce_and_step(unit, last)
+
+    def _reduce_and_step(self, unit: FlatUnit, last: bool):
         if self.fused is not None and self.fused.handles(unit) and not unit.opt_host_numel:
             self.fused.reduce_and_step(unit, last)
             return

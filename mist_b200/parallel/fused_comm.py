@@ -71,7 +71,9 @@ class FusedDPComm:
         torch.distributed.barrier(group=self.group)
 
     def _eligible(self, u: FlatUnit) -> bool:
-        return u.zero >= ZeroLevel.OPT and u.dp_size > 1
+        # a unit whose gradient is first summed with another pipeline stage's copy (tied table)
+        # stays on the library path: that sum sits between the backward pass and this reduction
+        return u.zero >= ZeroLevel.OPT and u.dp_size > 1 and not getattr(u, "tied_slices", None)
 
     def handles(self, u: FlatUnit) -> bool:
         return u.name in self.tables

@@ -243,6 +243,7 @@ class PipelineSchedule:
             _, grad = self._exchange(recv_bwd=True)
             gx = bwd(grad)
             self._exchange(send_bwd=gx)
+        self.engine.flush_tied()
         if self.last:
             return torch.stack(losses).mean()
         return torch.zeros((), device=self.device)

@@ -174,6 +174,26 @@ class ParallelState:
                 if rank in g:
                     self.dp_group, self.dp_ag_group, self.dp_rs_group = a, b, c
 
+    def create_embedding_group(self, timeout_s: int = 120):
+        """Pairs every rank of the first pipeline stage with the rank of the last stage that holds the
+        same (data-parallel, tensor-parallel) position: the two keep copies of a word-embedding table
+        that is tied to the output projection and sum its gradient over this group.  Collective over
+        the world (every rank creates every pair); returns this rank's pair or ``None``."""
+        first, last = self.plan.stage_to_ranks[0], self.plan.stage_to_ranks[self.num_stages - 1]
+        f0, l0 = self.plan.ranks[first[0]], self.plan.ranks[last[0]]
+        assert (len(f0.dp_ranks), len(f0.tp_ranks)) == (len(l0.dp_ranks), len(l0.tp_ranks)), \
+            "tied embeddings across pipeline stages need the same dp x tp layout on the first and the last stage"
+        mine = None
+        to = datetime.timedelta(seconds=timeout_s)
+        for a, b in zip(first, last):
+            grp = dist.new_group([a, b], timeout=to)
+            if self.rank in (a, b):
+                mine = grp
+        self.embedding_group = mine
+        self.embedding_src = first[last.index(self.rank)] if self.rank in last else (
+            self.rank if self.rank in first else None)
+        return mine
+
     @classmethod
     def from_config(cls, cfg, rank: Optional[int] = None, create_groups: bool = True) -> "ParallelState":
         mesh = (cfg.hardware.num_nodes, cfg.hardware.num_gpus_per_node)

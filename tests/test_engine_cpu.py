@@ -375,7 +375,7 @@ def test_three_stage_pipeline_with_fewer_or_more_micro_batches_than_stages(G):
         assert abs(ret[2][0][it] - tot) < 2e-4, (it, ret[2][0], tot)
 
 
-def _ppdp_worker(rank, world, port, zero, ret, offload="0,0,0,0"):
+def _ppdp_worker(rank, world, port, zero, ret, offload="0,0,0,0", extra=()):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -385,7 +385,7 @@ def _ppdp_worker(rank, world, port, zero, ret, offload="0,0,0,0"):
             "model.num_hidden_layers=4", "hardware.num_gpus_per_node=4", "training.global_batch_size=4",
             "strategy.layer_partitions=[2,2]", "strategy.device_assignment=[[1,2],[1,2]]",
             "strategy.gradient_checkpointing=[1,0]", "strategy.gradient_accumulation_steps=2",
-            f"strategy.stage_strategies=[{vec},{vec}]", f"strategy.pre_post_strategy_array={vec}"],
+            f"strategy.stage_strategies=[{vec},{vec}]", f"strategy.pre_post_strategy_array={vec}"] + list(extra),
             check_world_size=False)
         sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
         ps = sess.ps
@@ -405,16 +405,20 @@ def _ppdp_worker(rank, world, port, zero, ret, offload="0,0,0,0"):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("zero,offload", [((0, 0, 1), "0,0,0,0"), ((0, 1, 1), "0,0,0,0"), ((1, 1, 1), "0,0,0,0"),
-                                          ((0, 1, 1), "0.5,0.5,0.5,0"), ((1, 1, 1), "0.5,0.5,0.5,0")])
-def test_pipeline_with_data_parallel_stages_and_zero(zero, offload):
+@pytest.mark.parametrize("zero,offload,tied", [
+    ((0, 0, 1), "0,0,0,0", False), ((0, 1, 1), "0,0,0,0", False), ((1, 1, 1), "0,0,0,0", False),
+    ((0, 1, 1), "0.5,0.5,0.5,0", False), ((1, 1, 1), "0.5,0.5,0.5,0", False),
+    # word embeddings tied to the output projection, the two on different stages
+    ((0, 0, 1), "0,0,0,0", True), ((0, 1, 1), "0,0,0,0", True), ((1, 1, 1), "0,0,0,0", True)])
+def test_pipeline_with_data_parallel_stages_and_zero(zero, offload, tied):
     world = 4
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 28500 + (os.getpid() + hash((zero, offload))) % 1500
-    mp.spawn(_ppdp_worker, args=(world, port, zero, ret, offload), nprocs=world, join=True)
+    port = 28500 + (os.getpid() + hash((zero, offload, tied))) % 1500
+    extra = ["model.tie_word_embeddings=true"] if tied else []
+    mp.spawn(_ppdp_worker, args=(world, port, zero, ret, offload, extra), nprocs=world, join=True)
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + ["model.num_hidden_layers=4",
-                                                                    "strategy.layer_partitions=[4]"],
+                                                                    "strategy.layer_partitions=[4]"] + extra,
                          check_world_size=False)
     from mist_b200.models.provider import base_model_provider as bmp
     torch.manual_seed(0)
@@ -454,4 +458,6 @@ def test_pipeline_with_data_parallel_stages_and_zero(zero, offload):
                 head, rest = n.split(".layers.")
                 idx, tail = rest.split(".", 1)
                 n = f"{head}.layers.{int(idx) + 2 * stage}.{tail}"
+            if tied and n == "lm_head.proj.weight":      # the last stage's copy of the tied table
+                n = "language_model.embedding.word_embeddings.weight"
             assert (p - new_state[n].detach()).abs().max().item() < 2e-4, (r, n)
