@@ -18,7 +18,7 @@ import torch
 import torch.distributed as dist
 
 from .config import MistConfig, StageStrategy, load_config
-from .models.provider import base_model_provider, get_inputs_provider
+from .models.provider import base_model_provider, family_of, get_inputs_provider
 from .parallel.engine import TrainEngine
 from .parallel.state import ParallelState
 
@@ -62,7 +62,8 @@ class TrainingSession:
             device=device, dtype=dtype)
         # a table tied across the first and the last stage: pair the ranks and copy it over once
         tied_group = None
-        if bool(getattr(cfg.model, "tie_word_embeddings", False)) and multi_stage and world > 1:
+        ties = bool(getattr(cfg.model, "tie_word_embeddings", False)) or family_of(cfg.model.name) == "bert"
+        if ties and multi_stage and world > 1:
             tied_group = self.ps.create_embedding_group(getattr(cfg, "nccl_timeout", 120))
             tied = self.model.tied_parameter() if hasattr(self.model, "tied_parameter") else None
             if tied is not None:
@@ -103,8 +104,8 @@ class TrainingSession:
             parts = {k: v.chunk(self.G) for k, v in batch.items()}
             batches = [{k: parts[k][i] for k in batch} for i in range(self.G)]
         if self.pipeline is not None:
-            assert set(batch) <= {"input_ids", "labels", "position_ids"}, \
-                "pipeline stages exchange one hidden-state tensor: decoder-only families only"
+            assert not self.cfg.model.add_decoder, \
+                "pipeline stages exchange one hidden-state tensor: single-stack families only (no encoder-decoder)"
             return self.pipeline.train_step(batches)
         return self.engine.train_step(batches)
 

@@ -55,9 +55,25 @@ class BertModel(nn.Module):
                 self.word_embeddings = nn.Embedding(cfg.vocab_size // dist_ops.group_size(grp), cfg.hidden_size,
                                                     device=device, dtype=dtype)
                 self.word_embeddings.weight._shared_params = True
+        # the masked-LM head always uses the word table: split over pipeline stages, the two copies are
+        # kept equal by the training session (one copy at start-up) and the engine (gradient sum)
+        self.tied_across_stages = not (pre_process and post_process)
+        if self.tied_across_stages:
+            if pre_process:
+                self.language_model.embedding.word_embeddings.weight._tied_across_stages = True
+            elif post_process:
+                self.word_embeddings.weight._tied_across_stages = True
 
     def set_input_tensor(self, t):
         self.language_model.set_input_tensor(t)
+
+    def tied_parameter(self):
+        """This stage's copy of the word table when the model is split over pipeline stages."""
+        if not self.tied_across_stages:
+            return None
+        if self.pre_process:
+            return self.language_model.embedding.word_embeddings.weight
+        return self.word_embeddings.weight if self.post_process else None
 
     def forward(self, input_ids, attention_mask=None, tokentype_ids=None, lm_labels=None, labels=None,
                 sentence_order=None):

@@ -461,3 +461,77 @@ def test_pipeline_with_data_parallel_stages_and_zero(zero, offload, tied):
             if tied and n == "lm_head.proj.weight":      # the last stage's copy of the tied table
                 n = "language_model.embedding.word_embeddings.weight"
             assert (p - new_state[n].detach()).abs().max().item() < 2e-4, (r, n)
+
+
+def _bert_pp_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        vec = "[2,1,1,0,0,0,0,0,0,0]"
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=bert/1.3b"] + TINY + [
+            "model.num_hidden_layers=4", "hardware.num_gpus_per_node=2", "training.global_batch_size=4",
+            "strategy.layer_partitions=[2,2]", "strategy.device_assignment=[[1,1],[1,1]]",
+            "strategy.gradient_checkpointing=[0,1]", "strategy.gradient_accumulation_steps=2",
+            f"strategy.stage_strategies=[{vec},{vec}]", f"strategy.pre_post_strategy_array={vec}"],
+            check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            losses.append(float(sess.step_on_device_batch(prov(4, 32, 256, "cpu", seed=500 + it))))
+        sess.finish()
+        ret[rank] = (sess.ps.stage, losses, {n: p.detach().clone() for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+def test_bert_over_two_pipeline_stages_keeps_the_tied_word_table_in_step():
+    """BERT's masked-LM head uses the word table of the first stage: split over two stages, both
+    copies must follow single-process training."""
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_bert_pp_worker, args=(world, 28100 + os.getpid() % 800, ret), nprocs=world, join=True)
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=bert/1.3b"] + TINY + [
+        "model.num_hidden_layers=4", "strategy.layer_partitions=[4]"], check_world_size=False)
+    from mist_b200.models.provider import base_model_provider as bmp
+    torch.manual_seed(0)
+    ref = bmp(cfg.model, device="cpu", dtype=torch.float32)
+    sd = ref.state_dict()
+    for stage in range(2):
+        torch.manual_seed(0 + 17 * stage)
+        m = bmp(cfg.model, pre_process=stage == 0, post_process=stage == 1, layer_range=(2 * stage, 2 * stage + 2),
+                device="cpu", dtype=torch.float32)
+        for n, p in m.state_dict().items():
+            if n == "word_embeddings.weight":
+                continue                  # the copy is overwritten by the first stage's table
+            if ".layers." in n:
+                head, rest = n.split(".layers.")
+                idx, tail = rest.split(".", 1)
+                n = f"{head}.layers.{int(idx) + 2 * stage}.{tail}"
+            sd[n] = p.clone()
+    ref.load_state_dict(sd)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=500 + it)
+        opt.zero_grad()
+        tot = 0.0
+        for g in range(2):
+            l = ref(**{k: v[2 * g:2 * g + 2] for k, v in b.items()}) / 2
+            l.backward()
+            tot += l.item()
+        opt.step()
+        assert abs(ret[1][1][it] - tot) < 2e-4, (it, ret[1][1], tot)
+    new_state = dict(ref.named_parameters())
+    for r in range(2):
+        stage, _, params = ret[r]
+        for n, p in params.items():
+            if ".layers." in n:
+                head, rest = n.split(".layers.")
+                idx, tail = rest.split(".", 1)
+                n = f"{head}.layers.{int(idx) + 2 * stage}.{tail}"
+            if n == "word_embeddings.weight":
+                n = "language_model.embedding.word_embeddings.weight"
+            assert (p - new_state[n].detach()).abs().max().item() < 2e-4, (r, n)
