@@ -15,13 +15,17 @@ from .language_model import TransformerLanguageModel
 class T5LMHead(nn.Module):
     """Tied vocabulary projection with a per-rank bias slice."""
 
-    def __init__(self, local_vocab, process_group=None, device=None, dtype=None):
+    def __init__(self, local_vocab, process_group=None, device=None, dtype=None, sequence_parallel=False):
         super().__init__()
         self.process_group = process_group
+        self.sequence_parallel = sequence_parallel
         self.bias = nn.Parameter(torch.zeros(local_vocab, device=device, dtype=dtype))
 
     def forward(self, hidden, word_embeddings_weight):
-        x = dist_ops.copy_to_group(hidden, self.process_group)
+        if self.sequence_parallel:      # token shards -> all tokens; the backward pass reduce-scatters
+            x = dist_ops.all_gather(hidden.reshape(-1, hidden.shape[-1]), self.process_group)
+        else:
+            x = dist_ops.copy_to_group(hidden, self.process_group)
         return F.linear(x, word_embeddings_weight, self.bias)
 
 
@@ -31,15 +35,15 @@ class T5Model(nn.Module):
                  sequence_parallel=False, device=None, dtype=None):
         super().__init__()
         assert cfg.add_encoder and cfg.add_decoder, "t5: encoder and decoder stacks expected"
-        assert not sequence_parallel, "t5: sequence parallelism is not wired for cross attention"
         self.cfg, self.pre_process, self.post_process = cfg, pre_process, post_process
         dtype = dtype or cfg.params_dtype
         self.language_model = TransformerLanguageModel(
             cfg, pre_process, post_process, process_groups, pre_post_process_group, layer_range,
-            False, device, dtype)
+            sequence_parallel, device, dtype)
         if post_process:
             grp = self.language_model.pre_post_process_group
-            self.lm_head = T5LMHead(cfg.vocab_size // dist_ops.group_size(grp), grp, device, dtype)
+            self.lm_head = T5LMHead(cfg.vocab_size // dist_ops.group_size(grp), grp, device, dtype,
+                                    sequence_parallel and dist_ops.group_size(grp) > 1)
 
     def set_input_tensor(self, t):
         self.language_model.set_input_tensor(t)

@@ -347,8 +347,6 @@ def _family_worker(rank, world, port, fam, sp, ref_state, ret):
 @pytest.mark.parametrize("fam", ["bert/1.3b", "t5/1.7b", "falcon/1.3b"])
 @pytest.mark.parametrize("sp", [False, True])
 def test_tp2_other_families_match_single_process(fam, sp):
-    if sp and fam.startswith("t5"):
-        pytest.skip("sequence parallelism is not wired through cross attention (the model asserts)")
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b", f"model={fam}"] + TINY[:8], check_world_size=False)
     torch.manual_seed(7)
     ref = base_model_provider(cfg.model, device="cpu", dtype=torch.float32)
