@@ -62,8 +62,13 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 
-template <int BN>
-__global__ void __launch_bounds__(kThreads, (BN == 64 ? 2 : 1))
+// SPLIT: the V tiles are requested by a producer warp of their own (warp 6) instead of by the thread
+// that also requests K.  In the single-producer loop the request for K of block j+1 sits behind the
+// wait for V's stage of block j (free only after the PV product of block j-2), so it is issued about
+// one block time before the S product needs it; with two producers K is requested as soon as the S
+// product of block j-1 has read its stage, two block times ahead.
+template <int BN, bool SPLIT>
+__global__ void __launch_bounds__(kThreads + (SPLIT ? 32 : 0), (BN == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   using L = Smem<BN>;
@@ -152,11 +157,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_expect_tx(&k_full[st], p.nchunks * chunk_kv);
         for (int c = 0; c < p.nchunks; ++c)
           tma_load_4d(sk_ + c * chunk_kv, &tm_k, &k_full[st], 64 * c, head_kv, j * BN, batch);
+        if (SPLIT) continue;      // warp 6 requests V
         if (j >= kStages && !mbar_wait(&kv_empty[st], ((j / kStages) - 1) & 1)) {
           report(p.status, MB_ERR_TIMEOUT_EMPTY);
           ok = false;
           break;
         }
+        mbar_expect_tx(&v_full[st], p.nchunks * chunk_kv);
+        for (int c = 0; c < p.nchunks; ++c)
+          tma_load_4d(sv_ + c * chunk_kv, &tm_v, &v_full[st], 64 * c, head_kv, j * BN, batch);
+      }
+    }
+  } else if (SPLIT && warp == 6) {
+    // ---------------------------------------------------------- TMA producer for V
+    if (lane == 0) {
+      for (int j = 0; j < nblocks; ++j) {
+        int st = j % kStages;
+        if (j >= kStages && !mbar_wait(&kv_empty[st], ((j / kStages) - 1) & 1)) {
+          report(p.status, MB_ERR_TIMEOUT_EMPTY);
+          break;
+        }
+        uint8_t* sv_ = smem + L::oV + st * L::kKV;
         mbar_expect_tx(&v_full[st], p.nchunks * chunk_kv);
         for (int c = 0; c < p.nchunks; ++c)
           tma_load_4d(sv_ + c * chunk_kv, &tm_v, &v_full[st], 64 * c, head_kv, j * BN, batch);
@@ -404,9 +425,15 @@ bool make_map(CUtensorMap* m, const void* base, int batch, int tokens, int heads
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int g_fwd_variant = 0;      // 1: separate producer warp for V (block size 64)
+
 }  // namespace
 
 MB_API int* mb_status_device_ptr();
+
+// Chooses the forward kernel for later calls with block size 64: 0 = one producer thread for K and V
+// (default), 1 = K and V requested by two producer warps.
+MB_API void mb_attn_fwd_set_variant(int v) { g_fwd_variant = (v == 1) ? 1 : 0; }
 
 // q: [batch][sq][nh][d], k/v: [batch][sk][nh_kv][d], element strides given per tensor
 // (so views into a packed qkv buffer work).  o: [batch][sq][nh][d] with its own strides.
@@ -439,8 +466,17 @@ MB_API int mb_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   p.causal = causal;
   p.status = mb_status_device_ptr();
   dim3 grid((sq + BM - 1) / BM, nh, batch);
-  if (bn == 64) {
-    auto kern = attn_fwd_kernel<64>;
+  if (bn == 64 && g_fwd_variant == 1) {
+    auto kern = attn_fwd_kernel<64, true>;
+    static bool cfg = false;
+    if (!cfg) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               Smem<64>::kTotal) != cudaSuccess) return -3;
+      cfg = true;
+    }
+    kern<<<grid, kThreads + 32, Smem<64>::kTotal, stream>>>(tq, tk, tv, p);
+  } else if (bn == 64) {
+    auto kern = attn_fwd_kernel<64, false>;
     static bool cfg = false;
     if (!cfg) {
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -449,7 +485,7 @@ MB_API int mb_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
     }
     kern<<<grid, kThreads, Smem<64>::kTotal, stream>>>(tq, tk, tv, p);
   } else {
-    auto kern = attn_fwd_kernel<128>;
+    auto kern = attn_fwd_kernel<128, false>;
     static bool cfg = false;
     if (!cfg) {
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -71,8 +71,8 @@ def _native_backward(dout, q, k, v, o, lse, scale, causal, out):
     else:
         dq, dk, dv = out
     dout = dout.contiguous()
-    from .functional import Settings
-    native.kernels().mb_attn_bwd_set_variant(1 if Settings.attn_bwd_pipelined else 0)
+    from .functional import Settings, _select_variant
+    _select_variant("mb_attn_bwd_set_variant", 1 if Settings.attn_bwd_pipelined else 0)
     delta = torch.empty(b, nh, sq, dtype=torch.float32, device=q.device)
     dq_acc = torch.empty(b, nh, sq, d, dtype=torch.float32, device=q.device)   # zeroed by the launch wrapper
     call("mb_attn_bwd", ptr(dout), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(dq_acc),

@@ -47,6 +47,10 @@ class Settings:
     gemm_backend = "tcgen05"      # "tcgen05" (ours) | "cublas" (library, A/B baseline)
     attn_backend = "tcgen05"      # "tcgen05" (ours) | "sdpa" (library, A/B baseline)
     attn_block_n = 64
+    # Forward kernel with K and V requested by two producer warps (K is then requested two blocks ahead of
+    # its S product instead of one).  Same barriers as the default kernel; not yet timed or checked on a
+    # device, so it is opt-in (also MIST_B200_ATTN_FWD_SPLIT=1).
+    attn_fwd_split_producers = os.environ.get("MIST_B200_ATTN_FWD_SPLIT") == "1"
     # Backward kernel that overlaps the next block's S / dP products with the current block's softmax
     # (head size <= 96).  Its barrier protocol is model-checked on the CPU; its numerics have not been
     # checked on a device yet, so it is opt-in (also MIST_B200_ATTN_BWD_PIPELINED=1).
@@ -612,6 +616,17 @@ def _ref_attention(q, k, v, scale, causal):
     return o.to(q.dtype), lse
 
 
+_VARIANTS = {}
+
+
+def _select_variant(setter: str, want: int):
+    """Tells the library which kernel variant to launch; only called when the choice changes
+    (the library starts with variant 0)."""
+    if _VARIANTS.get(setter, 0) != want:
+        getattr(native.kernels(), setter)(want)
+        _VARIANTS[setter] = want
+
+
 def attn_fwd(q, k, v, scale, causal, block_n=None):
     """Forward only: returns (o [b,sq,nh,d], lse [b,nh,sq] fp32)."""
     if not use_native(q):
@@ -621,6 +636,7 @@ def attn_fwd(q, k, v, scale, causal, block_n=None):
     assert q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1
     o = torch.empty(b, sq, nh, d, dtype=q.dtype, device=q.device)
     lse = torch.empty(b, nh, sq, dtype=torch.float32, device=q.device)
+    _select_variant("mb_attn_fwd_set_variant", 1 if Settings.attn_fwd_split_producers else 0)
     call("mb_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), b, sq, sk, nh, nkv, d,
          q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
          v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),

@@ -78,6 +78,29 @@ def test_attention_qkvpacked_grad(d, rot):
 
 
 @pytest.mark.skipif(os.environ.get("MIST_B200_UNVALIDATED_KERNELS") != "1",
+                    reason="forward kernel with two producer warps: opt-in until it has been checked on a device")
+@pytest.mark.parametrize("d", [128, 80, 64])
+@pytest.mark.parametrize("causal", [True, False])
+def test_attn_fwd_split_producers_matches_reference(d, causal):
+    torch.manual_seed(5)
+    b, s, nh = 2, 1000, 3
+    qkv = torch.randn(b, s, 3, nh, d, device=DEV, dtype=torch.bfloat16)
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    scale = 1 / math.sqrt(d)
+    F.Settings.attn_fwd_split_producers = True
+    try:
+        o, lse = F.attn_fwd(q, k, v, scale, causal, block_n=64)
+        torch.cuda.synchronize()
+    finally:
+        F.Settings.attn_fwd_split_producers = False
+    from mist_b200.ops import native
+    native.check_status()
+    o_ref, lse_ref = F._ref_attention(q.float(), k.float(), v.float(), scale, causal)
+    assert _rel_err(o, o_ref) < 2e-2
+    assert torch.allclose(lse, lse_ref, atol=2e-2, rtol=1e-3)
+
+
+@pytest.mark.skipif(os.environ.get("MIST_B200_UNVALIDATED_KERNELS") != "1",
                     reason="pipelined backward kernel: opt-in until its numerics have been checked on a device")
 @pytest.mark.parametrize("d", [80, 64, 96])
 @pytest.mark.parametrize("causal", [True, False])
