@@ -37,6 +37,7 @@ _SIGNATURES = {
     "mb_gemm_pair_bf16": ([_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _f, _i, _p], _i),
     "mb_decode_attn": ([_p, _p, _p, _p, _i, _i, _i, _i, _i, _l, _l, _l, _l, _l, _l, _f, _p], _i),
     "mb_norm_bwd_scratch_rows": ([_i, _i], _i),
+    "mb_norm_set_variant": ([_i], None),
     "mb_norm_fwd": ([_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _p], _i),
     "mb_norm_bwd": ([_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p], _i),
     "mb_gelu_fwd": ([_p, _p, _p, _z, _i, _p], _i),
