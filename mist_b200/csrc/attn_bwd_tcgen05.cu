@@ -410,7 +410,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------------
-// Pipelined variant (head size <= 96).  Same math, tiles and shared-memory layouts as the kernel
+// Pipelined variant.  Same math, tiles and shared-memory layouts as the kernel
 // above; what changes is who waits for whom:
 //
 //   * S^T and dP^T are double buffered in tensor memory and the MMA warp issues the two products
@@ -421,18 +421,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 //   * the dQ^T read-out (tensor memory -> transposed staging -> TMA reduce-add) has its own four
 //     warps, so the softmax warps go straight from one block to the next.
 //
-// Tensor memory (512 columns): S^T[2] 0..127, dP^T[2] 128..255, dQ^T 256..319, dV 320..415,
-// dK 416..511.  Warps 0-7 softmax / dS (and the dK, dV epilogue), warps 8-11 dQ, 12 TMA, 13 MMA.
+// Tensor memory (512 columns), head size <= 96: S^T[2] 0..127, dP^T[2] 128..255, dQ^T 256..319,
+// dV 320..415, dK 416..511; the products of block it wait until the dQ warps have read dQ^T of block
+// it-1.  Head size up to 128: dV 256..383, dK 384..511 and dQ^T of block it is written over
+// S^T[it & 1] (by then that buffer is in the softmax warps' registers); the next product that writes
+// the buffer, S^T of block it+2, waits until the dQ warps have read dQ^T out.
+// Warps 0-7 softmax / dS (and the dK, dV epilogue), warps 8-11 dQ, 12 TMA, 13 MMA.
 //
 // Barriers and the iteration `it` they belong to (b = it & 1, st = it % 3):
 //   q_full[st]   producer -> MMA      Q, dO of block it are in stage st
 //   q_empty[st]  MMA commit -> producer  the dV / dK / dQ products of block it have read stage st
 //   sdp_full[b]  MMA commit -> softmax   S^T[b], dP^T[b] of block it are complete
 //   pds_full     softmax (256) -> MMA    P^T, dS^T of block it are in shared memory (and S^T[b],
-//                                        dP^T[b] are in registers: block it+2 may overwrite them; the
-//                                        MMA warp has always waited for pds_full of block it by then)
+//                                        dP^T[b] are in registers: dQ^T of this block may overwrite
+//                                        S^T[b], block it+2 may overwrite dP^T[b])
 //   pds_empty    MMA commit -> softmax   the products of block it have read P^T, dS^T
-//   dq_full      MMA commit -> dQ warps  dQ^T of block it is complete
+//   dq_full[b]   MMA commit -> dQ warps  dQ^T of block it is complete (one barrier per buffer: the
+//                                        products of block it+1 do not wait for the dQ warps, so a
+//                                        single barrier could run two phases ahead of them)
 //   dq_empty     dQ warps (128) -> MMA   dQ^T of block it is in registers
 // A thread can arrive on pds_full / dq_empty for block it+1 only after a wait that itself needs the
 // phase of block it to have completed, so no phase is entered twice.
@@ -445,7 +451,7 @@ struct SmemPipe {
   static constexpr int kKV = 2 * BKV * 128;
   static constexpr int kQ = 2 * BQ * 128;
   static constexpr int kP = BKV * 128;
-  static constexpr int kDQ = 3 * BQ * 128;      // head size <= 96: three chunks of [64 q][32 fp32]
+  static constexpr int kDQ = 4 * BQ * 128;      // four chunks of [64 q][32 fp32]
   static constexpr int oK = 0;
   static constexpr int oV = oK + kKV;
   static constexpr int oQ = oV + kKV;           // kQStages stages of (Q, dO)
@@ -453,8 +459,8 @@ struct SmemPipe {
   static constexpr int oDS = oP + kP;
   static constexpr int oDQ = oDS + kP;
   static constexpr int oBar = oDQ + kDQ;
-  // kv_full, q_full[3], q_empty[3], sdp_full[2], pds_full, pds_empty, dq_full, dq_empty, final_full
-  static constexpr int kNumBars = 14;
+  // kv_full, q_full[3], q_empty[3], sdp_full[2], pds_full, pds_empty, dq_full[2], dq_empty, final_full
+  static constexpr int kNumBars = 15;
   static constexpr int oVec = oBar + kNumBars * 8 + 16;
   static constexpr int kTotal = oVec + 2 * 2 * BQ * 4;
 };
@@ -474,8 +480,8 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   uint64_t* pds_full = bars + 9;
   uint64_t* pds_empty = bars + 10;
   uint64_t* dq_full = bars + 11;
-  uint64_t* dq_empty = bars + 12;
-  uint64_t* final_full = bars + 13;
+  uint64_t* dq_empty = bars + 13;
+  uint64_t* final_full = bars + 14;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
 
   const int warp = threadIdx.x >> 5;
@@ -507,7 +513,8 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     for (int s = 0; s < 2; ++s) mbar_init(&sdp_full[s], 1);
     mbar_init(pds_full, kWG);
     mbar_init(pds_empty, 1);
-    mbar_init(dq_full, 1);
+    mbar_init(&dq_full[0], 1);
+    mbar_init(&dq_full[1], 1);
     mbar_init(dq_empty, 128);
     mbar_init(final_full, 1);
     fence_barrier_init();
@@ -525,8 +532,10 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool alias_dq = p.d > 96;      // no room for a dQ^T buffer of its own
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 128;   // + 64 * (it & 1)
-  const uint32_t t_dq = tmem_base + 256, t_dv = tmem_base + 320, t_dk = tmem_base + 416;
+  const uint32_t t_dv = tmem_base + (alias_dq ? 256 : 320), t_dk = tmem_base + (alias_dq ? 384 : 416);
+  auto t_dq = [&](int it) -> uint32_t { return alias_dq ? t_s + (it & 1) * BQ : tmem_base + 256; };
 
   const uint32_t ck = BKV * 128;
   const uint32_t cq = BQ * 128;
@@ -571,7 +580,9 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       auto issue_sdp = [&](int it) -> bool {
         const int st = it % kQStages, b = it & 1;
         if (!mbar_wait(&q_full[st], (it / kQStages) & 1)) return false;
-        // S^T[b], dP^T[b] of block it-2 are free: the caller waited for pds_full of that block
+        // S^T[b], dP^T[b] of block it-2 are free (the caller waited for pds_full of that block); with
+        // the shared buffer S^T[b] held dQ^T of block it-2 since then
+        if (alias_dq && it >= 2 && !mbar_wait(dq_empty, (it - 2) & 1)) return false;
         tc_fence_after();
         if (lane == 0) {
           const uint32_t sq_ = smem_u32(smem + L::oQ + st * 2 * L::kQ), sdo_ = sq_ + L::kQ;
@@ -600,7 +611,7 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           ok = false;
           break;
         }
-        if (!mbar_wait(pds_full, it & 1) || (it > 0 && !mbar_wait(dq_empty, (it - 1) & 1))) {
+        if (!mbar_wait(pds_full, it & 1) || (!alias_dq && it > 0 && !mbar_wait(dq_empty, (it - 1) & 1))) {
           report(p.status, MB_ERR_TIMEOUT_TMEM);
           ok = false;
           break;
@@ -620,12 +631,12 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
 #pragma unroll
           for (int kk = 0; kk < BKV / 16; ++kk) {
-            mma_f16_ss(t_dq, make_smem_desc_sw128(sk_ + kk * 2048, ck, 1024),
+            mma_f16_ss(t_dq(it), make_smem_desc_sw128(sk_ + kk * 2048, ck, 1024),
                        make_smem_desc_sw128(sds_ + kk * 2048, ck, 1024), idesc_dq, kk != 0);
           }
           mma_commit(&q_empty[st]);
           mma_commit(pds_empty);
-          mma_commit(dq_full);
+          mma_commit(&dq_full[it & 1]);
         }
         __syncwarp();
       }
@@ -641,21 +652,21 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int q0 = (i_start + it) * BQ;
-      if (!mbar_wait(dq_full, it & 1)) {
+      if (!mbar_wait(&dq_full[it & 1], (it >> 1) & 1)) {
         report(p.status, MB_ERR_TIMEOUT_TMEM);
         ok = false;
         break;
       }
       tc_fence_after();
       uint32_t qr[BQ];
-      tmem_ld32(t_dq + lane_off, qr);
-      tmem_ld32(t_dq + 32 + lane_off, qr + 32);
+      tmem_ld32(t_dq(it) + lane_off, qr);
+      tmem_ld32(t_dq(it) + 32 + lane_off, qr + 32);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_empty);
       if (leader) tma_wait_read<0>();            // the previous reduce has read the staging tile
       asm volatile("bar.sync 2, 128;" ::: "memory");
-      if (r < 96) {
+      {
         // thread holds dQ[q0 + c][d = r]; staging chunk r / 32 is [64 q][32 d] fp32, 128-byte swizzled
         uint8_t* chunk = sdq_ + (r >> 5) * cq;
         const int dl = r & 31;
@@ -903,7 +914,7 @@ bool make_map_dq(CUtensorMap* m, float* base, int bh, int sq, int d) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int g_bwd_variant = 0;        // 0: one block at a time; 1: pipelined (head size <= 96)
+int g_bwd_variant = 0;        // 0: one block at a time; 1: pipelined
 int g_bwd_last_variant = 0;
 
 }  // namespace
@@ -911,7 +922,7 @@ int g_bwd_last_variant = 0;
 MB_API int* mb_status_device_ptr();
 
 // Chooses the main backward kernel for later calls: 0 = the kernel that finishes one query block
-// before it starts the next (default), 1 = the pipelined kernel where it applies (head size <= 96).
+// before it starts the next (default), 1 = the pipelined kernel.
 MB_API void mb_attn_bwd_set_variant(int v) { g_bwd_variant = (v == 1) ? 1 : 0; }
 // Variant the last call of mb_attn_bwd launched.
 MB_API int mb_attn_bwd_last_variant() { return g_bwd_last_variant; }
@@ -959,7 +970,7 @@ MB_API int mb_attn_bwd(const void* dout, const void* q, const void* k, const voi
   p.causal = causal;
   p.status = mb_status_device_ptr();
   dim3 grid((sk + BKV - 1) / BKV, nh, batch);
-  if (g_bwd_variant == 1 && d <= 96) {
+  if (g_bwd_variant == 1) {
     static bool cfg_pipe = false;
     if (!cfg_pipe) {
       if (cudaFuncSetAttribute(attn_bwd_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -51,8 +51,8 @@ class Settings:
     # its S product instead of one).  Same barriers as the default kernel; not yet timed or checked on a
     # device, so it is opt-in (also MIST_B200_ATTN_FWD_SPLIT=1).
     attn_fwd_split_producers = os.environ.get("MIST_B200_ATTN_FWD_SPLIT") == "1"
-    # Backward kernel that overlaps the next block's S / dP products with the current block's softmax
-    # (head size <= 96).  Its barrier protocol is model-checked on the CPU; its numerics have not been
+    # Backward kernel that overlaps the next block's S / dP products with the current block's softmax.
+    # Its barrier protocol is model-checked on the CPU; its numerics have not been
     # checked on a device yet, so it is opt-in (also MIST_B200_ATTN_BWD_PIPELINED=1).
     attn_bwd_pipelined = os.environ.get("MIST_B200_ATTN_BWD_PIPELINED") == "1"
     gemm_max_ctas = 0             # >0 leaves SMs free for a concurrent communication kernel

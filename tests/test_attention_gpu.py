@@ -102,7 +102,7 @@ def test_attn_fwd_split_producers_matches_reference(d, causal):
 
 @pytest.mark.skipif(os.environ.get("MIST_B200_UNVALIDATED_KERNELS") != "1",
                     reason="pipelined backward kernel: opt-in until its numerics have been checked on a device")
-@pytest.mark.parametrize("d", [80, 64, 96])
+@pytest.mark.parametrize("d", [80, 64, 96, 128])
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("s", [64, 256, 1000])
 def test_attn_bwd_pipelined_matches_reference(d, causal, s):

@@ -151,8 +151,10 @@ class TensorQueue:
         self.sim.at(max(self.free_at - self.sim.t, 0.0) + 1e-6, bar.arrive)
 
 
-def simulate(n_iter, seed, n_soft=3, n_dq=2, slow=None, drop=()):
-    """``drop`` names waits to leave out (mutation check: the model must then report a hazard)."""
+def simulate(n_iter, seed, n_soft=3, n_dq=2, slow=None, drop=(), alias=False):
+    """``drop`` names waits to leave out (mutation check: the model must then report a hazard).
+    ``alias``: the large-head layout, where dQ^T of a block is written over that block's S^T buffer;
+    otherwise dQ^T has a tensor-memory buffer of its own."""
     sim = Sim(seed)
     slow = slow or {}
 
@@ -165,14 +167,18 @@ def simulate(n_iter, seed, n_soft=3, n_dq=2, slow=None, drop=()):
     sdp_full = [MBar(sim, f"sdp_full{b}", 1) for b in range(2)]
     pds_full = MBar(sim, "pds_full", n_soft)
     pds_empty = MBar(sim, "pds_empty", 1)
-    dq_full = MBar(sim, "dq_full", 1)
+    dq_full = [MBar(sim, f"dq_full{b}", 1) for b in range(2)]
     dq_empty = MBar(sim, "dq_empty", n_dq)
     final_full = MBar(sim, "final_full", 1)
 
     Q = [Resource(f"Q{s}") for s in range(Q_STAGES)]
-    S = [Resource(f"S{b}") for b in range(2)]
-    P = Resource("P/dS", writers=n_soft)
+    # tensor-memory buffer b holds S^T / dP^T of block it (b = it & 1) and then dQ^T of the same block
+    S = [Resource(f"S/dQ{b}") for b in range(2)]
     DQ = Resource("dQ")
+
+    def dq_buf(it):
+        return S[it & 1] if alias else DQ
+    P = Resource("P/dS", writers=n_soft)
     STG = Resource("dq staging", writers=n_dq)
     VEC = [Resource(f"vec{b}") for b in range(2)]
     tq = TensorQueue(sim)
@@ -205,14 +211,16 @@ def simulate(n_iter, seed, n_soft=3, n_dq=2, slow=None, drop=()):
         def issue_sdp(it):
             st, b = it % Q_STAGES, it & 1
             yield ("wait", q_full[st], (it // Q_STAGES) & 1)
+            if alias and it >= 2 and "dq_empty" not in drop:
+                yield ("wait", dq_empty, (it - 2) & 1)
 
             def start():
                 Q[st].read_begin(it)
-                S[b].write_begin(it)
+                S[b].write_begin(("S", it))
 
             def end():
                 Q[st].read_end()
-                S[b].write_end(it)
+                S[b].write_end(("S", it))
             tq.op(lat("mma", 0.2, 0.6), start, end)
             tq.commit(sdp_full[b])
 
@@ -222,22 +230,22 @@ def simulate(n_iter, seed, n_soft=3, n_dq=2, slow=None, drop=()):
             if it + 1 < n_iter:
                 yield from issue_sdp(it + 1)
             yield ("wait", pds_full, it & 1)
-            if it > 0 and "dq_empty" not in drop:
+            if not alias and it > 0 and "dq_empty" not in drop:
                 yield ("wait", dq_empty, (it - 1) & 1)
 
             def start(it=it, st=st):
                 P.read_begin(it)
                 Q[st].read_begin(it)
-                DQ.write_begin(it)
+                dq_buf(it).write_begin(("DQ", it))
 
             def end(it=it, st=st):
                 P.read_end()
                 Q[st].read_end()
-                DQ.write_end(it)
+                dq_buf(it).write_end(("DQ", it))
             tq.op(lat("mma", 0.3, 0.9), start, end)
             tq.commit(q_empty[st])
             tq.commit(pds_empty)
-            tq.commit(dq_full)
+            tq.commit(dq_full[it & 1])
             yield ("sleep", 0.01)
         tq.commit(final_full)
 
@@ -250,7 +258,7 @@ def simulate(n_iter, seed, n_soft=3, n_dq=2, slow=None, drop=()):
             b = it & 1
             yield ("wait", sdp_full[b], (it >> 1) & 1)
             VEC[b].read_begin(it)
-            S[b].read_begin(it)
+            S[b].read_begin(("S", it))
             yield ("sleep", lat("soft", 0.2, 1.5))
             S[b].read_end()
             VEC[b].read_end()
@@ -270,10 +278,10 @@ def simulate(n_iter, seed, n_soft=3, n_dq=2, slow=None, drop=()):
 
     def dq(tid):
         for it in range(n_iter):
-            yield ("wait", dq_full, it & 1)
-            DQ.read_begin(it)
+            yield ("wait", dq_full[it & 1], (it >> 1) & 1)
+            dq_buf(it).read_begin(("DQ", it))
             yield ("sleep", lat("dq", 0.1, 0.5))
-            DQ.read_end()
+            dq_buf(it).read_end()
             dq_empty.arrive()
             if tid == 0 and sim.t < reduce_done["t"]:
                 yield ("sleep", reduce_done["t"] - sim.t)         # wait until the last reduce has read the tile
@@ -295,23 +303,26 @@ def simulate(n_iter, seed, n_soft=3, n_dq=2, slow=None, drop=()):
     stuck = [t.name for t in tasks if not t.done]
     assert not stuck, f"n_iter={n_iter} seed={seed}: stuck roles {stuck}"
     if n_iter > 0:
-        assert pds_full.completed == n_iter and dq_full.completed == n_iter and dq_empty.completed == n_iter
+        assert pds_full.completed == n_iter and dq_empty.completed == n_iter
+        assert sum(b.completed for b in dq_full) == n_iter
         assert sum(b.completed for b in sdp_full) == n_iter
     return sim.t
 
 
+@pytest.mark.parametrize("alias", [False, True])
 @pytest.mark.parametrize("n_iter", [0, 1, 2, 3, 4, 5, 8, 13])
-def test_pipelined_backward_protocol_random_latencies(n_iter):
+def test_pipelined_backward_protocol_random_latencies(n_iter, alias):
     for seed in range(60):
-        simulate(n_iter, seed)
+        simulate(n_iter, seed, alias=alias)
 
 
+@pytest.mark.parametrize("alias", [False, True])
 @pytest.mark.parametrize("role", ["tma", "mma", "soft", "dq"])
-def test_pipelined_backward_protocol_with_one_slow_role(role):
+def test_pipelined_backward_protocol_with_one_slow_role(role, alias):
     """One role twenty times slower than the rest: the others must wait for it, never run past it."""
     for seed in range(25):
-        simulate(9, seed, slow={role: 20.0})
-        simulate(9, 1000 + seed, slow={role: 0.05})
+        simulate(9, seed, slow={role: 20.0}, alias=alias)
+        simulate(9, 1000 + seed, slow={role: 0.05}, alias=alias)
 
 
 def test_pipelining_overlaps_tensor_work_with_softmax():
@@ -323,15 +334,16 @@ def test_pipelining_overlaps_tensor_work_with_softmax():
     assert per_block < 2.0
 
 
+@pytest.mark.parametrize("alias", [False, True])
 @pytest.mark.parametrize("wait", ["q_empty", "dq_empty", "pds_empty"])
-def test_model_reports_a_hazard_when_a_wait_is_left_out(wait):
+def test_model_reports_a_hazard_when_a_wait_is_left_out(wait, alias):
     """Mutation check of the model itself: without any one of the 'buffer free' waits some schedule
     must overwrite a buffer that is still needed (or desynchronise a barrier)."""
     failures = 0
     for seed in range(40):
         for slow in ({}, {"soft": 8.0}, {"mma": 8.0}, {"dq": 8.0}, {"tma": 0.05}):
             try:
-                simulate(9, seed, slow=slow, drop=(wait,))
+                simulate(9, seed, slow=slow, drop=(wait,), alias=alias)
             except AssertionError:
                 failures += 1
     assert failures > 0
