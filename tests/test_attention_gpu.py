@@ -81,18 +81,19 @@ def test_attention_qkvpacked_grad(d, rot):
                     reason="forward kernel with two producer warps: opt-in until it has been checked on a device")
 @pytest.mark.parametrize("d", [128, 80, 64])
 @pytest.mark.parametrize("causal", [True, False])
-def test_attn_fwd_split_producers_matches_reference(d, causal):
+@pytest.mark.parametrize("split,emu", [(True, 0), (False, 1), (False, 2), (True, 2)])
+def test_attn_fwd_split_producers_matches_reference(d, causal, split, emu):
     torch.manual_seed(5)
     b, s, nh = 2, 1000, 3
     qkv = torch.randn(b, s, 3, nh, d, device=DEV, dtype=torch.bfloat16)
     q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
     scale = 1 / math.sqrt(d)
-    F.Settings.attn_fwd_split_producers = True
+    F.Settings.attn_fwd_split_producers, F.Settings.attn_fwd_exp_emulation = split, emu
     try:
         o, lse = F.attn_fwd(q, k, v, scale, causal, block_n=64)
         torch.cuda.synchronize()
     finally:
-        F.Settings.attn_fwd_split_producers = False
+        F.Settings.attn_fwd_split_producers, F.Settings.attn_fwd_exp_emulation = False, 0
     from mist_b200.ops import native
     native.check_status()
     o_ref, lse_ref = F._ref_attention(q.float(), k.float(), v.float(), scale, causal)
