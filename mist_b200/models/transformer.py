@@ -30,8 +30,11 @@ class ParallelTransformerLayer(nn.Module):
                  device=None, dtype=None):
         super().__init__()
         assert cfg.num_experts is None, "mixture-of-experts blocks are not part of this model zoo"
-        assert cfg.prenorm, "post-norm blocks are not supported"
+        assert cfg.prenorm or not cfg.parallel_block, "parallel blocks take their residual from the block input"
         self.cfg, self.layer_idx, self.is_decoder = cfg, layer_idx, is_decoder
+        # prenorm = False: each residual connection starts from the *normalised* stream (the norm's
+        # output) instead of the norm's input (reference: mist/model/transformer.py:260-264,309-314)
+        self.residual_from_norm = not cfg.prenorm
         self.parallel_block = cfg.parallel_block
         self.tied_norm = cfg.parallel_block_tied_norm
         self.sequence_parallel = sequence_parallel
@@ -79,14 +82,20 @@ class ParallelTransformerLayer(nn.Module):
         bs = batch_size if batch_size is not None else hidden.shape[0]
         if not self.parallel_block:
             x, residual = self.norm1(hidden, residual)
+            if self.residual_from_norm:
+                residual = x
             hidden = self._drop(self.attn(x, batch_size=bs, attention_mask=attn_mask))
             if hidden.shape != residual.shape:
                 hidden = hidden.reshape(residual.shape)
             if self.is_decoder:
                 x, residual = self.norm_cross(hidden, residual)
+                if self.residual_from_norm:
+                    residual = x
                 hidden = self._drop(self.cross_attn(x, x_kv=encoder_output, batch_size=bs, attention_mask=attn_mask,
                                                     kv_mask=enc_mask)).reshape(residual.shape)
             x, residual = self.norm2(hidden, residual)
+            if self.residual_from_norm:
+                residual = x
             hidden = self._drop(self.mlp(x)).reshape(residual.shape)
             return hidden, residual
         # parallel block: attention and MLP read the same stream

@@ -174,3 +174,28 @@ def test_t5_cross_attention_ignores_padded_encoder_tokens():
     enc2 = enc.clone()
     enc2[0, 30] = (enc2[0, 30] + 7) % 256
     assert torch.allclose(m(enc2, dec, encoder_attn_mask=mask), logits, atol=1e-6)
+
+
+def test_residual_from_the_normalised_stream_when_prenorm_is_off():
+    """prenorm = False: x1 = LN1(h); a = x1 + attn(x1); x2 = LN2(a); out = x2 + mlp(x2)."""
+    import torch.nn.functional as TF
+    from mist_b200.models.transformer import ParallelTransformerLayer
+    torch.manual_seed(0)
+    cfg = ModelConfig(name="gpt2-t", encoder_attn_mask_type="causal", prenorm=False, **BASE)
+    layer = ParallelTransformerLayer(cfg, 0, device="cpu", dtype=torch.float32)
+    for n in (layer.norm1, layer.norm2):           # make the norms non-trivial
+        with torch.no_grad():
+            n.weight.uniform_(0.5, 1.5)
+            n.bias.uniform_(-0.2, 0.2)
+    h = torch.randn(2, 16, 64)
+    hidden, residual = layer(h, None)
+    x1 = TF.layer_norm(h, (64,), layer.norm1.weight, layer.norm1.bias, cfg.normalization_eps)
+    a = x1 + layer.attn(x1)
+    x2 = TF.layer_norm(a, (64,), layer.norm2.weight, layer.norm2.bias, cfg.normalization_eps)
+    want = x2 + layer.mlp(x2)
+    assert torch.allclose(hidden + residual, want, atol=1e-5)
+    # and the whole model still trains
+    m = base_model_provider(cfg, device="cpu", dtype=torch.float32)
+    loss = m(**get_inputs_provider("gpt")(2, 32, 256, "cpu", seed=2))
+    loss.backward()
+    assert torch.isfinite(loss)
