@@ -24,6 +24,12 @@ from ..modules.layers import ParallelGatedMlp, ParallelMHA, ParallelMLP, get_nor
 from ..ops import functional as F
 
 
+def _gate_activation(name: str) -> str:
+    """Gate activation of a gated MLP: the tanh-GELU default of the plain MLP means "not set" there."""
+    name = (name or "swiglu").lower()
+    return "swiglu" if name in ("gelu_new", "gelu_fast", "gelu_approx", "gelu_pytorch_tanh") else name
+
+
 class ParallelTransformerLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_idx: int, process_group=None, is_decoder: bool = False,
                  attn_mask_type: AttnMaskType = AttnMaskType.causal, sequence_parallel: bool = False,
@@ -35,6 +41,9 @@ class ParallelTransformerLayer(nn.Module):
         # prenorm = False: each residual connection starts from the *normalised* stream (the norm's
         # output) instead of the norm's input (reference: mist/model/transformer.py:260-264,309-314)
         self.residual_from_norm = not cfg.prenorm
+        if cfg.fp32_residual_connection:
+            raise NotImplementedError("fp32_residual_connection: the residual stream has the parameter dtype here "
+                                      "(the fused norm kernels read and write it in bf16)")
         self.parallel_block = cfg.parallel_block
         self.tied_norm = cfg.parallel_block_tied_norm
         self.sequence_parallel = sequence_parallel
@@ -44,28 +53,37 @@ class ParallelTransformerLayer(nn.Module):
         rot_dim = 0
         if cfg.position_embedding_type is PositionEmbeddingType.rotary:
             rot_dim = int(cfg.head_dim * cfg.rotary_emb_fraction) // 16 * 16
+        # softmax scale: 1/sqrt(head_dim) when scale_attn_weights, else 1; optionally divided by the
+        # 1-based layer index (reference: mist/model/transformer.py:33-37)
+        softmax_scale = cfg.head_dim ** -0.5 if cfg.scale_attn_weights else 1.0
+        if cfg.scale_attn_by_inverse_layer_idx:
+            softmax_scale /= float(layer_idx + 1)
         self.norm1 = get_norm(cfg.normalization, cfg.hidden_size, **nk)
         self.attn = ParallelMHA(
             cfg.hidden_size, cfg.num_attention_heads, cfg.num_heads_kv, process_group=process_group,
             qkv_proj_bias=cfg.qkv_proj_bias, out_proj_bias=cfg.out_proj_bias, dropout=cfg.attention_dropout,
             causal=attn_mask_type is AttnMaskType.causal, rotary_emb_dim=rot_dim,
-            rotary_emb_base=cfg.rotary_emb_base, use_flash_attn=cfg.use_flash_attn,
+            rotary_emb_base=cfg.rotary_emb_base, use_flash_attn=cfg.use_flash_attn, softmax_scale=softmax_scale,
+            rotary_emb_interleaved=cfg.rotary_emb_interleaved, rotary_emb_scale_base=cfg.rotary_emb_scale_base,
             sequence_parallel=sequence_parallel, layer_idx=layer_idx, **fk)
         if is_decoder:
             self.norm_cross = get_norm(cfg.normalization, cfg.hidden_size, **nk)
             self.cross_attn = ParallelMHA(
                 cfg.hidden_size, cfg.num_attention_heads, cfg.num_heads_kv, process_group=process_group,
                 qkv_proj_bias=cfg.qkv_proj_bias, out_proj_bias=cfg.out_proj_bias, cross_attn=True,
-                use_flash_attn=cfg.use_flash_attn, sequence_parallel=sequence_parallel, layer_idx=layer_idx, **fk)
+                use_flash_attn=cfg.use_flash_attn, softmax_scale=softmax_scale,
+                sequence_parallel=sequence_parallel, layer_idx=layer_idx, **fk)
         if not (self.parallel_block and self.tied_norm):
             self.norm2 = get_norm(cfg.normalization, cfg.hidden_size, **nk)
         if cfg.gated:
             self.mlp = ParallelGatedMlp(cfg.hidden_size, cfg.intermediate_size, process_group=process_group,
                                         bias1=cfg.mlp_fc1_bias, bias2=cfg.mlp_fc2_bias,
+                                        activation=_gate_activation(cfg.activation_function),
                                         sequence_parallel=sequence_parallel, **fk)
         else:
             self.mlp = ParallelMLP(cfg.hidden_size, cfg.intermediate_size, process_group=process_group,
                                    bias1=cfg.mlp_fc1_bias, bias2=cfg.mlp_fc2_bias,
+                                   activation=cfg.activation_function,
                                    sequence_parallel=sequence_parallel, **fk)
 
     def _drop(self, x):

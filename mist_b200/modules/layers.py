@@ -291,8 +291,13 @@ class ParallelMHA(nn.Module):
     def __init__(self, hidden_size, num_heads, num_heads_kv=None, process_group=None, qkv_proj_bias=True,
                  out_proj_bias=True, dropout=0.0, softmax_scale=None, causal=False, cross_attn=False,
                  rotary_emb_dim=0, rotary_emb_base=10000.0, use_flash_attn=True, sequence_parallel=False,
-                 layer_idx=None, device=None, dtype=None):
+                 layer_idx=None, device=None, dtype=None, rotary_emb_interleaved=False, rotary_emb_scale_base=None):
         super().__init__()
+        # interleaved: pairs (2i, 2i+1) rotate together instead of (i, i + rot/2); scale_base: position
+        # dependent scaling of the rotated q (up) and k (down) ("xpos").  Both take the general path
+        # below (rotary out of place), not the in-kernel rotation of the packed fast path.
+        self.rotary_interleaved = bool(rotary_emb_interleaved) and rotary_emb_dim > 0
+        self.rotary_scale_base = float(rotary_emb_scale_base) if (rotary_emb_scale_base and rotary_emb_dim > 0) else None
         ws = group_size(process_group)
         self.hidden_size, self.causal, self.cross_attn = hidden_size, causal, cross_attn
         self.num_heads = num_heads
@@ -332,6 +337,27 @@ class ParallelMHA(nn.Module):
             probs = torch.nn.functional.dropout(probs, self.dropout)
         return torch.matmul(probs, v.transpose(1, 2)).transpose(1, 2)
 
+    def _general_rotary(self, qk, num_q_heads: int):
+        """Rotary embedding of ``qk`` ``[b, s, q heads + k heads, d]`` for the interleaved and the
+        position-scaled forms.  Interleaved pairs are first moved to the half-split positions; q and
+        k get the same permutation of their head dimension, which leaves every q . k unchanged, so
+        nothing is permuted back."""
+        b, s, H, d = qk.shape
+        rot = self.rotary_emb_dim
+        if self.rotary_interleaved:
+            perm = torch.cat([torch.arange(0, rot, 2), torch.arange(1, rot, 2), torch.arange(rot, d)]).to(qk.device)
+            qk = qk.index_select(-1, perm)
+        cos, sin = F.rope_tables(s, rot, self.rotary_emb_base, qk.device)
+        qk = _RotaryOutOfPlace.apply(qk.unsqueeze(2), cos, sin, rot, 1).squeeze(2)
+        if self.rotary_scale_base is not None:
+            base = (torch.arange(0, rot, 2, dtype=torch.float32, device=qk.device) + 0.4 * rot) / (1.4 * rot)
+            power = (torch.arange(s, dtype=torch.float32, device=qk.device) - s // 2) / self.rotary_scale_base
+            sc = base[None, :] ** power[:, None]                          # [s, rot / 2]
+            full = torch.cat([sc, sc, torch.ones(s, d - rot, device=qk.device)], -1).to(qk.dtype)
+            qk = torch.cat([qk[:, :, :num_q_heads] * full[None, :, None, :],
+                            qk[:, :, num_q_heads:] / full[None, :, None, :]], 2)
+        return qk
+
     def _attend_masked(self, q, k, v, causal, q_mask: Optional[PaddingMask], k_mask: Optional[PaddingMask]):
         """Attention per sample over its real tokens; rows of padded queries are zero."""
         outs = []
@@ -354,6 +380,8 @@ class ParallelMHA(nn.Module):
         branches of mist/modules/mha.py:531-575,1110-1170)."""
         ip = self.inference_params
         assert not self.cross_attn and not self.sequence_parallel and x.dim() == 3
+        if self.rotary_interleaved or self.rotary_scale_base is not None:
+            raise NotImplementedError("cached generation with interleaved or position-scaled rotary embeddings")
         qkv = self.Wqkv(x)
         b, s = qkv.shape[:2]
         hq, hk, d = self.local_heads, self.local_heads_kv, self.head_dim
@@ -401,6 +429,16 @@ class ParallelMHA(nn.Module):
             if self.local_heads == self.local_heads_kv:
                 qkv = qkv.view(b, s, 3, self.local_heads, self.head_dim)
                 rotary = None
+                if self.rotary_interleaved or self.rotary_scale_base is not None:
+                    h = self.local_heads
+                    qk = self._general_rotary(qkv[:, :, :2].reshape(b, s, 2 * h, self.head_dim), h)
+                    if masked:
+                        ctx = self._attend_masked(qk[:, :, :h], qk[:, :, h:], qkv[:, :, 2], self.causal,
+                                                  attention_mask, attention_mask)
+                    else:
+                        ctx = self._attend(qk[:, :, :h], qk[:, :, h:], qkv[:, :, 2], self.causal)
+                    ctx = ctx.reshape(ctx.shape[0], ctx.shape[1], -1)
+                    return self.out_proj(ctx, residual=residual)
                 if self.rotary_emb_dim > 0:
                     cos, sin = F.rope_tables(s, self.rotary_emb_dim, self.rotary_emb_base, qkv.device)
                     rotary = (cos, sin, self.rotary_emb_dim)
@@ -417,7 +455,10 @@ class ParallelMHA(nn.Module):
                     ctx = self._attend(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], self.causal)
             else:
                 hq, hk, d = self.local_heads, self.local_heads_kv, self.head_dim
-                if self.rotary_emb_dim > 0:
+                if self.rotary_interleaved or self.rotary_scale_base is not None:
+                    qk = self._general_rotary(qkv[..., : (hq + hk) * d].reshape(b, s, hq + hk, d), hq)
+                    q, k = qk[:, :, :hq], qk[:, :, hq:]
+                elif self.rotary_emb_dim > 0:
                     # grouped-query layout [q heads | k heads | v heads]: rotate the q and k heads together
                     cos, sin = F.rope_tables(s, self.rotary_emb_dim, self.rotary_emb_base, qkv.device)
                     qk = qkv[..., : (hq + hk) * d].reshape(b, s, 1, hq + hk, d)
@@ -465,18 +506,49 @@ class _RotaryOutOfPlace(torch.autograd.Function):
 
 
 # --------------------------------------------------------------------------------- MLP
+_TANH_GELU = ("gelu_new", "gelu_fast", "gelu_approx", "gelu_pytorch_tanh")
+
+
+def get_activation(name: str):
+    """Element-wise activation by its configuration name (reference: ``get_activation``,
+    mist/modules/utils.py:39-53).  The tanh form of GELU is the one fused into the GEMM epilogues;
+    the others run as separate element-wise operations."""
+    import torch.nn.functional as TF
+    name = (name or "gelu_new").lower()
+    if name in _TANH_GELU:
+        return lambda x: TF.gelu(x, approximate="tanh")
+    if name in ("gelu", "geglu"):
+        return TF.gelu
+    if name == "relu":
+        return TF.relu
+    if name in ("sigmoid", "glu"):
+        return torch.sigmoid
+    if name == "sqrelu":
+        return lambda x: TF.relu(x).square()
+    if name in ("silu", "swiglu"):
+        return TF.silu
+    raise ValueError(f"activation '{name}' is not known")
+
+
 class ParallelMLP(nn.Module):
-    """fc1 (column parallel, GELU fused into the GEMM epilogue) -> fc2 (row parallel)."""
+    """fc1 (column parallel, tanh-GELU fused into the GEMM epilogue) -> fc2 (row parallel); other
+    activations run between the two GEMMs as an element-wise operation."""
 
     def __init__(self, hidden_size, intermediate_size, process_group=None, bias1=True, bias2=True,
-                 activation="gelu", sequence_parallel=False, device=None, dtype=None):
+                 activation="gelu_new", sequence_parallel=False, device=None, dtype=None):
         super().__init__()
         fk = dict(process_group=process_group, sequence_parallel=sequence_parallel, device=device, dtype=dtype)
-        self.fc1 = ColumnParallelLinear(hidden_size, intermediate_size, bias=bias1, activation="gelu", **fk)
+        self.activation = (activation or "gelu_new").lower()
+        self.fused_gelu = self.activation in _TANH_GELU
+        self.act = None if self.fused_gelu else get_activation(self.activation)
+        self.fc1 = ColumnParallelLinear(hidden_size, intermediate_size, bias=bias1,
+                                        activation="gelu" if self.fused_gelu else None, **fk)
         self.fc2 = RowParallelLinear(intermediate_size, hidden_size, bias=bias2, **fk)
 
     def forward(self, x, residual=None):
         fc1, fc2 = self.fc1, self.fc2
+        if not self.fused_gelu:
+            return fc2(self.act(fc1(x)), residual=residual)
         if (residual is None and isinstance(x, torch.Tensor) and F.mlp_gelu_fused_available(x)
                 and not fc1._fused(x) and x.dtype == fc1.weight.dtype):
             # local compute as one autograd node (GELU's derivative rides on a GEMM epilogue in the
@@ -500,14 +572,21 @@ class ParallelGatedMlp(nn.Module):
     """fc1 produces ``[gate | up]`` (each rank holds matching halves), SwiGLU, then fc2."""
 
     def __init__(self, hidden_size, intermediate_size, process_group=None, bias1=False, bias2=False,
-                 sequence_parallel=False, device=None, dtype=None):
+                 activation="swiglu", sequence_parallel=False, device=None, dtype=None):
         super().__init__()
         fk = dict(process_group=process_group, sequence_parallel=sequence_parallel, device=device, dtype=dtype)
+        self.activation = (activation or "swiglu").lower()
+        # silu gates use the fused SwiGLU kernel; "geglu" / "glu" ... gate with their own activation
+        self.gate_act = None if self.activation in ("silu", "swiglu") else get_activation(self.activation)
         self.fc1 = ColumnParallelLinear(hidden_size, 2 * intermediate_size, bias=bias1, multiple_of=2, **fk)
         self.fc2 = RowParallelLinear(intermediate_size, hidden_size, bias=bias2, **fk)
 
     def forward(self, x, residual=None):
-        return self.fc2(F.swiglu(self.fc1(x)), residual=residual)
+        y = self.fc1(x)
+        if self.gate_act is None:
+            return self.fc2(F.swiglu(y), residual=residual)
+        gate, up = y.chunk(2, dim=-1)
+        return self.fc2(self.gate_act(gate) * up, residual=residual)
 
 
 # -------------------------------------------------------------------------------- loss

@@ -199,3 +199,71 @@ def test_residual_from_the_normalised_stream_when_prenorm_is_off():
     loss = m(**get_inputs_provider("gpt")(2, 32, 256, "cpu", seed=2))
     loss.backward()
     assert torch.isfinite(loss)
+
+
+def test_activation_and_softmax_scale_flags_are_honoured():
+    import torch.nn.functional as TF
+    from mist_b200.modules.layers import ParallelGatedMlp, ParallelMLP
+    torch.manual_seed(0)
+    x = torch.randn(3, 5, 16)
+    for name, ref in (("relu", TF.relu), ("gelu", TF.gelu), ("sqrelu", lambda t: TF.relu(t) ** 2),
+                      ("gelu_fast", lambda t: TF.gelu(t, approximate="tanh"))):
+        mlp = ParallelMLP(16, 32, activation=name, device="cpu", dtype=torch.float32)
+        want = TF.linear(ref(TF.linear(x, mlp.fc1.weight, mlp.fc1.bias)), mlp.fc2.weight, mlp.fc2.bias)
+        assert torch.allclose(mlp(x), want, atol=1e-5), name
+    for name, ref in (("swiglu", TF.silu), ("geglu", TF.gelu), ("glu", torch.sigmoid)):
+        g = ParallelGatedMlp(16, 32, activation=name, device="cpu", dtype=torch.float32)
+        gate, up = TF.linear(x, g.fc1.weight).chunk(2, -1)
+        assert torch.allclose(g(x), TF.linear(ref(gate) * up, g.fc2.weight), atol=1e-5), name
+    cfg = ModelConfig(name="gpt2-t", encoder_attn_mask_type="causal", scale_attn_weights=True,
+                      scale_attn_by_inverse_layer_idx=True, **BASE)
+    m = base_model_provider(cfg, device="cpu", dtype=torch.float32)
+    scales = [l.attn.softmax_scale for l in m.language_model.encoder.layers]
+    assert scales == pytest.approx([16 ** -0.5, 16 ** -0.5 / 2])
+    cfg2 = ModelConfig(name="gpt2-t", encoder_attn_mask_type="causal", scale_attn_weights=False, **BASE)
+    m2 = base_model_provider(cfg2, device="cpu", dtype=torch.float32)
+    assert m2.language_model.encoder.layers[0].attn.softmax_scale == 1.0
+
+
+@pytest.mark.parametrize("interleaved,scale_base", [(True, None), (False, 512.0), (True, 64.0)])
+@pytest.mark.parametrize("heads_kv", [4, 2])
+def test_interleaved_and_position_scaled_rotary(interleaved, scale_base, heads_kv):
+    from mist_b200.modules.layers import ParallelMHA
+    from mist_b200.ops import functional as F
+    torch.manual_seed(0)
+    b, s, hdim, nh, rot = 2, 12, 64, 4, 8
+    d = hdim // nh
+    mha = ParallelMHA(hdim, nh, heads_kv, causal=True, rotary_emb_dim=rot, rotary_emb_interleaved=interleaved,
+                      rotary_emb_scale_base=scale_base, device="cpu", dtype=torch.float32)
+    x = torch.randn(b, s, hdim)
+    out = mha(x)
+    # direct formula
+    qkv = torch.nn.functional.linear(x, mha.Wqkv.weight, mha.Wqkv.bias)
+    if heads_kv == nh:
+        qkv = qkv.view(b, s, 3, nh, d)
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    else:
+        q = qkv[..., : nh * d].reshape(b, s, nh, d)
+        k = qkv[..., nh * d: (nh + heads_kv) * d].reshape(b, s, heads_kv, d)
+        v = qkv[..., (nh + heads_kv) * d:].reshape(b, s, heads_kv, d)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, rot, 2).float() / rot))
+    ang = torch.outer(torch.arange(s).float(), inv)                      # [s, rot/2]
+    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    sc = torch.ones(s, rot // 2)
+    if scale_base is not None:
+        base = (torch.arange(0, rot, 2).float() + 0.4 * rot) / (1.4 * rot)
+        sc = base[None, :] ** ((torch.arange(s).float() - s // 2) / scale_base)[:, None]
+    sc = sc[None, :, None, :]
+
+    def rope(t, scale):
+        t = t.clone()
+        if interleaved:
+            a, c = t[..., 0:rot:2], t[..., 1:rot:2]
+            t[..., 0:rot:2], t[..., 1:rot:2] = (a * cos - c * sin) * scale, (a * sin + c * cos) * scale
+        else:
+            a, c = t[..., : rot // 2], t[..., rot // 2: rot]
+            t[..., : rot // 2], t[..., rot // 2: rot] = (a * cos - c * sin) * scale, (a * sin + c * cos) * scale
+        return t
+    o, _ = F._ref_attention(rope(q, sc), rope(k, 1.0 / sc), v, mha.softmax_scale, True)
+    want = torch.nn.functional.linear(o.reshape(b, s, hdim), mha.out_proj.weight, mha.out_proj.bias)
+    assert torch.allclose(out, want, atol=1e-5)
