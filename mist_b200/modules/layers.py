@@ -590,10 +590,29 @@ class ParallelGatedMlp(nn.Module):
 
 
 # -------------------------------------------------------------------------------- loss
-def vocab_parallel_cross_entropy(logits, labels, process_group=None, ignore_index=-100):
-    """Per-token loss of ``[tokens, vocab/tp]`` logits against global labels."""
+def vocab_parallel_cross_entropy(logits, labels, process_group=None, ignore_index=-100, label_smoothing: float = 0.0):
+    """Per-token loss of ``[tokens, vocab/tp]`` logits against global labels.
+
+    ``label_smoothing`` = a moves the mass a from the label to the other K - 1 classes, evenly:
+    ``loss = (1 - s) * nll - s * mean_j log p_j`` with ``s = a * K / (K - 1)`` (reference:
+    mist/modules/losses.py:117-134).  The smoothing term is built from two row sums that are reduced
+    over the tensor-parallel group; it is not on the path the benchmarks use."""
     ws = group_size(process_group)
     rk = group_rank(process_group)
     group = None if (ws == 1 or isinstance(process_group, dist_ops.FakeGroup)) else process_group
-    return F.cross_entropy(logits, labels, vocab_start=rk * logits.shape[-1], group=group,
+    loss = F.cross_entropy(logits, labels, vocab_start=rk * logits.shape[-1], group=group,
                            ignore_index=ignore_index)
+    if label_smoothing <= 0.0 or not isinstance(logits, torch.Tensor):
+        return loss
+    assert label_smoothing < 1.0
+    K = logits.shape[-1] * ws
+    s = label_smoothing * K / (K - 1)
+    lf = logits.float()
+    lmax = lf.detach().max(-1).values
+    if group is not None:
+        torch.distributed.all_reduce(lmax, op=torch.distributed.ReduceOp.MAX, group=group)
+    sum_logits = dist_ops.all_reduce(lf.sum(-1), group)
+    sum_exp = dist_ops.all_reduce((lf - lmax[:, None]).exp().sum(-1), group)
+    mean_log_prob = sum_logits / K - (lmax + sum_exp.log())
+    smooth = (1.0 - s) * loss - s * mean_log_prob
+    return torch.where(labels.reshape(-1) == ignore_index, torch.zeros_like(smooth), smooth)

@@ -3,6 +3,11 @@ import sys
 
 import pytest
 
+# The CPU tests run tiny models in up to four gloo ranks at a time: a full thread pool per rank only
+# oversubscribes the cores.  Spawned ranks and driver subprocesses inherit these.
+os.environ.setdefault("OMP_NUM_THREADS", "2")
+os.environ.setdefault("MKL_NUM_THREADS", "2")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

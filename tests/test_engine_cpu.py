@@ -77,9 +77,9 @@ def _dp_worker(rank, world, port, zero_flags, G, ret, offload=(0, 0, 0, 0), ckpt
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("zero_flags", [(False, False, False), (False, False, True), (False, True, True),
-                                        (True, True, True)])
-@pytest.mark.parametrize("G", [1, 2])
+@pytest.mark.parametrize("zero_flags,G", [
+    ((False, False, False), 1), ((True, True, True), 1),
+    ((False, False, False), 2), ((False, False, True), 2), ((False, True, True), 2), ((True, True, True), 2)])
 def test_data_parallel_gloo_matches_single_process(zero_flags, G):
     world = 2
     mgr = mp.Manager()
@@ -406,10 +406,10 @@ def _ppdp_worker(rank, world, port, zero, ret, offload="0,0,0,0", extra=()):
 
 
 @pytest.mark.parametrize("zero,offload,tied", [
-    ((0, 0, 1), "0,0,0,0", False), ((0, 1, 1), "0,0,0,0", False), ((1, 1, 1), "0,0,0,0", False),
+    ((0, 0, 1), "0,0,0,0", False), ((1, 1, 1), "0,0,0,0", False),
     ((0, 1, 1), "0.5,0.5,0.5,0", False), ((1, 1, 1), "0.5,0.5,0.5,0", False),
     # word embeddings tied to the output projection, the two on different stages
-    ((0, 0, 1), "0,0,0,0", True), ((0, 1, 1), "0,0,0,0", True), ((1, 1, 1), "0,0,0,0", True)])
+    ((0, 0, 1), "0,0,0,0", True), ((1, 1, 1), "0,0,0,0", True)])
 def test_pipeline_with_data_parallel_stages_and_zero(zero, offload, tied):
     world = 4
     mgr = mp.Manager()

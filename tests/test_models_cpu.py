@@ -267,3 +267,24 @@ def test_interleaved_and_position_scaled_rotary(interleaved, scale_base, heads_k
     o, _ = F._ref_attention(rope(q, sc), rope(k, 1.0 / sc), v, mha.softmax_scale, True)
     want = torch.nn.functional.linear(o.reshape(b, s, hdim), mha.out_proj.weight, mha.out_proj.bias)
     assert torch.allclose(out, want, atol=1e-5)
+
+
+def test_label_smoothing_spreads_the_mass_over_the_other_classes():
+    """loss = (1 - s) * nll - s * mean_j log p_j with s = a K / (K - 1): the label keeps 1 - a and each of
+    the other K - 1 classes gets a / (K - 1) (torch's own label_smoothing spreads a over all K classes)."""
+    from mist_b200.modules.layers import vocab_parallel_cross_entropy
+    torch.manual_seed(0)
+    K, a = 50, 0.1
+    logits = torch.randn(7, K, requires_grad=True)
+    labels = torch.randint(0, K, (7,))
+    labels[3] = -100
+    ours = vocab_parallel_cross_entropy(logits, labels, label_smoothing=a)
+    ref_in = logits.detach().clone().requires_grad_(True)
+    target = torch.full((7, K), a / (K - 1))
+    keep = labels != -100
+    target[torch.arange(7)[keep], labels[keep]] = 1 - a
+    want = -(target * torch.log_softmax(ref_in, -1)).sum(-1) * keep
+    assert torch.allclose(ours, want, atol=1e-5)
+    ours.sum().backward()
+    want.sum().backward()
+    assert torch.allclose(logits.grad, ref_in.grad, atol=1e-5)
