@@ -473,3 +473,34 @@ def test_heterogeneous_pipeline_wide_stage_feeds_two_data_parallel_ranks():
     for r in range(3):
         for n, p in ret[r][3].items():
             assert (p - new_state[n].detach()).abs().max().item() < 2e-4, (r, n)
+
+
+def _smooth_worker(rank, world, port, logits, labels, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.modules.layers import vocab_parallel_cross_entropy
+        group = dist.new_group([0, 1])
+        per = logits.shape[1] // world
+        local = logits[:, rank * per:(rank + 1) * per].clone().requires_grad_(True)
+        loss = vocab_parallel_cross_entropy(local, labels, group, label_smoothing=0.2)
+        loss.sum().backward()
+        ret[rank] = (loss.detach().clone(), local.grad.clone())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_label_smoothing_over_vocabulary_shards():
+    from mist_b200.modules.layers import vocab_parallel_cross_entropy
+    torch.manual_seed(0)
+    logits = torch.randn(6, 32)
+    labels = torch.randint(0, 32, (6,))
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_smooth_worker, args=(2, 47100 + os.getpid() % 500, logits, labels, ret), nprocs=2, join=True)
+    full = logits.clone().requires_grad_(True)
+    want = vocab_parallel_cross_entropy(full, labels, label_smoothing=0.2)
+    want.sum().backward()
+    for r in range(2):
+        assert torch.allclose(ret[r][0], want.detach(), atol=1e-5)
+        assert torch.allclose(ret[r][1], full.grad[:, r * 16:(r + 1) * 16], atol=1e-5)
