@@ -429,7 +429,9 @@ class ParallelMHA(nn.Module):
             if self.local_heads == self.local_heads_kv:
                 qkv = qkv.view(b, s, 3, self.local_heads, self.head_dim)
                 rotary = None
-                if self.rotary_interleaved or self.rotary_scale_base is not None:
+                # (the symbolic trace of the analyzer prices these forms like the plain rotation)
+                general_rotary = (self.rotary_interleaved or self.rotary_scale_base is not None) and not F._sym(qkv)
+                if general_rotary:
                     h = self.local_heads
                     qk = self._general_rotary(qkv[:, :, :2].reshape(b, s, 2 * h, self.head_dim), h)
                     if masked:
@@ -455,7 +457,7 @@ class ParallelMHA(nn.Module):
                     ctx = self._attend(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], self.causal)
             else:
                 hq, hk, d = self.local_heads, self.local_heads_kv, self.head_dim
-                if self.rotary_interleaved or self.rotary_scale_base is not None:
+                if (self.rotary_interleaved or self.rotary_scale_base is not None) and not F._sym(qkv):
                     qk = self._general_rotary(qkv[..., : (hq + hk) * d].reshape(b, s, hq + hk, d), hq)
                     q, k = qk[:, :, :hq], qk[:, :, hq:]
                 elif self.rotary_emb_dim > 0:
