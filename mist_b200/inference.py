@@ -62,8 +62,9 @@ def kv_cache(model: nn.Module, max_batch_size: int, max_seqlen: int):
 @torch.no_grad()
 def generate(model: nn.Module, input_ids: torch.Tensor, max_new_tokens: int, eos_token_id: Optional[int] = None,
              temperature: float = 0.0, top_k: int = 0, generator: Optional[torch.Generator] = None,
-             tp_group=None) -> torch.Tensor:
-    """Greedy (``temperature == 0``) or sampled continuation of ``input_ids`` ``[batch, prompt]``.
+             tp_group=None, top_p: float = 0.0) -> torch.Tensor:
+    """Greedy (``temperature == 0``) or sampled continuation of ``input_ids`` ``[batch, prompt]``
+    (``top_k`` keeps the k most likely tokens, ``top_p`` the smallest set whose probability reaches p).
     Returns ``[batch, prompt + generated]``; sequences that hit ``eos_token_id`` keep emitting it.
     With a tensor-parallel model pass its group as ``tp_group``: the vocabulary-parallel logits of
     the last position are gathered so every rank picks the same token (sampling then needs the
@@ -91,6 +92,11 @@ def generate(model: nn.Module, input_ids: torch.Tensor, max_new_tokens: int, eos
                     if top_k > 0:
                         kth = torch.topk(last, top_k, dim=-1).values[:, -1:]
                         last = last.masked_fill(last < kth, float("-inf"))
+                    if 0.0 < top_p < 1.0:
+                        srt, idx = torch.sort(last, dim=-1, descending=True)
+                        cum = torch.softmax(srt, dim=-1).cumsum(-1)
+                        drop = cum - torch.softmax(srt, dim=-1) >= top_p      # mass before this token already reaches p
+                        last = last.masked_fill(drop.scatter(-1, idx, drop), float("-inf"))
                     nxt = torch.multinomial(torch.softmax(last, dim=-1), 1, generator=generator).squeeze(1)
                 else:
                     nxt = last.argmax(dim=-1)

@@ -57,3 +57,28 @@ def test_eos_stops_sequences():
     first = generate(model, prompt, max_new_tokens=1)[:, -1]
     out = generate(model, prompt, max_new_tokens=5, eos_token_id=int(first[0]))
     assert (out[0, 4:] == int(first[0])).all()
+
+
+def test_nucleus_sampling_only_draws_from_the_smallest_set_that_reaches_p():
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY, check_world_size=False)
+    torch.manual_seed(0)
+    model = base_model_provider(cfg.model, device="cpu", dtype=torch.float32).eval()
+    prompt = torch.randint(0, 128, (3, 5))
+    with torch.no_grad():
+        probs = torch.softmax(model(prompt).reshape(3, 5, -1)[:, -1].float(), -1)
+    srt, idx = probs.sort(-1, descending=True)
+    allowed = []
+    for b in range(3):
+        n = int((srt[b].cumsum(0) < 0.6).sum()) + 1          # smallest prefix whose mass reaches 0.6
+        allowed.append(set(idx[b, :n].tolist()))
+    gen = torch.Generator().manual_seed(3)
+    seen = [set() for _ in range(3)]
+    for _ in range(40):
+        out = generate(model, prompt, max_new_tokens=1, temperature=1.0, top_p=0.6, generator=gen)
+        for b in range(3):
+            seen[b].add(int(out[b, -1]))
+    for b in range(3):
+        assert seen[b] <= allowed[b], (b, seen[b] - allowed[b])
+    # a very small p is greedy decoding
+    greedy = generate(model, prompt, max_new_tokens=3)
+    assert torch.equal(generate(model, prompt, max_new_tokens=3, temperature=1.0, top_p=1e-6, generator=gen), greedy)
