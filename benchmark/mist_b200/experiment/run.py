@@ -47,24 +47,32 @@ def main(argv=None):
     ap.add_argument("--spaces", nargs="*", default=["mist"])
     ap.add_argument("--out", default="experiment_results")
     ap.add_argument("--skip-exec", action="store_true", help="tune + analyze only (no GPUs needed)")
+    ap.add_argument("--skip-tune", action="store_true",
+                    help="reuse the best_config.yaml an earlier run left in the output directory (exec only)")
+    ap.add_argument("--disable-flash-attn", action="store_true", help="materialised attention scores instead of flash attention")
     ap.add_argument("--hosts", default=None, help="comma separated worker hosts for multi-node exec (pdsh)")
     ap.add_argument("--master-addr", default=None, help="rendezvous address (default: the first host, or 127.0.0.1)")
     ap.add_argument("--master-port", type=int, default=29533)
     args = ap.parse_args(argv)
     base = [f"experiment={args.experiment}", f"model={args.model}", f"hardware.num_nodes={args.nnodes}",
             f"hardware.num_gpus_per_node={args.nproc_per_node}", f"training.global_batch_size={args.global_batch_size}",
-            f"training.max_sequence_length={args.seq_len}", "strategy.enabled=false"]
+            f"training.max_sequence_length={args.seq_len}", "strategy.enabled=false",
+            f"model.use_flash_attn={'false' if args.disable_flash_attn else 'true'}"]
     seen = {}
     for space in args.spaces:
         out = os.path.abspath(os.path.join(args.out, space))
         os.makedirs(out, exist_ok=True)
         best = os.path.join(out, "best_config.yaml")
-        r = sh([sys.executable, os.path.join(BENCH, "tune", "tune_one_case.py"), *base, *SPACES[space],
-                f"output_dir={out}", f"+output_path={best}"])
-        if r.returncode != 0 or not os.path.exists(best):
+        if not args.skip_tune:
+            r = sh([sys.executable, os.path.join(BENCH, "tune", "tune_one_case.py"), *base, *SPACES[space],
+                    f"output_dir={out}", f"+output_path={best}"])
+            if r.returncode != 0:
+                continue
+            sh([sys.executable, os.path.join(BENCH, "analysis", "run.py"), "--config-name", "best_config", "-cd", out,
+                f"output_dir={out}"])
+        if not os.path.exists(best):
+            print(f"[{space}] no tuned configuration at {best}")
             continue
-        sh([sys.executable, os.path.join(BENCH, "analysis", "run.py"), "--config-name", "best_config", "-cd", out,
-            f"output_dir={out}"])
         with open(os.path.join(out, "summary.json")) as f:
             sol = json.load(f).get("tuning_best_solution")
         if sol in seen:

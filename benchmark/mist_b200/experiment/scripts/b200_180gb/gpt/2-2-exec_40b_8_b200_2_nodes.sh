@@ -1,0 +1,4 @@
+#!/bin/bash
+# Two nodes: executes the strategy the tune script left behind.  HOSTS=host0,host1 must be set.
+source ./scripts/base.sh
+run 2       8               "gpt2"  "40b"       2048     256                true                 "--skip-tune"
