@@ -687,6 +687,28 @@ def attention(q, k, v, scale: Optional[float] = None, causal: bool = True):
     return _AttnFn.apply(q, k, v, float(scale), bool(causal))
 
 
+def attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k=None, scale: Optional[float] = None, causal: bool = True):
+    """Attention over sequences packed back to back without padding: q ``[total_q, nh, d]``, k / v
+    ``[total_k, nh_kv, d]``, ``cu_seqlens_*`` the ``batch + 1`` cumulative lengths (a tensor or a list;
+    a tensor is read back to the host once).  Returns ``[total_q, nh, d]``.  Each sequence is one launch
+    of the ordinary kernel on a view of the packed tensors (the interface of the reference's
+    ``flash_attn_varlen`` entry points, csrc/flash_attn/flash_api.cpp ``varlen_fwd`` / ``varlen_bwd``)."""
+    cq = cu_seqlens_q.tolist() if isinstance(cu_seqlens_q, torch.Tensor) else list(cu_seqlens_q)
+    ck = cq if cu_seqlens_k is None else (
+        cu_seqlens_k.tolist() if isinstance(cu_seqlens_k, torch.Tensor) else list(cu_seqlens_k))
+    assert len(cq) == len(ck) and cq[0] == 0 and ck[0] == 0
+    outs = []
+    for i in range(len(cq) - 1):
+        qi, ki, vi = q[cq[i]:cq[i + 1]], k[ck[i]:ck[i + 1]], v[ck[i]:ck[i + 1]]
+        if qi.shape[0] == 0:
+            continue
+        if ki.shape[0] == 0:
+            outs.append(torch.zeros_like(qi))
+            continue
+        outs.append(attention(qi.unsqueeze(0), ki.unsqueeze(0), vi.unsqueeze(0), scale, causal).squeeze(0))
+    return torch.cat(outs, 0) if outs else q.new_zeros(q.shape)
+
+
 class _PackedAttnFn(torch.autograd.Function):
     """Rotary embedding + attention on a packed ``[b, s, 3, heads, d]`` projection output.
 

@@ -288,3 +288,30 @@ def test_label_smoothing_spreads_the_mass_over_the_other_classes():
     ours.sum().backward()
     want.sum().backward()
     assert torch.allclose(logits.grad, ref_in.grad, atol=1e-5)
+
+
+def test_varlen_attention_equals_per_sequence_attention():
+    from mist_b200.ops import functional as F
+    torch.manual_seed(0)
+    lens = [5, 1, 9, 3]
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)))
+    q = torch.randn(sum(lens), 4, 16, requires_grad=True)
+    k = torch.randn(sum(lens), 2, 16, requires_grad=True)
+    v = torch.randn(sum(lens), 2, 16, requires_grad=True)
+    out = F.attention_varlen(q, k, v, cu, causal=True)
+    out.square().sum().backward()
+    grads = [t.grad.clone() for t in (q, k, v)]
+    for t in (q, k, v):
+        t.grad = None
+    start = 0
+    ref = []
+    for n in lens:
+        o, _ = F._ref_attention(q[None, start:start + n], k[None, start:start + n], v[None, start:start + n],
+                                16 ** -0.5, True)
+        ref.append(o[0])
+        start += n
+    ref = torch.cat(ref)
+    assert torch.allclose(out, ref, atol=1e-5)
+    ref.square().sum().backward()
+    for g, t in zip(grads, (q, k, v)):
+        assert torch.allclose(g, t.grad, atol=1e-4)
