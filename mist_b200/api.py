@@ -25,6 +25,8 @@ from .parallel.state import ParallelState
 
 def _stage_layer_range(cfg: MistConfig, stage: int):
     parts = cfg.strategy.layer_partitions
+    if cfg.model.add_decoder and len(parts) > 1 and stage == len(parts) - 1:
+        return 0, parts[stage]          # the last stage of an encoder-decoder pipeline: the whole decoder
     start = sum(parts[:stage])
     return start, start + parts[stage]
 
@@ -62,12 +64,16 @@ class TrainingSession:
             device=device, dtype=dtype)
         # a table tied across the first and the last stage: pair the ranks and copy it over once
         tied_group = None
-        ties = bool(getattr(cfg.model, "tie_word_embeddings", False)) or family_of(cfg.model.name) == "bert"
+        ties = bool(getattr(cfg.model, "tie_word_embeddings", False)) or family_of(cfg.model.name) in ("bert", "t5")
         if ties and multi_stage and world > 1:
             tied_group = self.ps.create_embedding_group(getattr(cfg, "nccl_timeout", 120))
-            tied = self.model.tied_parameter() if hasattr(self.model, "tied_parameter") else None
-            if tied is not None:
-                dist.broadcast(tied.data, src=self.ps.embedding_src, group=tied_group)
+            if hasattr(self.model, "tied_parameters"):
+                tied = self.model.tied_parameters()
+            else:
+                one = self.model.tied_parameter() if hasattr(self.model, "tied_parameter") else None
+                tied = [] if one is None else [one]
+            for t in tied:
+                dist.broadcast(t.data, src=self.ps.embedding_src, group=tied_group)
         pre_post = StageStrategy.from_vector(st.pre_post_strategy_array) if st.pre_post_strategy == "preset" else None
         self.engine = TrainEngine(self.model, self.ps, self.strategy, self.G, st.gradient_checkpointing[stage],
                                   hp=hp, comm_backend=self.comm_backend, overlap=bool(cfg.get("overlap", True)),
@@ -104,8 +110,6 @@ class TrainingSession:
             parts = {k: v.chunk(self.G) for k, v in batch.items()}
             batches = [{k: parts[k][i] for k in batch} for i in range(self.G)]
         if self.pipeline is not None:
-            assert not self.cfg.model.add_decoder, \
-                "pipeline stages exchange one hidden-state tensor: single-stack families only (no encoder-decoder)"
             return self.pipeline.train_step(batches)
         return self.engine.train_step(batches)
 

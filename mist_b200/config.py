@@ -343,8 +343,16 @@ class StrategyConfig:
     def verify_with_other_config(self, model: ModelConfig, training: TrainingConfig, hardware: HardwareConfig):
         gbs = training.global_batch_size
         G = self.gradient_accumulation_steps
-        assert sum(self.layer_partitions) == model.num_hidden_layers, \
-            f"layer_partitions sum to {sum(self.layer_partitions)}, model has {model.num_hidden_layers} layers"
+        L = model.num_hidden_layers
+        if model.add_decoder and self.num_stages > 1:
+            # encoder-decoder models over pipeline stages: the encoder blocks are split over all stages but
+            # the last, which holds the whole decoder
+            assert self.layer_partitions[-1] == L and sum(self.layer_partitions[:-1]) == L, (
+                f"encoder-decoder pipeline: layer_partitions {self.layer_partitions} must split the {L} encoder "
+                f"blocks over the first stages and give the last stage the {L} decoder blocks")
+        else:
+            assert sum(self.layer_partitions) == L, \
+                f"layer_partitions sum to {sum(self.layer_partitions)}, model has {L} layers"
         used = sum(n * m for n, m in self.device_assignment)
         assert used == hardware.num_devices, f"device_assignment uses {used} devices, hardware has {hardware.num_devices}"
         for ck, nl in zip(self.gradient_checkpointing, self.layer_partitions):

@@ -35,9 +35,13 @@ class Pooler(nn.Module):
 class TransformerLanguageModel(nn.Module):
     def __init__(self, cfg: ModelConfig, pre_process=True, post_process=True, process_groups=None,
                  pre_post_process_group=None, layer_range=None, sequence_parallel=False,
-                 device=None, dtype=None):
+                 device=None, dtype=None, stacks=("encoder", "decoder")):
+        """``stacks``: which of the model's stacks this pipeline stage holds (an encoder-decoder model
+        split over stages gives its first stages encoder blocks only and its last stage the decoder;
+        that last stage also gets an embedding, for the decoder's input tokens)."""
         super().__init__()
         self.cfg, self.pre_process, self.post_process = cfg, pre_process, post_process
+        self.enc_hidden_input = None      # encoder output received from the previous pipeline stage
         dtype = dtype or cfg.params_dtype
         L = cfg.num_hidden_layers
         if not isinstance(process_groups, (list, tuple)):
@@ -54,13 +58,18 @@ class TransformerLanguageModel(nn.Module):
                 cfg.num_tokentypes, process_group=self.pre_post_process_group,
                 sequence_parallel=sequence_parallel, padding_idx=cfg.padding_idx, device=device, dtype=dtype)
         self.encoder = None
-        if cfg.add_encoder:
+        if cfg.add_encoder and "encoder" in stacks:
+            # the encoder's final norm sits with its last block: on the last stage of a single-stack model,
+            # on the stage that also holds the decoder, or on the last encoder-only stage
+            last_encoder_stage = layer_range is None or layer_range[1] == L
             self.encoder = ParallelTransformer(
                 cfg, self.process_groups, layer_range=layer_range, attn_mask_type=cfg.encoder_attn_mask_type,
-                post_norm=post_process or cfg.add_decoder, sequence_parallel=sequence_parallel,
+                post_norm=post_process or (cfg.add_decoder and last_encoder_stage), sequence_parallel=sequence_parallel,
                 device=device, dtype=dtype)
         self.decoder = None
-        if cfg.add_decoder:
+        if cfg.add_decoder and "decoder" in stacks:
+            if "encoder" not in stacks:
+                layer_range = None        # the decoder is never split
             self.decoder = ParallelTransformer(
                 cfg, self.process_groups, layer_range=layer_range, is_decoder=True,
                 attn_mask_type=cfg.decoder_attn_mask_type, post_norm=post_process,
@@ -68,7 +77,12 @@ class TransformerLanguageModel(nn.Module):
         self.pooler = Pooler(cfg.hidden_size, device=device, dtype=dtype) if (post_process and cfg.add_pooler) else None
 
     def set_input_tensor(self, t):
-        (self.encoder or self.decoder).set_input_tensor(t)
+        if self.encoder is not None:
+            self.encoder.set_input_tensor(t)
+        elif self.cfg.add_encoder and self.decoder is not None:
+            self.enc_hidden_input = t      # decoder stage of an encoder-decoder pipeline: t is the encoder output
+        else:
+            self.decoder.set_input_tensor(t)
 
     def flop_estimate(self, batch_size: int, seq_len: int) -> float:
         """Training FLOPs of one micro-batch (forward + backward, no recomputation)."""
@@ -84,18 +98,22 @@ class TransformerLanguageModel(nn.Module):
         token) of the encoder / decoder tokens; ``enc_dec_attn_mask``: mask of the encoder tokens as
         cross attention sees them (defaults to ``enc_attn_mask``).  Masks without padding are dropped."""
         bs = enc_input_ids.shape[0] if enc_input_ids is not None else None
+        if enc_hidden_states is None and self.encoder is None and self.enc_hidden_input is not None:
+            enc_hidden_states = self.enc_hidden_input
         enc_mask = PaddingMask.prepare(enc_attn_mask)
         dec_mask = PaddingMask.prepare(dec_attn_mask)
         cross_mask = PaddingMask.prepare(enc_dec_attn_mask) if enc_dec_attn_mask is not None else enc_mask
-        if self.pre_process:
+        if self.pre_process and self.encoder is not None:
             hidden = self.embedding(enc_input_ids, enc_position_ids, tokentype_ids)
         else:
             hidden = None
         residual = None
         if self.encoder is not None and enc_hidden_states is None:
             out = self.encoder(hidden, residual, batch_size=bs, attn_mask=enc_mask)
-            if not (self.post_process or self.cfg.add_decoder):
-                return out      # (hidden, residual) handed to the next pipeline stage
+            if not self.post_process and self.decoder is None:
+                # handed to the next pipeline stage: (hidden, residual), or the normalised encoder output
+                # after the last encoder block of an encoder-decoder model
+                return out
             enc_out = out
         else:
             enc_out = enc_hidden_states

@@ -33,13 +33,22 @@ class T5Model(nn.Module):
     def __init__(self, cfg: ModelConfig, num_tokentypes=0, pre_process=True, post_process=True,
                  process_groups=None, pre_post_process_group=None, layer_range=None,
                  sequence_parallel=False, device=None, dtype=None):
+        """Over pipeline stages (``pre_process`` / ``post_process`` not both true) the encoder blocks
+        ``layer_range`` go to the stages before the last, the last stage holds the whole decoder, its
+        own copy of the word table (decoder input embedding and output projection) and the head."""
         super().__init__()
         assert cfg.add_encoder and cfg.add_decoder, "t5: encoder and decoder stacks expected"
         self.cfg, self.pre_process, self.post_process = cfg, pre_process, post_process
         dtype = dtype or cfg.params_dtype
+        self.tied_across_stages = not (pre_process and post_process)
+        stacks = ("encoder", "decoder") if not self.tied_across_stages else (("decoder",) if post_process else ("encoder",))
         self.language_model = TransformerLanguageModel(
-            cfg, pre_process, post_process, process_groups, pre_post_process_group, layer_range,
-            sequence_parallel, device, dtype)
+            cfg, pre_process or post_process, post_process, process_groups, pre_post_process_group, layer_range,
+            sequence_parallel, device, dtype, stacks=stacks)
+        if self.tied_across_stages and (pre_process or post_process):
+            # encoder and decoder share one embedding (word and position tables): both copies are tied
+            for p in self.language_model.embedding.parameters():
+                p._tied_across_stages = True
         if post_process:
             grp = self.language_model.pre_post_process_group
             self.lm_head = T5LMHead(cfg.vocab_size // dist_ops.group_size(grp), grp, device, dtype,
@@ -48,10 +57,18 @@ class T5Model(nn.Module):
     def set_input_tensor(self, t):
         self.language_model.set_input_tensor(t)
 
+    def tied_parameters(self):
+        """This stage's copies of the embedding tables when the model is split over pipeline stages."""
+        if not self.tied_across_stages or not (self.pre_process or self.post_process):
+            return []
+        return list(self.language_model.embedding.parameters())
+
     def forward(self, encoder_input_ids, decoder_input_ids, encoder_attn_mask=None, decoder_attn_mask=None,
                 encoder_decoder_attn_mask=None, tokentype_ids=None, lm_labels=None, labels=None,
                 enc_hidden_states=None):
         lm_labels = lm_labels if lm_labels is not None else labels
+        if self.language_model.decoder is None:      # encoder-only pipeline stage
+            return self.language_model(encoder_input_ids, enc_attn_mask=encoder_attn_mask, tokentype_ids=tokentype_ids)
         dec_out, enc_out = self.language_model(
             encoder_input_ids, dec_input_ids=decoder_input_ids, tokentype_ids=tokentype_ids,
             enc_hidden_states=enc_hidden_states, enc_attn_mask=encoder_attn_mask, dec_attn_mask=decoder_attn_mask,

@@ -124,17 +124,18 @@ class PipelineSchedule:
         else:
             x = None
         self.engine._micro = k
-        if self.first and self.engine.pre_unit is not None:
+        if self.engine.pre_unit is not None:      # the first stage; also the decoder stage of an encoder-decoder model
             self.engine._wait_params(self.engine.pre_unit)
         if self.last:
-            kwargs = dict(batch)
-            if not self.first:
-                kwargs["input_ids"] = batch["input_ids"]   # only the shape is used past stage 0
-            out = self.model(**kwargs)
+            out = self.model(**batch)
         else:
             kwargs = {k2: v for k2, v in batch.items() if k2 != "labels"}
-            hidden, residual = self.model(**kwargs)
-            out = hidden if residual is None else hidden + residual
+            res = self.model(**kwargs)
+            if isinstance(res, tuple):
+                hidden, residual = res
+                out = hidden if residual is None else hidden + residual
+            else:
+                out = res      # already one tensor (normalised output of an encoder's last block)
         return x, out
 
     def _backward(self, x, out, k: int, grad):

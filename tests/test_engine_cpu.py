@@ -535,3 +535,85 @@ def test_bert_over_two_pipeline_stages_keeps_the_tied_word_table_in_step():
             if n == "word_embeddings.weight":
                 n = "language_model.embedding.word_embeddings.weight"
             assert (p - new_state[n].detach()).abs().max().item() < 2e-4, (r, n)
+
+
+def _t5_pp_worker(rank, world, port, parts, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mist_b200.api import TrainingSession
+        vec = "[2,1,1,0,0,0,0,0,0,0]"
+        S = len(parts)
+        cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=t5/1.7b"] + TINY + [
+            "model.num_hidden_layers=2", f"hardware.num_gpus_per_node={S}", "training.global_batch_size=4",
+            f"strategy.layer_partitions={parts}", "strategy.device_assignment=[" + ",".join(["[1,1]"] * S) + "]",
+            "strategy.gradient_checkpointing=[" + ",".join(["0"] * (S - 1) + ["1"]) + "]",
+            "strategy.gradient_accumulation_steps=2",
+            "strategy.stage_strategies=[" + ",".join([vec] * S) + "]", f"strategy.pre_post_strategy_array={vec}"],
+            check_world_size=False)
+        sess = TrainingSession(cfg, seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        prov = get_inputs_provider(cfg.model.name)
+        losses = []
+        for it in range(2):
+            losses.append(float(sess.step_on_device_batch(prov(4, 32, 256, "cpu", seed=600 + it))))
+        sess.finish()
+        ret[rank] = (sess.ps.stage, losses, {n: p.detach().clone() for n, p in sess.model.named_parameters()})
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("parts", [[2, 2], [1, 1, 2]])
+def test_encoder_decoder_model_over_pipeline_stages(parts):
+    """T5: encoder blocks on the first stage(s), the whole decoder on the last one with its own copy of
+    the embedding tables; everything must follow single-process training."""
+    world = len(parts)
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_t5_pp_worker, args=(world, 27300 + os.getpid() % 600 + world, parts, ret), nprocs=world, join=True)
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=t5/1.7b"] + TINY + [
+        "model.num_hidden_layers=2", "strategy.layer_partitions=[2]"], check_world_size=False)
+    from mist_b200.models.provider import base_model_provider as bmp
+    torch.manual_seed(0)
+    ref = bmp(cfg.model, device="cpu", dtype=torch.float32)
+    sd = ref.state_dict()
+    enc_start = 0
+    for stage in range(world):
+        last = stage == world - 1
+        lr_ = (0, 2) if last else (enc_start, enc_start + parts[stage])
+        torch.manual_seed(0 + 17 * stage)
+        m = bmp(cfg.model, pre_process=stage == 0, post_process=last, layer_range=lr_, device="cpu", dtype=torch.float32)
+        for n, p in m.state_dict().items():
+            if last and ".embedding." in n:
+                continue                    # the copies are overwritten by the first stage's tables
+            if ".encoder.layers." in n:
+                head, rest = n.split(".layers.")
+                idx, tail = rest.split(".", 1)
+                n = f"{head}.layers.{int(idx) + enc_start}.{tail}"
+            sd[n] = p.clone()
+        if not last:
+            enc_start += parts[stage]
+    ref.load_state_dict(sd)
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    prov = get_inputs_provider(cfg.model.name)
+    for it in range(2):
+        b = prov(4, 32, 256, "cpu", seed=600 + it)
+        opt.zero_grad()
+        tot = 0.0
+        for g in range(2):
+            l = ref(**{k: v[2 * g:2 * g + 2] for k, v in b.items()}) / 2
+            l.backward()
+            tot += l.item()
+        opt.step()
+        assert abs(ret[world - 1][1][it] - tot) < 2e-4, (it, ret[world - 1][1], tot)
+    new_state = dict(ref.named_parameters())
+    enc_start = 0
+    for r in range(world):
+        stage, _, params = ret[r]
+        for n, p in params.items():
+            if ".encoder.layers." in n:
+                head, rest = n.split(".layers.")
+                idx, tail = rest.split(".", 1)
+                n = f"{head}.layers.{int(idx) + enc_start}.{tail}"
+            assert (p - new_state[n].detach()).abs().max().item() < 2e-4, (r, n)
+        if r < world - 1:
+            enc_start += parts[r]
