@@ -122,6 +122,11 @@ def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache
     gran = tun.tuning_granularity
     L = cfg.model.num_hidden_layers
     offset = int(getattr(tun, "layers_offset", 2))
+    # Encoder-decoder models run over pipeline stages in one fixed form only (encoder blocks on the
+    # first stages, the whole decoder on the last), which the layer-partition search does not
+    # describe: their strategies are searched within one stage.
+    if cfg.model.add_decoder:
+        gran = "no-pp"
     if gran == "inter-stage":
         return _inter_stage_tune_nonuniform(cfg, ev, cache_dir, tp)
     if gran == "no-pp":
