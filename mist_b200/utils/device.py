@@ -39,3 +39,12 @@ def join_streams(*streams):
         for j, ev in enumerate(events):
             if i != j:
                 s.wait_event(ev)
+
+
+def free_port(host: str = "127.0.0.1") -> int:
+    """A TCP port nothing listens on right now (the kernel picks it), for a local rendezvous."""
+    import socket
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
+        sock.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        sock.bind((host, 0))
+        return int(sock.getsockname()[1])

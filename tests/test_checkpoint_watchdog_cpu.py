@@ -9,6 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from mist_b200.utils.device import free_port
 from mist_b200.config import load_config
 from mist_b200.models.provider import get_inputs_provider
 
@@ -75,7 +76,7 @@ def test_checkpoint_resume_under_another_zero_level(tmp_path):
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 33500 + os.getpid() % 2000
+    port = free_port()
     mp.spawn(_ckpt_worker, args=(world, port, str(tmp_path / "ckpt"), ret), nprocs=world, join=True)
     assert ret["step"] == 2
     assert "meta.json" in ret["files"] and "strategy.yaml" in ret["files"]
@@ -116,7 +117,7 @@ def test_heartbeat_reports_a_rank_that_stopped():
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 35500 + os.getpid() % 2000
+    port = free_port()
     mp.spawn(_hb_worker, args=(world, port, ret), nprocs=world, join=True)
     assert ret["stale"] == [1]
     assert ret["raised"]
@@ -165,7 +166,7 @@ def _leaver_worker(rank, world, port, ret):
 def test_collective_after_a_rank_left_raises_within_the_timeout():
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 36500 + os.getpid() % 2000
+    port = free_port()
     ctx = mp.get_context("spawn")
     procs = [ctx.Process(target=_leaver_worker, args=(r, 2, port, ret)) for r in range(2)]
     for p in procs:
@@ -215,7 +216,7 @@ def test_checkpoint_roundtrip_pipeline_of_tensor_parallel_stages(tmp_path):
     rank), and a fresh session resumed from them continues with the same loss."""
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 38500 + os.getpid() % 1000
+    port = free_port()
     mp.spawn(_ckpt_pptp_worker, args=(4, port, str(tmp_path / "ck"), ret), nprocs=4, join=True)
     for s in range(2):
         for t in range(2):

@@ -8,6 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from mist_b200.utils.device import free_port
 from mist_b200.config import StageStrategy, load_config
 from mist_b200.models.provider import base_model_provider, get_inputs_provider
 from mist_b200.parallel.engine import TrainEngine
@@ -84,7 +85,7 @@ def test_data_parallel_gloo_matches_single_process(zero_flags, G):
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + (os.getpid() + hash((zero_flags, G))) % 2000
+    port = free_port()
     mp.spawn(_dp_worker, args=(world, port, zero_flags, G, ret), nprocs=world, join=True)
     # reference: one process sees both ranks' micro batches
     cfg, ref = _tiny_model()
@@ -107,7 +108,7 @@ def test_weight_grad_optimizer_offload_gloo_matches_single_process(zero_flags):
     world, G = 2, 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 31500 + (os.getpid() + hash(zero_flags)) % 2000
+    port = free_port()
     mp.spawn(_dp_worker, args=(world, port, zero_flags, G, ret, (0.5, 0.5, 0.5, 0)), nprocs=world, join=True)
     assert ret["offloaded"][0] > 0
     if zero_flags[1]:
@@ -133,7 +134,7 @@ def test_zero_with_activation_checkpointing_and_offload_gloo(zero_flags):
     world, G = 2, 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 32500 + (os.getpid() + hash(zero_flags)) % 2000
+    port = free_port()
     mp.spawn(_dp_worker, args=(world, port, zero_flags, G, ret, (0, 0, 0, 0.5), 3), nprocs=world, join=True)
     cfg, ref = _tiny_model()
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
@@ -196,7 +197,7 @@ def test_pipeline_1f1b_matches_single_process():
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + (os.getpid() + 77) % 2000
+    port = free_port()
     mp.spawn(_pp_worker, args=(world, port, ret), nprocs=world, join=True)
     # single-process reference with the same initial weights: build both stage models with the
     # same seeds the session uses and copy them into one 4-layer model
@@ -297,7 +298,7 @@ def test_encoder_decoder_model_data_parallel_zero(zero_flags):
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 34100 + (os.getpid() + hash(zero_flags)) % 1000
+    port = free_port()
     mp.spawn(_t5_dp_worker, args=(world, port, zero_flags, ret), nprocs=world, join=True)
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=t5/1.7b"] + TINY, check_world_size=False)
     torch.manual_seed(0)
@@ -343,7 +344,7 @@ def test_three_stage_pipeline_with_fewer_or_more_micro_batches_than_stages(G):
     world = 3
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 30500 + (os.getpid() + 13 * G) % 2000
+    port = free_port()
     mp.spawn(_pp3_worker, args=(world, port, G, ret), nprocs=world, join=True)
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY, check_world_size=False)
     torch.manual_seed(0)
@@ -414,7 +415,7 @@ def test_pipeline_with_data_parallel_stages_and_zero(zero, offload, tied):
     world = 4
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 28500 + (os.getpid() + hash((zero, offload, tied))) % 1500
+    port = free_port()
     extra = ["model.tie_word_embeddings=true"] if tied else []
     mp.spawn(_ppdp_worker, args=(world, port, zero, ret, offload, extra), nprocs=world, join=True)
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + ["model.num_hidden_layers=4",
@@ -492,7 +493,7 @@ def test_bert_over_two_pipeline_stages_keeps_the_tied_word_table_in_step():
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_bert_pp_worker, args=(world, 28100 + os.getpid() % 800, ret), nprocs=world, join=True)
+    mp.spawn(_bert_pp_worker, args=(world, free_port(), ret), nprocs=world, join=True)
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=bert/1.3b"] + TINY + [
         "model.num_hidden_layers=4", "strategy.layer_partitions=[4]"], check_world_size=False)
     from mist_b200.models.provider import base_model_provider as bmp
@@ -569,7 +570,7 @@ def test_encoder_decoder_model_over_pipeline_stages(parts):
     world = len(parts)
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_t5_pp_worker, args=(world, 27300 + os.getpid() % 600 + world, parts, ret), nprocs=world, join=True)
+    mp.spawn(_t5_pp_worker, args=(world, free_port(), parts, ret), nprocs=world, join=True)
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=t5/1.7b"] + TINY + [
         "model.num_hidden_layers=2", "strategy.layer_partitions=[2]"], check_world_size=False)
     from mist_b200.models.provider import base_model_provider as bmp

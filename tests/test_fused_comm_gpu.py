@@ -7,6 +7,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from mist_b200.utils.device import free_port
+
 pytestmark = pytest.mark.gpu
 
 
@@ -78,7 +80,7 @@ def test_fused_matches_nccl(zero_flags, G):
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + (os.getpid() + hash((zero_flags, G))) % 2000
+    port = free_port()
     mp.spawn(_worker, args=(world, port, zero_flags, G, ret), nprocs=world, join=True)
     for r in range(world):
         diff, scale = ret[r]

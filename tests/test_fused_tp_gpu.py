@@ -7,6 +7,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from mist_b200.utils.device import free_port
+
 pytestmark = pytest.mark.gpu
 
 
@@ -129,7 +131,7 @@ def test_two_gpus_match_nccl_path():
         pytest.skip("needs 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + (os.getpid() + 321) % 2000
+    port = free_port()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     for r in range(2):
         for k, v in ret[r].items():

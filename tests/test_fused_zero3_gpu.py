@@ -7,6 +7,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from mist_b200.utils.device import free_port
+
 pytestmark = pytest.mark.gpu
 
 
@@ -118,7 +120,7 @@ def test_two_gpus_gather_and_gemm():
         pytest.skip("needs 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + (os.getpid() + 777) % 2000
+    port = free_port()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     for r in range(2):
         for mismatch, err in ret[r]:
@@ -169,7 +171,7 @@ def test_engine_zero3_forward_gather_in_first_gemm_matches_prefetch():
         pytest.skip("needs 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + (os.getpid() + 913) % 2000
+    port = free_port()
     mp.spawn(_engine_worker, args=(2, port, ret), nprocs=2, join=True)
     for r in range(2):
         l_nccl, l_fused, wdiff = ret[r]

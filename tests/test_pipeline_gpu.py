@@ -6,6 +6,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from mist_b200.utils.device import free_port
+
 pytestmark = pytest.mark.gpu
 
 
@@ -46,7 +48,7 @@ def test_two_stage_pipeline_trains():
         pytest.skip("needs 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + (os.getpid() + 555) % 2000
+    port = free_port()
     mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
     losses = ret[1]                       # the last stage owns the loss
     assert all(l == l for l in losses) and losses[-1] < losses[0]

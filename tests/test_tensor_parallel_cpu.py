@@ -10,6 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+from mist_b200.utils.device import free_port
 from mist_b200.config import load_config
 from mist_b200.models.provider import base_model_provider, get_inputs_provider
 
@@ -79,7 +80,7 @@ def test_tp2_matches_single_process(exp, sp):
     ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 37500 + (os.getpid() + hash((exp, sp))) % 2000
+    port = free_port()
     mp.spawn(_worker, args=(2, port, exp, sp, ref_state, ret), nprocs=2, join=True)
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
     prov = get_inputs_provider(cfg.model.name)
@@ -151,7 +152,7 @@ def test_heterogeneous_pipeline_dp2_then_tp2_matches_single_process():
     ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 39500 + os.getpid() % 2000
+    port = free_port()
     mp.spawn(_hetero_worker, args=(4, port, ref_state, ret), nprocs=4, join=True)
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
     prov = get_inputs_provider(cfg.model.name)
@@ -218,7 +219,7 @@ def test_pipeline_of_tensor_parallel_stages_matches_single_process(sp):
     ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 41500 + (os.getpid() + int(sp)) % 2000
+    port = free_port()
     mp.spawn(_pptp_worker, args=(4, port, sp, ref_state, ret), nprocs=4, join=True)
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
     prov = get_inputs_provider(cfg.model.name)
@@ -298,7 +299,7 @@ def test_dp2_x_tp2_sequence_parallel_with_zero_matches_single_process(zero):
     ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 43500 + (os.getpid() + hash(zero)) % 2000
+    port = free_port()
     mp.spawn(_dptp_worker, args=(4, port, zero, ref_state, ret), nprocs=4, join=True)
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
     prov = get_inputs_provider(cfg.model.name)
@@ -353,7 +354,7 @@ def test_tp2_other_families_match_single_process(fam, sp):
     ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 45500 + (os.getpid() + hash((fam, sp))) % 2000
+    port = free_port()
     mp.spawn(_family_worker, args=(2, port, fam, sp, ref_state, ret), nprocs=2, join=True)
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
     prov = get_inputs_provider(cfg.model.name)
@@ -405,7 +406,7 @@ def test_tp2_cached_generation_matches_single_process():
     want = generate(ref, prompt, max_new_tokens=5)
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 47500 + os.getpid() % 2000
+    port = free_port()
     mp.spawn(_gen_worker, args=(2, port, ref_state, prompt, ret), nprocs=2, join=True)
     assert torch.equal(ret[0], want) and torch.equal(ret[1], want)
 
@@ -452,7 +453,7 @@ def test_heterogeneous_pipeline_wide_stage_feeds_two_data_parallel_ranks():
     ref_state = {n: p.detach().clone() for n, p in ref.named_parameters()}
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 49500 + os.getpid() % 1500
+    port = free_port()
     mp.spawn(_hetero2_worker, args=(3, port, ref_state, ret), nprocs=3, join=True)
     opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
     prov = get_inputs_provider(cfg.model.name)
@@ -497,7 +498,7 @@ def test_label_smoothing_over_vocabulary_shards():
     labels = torch.randint(0, 32, (6,))
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_smooth_worker, args=(2, 47100 + os.getpid() % 500, logits, labels, ret), nprocs=2, join=True)
+    mp.spawn(_smooth_worker, args=(2, free_port(), logits, labels, ret), nprocs=2, join=True)
     full = logits.clone().requires_grad_(True)
     want = vocab_parallel_cross_entropy(full, labels, label_smoothing=0.2)
     want.sum().backward()
