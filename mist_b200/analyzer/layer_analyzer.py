@@ -22,7 +22,6 @@ mist/benchmark/common.py:35-217 (trace one hidden layer with symbolic b, cache t
 """
 from __future__ import annotations
 
-import hashlib
 import os
 import pickle
 from dataclasses import dataclass, field

@@ -19,7 +19,6 @@ from __future__ import annotations
 
 import contextlib
 import itertools
-import math
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 

@@ -18,7 +18,7 @@ import torch
 import torch.distributed as dist
 
 from .config import MistConfig, StageStrategy, load_config
-from .models.provider import base_model_provider, family_of, get_inputs_provider
+from .models.provider import base_model_provider, family_of
 from .parallel.engine import TrainEngine
 from .parallel.state import ParallelState
 

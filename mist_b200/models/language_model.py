@@ -6,12 +6,11 @@ head (reference: mist/model/language_model.py:71-312; nested checkpoint layout :
 """
 from __future__ import annotations
 
-from typing import List, Optional
 
 import torch
 import torch.nn as nn
 
-from ..config import AttnMaskType, ModelConfig, PositionEmbeddingType
+from ..config import ModelConfig, PositionEmbeddingType
 from ..modules.layers import ColumnParallelLinear, PaddingMask, VocabParallelEmbedding, vocab_parallel_cross_entropy
 from ..ops import functional as F
 from ..parallel import dist_ops

@@ -10,9 +10,8 @@ always take precedence.
 """
 from __future__ import annotations
 
-import json
 import os
-from dataclasses import asdict, dataclass, field
+from dataclasses import dataclass, field
 from typing import Dict, Tuple
 
 from .node_spec import NodeSpec

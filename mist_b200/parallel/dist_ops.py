@@ -8,7 +8,6 @@ for the op set, mist/distributed/overrides.py:12-100 for the fake group idea).
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -28,7 +28,6 @@ import torch.nn as nn
 
 from ..config import StageStrategy, ZeroLevel
 from ..ops import functional as F
-from ..ops import native
 from ..utils.logging import record
 from .flat_unit import FlatUnit
 from .state import ParallelState

@@ -31,7 +31,7 @@ micro steps (there the division is commented out and gradients are summed).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 import torch.distributed as dist

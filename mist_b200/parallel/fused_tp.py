@@ -17,7 +17,7 @@ blocks are per (kernel mode, shape) call site with a launch counter as epoch.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Dict, Optional, Tuple
+from typing import Dict, Tuple
 
 import torch
 import torch.distributed as dist

@@ -11,7 +11,7 @@ buffer pools mist/re_swap_manager/mem_buffer_pool.py:60-195).
 from __future__ import annotations
 
 import weakref
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Optional
 
 import torch
 

@@ -23,7 +23,7 @@ import argparse
 import itertools
 import json
 import os
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 import torch
 import torch.distributed as dist

@@ -19,15 +19,15 @@ from __future__ import annotations
 
 import ctypes as C
 import math
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 
-from ..analyzer.stage_evaluator import StageEvaluator, pipeline_latency
+from ..analyzer.stage_evaluator import StageEvaluator
 from ..config import MistConfig
 from ..ops import native
 from .candidates import device_mesh_candidates, grad_accum_candidates, stage_count_candidates
-from .intra_stage import IntraStageResult, StagePoint, intra_stage_tune
+from .intra_stage import intra_stage_tune
 
 Solution = Tuple[int, List[Tuple[Tuple[Tuple[int, int], Tuple[int, int], int, int], Tuple[float, ...]]]]
 

@@ -23,12 +23,10 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
 
-from ..config import ZeroLevel
 from . import yamlconf
 
 
