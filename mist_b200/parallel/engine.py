@@ -225,7 +225,6 @@ class TrainEngine:
             biggest = max(u.padded for us in self.layer_units.values() for u in us)
             self._slots = [torch.empty(biggest, dtype=mk["dtype"], device=self.device) for _ in range(2)]
             self._slot_of: Dict[str, int] = {}
-            self._next_slot = 0
             self._gather_done: Dict[str, "torch.cuda.Event"] = {}
             if any(u.weight_split is not None for u in layer_units):
                 self._step_scratch = torch.empty(biggest, dtype=mk["dtype"], device=self.device)

@@ -333,20 +333,3 @@ class FlatUnit:
             self.grad_shard_acc.zero_()
         for p in self.params:
             p.grad_accumulate = False
-
-    # ------------------------------------------------------------------ checkpoint views
-    def state_for_checkpoint(self) -> Dict[str, torch.Tensor]:
-        return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq,
-                "step": torch.tensor(self.step_count)}
-
-    def load_state_from_checkpoint(self, sd: Dict[str, torch.Tensor]):
-        self.master.copy_(sd["master"])
-        self.exp_avg.copy_(sd["exp_avg"])
-        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
-        self.step_count = int(sd["step"])
-        if self.weight_split is not None:
-            raise NotImplementedError("loading a checkpoint into host-offloaded weights: load first, "
-                                      "then enable the offload")
-        dst = self.param_shard if self.param_shard is not None else (
-            self.flat_param[self.shard_range()] if self.sharded_state else self.flat_param)
-        dst.copy_(self.master.to(dst.dtype))
