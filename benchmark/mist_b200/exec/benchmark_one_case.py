@@ -44,6 +44,12 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
         torch.cuda.memory._record_memory_history()
     sess = TrainingSession(cfg, comm_backend=comm_backend, seed=seed)
     ps = sess.ps
+    # messages carry rank and stage; only the first data-parallel rank of each (stage, tp) position logs
+    from mist_b200.utils.logging import get_logger, log_memory, set_rank_filter
+    set_rank_filter(ps.dp_rank, tag=f"rank {rank} stage {ps.stage} tp {ps.tp_rank}")
+    log = get_logger()
+    log.info("model built: %d parameters on this rank", sess.engine.num_parameters())
+    log_memory("after model build:", log)
     mb, G, seq = sess.micro_batch, sess.G, sess.seq_len
     vocab = cfg.model.vocab_size
     gen = torch.Generator().manual_seed(seed + 31 * ps.dp_rank)     # same data on every tp / pp rank of a replica

@@ -367,8 +367,6 @@ def is_sym(*xs) -> bool:
 
 
 # ------------------------------------------------------------------------------ recording
-def _tid(x) -> Optional[int]:
-    return x.tid if isinstance(x, SymTensor) else None
 
 
 def record(op: str, inputs: Sequence, out_shapes: Sequence[Tuple[Sequence[Expr], torch.dtype]], *,

@@ -649,15 +649,6 @@ def attn_fwd(q, k, v, scale, causal, block_n=None):
     return o, lse
 
 
-def _attn_bwd_library(dout, q, k, v, o, lse, scale, causal):
-    """Backward through a library kernel (used until the tcgen05 backward covers the case)."""
-    qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
-    with torch.enable_grad():
-        nh, nkv = q.shape[2], k.shape[2]
-        out = F.scaled_dot_product_attention(
-            qq.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2), is_causal=causal, scale=scale,
-            enable_gqa=(nh != nkv))
-    return torch.autograd.grad(out, (qq, kk, vv), dout.transpose(1, 2))
 
 
 class _AttnFn(torch.autograd.Function):

@@ -18,8 +18,6 @@ import torch
 ACTIVATION_SWAP_MIN_NUMEL = 1 << 20   # smaller saved tensors stay on the device
 
 
-def _pin(t: torch.Tensor) -> torch.Tensor:
-    return t.pin_memory() if torch.cuda.is_available() else t
 
 
 class MemoryBuffer:
