@@ -70,7 +70,8 @@ class _TraceHooks:
     """Scope markers driven by the transformer stack's per-block callbacks."""
 
     def before_layer(self, stack, i, hidden, residual):
-        set_scope(f"block{i}")
+        # the blocks of a decoder stack (the second stack of an encoder-decoder model) get their own scopes
+        set_scope(f"{'dblock' if getattr(stack.layers[0], 'is_decoder', False) else 'block'}{i}")
         return hidden, residual
 
     def after_layer(self, stack, i, hidden, residual):
@@ -182,9 +183,14 @@ class ModelAnalysis:
     symbol_names: List[str]
     sequence_parallel: bool
     graph_nodes: int
+    enc_block: Optional[LayerInfo] = None      # encoder-decoder models only
+    dec_block: Optional[LayerInfo] = None
 
     def layer(self, which: str) -> LayerInfo:
-        return {"pre_layer": self.pre, "block_layer": self.block, "post_layer": self.post}[which]
+        table = {"pre_layer": self.pre, "block_layer": self.block, "post_layer": self.post,
+                 "enc_block_layer": getattr(self, "enc_block", None) or self.block,
+                 "dec_block_layer": getattr(self, "dec_block", None) or self.block}
+        return table[which]
 
 
 def trace_and_analyze(model_cfg: ModelConfig, seq_len: int, tp: int = 1, sequence_parallel: bool = False,
@@ -220,16 +226,26 @@ def trace_and_analyze(model_cfg: ModelConfig, seq_len: int, tp: int = 1, sequenc
             model(input_ids=ids, labels=labels)
     scopes = graph.scopes()
     block_scopes = [s for s in scopes if s.startswith("block")]
+    dec_scopes = [s for s in scopes if s.startswith("dblock")]
     pre_nodes = graph.nodes_of("pre")
-    # encoder-decoder models trace two stacks; the decoder block (with cross attention) is the
-    # heavier one and both are costed as "block" by the evaluator, so keep the last traced block
-    block_nodes = graph.nodes_of(block_scopes[-1]) if block_scopes else []
     post_nodes = graph.nodes_of("post")
     first_block_nodes = graph.nodes_of(block_scopes[0]) if block_scopes else []
     pre = _layer_info("pre_layer", pre_nodes, graph, first_block_nodes)
-    block = _layer_info("block_layer", block_nodes, graph, post_nodes)
     post = _layer_info("post_layer", post_nodes, graph, [])
-    return ModelAnalysis(pre, block, post, tp, seq_len, ["b"], sequence_parallel and tp > 1, len(graph.nodes))
+    enc_block = dec_block = None
+    if dec_scopes:
+        # Encoder-decoder models: one "layer" of a single-stage strategy is an encoder block plus a decoder
+        # block (both stacks have the same depth); pipeline strategies put encoder blocks on the first stages
+        # and the decoder on the last, so the two kinds are also kept apart.
+        enc_nodes, dec_nodes = graph.nodes_of(block_scopes[-1]), graph.nodes_of(dec_scopes[-1])
+        enc_block = _layer_info("enc_block_layer", enc_nodes, graph, post_nodes + graph.nodes_of(dec_scopes[0]))
+        dec_block = _layer_info("dec_block_layer", dec_nodes, graph, post_nodes)
+        block = _layer_info("block_layer", enc_nodes + dec_nodes, graph, post_nodes)
+    else:
+        block_nodes = graph.nodes_of(block_scopes[-1]) if block_scopes else []
+        block = _layer_info("block_layer", block_nodes, graph, post_nodes)
+    return ModelAnalysis(pre, block, post, tp, seq_len, ["b"], sequence_parallel and tp > 1, len(graph.nodes),
+                         enc_block, dec_block)
 
 
 # ------------------------------------------------------------------------------- caching

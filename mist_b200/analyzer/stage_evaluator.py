@@ -178,7 +178,8 @@ class StageEvaluator:
 
     # -------------------------------------------------------------------------- evaluate
     def evaluate(self, space: np.ndarray, num_layers: int, num_ckpt: int, grad_accum: int, has_pre: bool,
-                 has_post: bool, inflight_extra: int = 0, pre_post_space: Optional[np.ndarray] = None) -> Dict[str, np.ndarray]:
+                 has_post: bool, inflight_extra: int = 0, pre_post_space: Optional[np.ndarray] = None,
+                 block_kind: str = "block_layer") -> Dict[str, np.ndarray]:
         """``space``: [N, 10].  ``inflight_extra``: additional micro batches whose activations are
         alive at the memory peak (1F1B warm-up depth of this stage)."""
         N = space.shape[0]
@@ -234,7 +235,7 @@ class StageEvaluator:
             bwd = self._interf(b_c, b_g2g, b_c2g, b_g2c) + x["tp_bwd"] + (x["tp_fwd"] if ckpt else 0.0)
             return fwd, bwd
 
-        blk = gather("block_layer")
+        blk = gather(block_kind)      # "enc_block_layer" / "dec_block_layer" for the stages of an encoder-decoder pipeline
         f0, b0 = layer_cost(blk, False, False)
         f1, b1 = layer_cost(blk, True, False)
         _, b0l = layer_cost(blk, False, True)
@@ -300,8 +301,11 @@ def analyze_strategy(cfg: MistConfig, evaluator: Optional[StageEvaluator] = None
     for s in range(S):
         vec = np.array([st.stage_strategies[s]], dtype=np.float64)
         warm = min(S - 1 - s, max(G - 1, 0))
+        kind = "block_layer"
+        if cfg.model.add_decoder and S > 1:
+            kind = "dec_block_layer" if s == S - 1 else "enc_block_layer"
         res = ev.evaluate(vec, st.layer_partitions[s], st.gradient_checkpointing[s], G, has_pre=(s == 0),
-                          has_post=(s == S - 1), inflight_extra=warm)
+                          has_post=(s == S - 1), inflight_extra=warm, block_kind=kind)
         stables.append(float(res["stable"][0]))
         deltas.append(float(res["delta"][0]))
         peaks.append((float(res["peak_fwd"][0]), float(res["peak_bwd"][0])))

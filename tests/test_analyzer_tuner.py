@@ -297,3 +297,23 @@ def test_prediction_accuracy_report(tmp_path, capsys):
     acc.main([str(tmp_path)])
     text = capsys.readouterr().out
     assert "2 cases" in text and "mean abs rel err 5.50 %" in text and "memory : mean abs rel err 10.00 %" in text
+
+
+def test_encoder_decoder_blocks_are_priced_apart(monkeypatch):
+    """T5: a single-stage "layer" is an encoder block plus a decoder block; pipeline stages are priced with the
+    kind of block they hold, so an encoder stage costs less than a decoder stage of the same depth."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    from mist_b200.analyzer.layer_analyzer import trace_and_analyze
+    from mist_b200.analyzer.stage_evaluator import analyze_strategy
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b", "model=t5/1.7b"], check_world_size=False)
+    a = trace_and_analyze(cfg.model, 512, 1, False)
+    assert a.block.num_params == a.enc_block.num_params + a.dec_block.num_params
+    assert a.dec_block.num_params > a.enc_block.num_params            # cross attention
+    vec = "[4,1,1,0,0,0,0,0,0,0]"
+    cfg2, _ = load_config("config", ["experiment=gpt2-1.3b", "model=t5/1.7b", "hardware.num_gpus_per_node=2",
+                                     "training.global_batch_size=8", "strategy.layer_partitions=[16,16]",
+                                     "strategy.device_assignment=[[1,1],[1,1]]", "strategy.gradient_checkpointing=[0,0]",
+                                     "strategy.gradient_accumulation_steps=2", f"strategy.stage_strategies=[{vec},{vec}]",
+                                     f"strategy.pre_post_strategy_array={vec}"], check_world_size=False)
+    res = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))
+    assert res["stable"][0] < res["stable"][1]
