@@ -304,7 +304,9 @@ def analyze_strategy(cfg: MistConfig, evaluator: Optional[StageEvaluator] = None
         kind = "block_layer"
         if cfg.model.add_decoder and S > 1:
             kind = "dec_block_layer" if s == S - 1 else "enc_block_layer"
-        res = ev.evaluate(vec, st.layer_partitions[s], st.gradient_checkpointing[s], G, has_pre=(s == 0),
+        # the decoder stage of an encoder-decoder pipeline holds its own copy of the embedding tables
+        has_pre = s == 0 or kind == "dec_block_layer"
+        res = ev.evaluate(vec, st.layer_partitions[s], st.gradient_checkpointing[s], G, has_pre=has_pre,
                           has_post=(s == S - 1), inflight_extra=warm, block_kind=kind)
         stables.append(float(res["stable"][0]))
         deltas.append(float(res["delta"][0]))
