@@ -134,6 +134,8 @@ def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache
     else:
         stage_counts = stage_count_candidates(hw.num_devices, L)
     uniform_layers = gran in ("uniform-pp", "uniform-device-pp", "uniform-pp-simple-heuristic-mem-opt")
+    from ..models.provider import family_of
+    tied = bool(cfg.model.tie_word_embeddings) or family_of(cfg.model.name) == "bert"
     best_cost, best_sol = math.inf, None
     for S in stage_counts:
         mesh = uniform_mesh_for(S, hw.num_nodes, hw.num_gpus_per_node)
@@ -162,7 +164,20 @@ def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache
                         opt_ref.append((k, l, pi, p))
             if not opt_T:
                 continue
-            cost, chosen = solve_stage_assignment(S, L, g, opt_kind, opt_layers, opt_T, opt_D)
+            if tied and S > 1:
+                # tables tied across the first and the last stage pair the ranks of the two stages, which
+                # needs the same dp x tp layout on both: solve once per layout of the end stages
+                cost, chosen = math.inf, None
+                layouts = {(int(r[3].vector[1]), int(r[3].vector[2])) for r in opt_ref if r[0] in (0, 2)}
+                for lay in sorted(layouts):
+                    keep = [i for i, r in enumerate(opt_ref)
+                            if r[0] == 1 or (int(r[3].vector[1]), int(r[3].vector[2])) == lay]
+                    c, ch = solve_stage_assignment(S, L, g, [opt_kind[i] for i in keep], [opt_layers[i] for i in keep],
+                                                   [opt_T[i] for i in keep], [opt_D[i] for i in keep])
+                    if ch and c < cost:
+                        cost, chosen = c, [keep[i] for i in ch]
+            else:
+                cost, chosen = solve_stage_assignment(S, L, g, opt_kind, opt_layers, opt_T, opt_D)
             if verbose:
                 print(f"  stages={S} mesh={mesh} G={g}: cost={cost:.6f}")
             if not chosen or not math.isfinite(cost) or cost >= best_cost:
