@@ -179,7 +179,7 @@ class StageEvaluator:
     # -------------------------------------------------------------------------- evaluate
     def evaluate(self, space: np.ndarray, num_layers: int, num_ckpt: int, grad_accum: int, has_pre: bool,
                  has_post: bool, inflight_extra: int = 0, pre_post_space: Optional[np.ndarray] = None,
-                 block_kind: str = "block_layer") -> Dict[str, np.ndarray]:
+                 block_kind: str = "block_layer", tied_copy: bool = False) -> Dict[str, np.ndarray]:
         """``space``: [N, 10].  ``inflight_extra``: additional micro batches whose activations are
         alive at the memory peak (1F1B warm-up depth of this stage)."""
         N = space.shape[0]
@@ -273,6 +273,13 @@ class StageEvaluator:
             peak_f = np.maximum(peak_f, states + acts + st + x["fwd_peak"])
             peak_b = np.maximum(peak_b, states + acts + st + x["bwd_peak"])
 
+        if tied_copy:
+            # last stage of a pipeline whose model ties the output projection to the word table: the stage
+            # holds its own copy (bf16 weights and full-size gradients, optimizer state sharded like the rest)
+            Wt = 2.0 * self.cfg.model.vocab_size * self.cfg.model.hidden_size / tp
+            extra = Wt + Wt + 6.0 * np.where(ore, Wt / dp, Wt)
+            peak_f = peak_f + extra
+            peak_b = peak_b + extra
         cap = self.hw.memory_capacity * GB
         feasible = np.maximum(peak_f, peak_b) * MEMORY_FACTOR <= cap
         return {"stable": stable, "delta": delta, "peak_fwd": peak_f, "peak_bwd": peak_b, "feasible": feasible}
@@ -292,6 +299,16 @@ def pipeline_latency(stable: Sequence[float], delta: Sequence[float], grad_accum
     return sum(T) + (grad_accum - 1) * max(T) + max(worst, 0.0)
 
 
+def ties_across_stages(cfg: MistConfig) -> bool:
+    """Whether a pipeline of this model keeps a second copy of the word table on its last stage (models whose
+    output projection is the word table; encoder-decoder models count their copy as the decoder stage's
+    embedding instead)."""
+    from ..models.provider import family_of
+    if cfg.model.add_decoder:
+        return False
+    return bool(cfg.model.tie_word_embeddings) or family_of(cfg.model.name) == "bert"
+
+
 def analyze_strategy(cfg: MistConfig, evaluator: Optional[StageEvaluator] = None) -> Dict:
     """Predicted cost of the strategy written in ``cfg.strategy`` (the analyze entry point)."""
     ev = evaluator or StageEvaluator(cfg)
@@ -307,7 +324,8 @@ def analyze_strategy(cfg: MistConfig, evaluator: Optional[StageEvaluator] = None
         # the decoder stage of an encoder-decoder pipeline holds its own copy of the embedding tables
         has_pre = s == 0 or kind == "dec_block_layer"
         res = ev.evaluate(vec, st.layer_partitions[s], st.gradient_checkpointing[s], G, has_pre=has_pre,
-                          has_post=(s == S - 1), inflight_extra=warm, block_kind=kind)
+                          has_post=(s == S - 1), inflight_extra=warm, block_kind=kind,
+                          tied_copy=(S > 1 and s == S - 1 and ties_across_stages(cfg)))
         stables.append(float(res["stable"][0]))
         deltas.append(float(res["delta"][0]))
         peaks.append((float(res["peak_fwd"][0]), float(res["peak_bwd"][0])))

@@ -17,7 +17,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 
-from ..analyzer.stage_evaluator import StageEvaluator, create_search_space
+from ..analyzer.stage_evaluator import ties_across_stages, StageEvaluator, create_search_space
 from ..config import MistConfig
 from .pareto import dedup_samples, sample_pareto_frontier
 
@@ -66,7 +66,8 @@ def tune_stage_cell(ev: StageEvaluator, cfg: MistConfig, g: int, mesh: Tuple[int
     all_points: List[StagePoint] = []
     evaluated = 0
     for c in ckpt_candidates(layers, cfg):
-        res = ev.evaluate(space, layers, c, g, has_pre, has_post, inflight_extra=warm)
+        res = ev.evaluate(space, layers, c, g, has_pre, has_post, inflight_extra=warm,
+                          tied_copy=(kind == 2 and ties_across_stages(cfg)))
         evaluated += space.shape[0]
         idx = dedup_samples(sample_pareto_frontier(res["stable"], res["delta"], res["feasible"], S))
         for i in idx:
