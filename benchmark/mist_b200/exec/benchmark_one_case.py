@@ -43,6 +43,8 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
     if cfg.get("memory_debug", False) and cuda:
         torch.cuda.memory._record_memory_history()
     sess = TrainingSession(cfg, comm_backend=comm_backend, seed=seed)
+    if world > 1:
+        sess.enable_heartbeat()       # every step beats and checks its peers before it launches anything
     ps = sess.ps
     # messages carry rank and stage; only the first data-parallel rank of each (stage, tp) position logs
     from mist_b200.utils.logging import get_logger, log_memory, set_rank_filter
@@ -125,7 +127,22 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
 
 def main(argv=None):
     cfg, node = load_from_cli(argv)
-    res = run(cfg, node, comm_backend=node.get("comm_backend"))
+    try:
+        res = run(cfg, node, comm_backend=node.get("comm_backend"))
+    except RuntimeError as e:
+        # An unrecoverable error on one rank (out of memory, a kernel's bounded wait that ran out, a peer
+        # that stopped): mark the job as aborted and end this host's other ranks by their registered
+        # process ids, so nobody waits in a collective for a rank that is gone (reference:
+        # find_and_kill_other_processes by command-line pattern, benchmark_one_case.py:434-441).
+        print(f"[rank {os.environ.get('RANK', '0')}] error: {e}", file=sys.stderr)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            from mist_b200.utils.watchdog import Heartbeat, terminate_job
+            try:
+                store = dist.PrefixStore("mist_b200_hb", dist.distributed_c10d._get_default_store())
+                terminate_job(Heartbeat(store, dist.get_rank(), dist.get_world_size()))
+            except Exception:       # noqa: BLE001 - the store itself may be gone
+                pass
+        raise
     if res["rank"] == 0:
         print(f"Total Latency: {res['latency']:.4f}")
         print(f"Throughput: {res['tokens_per_s']:.1f} tokens/s")

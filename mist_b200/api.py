@@ -62,6 +62,19 @@ class TrainingSession:
             pre_process=self.ps.is_first_stage, post_process=self.ps.is_last_stage,
             layer_range=lr if multi_stage else None, sequence_parallel=self.sequence_parallel,
             device=device, dtype=dtype)
+        # Parameters that every tensor-parallel rank holds in full (norms, position tables, BERT's head
+        # transform, pooler ...) were drawn from a rank-dependent stream above: make them equal to the
+        # first rank's, as the gradient handling of replicated parameters assumes.
+        if self.ps.tp_size > 1 and world > 1:
+            src = dist.get_global_rank(self.ps.tp_group, 0)
+            for p in self.model.parameters():
+                if not getattr(p, "_tp_sharded", False):
+                    dist.broadcast(p.data, src=src, group=self.ps.tp_group)
+        # dropout masks of replicated activations must agree over the tensor-parallel group; where the
+        # tokens are sharded (sequence parallelism) every rank adds its own offset to the drawn seeds
+        _F.Settings.dropout_generator = torch.Generator()
+        _F.Settings.dropout_generator.manual_seed(seed + 17 * stage + 7919 * self.ps.dp_rank)
+        _F.Settings.dropout_seed_offset = 104729 * self.ps.tp_rank if self.sequence_parallel else 0
         # a table tied across the first and the last stage: pair the ranks and copy it over once
         tied_group = None
         ties = bool(getattr(cfg.model, "tie_word_embeddings", False)) or family_of(cfg.model.name) in ("bert", "t5")
@@ -85,6 +98,27 @@ class TrainingSession:
             from .parallel.pipeline import PipelineSchedule
             self.pipeline = PipelineSchedule(self)
         self._h2d_stream = torch.cuda.Stream() if device.type == "cuda" else None
+        # host-side failure detection between steps (see utils/watchdog.py); off unless asked for
+        self.heartbeat = None
+        self.heartbeat_max_age_s = float(cfg.get("heartbeat_max_age_s", 120.0))
+        if bool(cfg.get("heartbeat", False)) and world > 1:
+            self.enable_heartbeat()
+
+    def enable_heartbeat(self, store=None, max_age_s: Optional[float] = None):
+        """Registers this rank in the job's key-value store; from then on every :meth:`step` beats
+        and, before it launches anything, raises if a peer stopped beating or asked to abort."""
+        from .utils.watchdog import Heartbeat
+        if store is None:
+            store = dist.PrefixStore("mist_b200_hb", dist.distributed_c10d._get_default_store())
+        if max_age_s is not None:
+            self.heartbeat_max_age_s = float(max_age_s)
+        self.heartbeat = Heartbeat(store, dist.get_rank(), dist.get_world_size())
+        return self.heartbeat
+
+    def _beat(self):
+        if self.heartbeat is not None:
+            self.heartbeat.beat()
+            self.heartbeat.check(self.heartbeat_max_age_s)
 
     # ------------------------------------------------------------------------------ steps
     def _split_micro(self, ids, labels):
@@ -94,6 +128,7 @@ class TrainingSession:
 
     def step_on_device(self, input_ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
         """One iteration on tensors already on the device; returns the loss tensor (device)."""
+        self._beat()
         batches = self._split_micro(input_ids, labels)
         if self.pipeline is not None:
             return self.pipeline.train_step(batches)
@@ -104,6 +139,7 @@ class TrainingSession:
         returns: token ids, token types, decoder ids, labels ...), each with this rank's
         ``micro_batch * G`` samples along dimension 0; used for the encoder-only and
         encoder-decoder families whose forward takes more than ids and labels."""
+        self._beat()
         if self.G == 1:
             batches = [dict(batch)]
         else:
@@ -122,10 +158,38 @@ class TrainingSession:
         else:
             ids, lab = input_ids, labels
         loss = self.step_on_device(ids, lab)
-        return float(loss.item())
+        value = float(loss.item())
+        self.check_device_status()
+        return value
+
+    def check_device_status(self, collective: bool = True):
+        """Raises if a kernel's bounded wait ran out since the last check (the kernel then stopped
+        issuing work, so this step's results are not to be trusted).  With ``collective`` the status
+        is combined over all ranks first, so that every replica stops at the same step.  Call it
+        where the device is already synchronised: :meth:`step` does after reading the loss,
+        :meth:`finish` does once the outstanding optimizer steps are waited for; callers of
+        :meth:`step_on_device` (no host synchronisation per step) get the check in :meth:`finish`
+        or can call it themselves every few steps."""
+        if self.device.type != "cuda":
+            return
+        from .ops import native
+        code = native.read_and_clear_status()
+        world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+        if collective and world > 1:
+            t = torch.tensor([code], dtype=torch.int32, device=self.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            worst = int(t.item())
+            if worst and not code:
+                raise RuntimeError(f"another rank reported device status {worst} (a bounded wait ran out); "
+                                   "this replica stops at the same step")
+        if code:
+            raise RuntimeError(native.status_message(code))
 
     def finish(self):
         self.engine.finish()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+            self.check_device_status()
 
     # -------------------------------------------------------------------------- accounting
     def flops_per_step(self) -> float:

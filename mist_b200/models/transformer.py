@@ -88,7 +88,7 @@ class ParallelTransformerLayer(nn.Module):
 
     def _drop(self, x):
         if self.hidden_dropout > 0 and self.training:
-            seed = int(torch.randint(0, 2 ** 31 - 1, (1,)).item())
+            seed = F.next_dropout_seed()
             return F.bias_dropout_add(x, None, None, self.hidden_dropout, seed)
         return x
 

@@ -108,6 +108,10 @@ class ColumnParallelLinear(FusedDense):
         super().__init__(in_features, local_out, bias=bias, activation=activation, device=device, dtype=dtype)
         self.process_group, self.sequence_parallel = process_group, sequence_parallel
         self.global_out_features = out_features
+        # each rank holds its own slice: not to be made equal over the tensor-parallel group
+        self.weight._tp_sharded = True
+        if self.bias is not None:
+            self.bias._tp_sharded = True
 
     def _fused(self, x) -> bool:
         return (self.sequence_parallel and F.Settings.tp_backend == "fused" and isinstance(x, torch.Tensor)
@@ -138,6 +142,9 @@ class RowParallelLinear(FusedDense):
         local_in = dist_ops.dim_for_rank(in_features, ws, rk, multiple_of)
         super().__init__(local_in, out_features, bias=bias and rk == 0, device=device, dtype=dtype)
         self.process_group, self.sequence_parallel = process_group, sequence_parallel
+        self.weight._tp_sharded = True
+        if self.bias is not None:
+            self.bias._tp_sharded = True      # exists on the first rank only
         # the bias lives on the first rank only and its gradient there is already complete (the
         # backward pass of the reduce-scatter gathers the full output gradient), so it takes no
         # part in the tensor-parallel gradient sum
@@ -177,6 +184,7 @@ class VocabParallelEmbedding(nn.Module):
         self.vocab_start = rk * self.local_vocab
         self.padding_idx = padding_idx
         self.word_embeddings = nn.Embedding(self.local_vocab, hidden_size, device=device, dtype=dtype)
+        self.word_embeddings.weight._tp_sharded = True
         self.position_embeddings = (nn.Embedding(max_position_embeddings, hidden_size, device=device, dtype=dtype)
                                     if max_position_embeddings > 0 else None)
         self.tokentype_embeddings = (nn.Embedding(num_tokentypes, hidden_size, device=device, dtype=dtype)

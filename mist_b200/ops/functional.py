@@ -63,6 +63,19 @@ class Settings:
     gemm_pair = True              # large GEMMs on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2)
     fuse_mlp_gelu = True          # GELU MLP as one autograd node (gelu' folded into a dgrad GEMM epilogue)
     tp_backend = "nccl"           # "nccl" | "fused": sequence-parallel linears on the GEMM+collective kernels
+    # Source of the seeds of hidden-state dropout.  Seeded alike on every rank of a tensor-parallel group
+    # (the training session does that), so replicated activations get the same mask on every rank.
+    dropout_generator = None
+    dropout_seed_offset = 0       # added to every drawn seed; differs per rank only where tokens are sharded
+
+
+def next_dropout_seed() -> int:
+    """Seed for one dropout call, drawn from :attr:`Settings.dropout_generator`."""
+    if Settings.dropout_generator is None:
+        Settings.dropout_generator = torch.Generator()
+        Settings.dropout_generator.manual_seed(torch.initial_seed() & 0x7FFFFFFF)
+    s = int(torch.randint(0, 2 ** 31 - 1, (1,), generator=Settings.dropout_generator).item())
+    return (s + Settings.dropout_seed_offset) % (2 ** 31 - 1)
 
 
 _scratch = {}

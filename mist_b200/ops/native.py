@@ -150,12 +150,19 @@ _STATUS_NAMES = {1: "TMA stage wait timed out", 2: "free-stage wait timed out",
                  3: "accumulator wait timed out", 4: "peer flag wait timed out", 5: "bad argument"}
 
 
-def check_status():
-    """Reads (and clears) the device status word set by bounded waits that gave up."""
+def read_and_clear_status() -> int:
+    """The device status word set by bounded waits that gave up (0 = none); clears it."""
     lib = kernels()
-    if lib is None:
-        return 0
-    code = lib.mb_status_read_and_clear()
+    return 0 if lib is None else int(lib.mb_status_read_and_clear())
+
+
+def status_message(code: int) -> str:
+    return f"a kernel reported status {code}: {_STATUS_NAMES.get(code, 'unknown')}"
+
+
+def check_status():
+    """Reads (and clears) the device status word and raises if a bounded wait gave up."""
+    code = read_and_clear_status()
     if code != 0:
-        raise RuntimeError(f"a kernel reported status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
+        raise RuntimeError(status_message(code))
     return 0

@@ -20,14 +20,14 @@ TINY = ["model.num_hidden_layers=3", "model.hidden_size=64", "model.intermediate
         "strategy.gradient_accumulation_steps=2"]
 
 
-def _cfg(zero):
-    vec = f"[2,2,1,{zero[0]},{zero[1]},{zero[2]},0,0,0,0]"
+def _cfg(zero, offload=(0, 0, 0)):
+    vec = f"[2,2,1,{zero[0]},{zero[1]},{zero[2]},{offload[0]},{offload[1]},{offload[2]},0]"
     cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + [
         f"strategy.stage_strategies=[{vec}]", f"strategy.pre_post_strategy_array={vec}"], check_world_size=False)
     return cfg
 
 
-def _ckpt_worker(rank, world, port, path, ret):
+def _ckpt_worker(rank, world, port, path, ret, first=((0, 1, 1), (0, 0, 0)), second=((1, 1, 1), (0, 0, 0))):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -40,7 +40,7 @@ def _ckpt_worker(rank, world, port, path, ret):
             return b["input_ids"], b["labels"]
 
         # run A: ZeRO-2 for two steps, save, one more step
-        a = TrainingSession(_cfg((0, 1, 1)), seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        a = TrainingSession(_cfg(*first), seed=0, device=torch.device("cpu"), hp=dict(lr=1e-3))
         for it in range(2):
             a.step_on_device(*batch(it))
         a.finish()
@@ -48,7 +48,7 @@ def _ckpt_worker(rank, world, port, path, ret):
         loss_a = float(a.step_on_device(*batch(2)))
         a.finish()
         # run B: ZeRO-3 from another seed, resume, same third step
-        b = TrainingSession(_cfg((1, 1, 1)), seed=123, device=torch.device("cpu"), hp=dict(lr=1e-3))
+        b = TrainingSession(_cfg(*second), seed=123, device=torch.device("cpu"), hp=dict(lr=1e-3))
         step = checkpoint.load(b, path)
         loss_b = float(b.step_on_device(*batch(2)))
         b.finish()
@@ -83,6 +83,44 @@ def test_checkpoint_resume_under_another_zero_level(tmp_path):
     assert any(f.startswith("model_stage0") for f in ret["files"])
     assert abs(ret["losses"][0] - ret["losses"][1]) < 1e-5
     assert ret["diff"] < 1e-5
+    # one optimizer file per data-parallel rank (each holds that rank's shard and RNG state)
+    assert "optim_stage0_tp0_dp0.pt" in ret["files"] and "optim_stage0_tp0_dp1.pt" in ret["files"]
+
+
+@pytest.mark.parametrize("first,second", [
+    # ZeRO-3 with half of the weights, gradients and optimizer state on the host -> plain ZeRO-1
+    (((1, 1, 1), (0.5, 0.5, 0.5)), ((0, 0, 1), (0, 0, 0))),
+    # ZeRO-2 -> ZeRO-3 with offloaded weights and optimizer state (load writes through the host split)
+    (((0, 1, 1), (0, 0, 0)), ((1, 1, 1), (0.5, 0.5, 0.5))),
+    # ZeRO-2 with offloaded weights -> the same
+    (((0, 1, 1), (0.5, 0.5, 0)), ((0, 1, 1), (0.5, 0.5, 0))),
+])
+def test_checkpoint_roundtrip_with_offloaded_state(tmp_path, first, second):
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = free_port()
+    mp.spawn(_ckpt_worker, args=(world, port, str(tmp_path / "ckpt"), ret, first, second), nprocs=world, join=True)
+    assert ret["step"] == 2
+    assert abs(ret["losses"][0] - ret["losses"][1]) < 1e-5
+    assert ret["diff"] < 1e-5
+
+
+def test_checkpoint_restores_rng_per_rank(tmp_path):
+    """Each rank's optimizer file carries its own CPU generator state; loading puts it back."""
+    from mist_b200.api import TrainingSession
+    from mist_b200.utils import checkpoint
+    cfg, _ = load_config("config", ["experiment=gpt2-1.3b"] + TINY + [
+        "hardware.num_gpus_per_node=1", "strategy.device_assignment=[[1,1]]", "training.global_batch_size=4",
+        "strategy.stage_strategies=[[2,1,1,0,0,0,0,0,0,0]]", "strategy.pre_post_strategy_array=[2,1,1,0,0,0,0,0,0,0]"],
+        check_world_size=False)
+    a = TrainingSession(cfg, seed=0, device=torch.device("cpu"))
+    torch.manual_seed(4242)
+    checkpoint.save(a, str(tmp_path / "c"), step=5)
+    expect = torch.rand(3)
+    torch.manual_seed(1)
+    assert checkpoint.load(a, str(tmp_path / "c")) == 5
+    assert torch.equal(torch.rand(3), expect)
 
 
 def _hb_worker(rank, world, port, ret):
@@ -220,9 +258,47 @@ def test_checkpoint_roundtrip_pipeline_of_tensor_parallel_stages(tmp_path):
     mp.spawn(_ckpt_pptp_worker, args=(4, port, str(tmp_path / "ck"), ret), nprocs=4, join=True)
     for s in range(2):
         for t in range(2):
-            assert f"model_stage{s}_tp{t}.pt" in ret["files"] and f"optim_stage{s}_tp{t}.pt" in ret["files"]
+            assert f"model_stage{s}_tp{t}.pt" in ret["files"] and f"optim_stage{s}_tp{t}_dp0.pt" in ret["files"]
     for r in range(4):
         step, la, lb, stage = ret[r]
         assert step == 1
         if stage == 1:
             assert abs(la - lb) < 1e-5, (r, la, lb)
+
+
+class _DictStore:
+    """In-memory stand-in for the job's key-value store."""
+
+    def __init__(self):
+        self.d = {}
+
+    def set(self, k, v):
+        self.d[k] = v.encode() if isinstance(v, str) else v
+
+    def get(self, k):
+        return self.d[k]
+
+    def check(self, keys):
+        return all(k in self.d for k in keys)
+
+
+def test_terminate_job_signals_only_this_hosts_live_ranks(monkeypatch):
+    """Ranks registered from another host, and PIDs that now belong to another process, are left
+    alone; the abort key tells the other hosts' ranks to stop at their next check."""
+    from mist_b200.utils import watchdog
+    store = _DictStore()
+    me = watchdog.Heartbeat(store, 0, 4, host="node-a")
+    watchdog.Heartbeat(store, 1, 4, host="node-a")
+    other = watchdog.Heartbeat(store, 2, 4, host="node-b")
+    watchdog.Heartbeat(store, 3, 4, host="node-a")
+    # rank 3's PID was recycled: its recorded start time no longer matches
+    pid3, host3, _ = store.get("hb/pid/3").decode().split("|")
+    store.set("hb/pid/3", f"{pid3}|{host3}|1")
+    sent = []
+    monkeypatch.setattr(watchdog.os, "kill", lambda pid, sig: sent.append((pid, sig)))
+    signalled = watchdog.terminate_job(me)
+    assert signalled == [1]
+    assert len(sent) == 1
+    assert other.aborted()
+    with pytest.raises(RuntimeError, match="asked the job to stop"):
+        other.check(max_age_s=1e9)
