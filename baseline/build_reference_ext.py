@@ -3,7 +3,11 @@ csrc/layer_norm, Dockerfile:45-48) from the unmodified sources under baseline/_r
 only, into baseline/_ref/ext.  The reference's own setup.py files pin arch lists that stop at sm_90, so
 the sources are handed to torch's extension builder directly with the same defines.
 
-    python baseline/build_reference_ext.py
+    python baseline/build_reference_ext.py [fused_dense_lib] [dropout_layer_norm] [--sizes 2560,4096]
+
+``--sizes`` limits the layer-norm build to the instantiation files of those hidden sizes (each file
+registers its own launchers, so the others are simply not available at run time).  The default is the
+benchmark model's 2560 alone: all 14 sizes give a 300 MB library that every GPU call would carry.
 """
 import os
 import sys
@@ -28,7 +32,13 @@ def main():
             "-U__CUDA_NO_BFLOAT16_OPERATORS__", "-U__CUDA_NO_BFLOAT16_CONVERSIONS__",
             "-U__CUDA_NO_BFLOAT162_OPERATORS__", "-U__CUDA_NO_BFLOAT162_CONVERSIONS__",
             "--expt-relaxed-constexpr", "--expt-extended-lambda", "--use_fast_math"] + gen
-    which = sys.argv[1:] or ["fused_dense_lib", "dropout_layer_norm"]
+    argv = sys.argv[1:]
+    sizes = ["2560"]
+    if "--sizes" in argv:
+        i = argv.index("--sizes")
+        sizes = argv[i + 1].split(",")
+        del argv[i:i + 2]
+    which = argv or ["fused_dense_lib", "dropout_layer_norm"]
     if "fused_dense_lib" in which:
         d = CSRC / "fused_dense_lib"
         load(name="fused_dense_lib", sources=[str(d / "fused_dense.cpp"), str(d / "fused_dense_cuda.cu")],
@@ -36,7 +46,8 @@ def main():
              is_python_module=False, verbose=True)
     if "dropout_layer_norm" in which:
         d = CSRC / "layer_norm"
-        srcs = [str(d / "ln_api.cpp")] + sorted(str(p) for p in d.glob("ln_*.cu"))
+        srcs = [str(d / "ln_api.cpp")] + sorted(str(p) for p in d.glob("ln_*.cu")
+                                               if sizes == ["all"] or p.stem.rsplit("_", 1)[1] in sizes)
         load(name="dropout_layer_norm", sources=srcs, extra_cflags=["-O3"] + gen, extra_cuda_cflags=nvcc,
              extra_include_paths=[str(d)], build_directory=_bd("dropout_layer_norm"),
              is_python_module=False, verbose=True)

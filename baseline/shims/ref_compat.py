@@ -29,6 +29,37 @@ def apply():
     if not hasattr(tu, "is_peft_available"):
         tu.is_peft_available = lambda: False
         _note("transformers.utils.is_peft_available")
+    import types
+    import torch
+    # torch's functional optimizers are TorchScript classes compiled at import; the reference wraps
+    # torch.jit.script (mist/overrides/jit.py), which breaks the name lookup of that compilation, so the
+    # module is imported before the wrapper exists
+    import torch.distributed.optim  # noqa: F401
+    if "torch.distributed.pipeline" not in sys.modules:
+        try:
+            importlib.import_module("torch.distributed.pipeline")
+        except ImportError:
+            # removed from torch; the reference imports it and uses nothing of it
+            mod = types.ModuleType("torch.distributed.pipeline")
+            sys.modules["torch.distributed.pipeline"] = mod
+            torch.distributed.pipeline = mod
+            _note("torch.distributed.pipeline (empty module)")
+    import torch.optim.adam as _adam
+    import torch.optim.adamw as _adamw
+    for new, old in (("_fused_adamw", "_fused_adam"), ("_single_tensor_adamw", "_single_tensor_adam")):
+        if not hasattr(_adamw, new):
+            # imported by name in mist/optimizers/fused_adam.py:6-7, referenced only in comments there
+            setattr(_adamw, new, getattr(_adam, old))
+            _note(f"torch.optim.adamw.{new}")
+    import torch.distributed.fsdp as _fsdp
+    if "torch.distributed.fsdp.flat_param" not in sys.modules:
+        try:
+            importlib.import_module("torch.distributed.fsdp.flat_param")
+        except ImportError:
+            priv = importlib.import_module("torch.distributed.fsdp._flat_param")
+            sys.modules["torch.distributed.fsdp.flat_param"] = priv
+            _fsdp.flat_param = priv
+            _note("torch.distributed.fsdp.flat_param -> _flat_param")
     import einops.einops as ee
     if not hasattr(ee, "is_ellipsis_not_in_parenthesis"):
         # helper of einops <= 0.7 that the reference imports by name

@@ -7,7 +7,8 @@ and per-stage peak forward / backward memory (reference: benchmark/mist/analysis
 37-243; output keys :236-241).  Runs on CPU; operator latencies come from the database of
 the target GPU (``FAKE_DEVICE_NAME`` or the ``hardware.gpu_type`` of the configuration).
 With ``MIST_B200_PROFILE_OPS=1`` on a machine that has that GPU, operators the database does
-not know yet are measured and added (``MIST_B200_OP_CACHE`` chooses where).
+not know yet are measured and added (``MIST_B200_OP_CACHE`` chooses where);
+``MIST_B200_PROFILE_OPS=2`` also measures again the entries that carry no SM clock yet.
 """
 from __future__ import annotations
 
@@ -26,10 +27,11 @@ def analyze(cfg, cache_dir=None):
     assert cfg.strategy is not None, "analyze needs strategy.enabled=true"
     # MIST_B200_PROFILE_OPS=1 (on a machine with the target GPU): operators missing from the
     # database are timed on the device and stored, so later CPU-only runs find them.
-    profile_ops = os.environ.get("MIST_B200_PROFILE_OPS") == "1"
+    mode = os.environ.get("MIST_B200_PROFILE_OPS", "0")
+    profile_ops = mode in ("1", "2")
     if cfg.hardware.gpu_type and not os.environ.get("FAKE_DEVICE_NAME") and not profile_ops:
         os.environ["FAKE_DEVICE_NAME"] = str(cfg.hardware.gpu_type)
-    ev = StageEvaluator(cfg, OpDatabase(allow_profile=profile_ops), cache_dir=cache_dir)
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=profile_ops, refresh_unclocked=(mode == "2")), cache_dir=cache_dir)
     return analyze_strategy(cfg, ev)
 
 

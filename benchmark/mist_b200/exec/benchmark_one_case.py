@@ -51,6 +51,8 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
     set_rank_filter(ps.dp_rank, tag=f"rank {rank} stage {ps.stage} tp {ps.tp_rank}")
     log = get_logger()
     log.info("model built: %d parameters on this rank", sess.engine.num_parameters())
+    log.info("collectives: data-parallel gradients %s, tensor-parallel linears %s, ZeRO-3 weight gather %s",
+             sess.comm_backend, sess.tp_backend, sess.zero3_gather)
     log_memory("after model build:", log)
     mb, G, seq = sess.micro_batch, sess.G, sess.seq_len
     vocab = cfg.model.vocab_size
@@ -122,7 +124,9 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
         torch.cuda.memory._dump_snapshot(f"memory_snapshot_rank{rank}.pickle")
     tokens = cfg.training.global_batch_size * seq
     return {"latency": latency, "tokens_per_s": tokens / latency, "loss": float(loss) if loss is not None else None,
-            "peak_allocated": per_stage[:, 0].tolist(), "peak_reserved": per_stage[:, 1].tolist(), "rank": rank}
+            "peak_allocated": per_stage[:, 0].tolist(), "peak_reserved": per_stage[:, 1].tolist(), "rank": rank,
+            "backends": {"comm_backend": sess.comm_backend, "tp_backend": sess.tp_backend,
+                         "zero3_gather": sess.zero3_gather}}
 
 
 def main(argv=None):
@@ -146,11 +150,13 @@ def main(argv=None):
     if res["rank"] == 0:
         print(f"Total Latency: {res['latency']:.4f}")
         print(f"Throughput: {res['tokens_per_s']:.1f} tokens/s")
+        print(f"Collective back ends: {res['backends']}")
         print(f"Peak allocated memory per stage: {fmt_memories(res['peak_allocated'])}")
         print(f"Peak reserved memory per stage: {fmt_memories(res['peak_reserved'])}")
         update_summary(os.path.join(output_dir(node), "summary.json"), {
             "exec_total_cost": fmt_cost(res["latency"]),
             "exec_throughput": f"{res['tokens_per_s']:.1f}",
+            "exec_backends": res["backends"],
             "exec_stage_peak_allocated_memories": fmt_memories(res["peak_allocated"]),
             "exec_stage_peak_reserved_memories": fmt_memories(res["peak_reserved"]),
         })

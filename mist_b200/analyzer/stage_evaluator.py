@@ -178,10 +178,24 @@ class StageEvaluator:
 
     # -------------------------------------------------------------------------- evaluate
     def evaluate(self, space: np.ndarray, num_layers: int, num_ckpt: int, grad_accum: int, has_pre: bool,
-                 has_post: bool, inflight_extra: int = 0, pre_post_space: Optional[np.ndarray] = None,
-                 block_kind: str = "block_layer", tied_copy: bool = False) -> Dict[str, np.ndarray]:
+                 has_post: bool, inflight_extra: int = 0, pre_post_flags: Optional[Tuple[int, int, int]] = None,
+                 block_kind: str = "block_layer", tied_copy: bool = False, has_prev_stage: bool = False,
+                 has_next_stage: bool = False) -> Dict[str, np.ndarray]:
         """``space``: [N, 10].  ``inflight_extra``: additional micro batches whose activations are
-        alive at the memory peak (1F1B warm-up depth of this stage)."""
+        alive at the memory peak (1F1B warm-up depth of this stage).  ``pre_post_flags``: the
+        (wre, gre, ore) flags of the strategy vector that the embedding / head units run under
+        (``None``: ZeRO-1, what the tuner writes); the executor caps them at ZeRO-2, at ZeRO-1 when
+        a table is tied across stages, and never offloads those units, and so does this model.
+        ``has_prev_stage`` / ``has_next_stage``: the stage exchanges its boundary activation (and
+        its gradient) with a neighbour, which the schedule waits for (reference: the stage-output
+        p2p term of mist/analyzer/batched_module_analyzer.py:1299-1305, 2796, 2848).
+
+        The stage is costed as the sequence of units the executor walks -- embedding, blocks
+        (the checkpointed ones last), head -- with the executor's one-unit look-ahead: the
+        collectives and copies issued for unit ``u +- 1`` run while unit ``u`` computes, the
+        first gather of a pass and the last reduction of the iteration's last backward pass
+        have nothing to hide behind (reference: first / middle / last layer and first / last
+        micro batch priced apart, batched_module_analyzer.py:1432-1902)."""
         N = space.shape[0]
         b = space[:, 0].astype(int)
         dp = space[:, 1].astype(int)
@@ -189,6 +203,12 @@ class StageEvaluator:
         wre, gre, ore = space[:, 3] > 0, space[:, 4] > 0, space[:, 5] > 0
         wo, go, oo, ao = space[:, 6], space[:, 7], space[:, 8], space[:, 9]
         L, c, G = int(num_layers), int(num_ckpt), int(grad_accum)
+        zeros = np.zeros(N)
+        # embedding / head units: flags as the executor applies them
+        ppf = (0, 0, 1) if pre_post_flags is None else tuple(int(bool(v)) for v in pre_post_flags)
+        pp_gre = np.full(N, bool(ppf[1]) and not tied_copy) & (dp > 1)
+        pp_ore = np.full(N, bool(ppf[2]) or bool(ppf[1])) & (dp > 1)
+        pp_wre = np.zeros(N, dtype=bool)
 
         def gather(which: str) -> Dict[str, np.ndarray]:
             fields = ("exec_fwd", "exec_bwd", "tp_fwd", "tp_bwd", "fwd_peak", "bwd_peak", "saved", "input_bytes",
@@ -201,47 +221,96 @@ class StageEvaluator:
                     out[f][sel] = getattr(num, f)
             return out
 
-        def layer_cost(x: Dict[str, np.ndarray], ckpt: bool, last_micro: bool):
-            """(forward seconds, backward seconds) of one layer for every candidate."""
+        def unit_terms(x: Dict[str, np.ndarray], ckpt: bool, block: bool) -> Dict[str, np.ndarray]:
+            """Per-channel seconds of one unit: what its own passes compute, and what is issued on
+            its behalf while a neighbour computes."""
             W = x["weight_bytes"]
-            w_shard = np.where(wre, W / dp, W)
-            g_shard = np.where(gre, W / dp, W)
+            u_wre, u_gre, u_ore = (wre, gre, ore) if block else (pp_wre, pp_gre, pp_ore)
+            u_wo, u_go, u_oo, u_ao = (wo, go, oo, ao) if block else (zeros, zeros, zeros, zeros)
+            w_shard = np.where(u_wre, W / dp, W)
+            g_shard = np.where(u_gre, W / dp, W)
             kept = x["input_bytes"] if ckpt else x["saved"]
-            ag_w = np.where(wre, self._coll("all_gather", W, dp), 0.0)
-            # forward
-            f_c = x["exec_fwd"]
-            f_g2g = ag_w
-            f_c2g = self._h2d(wo * w_shard)
-            f_g2c = self._d2h(ao * kept)
-            fwd = self._interf(f_c, f_g2g, f_c2g, f_g2c) + x["tp_fwd"]
-            # backward
-            b_c = x["exec_bwd"] + (x["exec_fwd"] if ckpt else 0.0)
-            rs_every = np.where(gre, self._coll("reduce_scatter", W, dp), 0.0)
-            b_g2g = ag_w + rs_every
-            b_c2g = self._h2d(wo * w_shard + ao * kept + (go * g_shard if G > 1 else 0.0))
-            b_g2c = self._d2h(go * g_shard)
-            if last_micro:
-                # gradient sync that waits for the last micro batch, optimizer, weight refresh
-                sync = np.where(gre, 0.0, np.where(ore, self._coll("reduce_scatter", W, dp),
-                                                   self._coll("all_reduce", W, dp)))
-                refresh = np.where(ore & ~wre, self._coll("all_gather", W, dp), 0.0)
-                shard_params = np.where(ore, x["params"] / dp, x["params"])
-                adam = shard_params * ADAM_BYTES_PER_PARAM / (self.db.model.hbm_gbs * 1e9)
-                opt_bytes = 12.0 * shard_params * oo
-                b_c = b_c + adam
-                b_g2g = b_g2g + sync + refresh
-                b_c2g = b_c2g + self._h2d(opt_bytes)
-                b_g2c = b_g2c + self._d2h(opt_bytes)
-            bwd = self._interf(b_c, b_g2g, b_c2g, b_g2c) + x["tp_bwd"] + (x["tp_fwd"] if ckpt else 0.0)
-            return fwd, bwd
+            shard_params = np.where(u_ore, x["params"] / dp, x["params"])
+            opt_bytes = 12.0 * shard_params * u_oo
+            return dict(
+                cf=x["exec_fwd"] + x["tp_fwd"],
+                cb=x["exec_bwd"] + x["tp_bwd"] + ((x["exec_fwd"] + x["tp_fwd"]) if ckpt else 0.0),
+                ag=np.where(u_wre, self._coll("all_gather", W, dp), 0.0),
+                rs=np.where(u_gre, self._coll("reduce_scatter", W, dp), 0.0),
+                # only at the last micro batch: the reduction that waited for it, the refresh of the
+                # other ranks' weights after the step, the optimizer kernel and the optimizer-state copies
+                sync=np.where(u_gre, 0.0, np.where(u_ore, self._coll("reduce_scatter", W, dp),
+                                                   self._coll("all_reduce", W, dp))),
+                refresh=np.where(u_ore & ~u_wre, self._coll("all_gather", W, dp), 0.0),
+                adam=shard_params * ADAM_BYTES_PER_PARAM / (self.db.model.hbm_gbs * 1e9),
+                h2d_w=self._h2d(u_wo * w_shard),
+                h2d_a=self._h2d(u_ao * kept),
+                d2h_a=self._d2h(u_ao * kept),
+                h2d_g=self._h2d(u_go * g_shard) if G > 1 else zeros,
+                d2h_g=self._d2h(u_go * g_shard),
+                h2d_o=self._h2d(opt_bytes), d2h_o=self._d2h(opt_bytes))
 
         blk = gather(block_kind)      # "enc_block_layer" / "dec_block_layer" for the stages of an encoder-decoder pipeline
-        f0, b0 = layer_cost(blk, False, False)
-        f1, b1 = layer_cost(blk, True, False)
-        _, b0l = layer_cost(blk, False, True)
-        _, b1l = layer_cost(blk, True, True)
-        stable = (L - c) * (f0 + b0) + c * (f1 + b1)
-        delta = (L - c) * (b0l - b0) + c * (b1l - b1)
+        kinds = {"b0": unit_terms(blk, False, True), "b1": unit_terms(blk, True, True)}
+        pre = post = None
+        if has_pre:
+            pre = gather("pre_layer")
+            kinds["pre"] = unit_terms(pre, False, False)
+        if has_post:
+            post = gather("post_layer")
+            kinds["post"] = unit_terms(post, False, False)
+        seq = (["pre"] if has_pre else []) + ["b0"] * (L - c) + ["b1"] * c + (["post"] if has_post else [])
+        none = {k: zeros for k in kinds["b0"]}
+
+        memo: Dict[Tuple, np.ndarray] = {}
+
+        def fwd_unit(u: str, nxt: Optional[str]) -> np.ndarray:
+            key = ("f", u, nxt)
+            if key not in memo:
+                me, nx = kinds[u], (kinds[nxt] if nxt else none)
+                memo[key] = self._interf(me["cf"], nx["ag"], nx["h2d_w"], me["d2h_a"])
+            return memo[key]
+
+        def bwd_unit(u: str, nxt: Optional[str], prv: Optional[str], last: bool) -> np.ndarray:
+            """Backward pass of ``u`` while the unit that follows it in the model (``nxt``, whose backward
+            pass has just ended) reduces its gradients and the one before it (``prv``) is fetched."""
+            key = ("b", u, nxt, prv, last)
+            if key not in memo:
+                me, nx, pv = kinds[u], (kinds[nxt] if nxt else none), (kinds[prv] if prv else none)
+                g2g = pv["ag"] + nx["rs"]
+                c2g = pv["h2d_w"] + pv["h2d_a"] + me["h2d_g"]
+                g2c = nx["d2h_g"]
+                comp = me["cb"]
+                if last:
+                    g2g = g2g + nx["sync"] + nx["refresh"]
+                    comp = comp + nx["adam"]
+                    c2g = c2g + nx["h2d_o"]
+                    g2c = g2c + nx["d2h_o"]
+                memo[key] = self._interf(comp, g2g, c2g, g2c)
+            return memo[key]
+
+        n = len(seq)
+        fwd = sum((fwd_unit(seq[i], seq[i + 1] if i + 1 < n else None) for i in range(n)), zeros)
+        first_block = next((k for k in seq if k in ("b0", "b1")), None)
+        if first_block is not None:
+            fwd = fwd + kinds[first_block]["ag"] + kinds[first_block]["h2d_w"]     # nothing computes while it arrives
+        bwd = sum((bwd_unit(seq[i], seq[i + 1] if i + 1 < n else None, seq[i - 1] if i > 0 else None, False)
+                   for i in range(n)), zeros)
+        bwd_last = sum((bwd_unit(seq[i], seq[i + 1] if i + 1 < n else None, seq[i - 1] if i > 0 else None, True)
+                        for i in range(n)), zeros)
+        head = kinds[seq[0]]
+        # after the last backward pass of the iteration the first unit's reduction, optimizer step and weight
+        # refresh run with nothing left to overlap; the next iteration's first forward waits for them
+        tail_last = (self._interf(head["adam"], head["rs"] + head["sync"] + head["refresh"], head["h2d_o"],
+                                  head["d2h_o"] + head["d2h_g"]))
+        # boundary activations: the schedule waits for each receive and each send of a micro batch
+        p2p = zeros
+        if has_prev_stage or has_next_stage:
+            per = comm_model.gpu_gpu_latency("p2p", blk["input_bytes"] / 1e9, None,
+                                             2 if self.hw.num_nodes > 1 else 1, self.hw.gpu_gpu_comm_params)
+            p2p = 2.0 * per * (int(has_prev_stage) + int(has_next_stage))     # activation forward + gradient backward
+        stable = fwd + bwd + p2p
+        delta = (bwd_last - bwd) + tail_last
 
         # ---- memory of the stage
         W = blk["weight_bytes"]
@@ -258,16 +327,12 @@ class StageEvaluator:
         bwd_tr = np.maximum(blk["bwd_peak"], (blk["fwd_peak"] + blk["bwd_peak"]) if c > 0 else 0.0)
         peak_b = states + acts + bwd_tr
 
-        for present, which in ((has_pre, "pre_layer"), (has_post, "post_layer")):
-            if not present:
+        for x in (pre, post):
+            if x is None:
                 continue
-            x = gather(which)
-            f, bw = layer_cost(x, False, False)
-            _, bwl = layer_cost(x, False, True)
-            stable = stable + f + bw
-            delta = delta + (bwl - bw)
             Wp = x["weight_bytes"]
-            st = np.where(wre, Wp / dp, Wp) + np.where(gre, Wp / dp, Wp) + 6.0 * np.where(ore, Wp / dp, Wp)
+            # full weights, gradient bucket (full: these units reduce in place), optimizer state
+            st = Wp + Wp * (2.0 if (G > 1 and not ppf[1]) else 1.0) + 6.0 * np.where(pp_ore, Wp / dp, Wp)
             peak_f = peak_f + st + inflight * x["saved"]
             peak_b = peak_b + st + inflight * x["saved"]
             peak_f = np.maximum(peak_f, states + acts + st + x["fwd_peak"])
@@ -277,7 +342,7 @@ class StageEvaluator:
             # last stage of a pipeline whose model ties the output projection to the word table: the stage
             # holds its own copy (bf16 weights and full-size gradients, optimizer state sharded like the rest)
             Wt = 2.0 * self.cfg.model.vocab_size * self.cfg.model.hidden_size / tp
-            extra = Wt + Wt + 6.0 * np.where(ore, Wt / dp, Wt)
+            extra = Wt + Wt + 6.0 * np.where(pp_ore, Wt / dp, Wt)
             peak_f = peak_f + extra
             peak_b = peak_b + extra
         cap = self.hw.memory_capacity * GB
@@ -323,9 +388,12 @@ def analyze_strategy(cfg: MistConfig, evaluator: Optional[StageEvaluator] = None
             kind = "dec_block_layer" if s == S - 1 else "enc_block_layer"
         # the decoder stage of an encoder-decoder pipeline holds its own copy of the embedding tables
         has_pre = s == 0 or kind == "dec_block_layer"
+        ppa = st.pre_post_strategy_array if st.pre_post_strategy == "preset" else None
         res = ev.evaluate(vec, st.layer_partitions[s], st.gradient_checkpointing[s], G, has_pre=has_pre,
                           has_post=(s == S - 1), inflight_extra=warm, block_kind=kind,
-                          tied_copy=(S > 1 and s == S - 1 and ties_across_stages(cfg)))
+                          tied_copy=(S > 1 and s == S - 1 and ties_across_stages(cfg)),
+                          pre_post_flags=(tuple(ppa[3:6]) if ppa is not None else None),
+                          has_prev_stage=(s > 0), has_next_stage=(s < S - 1))
         stables.append(float(res["stable"][0]))
         deltas.append(float(res["delta"][0]))
         peaks.append((float(res["peak_fwd"][0]), float(res["peak_bwd"][0])))

@@ -49,9 +49,29 @@ class TrainingSession:
         self.micro_batch = self.strategy.micro_batch_size
         self.seq_len = cfg.training.max_sequence_length
         self.sequence_parallel = bool(cfg.get("sequence_parallel", False)) and self.ps.tp_size > 1
-        self.comm_backend = comm_backend or cfg.get("comm_backend", "nccl")
         from .ops import functional as _F
-        _F.Settings.tp_backend = cfg.get("tp_backend", _F.Settings.tp_backend)
+        # Collective back ends.  "auto" (the default) selects the hand-written NVLink kernels wherever
+        # they apply: CUDA, the tcgen05 GEMM back end, and every rank of the group on this node (peer
+        # memory); groups that span nodes, CPU runs and the library GEMM back end use NCCL / gloo.
+        on_gpu = device.type == "cuda" and world > 1 and _F.Settings.gemm_backend == "tcgen05"
+
+        def _one_node(group):
+            from .parallel.symm import group_on_one_node
+            return group_on_one_node(group)
+
+        want = comm_backend or str(cfg.get("comm_backend", "auto"))
+        if want == "auto":
+            want = "fused" if (on_gpu and self.ps.dp_size > 1 and _one_node(self.ps.dp_group)) else "nccl"
+        self.comm_backend = want
+        tpb = str(cfg.get("tp_backend", "auto"))
+        if tpb == "auto":
+            tpb = "fused" if (on_gpu and self.ps.tp_size > 1 and self.sequence_parallel
+                              and _one_node(self.ps.tp_group)) else "nccl"
+        _F.Settings.tp_backend = self.tp_backend = tpb
+        z3 = str(cfg.get("zero3_gather", "auto"))
+        if z3 == "auto":
+            z3 = "fused" if (on_gpu and self.ps.dp_size > 1) else "nccl"
+        self.zero3_gather = z3
         dtype = cfg.training.params_dtype
         # same seed on every data-parallel replica; tensor-parallel ranks draw different slices
         torch.manual_seed(seed + 1000 * self.ps.tp_rank + 17 * stage)
@@ -90,9 +110,13 @@ class TrainingSession:
         pre_post = StageStrategy.from_vector(st.pre_post_strategy_array) if st.pre_post_strategy == "preset" else None
         self.engine = TrainEngine(self.model, self.ps, self.strategy, self.G, st.gradient_checkpointing[stage],
                                   hp=hp, comm_backend=self.comm_backend, overlap=bool(cfg.get("overlap", True)),
-                                  zero3_gather=str(cfg.get("zero3_gather", "nccl")),
+                                  zero3_gather=self.zero3_gather,
                                   use_grad_ring=bool(cfg.get("use_memory_buffer", True)),
                                   pre_post_strategy=pre_post, tied_group=tied_group)
+        # what the engine settled on (it falls back to the library collectives where a fused path does
+        # not apply: offloaded weights or gradients, units with tied tables, groups across nodes)
+        self.comm_backend = "fused" if self.engine.fused is not None else "nccl"
+        self.zero3_gather = "fused" if self.engine.param_gather is not None else "nccl"
         self.pipeline = None
         if multi_stage:
             from .parallel.pipeline import PipelineSchedule

@@ -9,10 +9,15 @@
 //       once; afterwards the whole gathered A sits in local memory for any other consumer.
 //
 //   mode GEMM -> RS   C_shard = reduce_scatter(A * B^T)
-//       The epilogue adds every output tile into the fp32 accumulator of the rank that owns
-//       those rows with a TMA reduce-add (through NVLink for remote owners), so the
-//       reduction overlaps the main loop tile by tile.  A flag round before the first add
-//       (accumulators zeroed everywhere) and one after the last (all adds landed) bracket it.
+//       The epilogue sends every output tile to the rank that owns those rows as soon as the tile is
+//       finished, so the transfer overlaps the main loop tile by tile.  Default form ("store"): the
+//       tile goes, as bf16, into the slot that the owner keeps for this source rank (a TMA store,
+//       through NVLink for remote owners); after the closing flag round (all stores landed) the
+//       owner sums its R slots in rank order (mb_rs_sum), so the result does not depend on arrival
+//       order for any number of ranks, and nothing has to be zeroed first.  The slots alternate
+//       between two sets from launch to launch, which is what lets a rank start its next launch
+//       while a peer is still summing the previous one.  Older form ("add"): TMA reduce-add into
+//       one zeroed accumulator per owner, bracketed by an opening flag round as well.
 //
 //   mode weight-AG -> GEMM   C = A * W^T + bias, W inside a flat parameter buffer sharded over ranks
 //       ZeRO-3 keeps 1/R of a block's flat bf16 parameters per rank.  Every rank holds its
@@ -41,8 +46,14 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int kThreads = 192;
 constexpr int kMaxRanks = 8;
-constexpr int kCopyBufs = 11;   // 11 x 16 KB of the 192 KB stage area in flight per gather CTA
+constexpr int kCopyBufs = 11;   // ring of 11 x 16 KB buffers in the 192 KB stage area of a gather CTA
 constexpr int kCopyBytes = 16384;
+// At most this many peer loads are outstanding; the other buffers of the ring hold data whose store to
+// local memory is still running.  A buffer is loaded into again once the store that read it is among the
+// completed ones: with kCopyLoads loads ahead at most kCopyBufs - 1 - kCopyLoads younger stores may still
+// be pending then, so the wait before a load never drains the whole store queue.
+constexpr int kCopyLoads = 6;
+constexpr int kCopyStoresPending = kCopyBufs - 1 - kCopyLoads;
 
 enum Mode : int { MODE_AG = 1, MODE_RS = 2, MODE_AGW = 3 };
 
@@ -53,6 +64,7 @@ struct CommParams {
   int rows_per_rank;
   int n_gather;                         // gather CTAs at the end of the grid (AG mode)
   int acc_bf16;                         // RS: accumulators are bf16 (two ranks: order-independent sum)
+  int rs_store;                         // RS: store bf16 tiles into per-source slots instead of reduce-add
   // AG: every rank's gathered-A buffer (row-major [M][K] bf16); weight-AG: every rank's flat buffer
   const uint8_t* a_peer[kMaxRanks];
   uint8_t* a_local;
@@ -193,8 +205,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int m_tiles_per_rank = p.rows_per_rank / TM;
   const int ag_chunks_per_rank = p.rows_per_rank / BM;   // all-gather flags: one per 128-row block
 
-  // Tile order: all column tiles of one row block, row blocks starting with the locally owned
-  // ones (AG: their data is there at once) / ending with them (RS: remote adds go out first).
+  // Tile order: all column tiles of one row block; AG: row blocks starting with the locally owned ones
+  // (their data is there at once); RS: row blocks of the owners in turn.
   auto tile_coords = [&](int t, int& m0, int& n0) {
     if (p.mode == MODE_AGW) {
       // all row tiles of one column tile, column tiles in the order their weights arrive
@@ -204,8 +216,16 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       return;
     }
     int mt = t / num_n, nt = t - mt * num_n;
-    int shift = (p.mode == MODE_AG) ? p.me : (p.me + 1) % R;
-    int mt_rot = (mt + shift * m_tiles_per_rank) % num_m;
+    int mt_rot;
+    if (p.mode == MODE_AG) {
+      mt_rot = (mt + p.me * m_tiles_per_rank) % num_m;
+    } else {
+      // RS: consecutive row blocks go to different owners (the next rank first, this rank every R-th
+      // time), so the tiles that cross NVLink are spread over the whole kernel instead of filling its
+      // first (R - 1) / R and leaving the links idle afterwards
+      const int owner = (mt % R + p.me + 1) % R;
+      mt_rot = owner * m_tiles_per_rank + mt / R;
+    }
     m0 = mt_rot * TM + static_cast<int>(rank) * BM;      // this CTA's rows
     n0 = nt * BN;
   };
@@ -263,9 +283,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int pieces = static_cast<int>((bytes + kCopyBytes - 1) / kCopyBytes);
         int ld = 0, stp = 0;
         while (stp < pieces && ok) {
-          while (ld < pieces && issued - stored < kCopyBufs) {
+          while (ld < pieces && issued - stored < kCopyLoads) {
             const uint32_t b = issued % kCopyBufs;
-            if (issued >= kCopyBufs) tma_wait_read<0>();   // the store that last used this buffer has read it
+            if (issued >= kCopyBufs) tma_wait_read<kCopyStoresPending>();   // the store that last used this buffer has read it
             const uint32_t nb = static_cast<uint32_t>(min(static_cast<size_t>(kCopyBytes),
                                                          bytes - static_cast<size_t>(ld) * kCopyBytes));
             mbar_expect_tx(&copy_bar[b], nb);
@@ -454,7 +474,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     bool ok = true;
     const bool rs = (p.mode == MODE_RS);
     __shared__ int peers_ok_s;
-    if (rs) {
+    if (rs && !p.rs_store) {
       // peers' accumulators are zeroed once their ready flag shows this epoch
       if (leader) {
         int okf = 1;
@@ -485,7 +505,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       const int owner = rs ? (m0 / p.rows_per_rank) : 0;
-      const bool f32_units = rs && !p.acc_bf16;
+      const bool f32_units = rs && !p.acc_bf16 && !p.rs_store;
       const int cols_per_unit = f32_units ? 32 : 64;     // fp32 accumulator tiles vs bf16 tiles
       const int units = BN / cols_per_unit;
       for (int u = 0; u < units; ++u) {
@@ -502,7 +522,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rr[i]);
-          if (!rs && p.bias) {
+          if (p.bias) {     // RS: only the rank that holds the row-parallel bias passes it, so it is counted once
             const int col0 = ucol0 + hh * 32;
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] += __bfloat162float(p.bias[min(col0 + i, p.N - 1)]);
@@ -521,7 +541,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         fence_async_smem();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (leader) {
-          if (rs) {
+          if (rs && p.rs_store) {
+            tma_store_2d(acc_maps[owner], stg, ucol0, m0 - owner * p.rows_per_rank);
+          } else if (rs) {
             asm volatile(
                 "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];\n" ::
                     "l"(reinterpret_cast<uint64_t>(acc_maps[owner])),
@@ -661,8 +683,10 @@ int plan_grid(bool pair, long tiles, int& n_gather) {
 MB_API int* mb_status_device_ptr();
 
 // mode 1 (AG -> GEMM): a_ptrs[r] = rank r's symmetric [M][K] bf16 buffer (own rows valid), C [M][N] bf16.
-// mode 2 (GEMM -> RS): A = local [M][K]; acc_ptrs[r] = rank r's fp32 accumulator [M/R][N] (zeroed by its owner
-// before the launch; bf16 when acc_bf16 != 0); C unused.  B: [N][K] (b_mn = 0) or [K][N] (b_mn = 1).  chunk_flags: local int array
+// mode 2 (GEMM -> RS): A = local [M][K]; C unused.  acc_bf16 = 2 (store form): acc_ptrs[r] = the bf16 slot
+// [M/R][N] that rank r keeps for tiles from this rank (nothing to zero; sum the slots with mb_rs_sum after the
+// launch).  acc_bf16 = 0 / 1 (add form): acc_ptrs[r] = rank r's fp32 / bf16 accumulator [M/R][N], zeroed by its
+// owner before the launch.  B: [N][K] (b_mn = 0) or [K][N] (b_mn = 1).  chunk_flags: local int array
 // [R][M/R/128] (AG only).  flag_ptrs[r]: per-rank flag block (2R + 1 ints) reserved for this call site; `epoch`
 // counts launches on it from 1.  M/R must be a multiple of 128, K of 8.
 MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void* B, void* C, void* const* acc_ptrs,
@@ -683,7 +707,8 @@ MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void
   p.nranks = nranks; p.me = me; p.epoch = epoch;
   p.rows_per_rank = rows_per_rank;
   p.n_gather = (mode == MODE_AG) ? (n_gather > 0 ? n_gather : 8) : 0;
-  p.acc_bf16 = acc_bf16;
+  p.acc_bf16 = acc_bf16 ? 1 : 0;
+  p.rs_store = (acc_bf16 == 2) ? 1 : 0;
   if (nranks == 1) p.n_gather = 0, p.mode = (mode == MODE_AG) ? MODE_AG : MODE_RS;
   p.chunk_flags = chunk_flags;
   p.C = C; p.ldc = ldc;

@@ -507,7 +507,7 @@ int pick_vpt(int h) {
 // MB_NORM_VARIANT sets the start value; mb_norm_set_variant changes it.
 int g_norm_variant = -1;
 int norm_variant() {
-  if (g_norm_variant < 0) g_norm_variant = env_int("MB_NORM_VARIANT", 0);
+  if (g_norm_variant < 0) g_norm_variant = env_int("MB_NORM_VARIANT", 2);
   return g_norm_variant;
 }
 

@@ -117,6 +117,57 @@ __device__ __forceinline__ void add8_bf16(float* acc, uint4 raw) {
   }
 }
 
+// One vector (8 elements) of the fused update: reduced gradient in g[], Adam on the fp32 state, new bf16
+// weights to every rank.
+__device__ __forceinline__ void fused_step8(const FusedArgs& a, size_t i, size_t base, float* g, int R) {
+  if (a.grad_acc) {
+    float4 x = reinterpret_cast<float4*>(a.grad_acc)[2 * i];
+    float4 y = reinterpret_cast<float4*>(a.grad_acc)[2 * i + 1];
+    g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
+    g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+    if (!a.do_step) {
+      reinterpret_cast<float4*>(a.grad_acc)[2 * i] = make_float4(g[0], g[1], g[2], g[3]);
+      reinterpret_cast<float4*>(a.grad_acc)[2 * i + 1] = make_float4(g[4], g[5], g[6], g[7]);
+    } else {
+      reinterpret_cast<float4*>(a.grad_acc)[2 * i] = make_float4(0, 0, 0, 0);
+      reinterpret_cast<float4*>(a.grad_acc)[2 * i + 1] = make_float4(0, 0, 0, 0);
+    }
+  }
+  if (!a.do_step) return;
+  float4 p0 = reinterpret_cast<float4*>(a.master)[2 * i], p1 = reinterpret_cast<float4*>(a.master)[2 * i + 1];
+  float4 m0 = reinterpret_cast<float4*>(a.exp_avg)[2 * i], m1 = reinterpret_cast<float4*>(a.exp_avg)[2 * i + 1];
+  float4 v0 = reinterpret_cast<float4*>(a.exp_avg_sq)[2 * i], v1 = reinterpret_cast<float4*>(a.exp_avg_sq)[2 * i + 1];
+  float p[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+  float m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+  float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    float gg = g[k] * a.inv_scale;
+    if (!a.adamw) gg += a.weight_decay * p[k];
+    m[k] = a.beta1 * m[k] + (1.f - a.beta1) * gg;
+    v[k] = a.beta2 * v[k] + (1.f - a.beta2) * gg * gg;
+    float upd = (m[k] / a.bias_c1) / (sqrtf(v[k] / a.bias_c2) + a.eps);
+    if (a.adamw) upd += a.weight_decay * p[k];
+    p[k] -= a.lr * upd;
+  }
+  reinterpret_cast<float4*>(a.master)[2 * i] = make_float4(p[0], p[1], p[2], p[3]);
+  reinterpret_cast<float4*>(a.master)[2 * i + 1] = make_float4(p[4], p[5], p[6], p[7]);
+  reinterpret_cast<float4*>(a.exp_avg)[2 * i] = make_float4(m[0], m[1], m[2], m[3]);
+  reinterpret_cast<float4*>(a.exp_avg)[2 * i + 1] = make_float4(m[4], m[5], m[6], m[7]);
+  reinterpret_cast<float4*>(a.exp_avg_sq)[2 * i] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(a.exp_avg_sq)[2 * i + 1] = make_float4(v[4], v[5], v[6], v[7]);
+  mb::bf16x8 w = mb::pack8(p);
+  const uint4 wr = *reinterpret_cast<uint4*>(&w);
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r)
+    if (r < R && a.params.p[r])
+      st_peer16(reinterpret_cast<__nv_bfloat16*>(a.params.p[r]) + base + 8 * i, wr);
+}
+
+// RMAX: upper bound of the rank count this instantiation serves; U: vectors whose peer loads a thread
+// issues before it consumes any of them.  NVLink loads take microseconds, so the bytes a thread keeps in
+// flight decide the bandwidth: U * R loads of 16 bytes per thread, bounded by the registers they land in.
+template <int RMAX, int U, bool FP32>
 __global__ void __launch_bounds__(512)
 fused_grad_reduce_adam_kernel(const FusedArgs a) {
   int* my_flags = a.flags.p[a.me];
@@ -132,83 +183,62 @@ fused_grad_reduce_adam_kernel(const FusedArgs a) {
   if (ok) {
     const size_t nvec = a.shard_numel >> 3;
     const size_t base = static_cast<size_t>(a.me) * a.shard_numel;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-      float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      if (a.grad_is_fp32) {
-        uint4 lo[kMaxRanks], hi[kMaxRanks];
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += stride * U) {
+      if (FP32) {
+        uint4 lo[U][RMAX], hi[U][RMAX];
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {
-          if (r < R) {
-            const float* src = reinterpret_cast<const float*>(a.grads.p[r]) + base + 8 * i;
-            lo[r] = ld_peer16(src);
-            hi[r] = ld_peer16(src + 4);
-          }
-        }
+        for (int u = 0; u < U; ++u) {
+          const size_t i = i0 + u * stride;
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {
-          if (r < R) {
-            const float* l = reinterpret_cast<const float*>(&lo[r]);
-            const float* h = reinterpret_cast<const float*>(&hi[r]);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              g[k] += l[k];
-              g[4 + k] += h[k];
+          for (int r = 0; r < RMAX; ++r) {
+            if (r < R && i < nvec) {
+              const float* src = reinterpret_cast<const float*>(a.grads.p[r]) + base + 8 * i;
+              lo[u][r] = ld_peer16(src);
+              hi[u][r] = ld_peer16(src + 4);
             }
           }
         }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const size_t i = i0 + u * stride;
+          if (i >= nvec) continue;
+          float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+          for (int r = 0; r < RMAX; ++r) {      // rank order: the same sum on every run
+            if (r < R) {
+              const float* l = reinterpret_cast<const float*>(&lo[u][r]);
+              const float* h = reinterpret_cast<const float*>(&hi[u][r]);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                g[k] += l[k];
+                g[4 + k] += h[k];
+              }
+            }
+          }
+          fused_step8(a, i, base, g, R);
+        }
       } else {
-        uint4 raw[kMaxRanks];
+        uint4 raw[U][RMAX];
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-          if (r < R)
-            raw[r] = ld_peer16(reinterpret_cast<const __nv_bfloat16*>(a.grads.p[r]) + base + 8 * i);
+        for (int u = 0; u < U; ++u) {
+          const size_t i = i0 + u * stride;
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-          if (r < R) add8_bf16(g, raw[r]);
-      }
-      if (a.grad_acc) {
-        float4 x = reinterpret_cast<float4*>(a.grad_acc)[2 * i];
-        float4 y = reinterpret_cast<float4*>(a.grad_acc)[2 * i + 1];
-        g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w;
-        g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
-        if (!a.do_step) {
-          reinterpret_cast<float4*>(a.grad_acc)[2 * i] = make_float4(g[0], g[1], g[2], g[3]);
-          reinterpret_cast<float4*>(a.grad_acc)[2 * i + 1] = make_float4(g[4], g[5], g[6], g[7]);
-        } else {
-          reinterpret_cast<float4*>(a.grad_acc)[2 * i] = make_float4(0, 0, 0, 0);
-          reinterpret_cast<float4*>(a.grad_acc)[2 * i + 1] = make_float4(0, 0, 0, 0);
+          for (int r = 0; r < RMAX; ++r)
+            if (r < R && i < nvec)
+              raw[u][r] = ld_peer16(reinterpret_cast<const __nv_bfloat16*>(a.grads.p[r]) + base + 8 * i);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const size_t i = i0 + u * stride;
+          if (i >= nvec) continue;
+          float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+          for (int r = 0; r < RMAX; ++r)
+            if (r < R) add8_bf16(g, raw[u][r]);
+          fused_step8(a, i, base, g, R);
         }
       }
-      if (!a.do_step) continue;
-      float4 p0 = reinterpret_cast<float4*>(a.master)[2 * i], p1 = reinterpret_cast<float4*>(a.master)[2 * i + 1];
-      float4 m0 = reinterpret_cast<float4*>(a.exp_avg)[2 * i], m1 = reinterpret_cast<float4*>(a.exp_avg)[2 * i + 1];
-      float4 v0 = reinterpret_cast<float4*>(a.exp_avg_sq)[2 * i], v1 = reinterpret_cast<float4*>(a.exp_avg_sq)[2 * i + 1];
-      float p[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-      float m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
-      float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        float gg = g[k] * a.inv_scale;
-        if (!a.adamw) gg += a.weight_decay * p[k];
-        m[k] = a.beta1 * m[k] + (1.f - a.beta1) * gg;
-        v[k] = a.beta2 * v[k] + (1.f - a.beta2) * gg * gg;
-        float upd = (m[k] / a.bias_c1) / (sqrtf(v[k] / a.bias_c2) + a.eps);
-        if (a.adamw) upd += a.weight_decay * p[k];
-        p[k] -= a.lr * upd;
-      }
-      reinterpret_cast<float4*>(a.master)[2 * i] = make_float4(p[0], p[1], p[2], p[3]);
-      reinterpret_cast<float4*>(a.master)[2 * i + 1] = make_float4(p[4], p[5], p[6], p[7]);
-      reinterpret_cast<float4*>(a.exp_avg)[2 * i] = make_float4(m[0], m[1], m[2], m[3]);
-      reinterpret_cast<float4*>(a.exp_avg)[2 * i + 1] = make_float4(m[4], m[5], m[6], m[7]);
-      reinterpret_cast<float4*>(a.exp_avg_sq)[2 * i] = make_float4(v[0], v[1], v[2], v[3]);
-      reinterpret_cast<float4*>(a.exp_avg_sq)[2 * i + 1] = make_float4(v[4], v[5], v[6], v[7]);
-      mb::bf16x8 w = mb::pack8(p);
-      const uint4 wr = *reinterpret_cast<uint4*>(&w);
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < R && a.params.p[r])
-          st_peer16(reinterpret_cast<__nv_bfloat16*>(a.params.p[r]) + base + 8 * i, wr);
     }
   }
 
@@ -340,6 +370,29 @@ p2p_reduce_scatter_kernel(const ReduceScatterArgs a) {
   }
 }
 
+// Sum of the R per-source slots that the store form of the GEMM -> reduce-scatter kernel fills
+// (gemm_comm_tcgen05.cu): out = bf16(slot[0] + slot[1] + ... (+ bias) (+ residual)), added in fp32
+// in rank order, so the result is the same on every run and for every arrival order.
+__global__ void __launch_bounds__(256)
+rs_sum_kernel(const __nv_bfloat16* __restrict__ slots, size_t slot_stride, int R, size_t nvec, int ncols,
+              const __nv_bfloat16* __restrict__ bias, const __nv_bfloat16* __restrict__ residual,
+              __nv_bfloat16* __restrict__ out) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    uint4 raw[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < R) raw[r] = *reinterpret_cast<const uint4*>(slots + r * slot_stride + 8 * i);
+    float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < R) add8_bf16(g, raw[r]);
+    if (bias) add8_bf16(g, *reinterpret_cast<const uint4*>(bias + (8 * i) % ncols));
+    if (residual) add8_bf16(g, *reinterpret_cast<const uint4*>(residual + 8 * i));
+    reinterpret_cast<mb::bf16x8*>(out)[i] = mb::pack8(g);
+  }
+}
+
 // A wait that nothing satisfies: used by the tests of the time limit.
 __global__ void wait_on_flag_kernel(const int* flags, int nranks, int epoch, int* status) {
   wait_flags(flags, nranks, -1, epoch, status);
@@ -348,6 +401,10 @@ __global__ void wait_on_flag_kernel(const int* flags, int nranks, int epoch, int
 }  // namespace
 
 MB_API int* mb_status_device_ptr();
+
+// CTAs of the fused gradient kernel when the caller passes none (mb_set_fused_grad_ctas changes it)
+static int g_fused_ctas = 96;
+MB_API void mb_set_fused_grad_ctas(int n) { g_fused_ctas = n > 0 ? n : 96; }
 
 MB_API int mb_set_peer_wait_ms(int ms) {
   unsigned long long ns = static_cast<unsigned long long>(ms) * 1000000ull;
@@ -399,8 +456,17 @@ MB_API int mb_fused_grad_reduce_adam(void* const* grad_ptrs, void* const* param_
   a.bias_c2 = 1.f - powf(beta2, static_cast<float>(step));
   a.inv_scale = inv_scale; a.adamw = adamw;
   a.status = mb_status_device_ptr();
-  if (num_ctas <= 0) num_ctas = 48;
-  fused_grad_reduce_adam_kernel<<<num_ctas, 512, 0, stream>>>(a);
+  if (num_ctas <= 0) num_ctas = g_fused_ctas;
+  // the flag counter of a call site assumes the same grid on every launch of that site
+  if (grad_is_fp32) {
+    if (nranks <= 2) fused_grad_reduce_adam_kernel<2, 2, true><<<num_ctas, 512, 0, stream>>>(a);
+    else if (nranks <= 4) fused_grad_reduce_adam_kernel<4, 1, true><<<num_ctas, 512, 0, stream>>>(a);
+    else fused_grad_reduce_adam_kernel<8, 1, true><<<num_ctas, 512, 0, stream>>>(a);
+  } else {
+    if (nranks <= 2) fused_grad_reduce_adam_kernel<2, 4, false><<<num_ctas, 512, 0, stream>>>(a);
+    else if (nranks <= 4) fused_grad_reduce_adam_kernel<4, 2, false><<<num_ctas, 512, 0, stream>>>(a);
+    else fused_grad_reduce_adam_kernel<8, 1, false><<<num_ctas, 512, 0, stream>>>(a);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -435,6 +501,22 @@ MB_API int mb_p2p_reduce_scatter(void* const* src_ptrs, void* dst, void* const* 
   a.status = mb_status_device_ptr();
   if (num_ctas <= 0) num_ctas = 48;
   p2p_reduce_scatter_kernel<<<num_ctas, 512, 0, stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// out[numel] = sum over r < nranks of slots[r * slot_stride + ...] (+ bias[col]) (+ residual), bf16 in and
+// out, fp32 sum in rank order.  numel and ncols multiples of 8.
+MB_API int mb_rs_sum(const void* slots, size_t slot_stride, int nranks, size_t numel, int ncols, const void* bias,
+                     const void* residual, void* out, cudaStream_t stream) {
+  if (nranks < 1 || nranks > kMaxRanks || (numel & 7) || (ncols & 7) || (slot_stride & 7)) return -1;
+  const size_t nvec = numel >> 3;
+  int blocks = static_cast<int>((nvec + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  rs_sum_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(slots), slot_stride, nranks, nvec,
+                                            ncols, reinterpret_cast<const __nv_bfloat16*>(bias),
+                                            reinterpret_cast<const __nv_bfloat16*>(residual),
+                                            reinterpret_cast<__nv_bfloat16*>(out));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -156,9 +156,9 @@ class RowParallelLinear(FusedDense):
         if (self.sequence_parallel and F.Settings.tp_backend == "fused" and isinstance(x, torch.Tensor) and x.is_cuda
                 and not isinstance(self.process_group, dist_ops.FakeGroup)):
             from ..parallel import fused_tp
-            y = fused_tp.linear_rs(x.reshape(-1, x.shape[-1]), self.weight, self.bias,
-                                   fused_tp.context_for(self.process_group))
-            return y if residual is None else y + residual.reshape(y.shape)
+            res2 = None if residual is None else residual.reshape(-1, residual.shape[-1])
+            return fused_tp.linear_rs(x.reshape(-1, x.shape[-1]), self.weight, self.bias,
+                                      fused_tp.context_for(self.process_group), residual=res2)
         y = F.linear(x, self.weight, self.bias)
         if self.sequence_parallel:
             y = dist_ops.reduce_scatter(y.reshape(-1, y.shape[-1]), self.process_group)

@@ -36,18 +36,25 @@ def device_name() -> str:
 
 
 class OpDatabase:
-    def __init__(self, device: Optional[str] = None, root: Optional[os.PathLike] = None, allow_profile: bool = True):
+    def __init__(self, device: Optional[str] = None, root: Optional[os.PathLike] = None, allow_profile: bool = True,
+                 refresh_unclocked: bool = False):
         self.device = (device or device_name()).replace(" ", "_")
         base = Path(root or os.environ.get("MIST_B200_OP_CACHE", _HERE))
         self.dir = base / f"cache_{self.device}"
         self.allow_profile = allow_profile and torch.cuda.is_available() and not os.environ.get("FAKE_DEVICE_NAME")
+        #: measure again the entries that were stored without the SM clock they ran at
+        self.refresh_unclocked = bool(refresh_unclocked) and self.allow_profile
         self.model = analytic.device_model(self.device)
         self._mem: Dict[str, Dict[str, Dict]] = {}
-        # Entries are timed one operator at a time, at boost clocks.  A training step keeps the
-        # tensor cores busy for seconds and settles at the power-capped clock, so tensor-core
-        # bound operators run slower there by the ratio of the burst to the sustained GEMM
-        # rate of the device; ``_meta.json`` beside the entries holds that ratio.
-        self.sustained_scale, self.scaled_ops = 1.0, ()
+        # Entries are timed one operator at a time, in short bursts, and carry the SM clock that was
+        # read while they ran (``sm_mhz``).  A training step keeps the tensor cores busy for seconds
+        # and settles at a lower, power-capped clock; the time of an operator that is bound by the SMs
+        # (tensor cores, exponentials) scales with the inverse of that clock, so such an entry is
+        # multiplied by ``sm_mhz / sm_mhz_under_load``.  ``_meta.json`` beside the entries names the
+        # operators this applies to and the clock measured under a training load (the median that
+        # bench.py samples during its timed region).  Entries without a recorded clock fall back to the
+        # fixed ``sustained_scale`` of the file.
+        self.sustained_scale, self.scaled_ops, self.sm_mhz_under_load = 1.0, (), None
         meta = self.dir / "_meta.json"
         if meta.exists():
             try:
@@ -55,6 +62,8 @@ class OpDatabase:
                     m = json.load(f)
                 self.sustained_scale = float(m.get("sustained_scale", 1.0))
                 self.scaled_ops = tuple(m.get("scaled_ops", ()))
+                if m.get("sm_mhz_under_load"):
+                    self.sm_mhz_under_load = float(m["sm_mhz_under_load"])
             except (json.JSONDecodeError, OSError, ValueError):
                 pass
         self.hits = self.misses = self.profiled = 0
@@ -104,10 +113,11 @@ class OpDatabase:
         entries = self._load(spec.op)
         key = spec.key()
         e = entries.get(key)
+        if e is not None and self.refresh_unclocked and "sm_mhz" not in e and spec.op in self.scaled_ops:
+            e = None
         if e is not None:
             self.hits += 1
-            k = self.sustained_scale if spec.op in self.scaled_ops else 1.0
-            return float(e["fwd"]) * k, float(e["bwd"]) * k
+            return float(e["fwd"]) * self._clock_scale(spec.op, e), float(e["bwd"]) * self._clock_scale(spec.op, e)
         self.misses += 1
         if self.allow_profile:
             from . import profiler
@@ -116,9 +126,21 @@ class OpDatabase:
                 self.profiled += 1
                 entry = {"spec": spec.as_dict(), "fwd": measured[0], "bwd": measured[1], "flops_fwd": flops_fwd,
                          "flops_bwd": flops_bwd, "bytes_fwd": bytes_fwd, "bytes_bwd": bytes_bwd}
+                mhz = profiler.median_clock()
+                if mhz:
+                    entry["sm_mhz"] = mhz
                 self._store(spec.op, key, entry)
-                return measured
+                return measured[0] * self._clock_scale(spec.op, entry), measured[1] * self._clock_scale(spec.op, entry)
         return analytic.estimate(spec, flops_fwd, flops_bwd, bytes_fwd, bytes_bwd, self.model)
+
+    def _clock_scale(self, op: str, entry: Dict) -> float:
+        """Factor from the entry's profiling conditions to a training step (see ``__init__``)."""
+        if op not in self.scaled_ops:
+            return 1.0
+        mhz = entry.get("sm_mhz")
+        if mhz and self.sm_mhz_under_load:
+            return max(1.0, float(mhz) / self.sm_mhz_under_load)
+        return self.sustained_scale
 
     def add(self, spec: NodeSpec, fwd: float, bwd: float, **extra):
         self._store(spec.op, spec.key(), dict({"spec": spec.as_dict(), "fwd": fwd, "bwd": bwd}, **extra))

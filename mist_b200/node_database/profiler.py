@@ -19,6 +19,32 @@ from .node_spec import NodeSpec
 
 WARMUP, REPEAT = 3, 5
 _flush = None
+_nvml = None
+#: SM clocks (MHz) read while the most recent operator was being timed
+clock_samples = []
+
+
+def _sm_mhz() -> Optional[float]:
+    """Current SM clock of the device in use, read through NVML (None when NVML is not there)."""
+    global _nvml
+    try:
+        import pynvml
+        if _nvml is None:
+            pynvml.nvmlInit()
+            uuid = torch.cuda.get_device_properties(torch.cuda.current_device()).uuid
+            _nvml = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+        return float(pynvml.nvmlDeviceGetClockInfo(_nvml, pynvml.NVML_CLOCK_SM))
+    except Exception:      # noqa: BLE001 - clocks are an annotation, never a reason to fail
+        _nvml = False if _nvml is None else _nvml
+        return None
+
+
+def median_clock() -> Optional[float]:
+    """Median of the SM clocks sampled since the last :func:`profile` call started."""
+    if not clock_samples:
+        return None
+    xs = sorted(clock_samples)
+    return xs[len(xs) // 2]
 
 
 def _flush_l2():
@@ -39,6 +65,9 @@ def _time(fn: Callable[[], None]) -> float:
         a.record()
         fn()
         b.record()
+        mhz = _sm_mhz() if _nvml is not False else None      # read while the kernels are (still) running
+        if mhz:
+            clock_samples.append(mhz)
         torch.cuda.synchronize()
         ts.append(a.elapsed_time(b) * 1e-3)
     ts.sort()
@@ -71,6 +100,7 @@ def profile(spec: NodeSpec, dtype=torch.bfloat16) -> Optional[Tuple[float, float
     dev = "cuda"
     op = spec.op
     g = spec.get
+    del clock_samples[:]
 
     def rnd(*shape, grad=True, scale=1.0):
         return (torch.randn(*shape, device=dev, dtype=dtype) * scale).requires_grad_(grad)

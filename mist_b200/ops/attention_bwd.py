@@ -47,11 +47,21 @@ def backward(dout, q, k, v, o, lse, scale, causal, out=None):
     """Returns (dq, dk, dv); with ``out=(dq, dk, dv)`` writes into those (possibly strided) views."""
     if not q.is_cuda:
         grads = _reference(dout, q, k, v, scale, causal)
-    elif has_native_backward() and q.shape[2] == k.shape[2]:
+    elif has_native_backward():
         from .functional import Settings
         if Settings.attn_backend == "tcgen05":
-            return _native_backward(dout, q, k, v, o, lse, scale, causal, out)
-        grads = _library(dout, q, k, v, scale, causal)
+            if q.shape[2] == k.shape[2]:
+                return _native_backward(dout, q, k, v, o, lse, scale, causal, out)
+            # grouped-query heads: every query head gets its own copy of its group's key / value head,
+            # and the gradients of the copies are summed over the group afterwards
+            g = q.shape[2] // k.shape[2]
+            dq, dk, dv = _native_backward(dout, q, k.repeat_interleave(g, dim=2), v.repeat_interleave(g, dim=2),
+                                          o, lse, scale, causal, None)
+            b, sk, nkv, d = k.shape
+            grads = (dq, dk.view(b, sk, nkv, g, d).float().sum(3).to(k.dtype),
+                     dv.view(b, sk, nkv, g, d).float().sum(3).to(v.dtype))
+        else:
+            grads = _library(dout, q, k, v, scale, causal)
     else:
         grads = _library(dout, q, k, v, scale, causal)
     if out is not None:

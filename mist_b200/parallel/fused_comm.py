@@ -25,7 +25,7 @@ FLAG_SLOT_INTS = 32   # ready[R] + done[R] + counter, padded
 
 
 class FusedDPComm:
-    def __init__(self, engine, num_ctas: int = 48):
+    def __init__(self, engine, num_ctas: int = 0):
         self.engine = engine
         ps = engine.ps
         self.group = ps.dp_group

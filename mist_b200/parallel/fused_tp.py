@@ -32,6 +32,8 @@ native.register_signature(
     [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
      C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p])
 
+native.register_signature(
+    "mb_rs_sum", [C.c_void_p, C.c_size_t, C.c_int, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p])
 native.register_signature("mb_gemm_comm_set_pair", [C.c_int], None)
 native.register_signature("mb_gemm_comm_last_pair", [], C.c_int)
 
@@ -83,6 +85,27 @@ class FusedTPContext:
     def accumulator(self, rows, N, dtype=torch.float32):
         return self._alloc(("acc", rows, N, dtype), rows * N, dtype)
 
+    def rs_slots(self, rows, N):
+        """Slots of the store form of GEMM -> reduce-scatter: two sets (used alternately, launch by
+        launch) of one ``[rows, N]`` bf16 slot per source rank, in every rank's memory.  Returns
+        ``(local tensor [2, R, rows * N], per-set pointer tables)`` where table ``s`` holds, for every
+        owner rank, the address of the slot it keeps for tiles from this rank in set ``s``."""
+        key = ("rs_slots", rows, N)
+        if key not in self._bufs:
+            n = rows * N
+            if self.heap is not None:
+                t, off = self.heap.alloc(2 * self.R * n, torch.bfloat16)
+                bases = self.heap.peer_ptrs(off)
+            else:
+                ts = [torch.zeros(2 * self.R * n, dtype=torch.bfloat16, device=self.device) for _ in range(self.R)]
+                t, bases = ts[0], [x.data_ptr() for x in ts]
+                self._keep = getattr(self, "_keep", []) + ts
+            tables = [ptr_table([b + 2 * ((s * self.R + self.me) * n) for b in bases]) for s in range(2)]
+            self._bufs[key] = (t.view(2, self.R, n), tables)
+            self._rs_seq = getattr(self, "_rs_seq", {})
+            self._rs_seq[key] = 0
+        return self._bufs[key]
+
 
 def _ag_gemm(ctx: FusedTPContext, x_shard: torch.Tensor, w: torch.Tensor, bias, b_mn: bool, tag: str):
     """C[M, N] = allgather(x_shard)[M, K] * B^T; returns (C, gathered A view)."""
@@ -100,8 +123,41 @@ def _ag_gemm(ctx: FusedTPContext, x_shard: torch.Tensor, w: torch.Tensor, bias, 
     return out, a2
 
 
-def _gemm_rs(ctx: FusedTPContext, x: torch.Tensor, w: torch.Tensor, b_mn: bool):
-    """reduce_scatter(x[M, K] * B^T) -> fp32 accumulator rows of this rank, as bf16 [M/R, N]."""
+#: "store" (default): tiles go into per-source slots and are summed in rank order afterwards;
+#: "add": the earlier form with TMA reduce-add into one zeroed accumulator (kept for A/B timing)
+RS_FORM = "store"
+
+
+def _gemm_rs(ctx: FusedTPContext, x: torch.Tensor, w: torch.Tensor, b_mn: bool, bias=None, residual=None):
+    """``reduce_scatter(x[M, K] * B^T) (+ bias) (+ residual)`` -> this rank's rows, bf16 ``[M/R, N]``.
+
+    Every rank must make the same sequence of calls (the slot set alternates per call)."""
+    M, K = x.shape
+    N = w.shape[1] if b_mn else w.shape[0]
+    rows = M // ctx.R
+    if RS_FORM == "store":
+        slots, tables = ctx.rs_slots(rows, N)
+        key = ("rs_slots", rows, N)
+        parity = ctx._rs_seq[key] & 1
+        ctx._rs_seq[key] += 1
+        s = ctx.site((MODE_RS, M, N, K, b_mn))
+        s["epoch"] += 1
+        # a bias is added to this rank's partial product inside the kernel: the rank that holds the
+        # row-parallel bias (the first) passes it, the others pass none, so every token gets it once
+        call("mb_gemm_comm", MODE_RS, None, ptr(x), ptr(w), None, tables[parity], s["flags"], None, M, N, K,
+             w.stride(0), N, int(b_mn), ptr(bias), ctx.R, ctx.me, s["epoch"], 0, 0, 2, native.stream())
+        out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
+        res = residual.contiguous() if residual is not None else None
+        call("mb_rs_sum", ptr(slots[parity]), rows * N, ctx.R, rows * N, N, None, ptr(res), ptr(out), native.stream())
+        return out
+    out = _gemm_rs_add(ctx, x, w, b_mn, bias)
+    if residual is not None:
+        out = out + residual.reshape(out.shape)
+    return out
+
+
+def _gemm_rs_add(ctx: FusedTPContext, x: torch.Tensor, w: torch.Tensor, b_mn: bool, bias=None):
+    """The reduce-add form: fp32 accumulator rows of this rank, as bf16 [M/R, N]."""
     M, K = x.shape
     N = w.shape[1] if b_mn else w.shape[0]
     rows = M // ctx.R
@@ -114,7 +170,7 @@ def _gemm_rs(ctx: FusedTPContext, x: torch.Tensor, w: torch.Tensor, b_mn: bool):
     s = ctx.site((MODE_RS, M, N, K, b_mn))
     s["epoch"] += 1
     call("mb_gemm_comm", MODE_RS, None, ptr(x), ptr(w), None, acc_table, s["flags"], None, M, N, K, w.stride(0), N,
-         int(b_mn), None, ctx.R, ctx.me, s["epoch"], 0, 0, int(bf16_acc), native.stream())
+         int(b_mn), ptr(bias), ctx.R, ctx.me, s["epoch"], 0, 0, int(bf16_acc), native.stream())
     if bf16_acc:
         return acc.view(rows, N).clone()
     out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
@@ -158,14 +214,13 @@ class _AGLinear(torch.autograd.Function):
 
 class _LinearRS(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, tp):
+    def forward(ctx, x, weight, bias, tp, residual=None):
         x2 = x.contiguous()
-        y = _gemm_rs(tp, x2, weight, False)
-        if bias is not None:
-            y = y + bias
+        y = _gemm_rs(tp, x2, weight, False, bias=bias, residual=residual)
         ctx.tp = tp
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
         return y
 
     @staticmethod
@@ -183,7 +238,7 @@ class _LinearRS(torch.autograd.Function):
         else:
             dw = F.gemm(dy_full, x2, a_mn=True, b_mn=True)
         db = F.colsum(dy_shard.contiguous()) if ctx.has_bias else None
-        return dx, dw, db, None
+        return dx, dw, db, None, (dy_shard if ctx.has_res else None)
 
 
 def ag_linear(x_shard, weight, bias, tp: FusedTPContext):
@@ -191,9 +246,10 @@ def ag_linear(x_shard, weight, bias, tp: FusedTPContext):
     return _AGLinear.apply(x_shard, weight, bias, tp)
 
 
-def linear_rs(x, weight, bias, tp: FusedTPContext):
-    """Row-parallel linear ``[tokens, K_local]`` -> this rank's ``[tokens / tp, N]`` rows of the sum."""
-    return _LinearRS.apply(x, weight, bias, tp)
+def linear_rs(x, weight, bias, tp: FusedTPContext, residual=None):
+    """Row-parallel linear ``[tokens, K_local]`` -> this rank's ``[tokens / tp, N]`` rows of the sum
+    (+ bias, + ``residual`` of that shape; both are added while the per-rank partial sums are added)."""
+    return _LinearRS.apply(x, weight, bias, tp, residual)
 
 
 _CONTEXTS: Dict[int, FusedTPContext] = {}

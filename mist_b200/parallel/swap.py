@@ -5,8 +5,9 @@ Everything here is ``cudaMemcpyAsync`` between device memory and pinned host mem
 two dedicated streams (one per direction), ordered against the compute stream with
 events; no SM time is spent on the copies (reference: mist/re_swap_manager/
 swap_backend.py:113-169 ``swap_``, :172-513 TensorSwapHandle, :516-567; activation hooks
-mist/re_swap_manager/manager.py:525-710 with the 1 Mi element threshold at :49,634,676;
-buffer pools mist/re_swap_manager/mem_buffer_pool.py:60-195).
+mist/re_swap_manager/manager.py:525-710 with the 1 Mi element threshold at :49,634,676).
+The two-slot rings of full weights and of gradient buckets (reference: mist/re_swap_manager/
+mem_buffer_pool.py:60-195) are plain tensors owned by the training engine.
 """
 from __future__ import annotations
 
@@ -16,61 +17,6 @@ from typing import Dict, Optional
 import torch
 
 ACTIVATION_SWAP_MIN_NUMEL = 1 << 20   # smaller saved tensors stay on the device
-
-
-
-
-class MemoryBuffer:
-    """A named contiguous device buffer with bump allocation and usage statistics."""
-
-    def __init__(self, name: str, numel: int, dtype, device):
-        self.name, self.numel, self.dtype = name, int(numel), dtype
-        self.data = torch.empty(self.numel, dtype=dtype, device=device)
-        self.offset = 0
-        self.in_use = False
-        self._peak, self._uses, self._sum = 0, 0, 0
-
-    def reset(self):
-        self._uses += 1
-        self._sum += self.offset
-        self.offset = 0
-
-    def get(self, shape) -> torch.Tensor:
-        n = 1
-        for s in shape:
-            n *= int(s)
-        if self.offset + n > self.numel:
-            raise MemoryError(f"buffer '{self.name}' exhausted: need {n}, {self.numel - self.offset} left")
-        t = self.data[self.offset:self.offset + n].view(*shape)
-        self.offset += n
-        self._peak = max(self._peak, self.offset)
-        return t
-
-    def average_usage(self) -> float:
-        return (self._sum / self._uses / self.numel) if self._uses else 0.0
-
-
-class RingMemoryBuffer:
-    """``num_buffers`` equally sized buffers handed out in turn; asking for one while all are
-    in use is an error (the schedule guarantees at most ``num_buffers`` live users)."""
-
-    def __init__(self, name: str, num_buffers: int, numel: int, dtype, device):
-        self.buffers = [MemoryBuffer(f"{name}[{i}]", numel, dtype, device) for i in range(num_buffers)]
-        self._next = 0
-
-    def get_next_buffer(self) -> MemoryBuffer:
-        for _ in range(len(self.buffers)):
-            b = self.buffers[self._next]
-            self._next = (self._next + 1) % len(self.buffers)
-            if not b.in_use:
-                b.in_use = True
-                b.reset()
-                return b
-        raise RuntimeError("all ring buffers are in use")
-
-    @staticmethod
-    def release(buf: MemoryBuffer):
-        buf.in_use = False
 
 
 class SwapStreams:

@@ -29,6 +29,7 @@ native.register_signature("mb_ipc_get_handle", [C.c_void_p, C.c_void_p])
 native.register_signature("mb_ipc_open_handle", [C.c_void_p, C.POINTER(C.c_void_p)])
 native.register_signature("mb_ipc_close_handle", [C.c_void_p])
 native.register_signature("mb_set_peer_wait_ms", [C.c_int])
+native.register_signature("mb_set_fused_grad_ctas", [C.c_int], None)
 native.register_signature("mb_wait_on_flags", [C.c_void_p, C.c_int, C.c_int, C.c_void_p])
 native.register_signature(
     "mb_fused_grad_reduce_adam",

@@ -66,8 +66,10 @@ def tune_stage_cell(ev: StageEvaluator, cfg: MistConfig, g: int, mesh: Tuple[int
     all_points: List[StagePoint] = []
     evaluated = 0
     for c in ckpt_candidates(layers, cfg):
+        # kinds: 0 first stage of a pipeline, 1 middle, 2 last, 3 the only stage (no neighbours to exchange with)
         res = ev.evaluate(space, layers, c, g, has_pre, has_post, inflight_extra=warm,
-                          tied_copy=(kind == 2 and ties_across_stages(cfg)))
+                          tied_copy=(kind == 2 and ties_across_stages(cfg)),
+                          has_prev_stage=kind in (1, 2), has_next_stage=kind in (0, 1))
         evaluated += space.shape[0]
         idx = dedup_samples(sample_pareto_frontier(res["stable"], res["delta"], res["feasible"], S))
         for i in idx:

@@ -35,6 +35,139 @@ def test_flag_wait_gives_up_with_status():
         lib.mb_set_peer_wait_ms(2000)
 
 
+def _emulated_flags(R):
+    """Flag blocks of R emulated ranks on one GPU: every peer already shows 'ready' and 'done'."""
+    from mist_b200.parallel.symm import ptr_table
+    fl = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(R)]
+    fl[0][: 2 * R].fill_(1 << 30)
+    return fl, ptr_table([f.data_ptr() for f in fl])
+
+
+@pytest.mark.parametrize("R", [2, 4, 8])
+@pytest.mark.parametrize("grad_fp32", [False, True])
+def test_fused_grad_reduce_adam_emulated_ranks(R, grad_fp32):
+    """The fused reduce-scatter + Adam + weight write-back kernel on one GPU: the peers' buckets and
+    weight buffers are further local buffers and their flags are pre-set, so the launch waits for
+    nobody.  Checked against the same arithmetic in PyTorch: the reduced shard bit for bit (fp32 sum
+    in rank order), master weights and moments to fp32 rounding, and every 'rank' got the new weights."""
+    from mist_b200.ops import native
+    from mist_b200.ops.native import call, ptr
+    from mist_b200.parallel.symm import ptr_table
+    torch.manual_seed(R)
+    shard = 256 * 1000 + 8              # not a multiple of the block size
+    n = shard * R
+    gdt = torch.float32 if grad_fp32 else torch.bfloat16
+    grads = [(torch.randn(n, device="cuda") * 0.01).to(gdt) for _ in range(R)]
+    params = [torch.zeros(n, dtype=torch.bfloat16, device="cuda") for _ in range(R)]
+    master = torch.randn(shard, device="cuda")
+    m, v = torch.zeros_like(master), torch.zeros_like(master)
+    acc = torch.randn(shard, device="cuda") * 0.01
+    master0, acc0 = master.clone(), acc.clone()
+    flags, ftab = _emulated_flags(R)
+    lr, b1, b2, eps, wd, inv = 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.25
+    me = 0
+    # micro step 1 of 2: only accumulate the reduced shard
+    call("mb_fused_grad_reduce_adam", ptr_table([g.data_ptr() for g in grads]), ptr_table([p_.data_ptr() for p_ in params]),
+         ftab, ptr(master), ptr(m), ptr(v), ptr(acc), shard, R, me, 1, int(grad_fp32), 0, lr, b1, b2, eps, wd, 1, inv, 1, 0,
+         native.stream())
+    torch.cuda.synchronize()
+    native.check_status()
+    red = torch.zeros(shard, device="cuda")
+    for r in range(R):                   # rank order, fp32
+        red += grads[r][me * shard:(me + 1) * shard].float()
+    assert torch.equal(acc, acc0 + red)
+    assert torch.equal(master, master0)
+    # micro step 2: reduce, add the accumulator, Adam, write the new weights to every rank
+    call("mb_fused_grad_reduce_adam", ptr_table([g.data_ptr() for g in grads]), ptr_table([p_.data_ptr() for p_ in params]),
+         ftab, ptr(master), ptr(m), ptr(v), ptr(acc), shard, R, me, 2, int(grad_fp32), 1, lr, b1, b2, eps, wd, 1, inv, 1, 0,
+         native.stream())
+    torch.cuda.synchronize()
+    native.check_status()
+    g = (red + (acc0 + red)) * inv
+    m_ref = (1 - b1) * g
+    v_ref = (1 - b2) * g * g
+    upd = (m_ref / (1 - b1)) / ((v_ref / (1 - b2)).sqrt() + eps) + wd * master0
+    ref = master0 - lr * upd
+    assert (master - ref).abs().max().item() <= 1e-6 * ref.abs().max().item() + 1e-7
+    assert (master - master0).abs().max().item() > 1e-4          # the weights did move
+    assert torch.allclose(m, m_ref, rtol=1e-5, atol=1e-9) and torch.allclose(v, v_ref, rtol=1e-5, atol=1e-12)
+    assert float(acc.abs().max()) == 0.0                          # accumulator cleared for the next iteration
+    for r in range(R):
+        assert torch.equal(params[r][me * shard:(me + 1) * shard], master.to(torch.bfloat16))
+        if R > 1:
+            other = (me + 1) % R
+            assert float(params[r][other * shard:(other + 1) * shard].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("R", [2, 4])
+def test_p2p_all_gather_and_reduce_scatter_emulated_ranks(R):
+    from mist_b200.ops import native
+    from mist_b200.ops.native import call, ptr
+    from mist_b200.parallel.symm import ptr_table
+    torch.manual_seed(10 + R)
+    shard = 128 * 1031
+    shards = [torch.randn(shard, device="cuda").to(torch.bfloat16) for _ in range(R)]
+    dst = torch.full((R * shard,), float("nan"), dtype=torch.bfloat16, device="cuda")
+    flags, ftab = _emulated_flags(R)
+    call("mb_p2p_all_gather", ptr_table([s_.data_ptr() for s_ in shards]), ptr(dst), ftab, shard * 2, R, 0, 1, 0,
+         native.stream())
+    torch.cuda.synchronize()
+    native.check_status()
+    assert torch.equal(dst, torch.cat(shards))
+    fulls = [torch.randn(R * shard, device="cuda").to(torch.bfloat16) for _ in range(R)]
+    flags, ftab = _emulated_flags(R)
+    for dst_fp32 in (0, 1):
+        out = torch.zeros(shard, dtype=torch.float32 if dst_fp32 else torch.bfloat16, device="cuda")
+        call("mb_p2p_reduce_scatter", ptr_table([f.data_ptr() for f in fulls]), ptr(out), ftab, shard, R, 0, 1 + dst_fp32,
+             dst_fp32, 0, 0, native.stream())
+        torch.cuda.synchronize()
+        native.check_status()
+        red = torch.zeros(shard, device="cuda")
+        for r in range(R):
+            red += fulls[r][:shard].float()
+        assert torch.equal(out, red if dst_fp32 else red.to(torch.bfloat16))
+
+
+def _rs_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from mist_b200.ops import native
+        from mist_b200.ops.native import call, ptr
+        from mist_b200.parallel.symm import SymmetricHeap, ptr_table
+        g = dist.new_group(list(range(world)))
+        shard = 128 * 4099
+        heap = SymmetricHeap(world * shard * 2 + (1 << 20), g)
+        full, off = heap.alloc(world * shard, torch.bfloat16)
+        flags, foff = heap.alloc(32, torch.int32)
+        torch.manual_seed(100 + rank)
+        full.copy_((torch.randn(world * shard, device="cuda") * 0.05).to(torch.bfloat16))
+        torch.cuda.synchronize()
+        dist.barrier(group=g)
+        out = torch.empty(shard, dtype=torch.bfloat16, device="cuda")
+        call("mb_p2p_reduce_scatter", ptr_table(heap.peer_ptrs(off)), ptr(out), ptr_table(heap.peer_ptrs(foff)), shard,
+             world, rank, 1, 0, 0, 0, native.stream())
+        ref = torch.empty(shard, dtype=torch.bfloat16, device="cuda")
+        dist.reduce_scatter_tensor(ref, full.clone(), group=g)
+        torch.cuda.synchronize()
+        native.check_status()
+        ret[rank] = bool(torch.equal(out, ref))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reduced_gradient_shard_equals_nccl_bit_for_bit():
+    """Two ranks: a + b is one rounding in either implementation, so the bf16 shards must be equal."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rs_worker, args=(2, free_port(), ret), nprocs=2, join=True)
+    assert ret[0] and ret[1]
+
+
 def _worker(rank, world, port, zero_flags, G, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
@@ -58,6 +191,10 @@ def _worker(rank, world, port, zero_flags, G, ret):
             torch.manual_seed(0)
             model = base_model_provider(cfg.model, device="cuda", dtype=torch.bfloat16)
             eng = TrainEngine(model, ps, strat, grad_accum_steps=G, hp=dict(lr=1e-3), comm_backend=backend)
+            if backend == "fused":
+                assert eng.fused is not None and all(eng.fused.handles(u) for u in eng.units)
+            start = torch.cat([u.master.clone() for u in eng.units])
+            fp32_buckets = eng.grad_dtype == torch.float32
             prov = get_inputs_provider(cfg.model.name)
             for it in range(3):
                 batches = [prov(2, 128, 1024, "cuda", seed=1000 * it + 10 * k + rank) for k in range(G)]
@@ -66,15 +203,28 @@ def _worker(rank, world, port, zero_flags, G, ret):
             torch.cuda.synchronize()
             native.check_status()
             finals[backend] = torch.cat([u.master.clone() for u in eng.units])
-        diff = (finals["nccl"] - finals["fused"]).abs().max().item()
-        scale = finals["nccl"].abs().max().item()
-        ret[rank] = (diff, scale)
+        moved = (finals["nccl"] - start).abs()
+        diff = (finals["nccl"] - finals["fused"]).abs()
+        ret[rank] = dict(max_diff=diff.max().item(), mean_diff=diff.mean().item(), mean_moved=moved.mean().item(),
+                         max_moved=moved.max().item(), fused_moved=(finals["fused"] - start).abs().mean().item(),
+                         equal=bool(torch.equal(finals["nccl"], finals["fused"])), fp32_buckets=fp32_buckets)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("zero_flags,G", [((False, False, True), 1), ((False, True, True), 1), ((False, True, True), 2)])
+@pytest.mark.parametrize("zero_flags,G", [((False, False, True), 1), ((False, True, True), 1), ((False, True, True), 2),
+                                          ((False, False, True), 2)])
 def test_fused_matches_nccl(zero_flags, G):
+    """Three Adam steps at lr 1e-3 through the fused NVLink path and through NCCL, from the same start.
+    Every weight moves by about lr per step, so the test first checks that both paths moved the weights
+    (a path that updated nothing would sit 3e-3 away from the other).  The two runs cannot be equal bit
+    for bit: the attention backward kernel sums dQ contributions of its key blocks in arrival order, so
+    two backward passes of one model already differ in the last bits, and Adam turns a sign change of a
+    near-zero gradient into a full step for that one element.  What must hold is that such elements are
+    rare: with fp32 gradient buckets (ZeRO-1, two micro steps) both paths add the same fp32 numbers and
+    the mean difference stays below 1e-3 of the mean movement; with bf16 buckets NCCL rounds the reduced
+    gradient to bf16 and the fused kernel does not, which allows 2e-2.  (That the reduction itself equals
+    NCCL's bit for bit is checked on its own above.)"""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world = 2
@@ -83,7 +233,6 @@ def test_fused_matches_nccl(zero_flags, G):
     port = free_port()
     mp.spawn(_worker, args=(world, port, zero_flags, G, ret), nprocs=world, join=True)
     for r in range(world):
-        diff, scale = ret[r]
-        # identical math up to bf16 rounding of the reduced gradient: Adam steps differ by
-        # at most a few lr in rare sign flips
-        assert diff < 5e-3, (diff, scale)
+        m = ret[r]
+        assert m["mean_moved"] > 1e-3 and m["fused_moved"] > 1e-3, m       # ~3 steps of lr = 1e-3
+        assert m["mean_diff"] < (1e-3 if m["fp32_buckets"] else 2e-2) * m["mean_moved"], m

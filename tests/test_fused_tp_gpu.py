@@ -41,11 +41,24 @@ def test_emulated_two_ranks_one_gpu(b_mn):
     assert _rel(y, ref) < 1e-2
     # GEMM -> RS: rank 0 keeps rows [0, rows) of its own partial product (the emulated peer adds nothing)
     x = torch.randn(2 * rows, K, device="cuda", dtype=torch.bfloat16)
-    out = fused_tp._gemm_rs(ctx, x, w, b_mn)
+    for form in ("store", "store", "add"):        # two launches of the default form: the slot sets alternate
+        fused_tp.RS_FORM = form
+        try:
+            out = fused_tp._gemm_rs(ctx, x, w, b_mn)
+        finally:
+            fused_tp.RS_FORM = "store"
+        torch.cuda.synchronize()
+        native.check_status()
+        ref = x.float() @ (w.float() if b_mn else w.float().t())
+        assert _rel(out, ref[:rows]) < 1e-2
+        assert (out.float() - ref[:rows]).abs().max().item() < 0.05 * ref.abs().max().item()
+    # bias and residual are added where the per-rank partial products are summed
+    bias = torch.randn(N if not b_mn else w.shape[1], device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(rows, bias.numel(), device="cuda", dtype=torch.bfloat16)
+    out = fused_tp._gemm_rs(ctx, x, w, b_mn, bias=bias, residual=res)
     torch.cuda.synchronize()
     native.check_status()
-    ref = x.float() @ (w.float() if b_mn else w.float().t())
-    assert _rel(out, ref[:rows]) < 1e-2
+    assert _rel(out, ref[:rows] + bias.float() + res.float()) < 1e-2
 
 
 @pytest.mark.parametrize("b_mn", [False, True])
@@ -106,33 +119,51 @@ def _worker(rank, world, port, ret):
         x_shard = torch.randn(T // world, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
         w1 = (torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_(True)
         w2 = (torch.randn(K, N, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_(True)
+        # the row-parallel bias lives on the first rank only; the residual is this rank's token shard
+        b2 = (torch.randn(K, device="cuda", dtype=torch.bfloat16) * 0.5).requires_grad_(True) if rank == 0 else None
+        res = torch.randn(T // world, K, device="cuda", dtype=torch.bfloat16, requires_grad=True)
         errs = {}
-        for it in range(2):
+        firsts = None
+        for it in range(3):
             # fused: column-parallel then row-parallel, as in an MLP
             h = fused_tp.ag_linear(x_shard, w1, None, tp)
-            y = fused_tp.linear_rs(h, w2, None, tp)
+            y = fused_tp.linear_rs(h, w2, b2, tp, residual=res)
             gy = torch.ones_like(y) * 0.01
-            gx, gw1, gw2 = torch.autograd.grad(y, (x_shard, w1, w2), gy)
+            gx, gw1, gw2, gres = torch.autograd.grad(y, (x_shard, w1, w2, res), gy)
             # reference: NCCL collectives + plain linears
             xr = dist_ops.all_gather(x_shard, g)
             hr = F.linear(xr, w1)
-            yr = dist_ops.reduce_scatter(F.linear(hr, w2), g)
+            yr = dist_ops.reduce_scatter(F.linear(hr, w2, b2), g) + res
             gxr, gw1r, gw2r = torch.autograd.grad(yr, (x_shard, w1, w2), gy)
             torch.cuda.synchronize()
             native.check_status()
-            errs = {"y": _rel(y, yr), "gx": _rel(gx, gxr), "gw1": _rel(gw1, gw1r), "gw2": _rel(gw2, gw2r)}
+            errs = {"y": _rel(y, yr), "gx": _rel(gx, gxr), "gw1": _rel(gw1, gw1r), "gw2": _rel(gw2, gw2r),
+                    "gres": _rel(gres, gy), "max_y": (y.float() - yr.float()).abs().max().item()}
+            # the same inputs give the same bits on every launch, whatever order the peers' tiles arrive in
+            if firsts is None:
+                firsts = (y.clone(), gx.clone())
+            else:
+                errs["repeat"] = float(not (torch.equal(y, firsts[0]) and torch.equal(gx, firsts[1])))
         ret[rank] = errs
     finally:
         dist.destroy_process_group()
 
 
-def test_two_gpus_match_nccl_path():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4])
+def test_multi_gpu_matches_nccl_path(world):
+    """Column-parallel + row-parallel linear (bias on the first rank, residual) forward and backward
+    on 2 and on 4 GPUs against the NCCL collectives around plain linears, three launches in a row
+    (the slot sets alternate), with bit-equal results from launch to launch."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
     port = free_port()
-    mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
-    for r in range(2):
+    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    for r in range(world):
+        assert ret[r]["repeat"] == 0.0, (r, "results differ between launches")
         for k, v in ret[r].items():
-            assert v < 2e-2, (r, k, v)
+            if k == "max_y":
+                assert v < 0.1, (r, k, v)
+            else:
+                assert v < 2e-2, (r, k, v)

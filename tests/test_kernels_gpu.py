@@ -183,8 +183,6 @@ def test_norm_fwd_bwd(h, rms):
         assert _rel_err(b.grad, br.grad) < 2e-2
 
 
-@pytest.mark.skipif(os.environ.get("MIST_B200_UNVALIDATED_KERNELS") != "1",
-                    reason="norm variants (warp-per-row forward, prefetching backward): opt-in until checked on a device")
 @pytest.mark.parametrize("h", [1024, 2048, 2560])
 @pytest.mark.parametrize("rms", [False, True])
 def test_norm_variants_match_the_default_kernels(h, rms):
