@@ -198,7 +198,8 @@ def main(argv=None) -> int:
         e1.record()
         sync()
         record["e2e_ms"] = max(e0.elapsed_time(e1), (time.perf_counter() - wall) * 1e3)
-        lat = [record["dev_ms"] / 1e3 / args.steps] * max(args.steps, 1)
+        import numpy as np
+        lat = np.array([record["dev_ms"] / 1e3 / args.steps] * max(args.steps, 1))
         return lat, ([record["alloc"]], [torch.cuda.max_memory_reserved() / 2 ** 20])
     ref.benchmark_func_walltime = timed
 

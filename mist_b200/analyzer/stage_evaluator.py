@@ -107,6 +107,15 @@ class LayerNumbers:
     output_bytes: float
     weight_bytes: float
     params: float
+    first_gemm_fwd: float = 0.0      # forward seconds of the block's first GEMM (the one a fused weight gather rides on)
+
+
+def fused_time(compute, comm, kappa: float, tau: float):
+    """Seconds of a kernel that overlaps a GEMM with its collective tile by tile: the longer of the two,
+    plus the share ``kappa`` of the shorter one that is not hidden, plus a fixed cost ``tau`` (flag rounds,
+    the pass that sums the partial products).  ``kappa`` and ``tau`` are fitted to timings of the fused
+    kernels on real peers (``fused_overlap`` in the operator database's ``_meta.json``)."""
+    return np.maximum(compute, comm) + kappa * np.minimum(compute, comm) + tau
 
 
 class StageEvaluator:
@@ -118,6 +127,18 @@ class StageEvaluator:
         self._analysis: Dict[int, ModelAnalysis] = {}
         self._numbers: Dict[Tuple[int, int, str], LayerNumbers] = {}
         self._b = sp.Symbol("b", integer=True, positive=True)
+        # Which collectives run on the fused kernels ("auto" = wherever the executor would use them: groups
+        # inside one node).  The analyzer then prices a sequence-parallel linear together with the
+        # collective next to it (reference: the collectives attached to an operator are priced inside
+        # its spec, mist/node_database/node_spec.py:249-320).
+        one_node_tp = True      # tensor-parallel groups never leave a node (the search space enforces it)
+        tpb = str(cfg.get("tp_backend", "auto"))
+        self.tp_fused = (tpb == "fused") or (tpb == "auto" and one_node_tp and bool(cfg.get("sequence_parallel", False))
+                                             and str(self.hw.gpu_type or "").upper().find("B200") >= 0)
+        z3 = str(cfg.get("zero3_gather", "auto"))
+        self.zero3_fused = (z3 == "fused") or (z3 == "auto" and self.hw.num_nodes == 1
+                                               and str(self.hw.gpu_type or "").upper().find("B200") >= 0)
+        self.fused_overlap = dict(getattr(self.db, "fused_overlap", {}) or {})
 
     # ------------------------------------------------------------------------- analysis
     def analysis(self, tp: int) -> ModelAnalysis:
@@ -137,26 +158,60 @@ class StageEvaluator:
         info: LayerInfo = self.analysis(tp).layer(which)
         ef = eb = 0.0
         tpf = tpb = 0.0
-        for n in info.nodes:
-            fl_f, fl_b = self._val(n.flops_fwd, b), self._val(n.flops_bwd, b)
-            by_f, by_b = self._val(n.bytes_fwd, b), self._val(n.bytes_bwd, b)
+        first_gemm = 0.0
+
+        def comm_t(comm) -> float:
+            return float(comm_model.gpu_gpu_latency(comm.kind, np.array([self._val(comm.nbytes, b) / 1e9]), tp, 1,
+                                                    self.hw.gpu_gpu_comm_params)[0])
+
+        nodes = list(info.nodes)
+        lat = {}
+        for k, n in enumerate(nodes):
             if n.comm_fwd is None and n.comm_bwd is None:
                 spec = NodeSpec.from_dict(n.spec, {"b": b})
-                f, w = self.db.latency(spec, fl_f, fl_b, by_f, by_b)
-                ef += f
-                eb += w
+                lat[k] = self.db.latency(spec, self._val(n.flops_fwd, b), self._val(n.flops_bwd, b),
+                                         self._val(n.bytes_fwd, b), self._val(n.bytes_bwd, b))
+                if n.spec.get("op") == "linear" and first_gemm == 0.0:
+                    first_gemm = lat[k][0]
+        fused_with = {}
+        if self.tp_fused and tp > 1:
+            # all-gather directly before a linear, reduce-scatter directly after one: one kernel each
+            for k, n in enumerate(nodes):
+                if n.comm_fwd is None or n.comm_fwd.kind not in ("all_gather", "reduce_scatter"):
+                    continue
+                j = k + 1 if n.comm_fwd.kind == "all_gather" else k - 1
+                if 0 <= j < len(nodes) and j in lat and nodes[j].spec.get("op") == "linear" and j not in fused_with.values():
+                    fused_with[k] = j
+        ag = self.fused_overlap.get("ag_gemm", {"kappa": 1.0, "tau": 0.0})
+        rs = self.fused_overlap.get("gemm_rs", {"kappa": 1.0, "tau": 0.0})
+        done = set()
+        for k, j in fused_with.items():
+            n = nodes[k]
+            f, w = lat[j]
+            fo = ag if n.comm_fwd.kind == "all_gather" else rs          # forward kernel of this pair
+            bo = rs if n.comm_fwd.kind == "all_gather" else ag          # backward: the roles swap
+            ef += float(fused_time(f, comm_t(n.comm_fwd), fo["kappa"], fo["tau"]))
+            # backward: the input-gradient GEMM (half of the linear's backward) carries the collective,
+            # the weight-gradient GEMM runs beside it
+            eb += 0.5 * w + float(fused_time(0.5 * w, comm_t(n.comm_bwd) if n.comm_bwd is not None else 0.0,
+                                             bo["kappa"], bo["tau"]))
+            done.update((k, j))
+        for k, n in enumerate(nodes):
+            if k in done:
+                continue
+            if k in lat:
+                ef += lat[k][0]
+                eb += lat[k][1]
             for comm, fwd in ((n.comm_fwd, True), (n.comm_bwd, False)):
                 if comm is None:
                     continue
-                t = float(comm_model.gpu_gpu_latency(comm.kind, np.array([self._val(comm.nbytes, b) / 1e9]), tp, 1,
-                                                     self.hw.gpu_gpu_comm_params)[0])
                 if fwd:
-                    tpf += t
+                    tpf += comm_t(comm)
                 else:
-                    tpb += t
+                    tpb += comm_t(comm)
         num = LayerNumbers(ef, eb, tpf, tpb, self._val(info.fwd.peak, b), self._val(info.bwd.peak, b),
                            self._val(info.fwd.saved, b), self._val(info.input_bytes, b), self._val(info.fwd.output, b),
-                           float(info.weight_bytes), float(info.num_params))
+                           float(info.weight_bytes), float(info.num_params), first_gemm)
         self._numbers[key] = num
         return num
 
@@ -212,7 +267,7 @@ class StageEvaluator:
 
         def gather(which: str) -> Dict[str, np.ndarray]:
             fields = ("exec_fwd", "exec_bwd", "tp_fwd", "tp_bwd", "fwd_peak", "bwd_peak", "saved", "input_bytes",
-                      "output_bytes", "weight_bytes", "params")
+                      "output_bytes", "weight_bytes", "params", "first_gemm_fwd")
             out = {f: np.zeros(N) for f in fields}
             for (t, bb) in set(zip(tp.tolist(), b.tolist())):
                 sel = (tp == t) & (b == bb)
@@ -232,10 +287,21 @@ class StageEvaluator:
             kept = x["input_bytes"] if ckpt else x["saved"]
             shard_params = np.where(u_ore, x["params"] / dp, x["params"])
             opt_bytes = 12.0 * shard_params * u_oo
+            cf = x["exec_fwd"] + x["tp_fwd"]
+            ag_all = np.where(u_wre, self._coll("all_gather", W, dp), 0.0)
+            ag_fwd = ag_all
+            if block and self.zero3_fused and not (self.tp_fused and np.any(tp > 1)):
+                # forward pass: the gather rides on the block's first GEMM instead of running one block ahead
+                zo = self.fused_overlap.get("zero3_gather", {"kappa": 1.0, "tau": 0.0})
+                g1 = x["first_gemm_fwd"]
+                fused = fused_time(g1, ag_all, zo["kappa"], zo["tau"])
+                plain = u_wre & (u_wo == 0) & (g1 > 0)
+                cf = np.where(plain, cf - g1 + fused, cf)
+                ag_fwd = np.where(plain, 0.0, ag_all)
             return dict(
-                cf=x["exec_fwd"] + x["tp_fwd"],
+                cf=cf, ag_fwd=ag_fwd,
                 cb=x["exec_bwd"] + x["tp_bwd"] + ((x["exec_fwd"] + x["tp_fwd"]) if ckpt else 0.0),
-                ag=np.where(u_wre, self._coll("all_gather", W, dp), 0.0),
+                ag=ag_all,
                 rs=np.where(u_gre, self._coll("reduce_scatter", W, dp), 0.0),
                 # only at the last micro batch: the reduction that waited for it, the refresh of the
                 # other ranks' weights after the step, the optimizer kernel and the optimizer-state copies
@@ -268,7 +334,7 @@ class StageEvaluator:
             key = ("f", u, nxt)
             if key not in memo:
                 me, nx = kinds[u], (kinds[nxt] if nxt else none)
-                memo[key] = self._interf(me["cf"], nx["ag"], nx["h2d_w"], me["d2h_a"])
+                memo[key] = self._interf(me["cf"], nx["ag_fwd"], nx["h2d_w"], me["d2h_a"])
             return memo[key]
 
         def bwd_unit(u: str, nxt: Optional[str], prv: Optional[str], last: bool) -> np.ndarray:
@@ -293,7 +359,7 @@ class StageEvaluator:
         fwd = sum((fwd_unit(seq[i], seq[i + 1] if i + 1 < n else None) for i in range(n)), zeros)
         first_block = next((k for k in seq if k in ("b0", "b1")), None)
         if first_block is not None:
-            fwd = fwd + kinds[first_block]["ag"] + kinds[first_block]["h2d_w"]     # nothing computes while it arrives
+            fwd = fwd + kinds[first_block]["ag_fwd"] + kinds[first_block]["h2d_w"]     # nothing computes while it arrives
         bwd = sum((bwd_unit(seq[i], seq[i + 1] if i + 1 < n else None, seq[i - 1] if i > 0 else None, False)
                    for i in range(n)), zeros)
         bwd_last = sum((bwd_unit(seq[i], seq[i + 1] if i + 1 < n else None, seq[i - 1] if i > 0 else None, True)

@@ -284,14 +284,26 @@ p2p_all_gather_kernel(const GatherArgs a) {
   if (ok) {
     const size_t nvec = a.shard_bytes >> 4;
     const size_t total = nvec * R;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-      // start with the next rank's shard so the ranks do not all read the same peer at once
-      const size_t k = i / nvec;
-      const int r = static_cast<int>((a.me + 1 + k) % R);
-      const size_t j = i - k * nvec;
-      uint4 v = ld_peer16(reinterpret_cast<const uint4*>(a.src.p[r]) + j);
-      reinterpret_cast<uint4*>(a.dst)[static_cast<size_t>(r) * nvec + j] = v;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    constexpr int U = 4;      // loads a thread issues before it stores any of them (NVLink latency is microseconds)
+    for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * U) {
+      uint4 v[U];
+      size_t dsti[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t i = i0 + u * stride;
+        if (i < total) {
+          // start with the next rank's shard so the ranks do not all read the same peer at once
+          const size_t k = i / nvec;
+          const int r = static_cast<int>((a.me + 1 + k) % R);
+          const size_t j = i - k * nvec;
+          v[u] = ld_peer16(reinterpret_cast<const uint4*>(a.src.p[r]) + j);
+          dsti[u] = static_cast<size_t>(r) * nvec + j;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < total) reinterpret_cast<uint4*>(a.dst)[dsti[u]] = v[u];
     }
   }
   __threadfence_system();

@@ -55,6 +55,7 @@ class OpDatabase:
         # bench.py samples during its timed region).  Entries without a recorded clock fall back to the
         # fixed ``sustained_scale`` of the file.
         self.sustained_scale, self.scaled_ops, self.sm_mhz_under_load = 1.0, (), None
+        self.fused_overlap = {}
         meta = self.dir / "_meta.json"
         if meta.exists():
             try:
@@ -64,6 +65,8 @@ class OpDatabase:
                 self.scaled_ops = tuple(m.get("scaled_ops", ()))
                 if m.get("sm_mhz_under_load"):
                     self.sm_mhz_under_load = float(m["sm_mhz_under_load"])
+                # overlap of the fused GEMM + collective kernels: {"ag_gemm": {"kappa", "tau"}, ...}
+                self.fused_overlap = dict(m.get("fused_overlap", {}))
             except (json.JSONDecodeError, OSError, ValueError):
                 pass
         self.hits = self.misses = self.profiled = 0

@@ -7,7 +7,11 @@ receive backward" / "send backward, receive forward"), in the same order on both
 neighbours, because NCCL executes a rank's p2p calls towards one peer in issue order.
 The calls are ordered against the compute stream by NCCL's own events, so the host
 never blocks (the reference follows every p2p call with a device-wide
-``torch.cuda.synchronize()``, schedules.py:506-657).
+``torch.cuda.synchronize()``, schedules.py:506-657).  The compute stream waits for a
+transfer only where it consumes what was received: a step that only sends (the
+activations of the warm-up forwards, the gradients of the cool-down backwards) is left
+in flight behind the next forward / backward pass, its payload kept alive until the next
+p2p step, where the stream joins it before anything else is posted.
 
 Stage boundary tensor: a stage hands on ``hidden + residual`` as one ``[b, s, h]`` tensor
 (one add), and the next stage starts with ``residual = None``; this is the same math as
@@ -57,13 +61,15 @@ class P2PHandler:
         if (tag, peer) in self._meta:
             return
         meta = torch.tensor(encode_meta(t), dtype=torch.int64, device=self.device)
-        dist.send(meta, peer)
+        for r in dist.batch_isend_irecv([dist.P2POp(dist.isend, meta, peer)]):
+            r.wait()
         self._meta[(tag, peer)] = (tuple(t.shape), t.dtype, t.requires_grad)
 
     def _exchange_meta_recv(self, peer: int, tag: str):
         if (tag, peer) not in self._meta:
             meta = torch.empty(META_LEN, dtype=torch.int64, device=self.device)
-            dist.recv(meta, peer)
+            for r in dist.batch_isend_irecv([dist.P2POp(dist.irecv, meta, peer)]):
+                r.wait()
             self._meta[(tag, peer)] = decode_meta(meta.tolist())
         return self._meta[(tag, peer)]
 
@@ -114,6 +120,16 @@ class PipelineSchedule:
         self.first, self.last = self.ps.is_first_stage, self.ps.is_last_stage
         S = self.ps.num_stages
         self.num_warmup = min(S - 1 - self.ps.stage, self.G)
+        #: send-only steps still in flight: (requests, payload tensors kept alive until joined)
+        self._sends_in_flight: List[Tuple[list, list]] = []
+        #: set False to wait for every send where it is posted (A/B timing of the overlap)
+        self.overlap_sends = True
+
+    def _join_sends(self):
+        for reqs, _keep in self._sends_in_flight:
+            for r in reqs:
+                r.wait()
+        self._sends_in_flight = []
 
     # ---------------------------------------------------------------------- single steps
     def _forward(self, batch: Optional[Dict], k: int, recv):
@@ -157,6 +173,7 @@ class PipelineSchedule:
         (NCCL runs a rank's p2p calls towards one peer in issue order, so un-paired calls
         on the two sides deadlock).  Returns (received forward input, received gradient)."""
         ps = self.ps
+        self._join_sends()
         ops, keep, slots = [], [], {}
         if send_fwd is not None and not self.last:
             for peer, info in ps.send_next:
@@ -184,8 +201,12 @@ class PipelineSchedule:
                 slots["fwd"].append((info, buf))
                 ops.append(dist.P2POp(dist.irecv, buf, peer))
         if ops:
-            for r in dist.batch_isend_irecv(ops):
-                r.wait()
+            reqs = dist.batch_isend_irecv(ops)
+            if not slots and self.overlap_sends:
+                self._sends_in_flight.append((reqs, keep))     # nothing to consume: let it run behind the next pass
+            else:
+                for r in reqs:
+                    r.wait()
 
         def assemble(parts):
             """Concatenates batch slices in slice order.  Several peers may return the same slice
@@ -244,6 +265,7 @@ class PipelineSchedule:
             _, grad = self._exchange(recv_bwd=True)
             gx = bwd(grad)
             self._exchange(send_bwd=gx)
+        self._join_sends()
         self.engine.flush_tied()
         if self.last:
             return torch.stack(losses).mean()

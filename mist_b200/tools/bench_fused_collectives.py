@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="ag,rs,zero3,dp")
+    ap.add_argument("--only", default="p2p,ag,rs,zero3,dp")
     ap.add_argument("--tflops", type=float, default=1601.6)
     ap.add_argument("--link-gbs", type=float, default=770.0)
     ap.add_argument("--hbm-gbs", type=float, default=6544.0)
@@ -69,13 +69,44 @@ def main(argv=None):
 
     rows_out = []
 
-    def report(kind, shape, t_fused, t_lib, flops, link_bytes, extra=""):
+    def report(kind, shape, t_fused, t_lib, flops, link_bytes, extra="", parts=None):
+        """``parts``: (GEMM alone, collective alone) in ms -- what the cost model's overlap terms are fitted to."""
         roof = max(flops / PEAK, link_bytes / LINK) * 1e3
-        rows_out.append(dict(kernel=kind, shape=shape, ranks=world, fused_ms=round(t_fused, 4), library_ms=round(t_lib, 4),
-                             roofline_ms=round(roof, 4), fraction=round(roof / t_fused, 3), note=extra))
+        row = dict(kernel=kind, shape=shape, ranks=world, fused_ms=round(t_fused, 4), library_ms=round(t_lib, 4),
+                   roofline_ms=round(roof, 4), fraction=round(roof / t_fused, 3), note=extra)
+        if parts is not None:
+            row["gemm_ms"], row["collective_ms"] = round(parts[0], 4), round(parts[1], 4)
+        rows_out.append(row)
         if rank == 0:
             print(f"{kind:34s} R{world} {shape:34s} fused {t_fused:7.3f} ms  library {t_lib:7.3f} ms  "
                   f"roofline {roof:6.3f} ms -> {roof / t_fused:4.2f} {extra}", flush=True)
+
+    if "p2p" in only and world > 1:
+        # what SM-issued peer loads reach on this box, per grid size, beside NCCL's all-gather: the link rate
+        # that the kernels below can hope for (the roofline's 770 GB/s is a copy-engine figure)
+        shard = 64 << 20
+        heap = SymmetricHeap(shard + (4 << 20), g)
+        src, soff = heap.alloc(shard // 2, torch.bfloat16)
+        flags, foff = heap.alloc(32, torch.int32)
+        dst = torch.empty(world * shard // 2, dtype=torch.bfloat16, device="cuda")
+        st, ft = ptr_table(heap.peer_ptrs(soff)), ptr_table(heap.peer_ptrs(foff))
+        ep = [0]
+        torch.cuda.synchronize()
+        dist.barrier()
+        t_nccl = timeit(lambda: dist.all_gather_into_tensor(dst, src, group=g))
+        inbound = shard * (world - 1)
+        for ctas in (32, 64, 128, 148):
+            def gather():
+                ep[0] += 1
+                call("mb_p2p_all_gather", st, ptr(dst), ft, shard, world, rank, ep[0], ctas, native.stream())
+            t = timeit(gather)
+            rows_out.append(dict(kernel="peer all-gather (SM loads)", ranks=world, ctas=ctas, fused_ms=round(t, 4),
+                                 library_ms=round(t_nccl, 4), inbound_gbs=round(inbound / t / 1e6, 1),
+                                 nccl_inbound_gbs=round(inbound / t_nccl / 1e6, 1)))
+            if rank == 0:
+                print(f"peer all-gather, 64 MiB per rank, R{world} ctas {ctas:3d}: {t:6.3f} ms = {inbound / t / 1e6:5.0f} GB/s inbound"
+                      f"   (NCCL all-gather {t_nccl:6.3f} ms = {inbound / t_nccl / 1e6:5.0f} GB/s)", flush=True)
+        del heap
 
     # shapes: tokens per micro batch T, model width h, per-rank widths of the four sequence-parallel linears
     if world <= 2:
@@ -96,8 +127,10 @@ def main(argv=None):
                 xf = torch.empty(T, h, device="cuda", dtype=torch.bfloat16)
                 dist.all_gather_into_tensor(xf, x, group=g)
                 return xf @ w.t()
+            xf0 = torch.empty(T, h, device="cuda", dtype=torch.bfloat16)
+            parts = (timeit(lambda: F.gemm(xf0, w)), timeit(lambda: dist.all_gather_into_tensor(xf0, x, group=g)))
             report("AG->GEMM " + name, f"{tag} T{T} K{h} N{N}", t_f, timeit(lib), 2.0 * T * h * N,
-                   T * h * 2 * (world - 1) / world)
+                   T * h * 2 * (world - 1) / world, parts=parts)
     if "rs" in only:
         for K, name in ((h // world, "out_proj"), (ffn, "fc2")):
             x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
@@ -111,11 +144,14 @@ def main(argv=None):
                 return o + res
             link = T * h * 2 * (world - 1) / world
             t_lib = timeit(lib)
+            y0 = torch.empty(T, h, device="cuda", dtype=torch.bfloat16)
+            o0 = torch.empty(T // world, h, device="cuda", dtype=torch.bfloat16)
+            parts = (timeit(lambda: F.gemm(x, w, out=y0)), timeit(lambda: dist.reduce_scatter_tensor(o0, y0, group=g)))
             for form in ("store", "add"):
                 fused_tp.RS_FORM = form
                 t_f = timeit(lambda: fused_tp._gemm_rs(tp, x, w, False, residual=res))
                 report(f"GEMM->RS {name} ({form})", f"{tag} T{T} K{K} N{h}", t_f, t_lib, 2.0 * T * K * h,
-                       link * (2 if (form == "add" and world > 2) else 1), "+residual")
+                       link * (2 if (form == "add" and world > 2) else 1), "+residual", parts=parts)
             fused_tp.RS_FORM = "store"
     if "zero3" in only and world > 1:
         from mist_b200.parallel.fused_zero3 import ParamGatherContext
@@ -135,8 +171,10 @@ def main(argv=None):
             def lib():
                 dist.all_gather_into_tensor(full, shard, group=g)
                 return x @ full[b_off:b_off + 3 * hh * hh].view(3 * hh, hh).t()
+            wq = full[b_off:b_off + 3 * hh * hh].view(3 * hh, hh)
+            parts = (timeit(lambda: F.gemm(x, wq)), timeit(lambda: dist.all_gather_into_tensor(full, shard, group=g)))
             report("ZeRO-3 weight-AG->GEMM", f"{name} M{M} N{3 * hh} K{hh}", timeit(fused), timeit(lib),
-                   2.0 * M * 3 * hh * hh, padded * 2 * (world - 1) / world)
+                   2.0 * M * 3 * hh * hh, padded * 2 * (world - 1) / world, parts=parts)
             del ctx
     if "dp" in only and world > 1:
         # gradient reduce-scatter + Adam + weight write-back of one GPT-3 2.7B block (78.7 M parameters)

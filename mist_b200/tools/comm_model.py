@@ -164,6 +164,36 @@ def fit_interference_params(C, G2G, C2G, G2C, measured, x0: Optional[Sequence[fl
     return [float(v) for v in p]
 
 
+def fit_fused_overlap(rows: List[Dict]) -> Dict[str, Dict[str, float]]:
+    """Fits ``fused = max(gemm, coll) + kappa * min(gemm, coll) + tau`` per kind of fused kernel from the rows
+    that :mod:`mist_b200.tools.bench_fused_collectives` writes (``fused_ms``, ``gemm_ms``, ``collective_ms``).
+    ``kappa`` is kept in [0, 1] (0: the shorter part is hidden completely, 1: nothing overlaps), ``tau`` >= 0.
+    With a single row per kind ``tau`` stays 0."""
+    kinds = {"AG->GEMM": "ag_gemm", "GEMM->RS": "gemm_rs", "ZeRO-3": "zero3_gather"}
+    groups: Dict[str, List[Tuple[float, float, float]]] = {}
+    for r in rows:
+        if "gemm_ms" not in r or "(add)" in r.get("kernel", ""):
+            continue
+        for prefix, key in kinds.items():
+            if r["kernel"].startswith(prefix):
+                groups.setdefault(key, []).append((r["fused_ms"] * 1e-3, r["gemm_ms"] * 1e-3, r["collective_ms"] * 1e-3))
+    out = {}
+    for key, pts in groups.items():
+        f = np.array([p[0] for p in pts])
+        hi = np.array([max(p[1], p[2]) for p in pts])
+        lo = np.array([min(p[1], p[2]) for p in pts])
+        if len(pts) >= 3:
+            A = np.stack([lo, np.ones_like(lo)], axis=1)
+            sol, *_ = np.linalg.lstsq(A, f - hi, rcond=None)
+            kappa, tau = float(sol[0]), float(sol[1])
+        else:
+            kappa, tau = float(np.sum((f - hi) * lo) / max(np.sum(lo * lo), 1e-30)), 0.0
+        if tau < 0:
+            kappa, tau = float(np.sum((f - hi) * lo) / max(np.sum(lo * lo), 1e-30)), 0.0
+        out[key] = {"kappa": round(min(max(kappa, 0.0), 1.5), 4), "tau": round(max(tau, 0.0), 7), "rows": len(pts)}
+    return out
+
+
 def fit_all(records: List[Dict]) -> Dict[str, List[float]]:
     """``records``: output of :mod:`mist_b200.tools.profile_interference` -- dicts with the
     per-channel standalone times ``C``, ``G2G``, ``C2G``, ``G2C``, the concurrent ``latency``,
