@@ -187,7 +187,10 @@ def generate(root: Path = HERE):
                 extra=dict(sequence_parallel=True, model=dict(vocab_size=32000, rotary_emb_fraction=1.0)))
     _experiment(root / "experiment" / "b200-gpt3-13b-pp2-tp4.yaml", "gpt2/13b", b200, _training(128),
                 _strategy([(20, (1, 4), 20, [2, 1, 4, 0, 0, 0, 0, 0, 1.0, 0]),
-                           (20, (1, 4), 20, [2, 1, 4, 0, 0, 0, 0, 0, 1.0, 0])], 64))
+                           (20, (1, 4), 20, [2, 1, 4, 0, 0, 0, 0, 0, 1.0, 0])], 64),
+                # sequence-sharded activations between the tensor-parallel linears: the all-reduce of plain tensor
+                # parallelism becomes all-gather + reduce-scatter, which the fused GEMM + collective kernels run
+                extra=dict(sequence_parallel=True))
     _experiment(root / "experiment" / "b200-gpt3-22b-zero3.yaml", "gpt2/22b", b200, _training(64),
                 _strategy([(48, (1, 8), 0, [8, 8, 1, 1, 1, 1, 0, 0, 0, 0.5])], 1),
                 extra=dict(model=dict(num_attention_heads=48)))

@@ -46,14 +46,16 @@ class OpDatabase:
         self.refresh_unclocked = bool(refresh_unclocked) and self.allow_profile
         self.model = analytic.device_model(self.device)
         self._mem: Dict[str, Dict[str, Dict]] = {}
-        # Entries are timed one operator at a time, in short bursts, and carry the SM clock that was
-        # read while they ran (``sm_mhz``).  A training step keeps the tensor cores busy for seconds
-        # and settles at a lower, power-capped clock; the time of an operator that is bound by the SMs
-        # (tensor cores, exponentials) scales with the inverse of that clock, so such an entry is
-        # multiplied by ``sm_mhz / sm_mhz_under_load``.  ``_meta.json`` beside the entries names the
-        # operators this applies to and the clock measured under a training load (the median that
-        # bench.py samples during its timed region).  Entries without a recorded clock fall back to the
-        # fixed ``sustained_scale`` of the file.
+        # An entry holds two timings of its operator: one cold call on a quiet chip (``fwd`` / ``bwd``,
+        # boost clock, L2 flushed) and a quarter of a second of back-to-back calls (``fwd_sus`` /
+        # ``bwd_sus``) with the SM clock that the chip settled at under that load (``sm_mhz_fwd`` /
+        # ``sm_mhz_bwd``).  A training step keeps the chip at its own power-capped clock; the time of an
+        # operator that is bound by the SMs (tensor cores, exponentials) scales with the inverse of the
+        # clock, so its sustained timing is multiplied by ``sm_mhz / sm_mhz_under_load``.  ``_meta.json``
+        # beside the entries names the operators this applies to and the clock measured under a training
+        # load (the median that bench.py samples during its timed region); nothing in it is fitted to a
+        # training-step time.  Entries without sustained timings fall back to the fixed
+        # ``sustained_scale`` of the file applied to the cold timing.
         self.sustained_scale, self.scaled_ops, self.sm_mhz_under_load = 1.0, (), None
         self.fused_overlap = {}
         meta = self.dir / "_meta.json"
@@ -116,34 +118,48 @@ class OpDatabase:
         entries = self._load(spec.op)
         key = spec.key()
         e = entries.get(key)
-        if e is not None and self.refresh_unclocked and "sm_mhz" not in e and spec.op in self.scaled_ops:
+        if e is not None and self.refresh_unclocked and "fwd_sus" not in e and spec.op in self.scaled_ops:
             e = None
         if e is not None:
             self.hits += 1
-            return float(e["fwd"]) * self._clock_scale(spec.op, e), float(e["bwd"]) * self._clock_scale(spec.op, e)
+            return self._in_step(spec.op, e)
         self.misses += 1
         if self.allow_profile:
             from . import profiler
-            measured = profiler.profile(spec)
+            try:
+                measured = profiler.profile(spec)
+            except RuntimeError as e:      # a launch that the kernels refuse: say which operator, estimate it instead
+                import warnings
+                warnings.warn(f"could not time {spec.key()} on the device ({e}); using the analytic estimate")
+                measured = None
             if measured is not None:
                 self.profiled += 1
                 entry = {"spec": spec.as_dict(), "fwd": measured[0], "bwd": measured[1], "flops_fwd": flops_fwd,
                          "flops_bwd": flops_bwd, "bytes_fwd": bytes_fwd, "bytes_bwd": bytes_bwd}
-                mhz = profiler.median_clock()
-                if mhz:
-                    entry["sm_mhz"] = mhz
+                sus = dict(profiler.last_sustained)
+                if sus.get("fwd") and sus.get("mhz_fwd"):
+                    entry["fwd_sus"], entry["sm_mhz_fwd"] = sus["fwd"], sus["mhz_fwd"]
+                    if sus.get("both") and sus.get("mhz_both"):
+                        # the forward + backward loop ran at its own clock: bring the forward part to that clock
+                        # before taking it out
+                        f_at = sus["fwd"] * sus["mhz_fwd"] / sus["mhz_both"]
+                        entry["bwd_sus"], entry["sm_mhz_bwd"] = max(sus["both"] - f_at, 0.0), sus["mhz_both"]
                 self._store(spec.op, key, entry)
-                return measured[0] * self._clock_scale(spec.op, entry), measured[1] * self._clock_scale(spec.op, entry)
+                return self._in_step(spec.op, entry)
         return analytic.estimate(spec, flops_fwd, flops_bwd, bytes_fwd, bytes_bwd, self.model)
 
-    def _clock_scale(self, op: str, entry: Dict) -> float:
-        """Factor from the entry's profiling conditions to a training step (see ``__init__``)."""
+    def _in_step(self, op: str, e: Dict) -> Tuple[float, float]:
+        """(forward, backward) seconds of an entry under training-step conditions (see ``__init__``)."""
+        fwd, bwd = float(e["fwd"]), float(e["bwd"])
         if op not in self.scaled_ops:
-            return 1.0
-        mhz = entry.get("sm_mhz")
-        if mhz and self.sm_mhz_under_load:
-            return max(1.0, float(mhz) / self.sm_mhz_under_load)
-        return self.sustained_scale
+            return fwd, bwd
+        if self.sm_mhz_under_load and e.get("fwd_sus") and e.get("sm_mhz_fwd"):
+            f = float(e["fwd_sus"]) * float(e["sm_mhz_fwd"]) / self.sm_mhz_under_load
+            b = bwd * self.sustained_scale
+            if e.get("bwd_sus") is not None and e.get("sm_mhz_bwd"):
+                b = float(e["bwd_sus"]) * float(e["sm_mhz_bwd"]) / self.sm_mhz_under_load
+            return f, b
+        return fwd * self.sustained_scale, bwd * self.sustained_scale
 
     def add(self, spec: NodeSpec, fwd: float, bwd: float, **extra):
         self._store(spec.op, spec.key(), dict({"spec": spec.as_dict(), "fwd": fwd, "bwd": bwd}, **extra))

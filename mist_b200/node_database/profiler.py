@@ -18,6 +18,9 @@ import torch
 from .node_spec import NodeSpec
 
 WARMUP, REPEAT = 3, 5
+#: seconds an operator is run back to back for its sustained timing (long enough for the SM clock to
+#: settle under the power cap and for NVML's clock reading to mean something)
+SUSTAIN_S = 0.25
 _flush = None
 _nvml = None
 #: SM clocks (MHz) read while the most recent operator was being timed
@@ -74,14 +77,45 @@ def _time(fn: Callable[[], None]) -> float:
     return ts[len(ts) // 2]
 
 
+#: (sustained forward seconds, sustained forward+backward seconds, median SM MHz) of the last profile() call
+last_sustained = {}
+
+
+def _sustained(fn: Callable[[], None], one: float) -> Tuple[float, Optional[float]]:
+    """Seconds per call of ``fn`` run back to back for about SUSTAIN_S, and the median SM clock over the
+    second half of that time.  A single cold call says how long the kernel takes at boost clock on a quiet
+    chip; inside a training step the chip sits at its power-capped clock, which this loop reproduces."""
+    reps = int(min(max(SUSTAIN_S / max(one, 1e-6), 3), 4000))
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    clocks = []
+    import time
+    t0 = time.perf_counter()
+    while not b.query():
+        mhz = _sm_mhz() if _nvml is not False else None
+        if mhz and time.perf_counter() - t0 > 0.4 * reps * one:
+            clocks.append(mhz)
+        time.sleep(0.01)
+    torch.cuda.synchronize()
+    per = a.elapsed_time(b) * 1e-3 / reps
+    clocks.sort()
+    return per, (clocks[len(clocks) // 2] if clocks else None)
+
+
 def _fwd_bwd(make_inputs, op) -> Tuple[float, float]:
     """Times ``op(*inputs)`` and the backward of its first output."""
     inputs = make_inputs()
     out = op(*inputs)
     first = out[0] if isinstance(out, (tuple, list)) else out
     g = torch.randn_like(first) if first.dtype.is_floating_point else None
+    last_sustained.clear()
     with torch.no_grad():
-        fwd = _time(lambda: op(*[t.detach() if isinstance(t, torch.Tensor) else t for t in inputs]))
+        det = [t.detach() if isinstance(t, torch.Tensor) else t for t in inputs]
+        fwd = _time(lambda: op(*det))
+        last_sustained["fwd"], last_sustained["mhz_fwd"] = _sustained(lambda: op(*det), fwd)
     if g is None or not first.requires_grad:
         return fwd, 0.0
     leaves = [t for t in inputs if isinstance(t, torch.Tensor) and t.requires_grad]
@@ -92,6 +126,7 @@ def _fwd_bwd(make_inputs, op) -> Tuple[float, float]:
         torch.autograd.grad(o0, leaves, g, allow_unused=True)
 
     total = _time(both)
+    last_sustained["both"], last_sustained["mhz_both"] = _sustained(both, total)
     return fwd, max(total - fwd, 0.0)
 
 
@@ -101,6 +136,7 @@ def profile(spec: NodeSpec, dtype=torch.bfloat16) -> Optional[Tuple[float, float
     op = spec.op
     g = spec.get
     del clock_samples[:]
+    last_sustained.clear()
 
     def rnd(*shape, grad=True, scale=1.0):
         return (torch.randn(*shape, device=dev, dtype=dtype) * scale).requires_grad_(grad)

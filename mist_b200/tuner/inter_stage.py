@@ -23,7 +23,7 @@ from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 
-from ..analyzer.stage_evaluator import StageEvaluator
+from ..analyzer.stage_evaluator import StageEvaluator, ties_across_stages
 from ..config import MistConfig
 from ..ops import native
 from .candidates import device_mesh_candidates, grad_accum_candidates, stage_count_candidates
@@ -192,13 +192,31 @@ def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache
     return best_cost, best_sol
 
 
+def _prune_dominated(labels: List[Tuple]) -> List[Tuple]:
+    """Keeps the labels ``(sum T, max T, exposed delta, path)`` that no other label beats in all three
+    numbers.  The iteration time ``(G - 1) max T + sum T + max(exposed, 0)`` grows with each of them, and
+    appending a stage adds the same amounts to every label of a state, so a dominated label can never
+    end up in the best complete pipeline: the search stays exact."""
+    labels = sorted(labels, key=lambda x: (x[0], x[1], x[2]))
+    kept: List[Tuple] = []
+    for lab in labels:
+        if not any(k[0] <= lab[0] and k[1] <= lab[1] and k[2] <= lab[2] for k in kept):
+            kept.append(lab)
+    return kept
+
+
 def _inter_stage_tune_nonuniform(cfg, ev, cache_dir, tp):
-    """Stages may differ in device count: DP over (layers assigned, devices used) keeping the best
-    (sum T, max T, exposed delta) summary per state for a fixed G; scans G outside."""
+    """Stages may differ in device count: dynamic program over (stage, layers assigned, devices used
+    [, layout of the first stage]) that keeps every non-dominated (sum T, max T, exposed delta) summary
+    per state for a fixed G; G is scanned outside (reference: the ``inter-stage`` dynamic program of
+    mist/analyzer/inter_tuning.py:222-355).  Models that tie a table across the first and the last
+    stage carry the first stage's dp x tp layout in the state, and the last stage only takes
+    strategies with that layout (the executor pairs the ranks of the two stages)."""
     hw = cfg.hardware
     L = cfg.model.num_hidden_layers
     meshes = [m for m in device_mesh_candidates(hw.num_nodes, hw.num_gpus_per_node)]
     total_dev = hw.num_devices
+    tied = ties_across_stages(cfg)
     best_cost, best_sol = math.inf, None
     max_stages = min(total_dev, L, 8)
     for g in grad_accum_candidates(cfg.training.global_batch_size):
@@ -208,12 +226,12 @@ def _inter_stage_tune_nonuniform(cfg, ev, cache_dir, tp):
             lc = {(tuple(m), k): counts for m in meshes for k in kinds}
             intra = intra_stage_tune(cfg, ev, grad_accums=[g], meshes=meshes, layer_counts=lc, tp=tp,
                                      cache_dir=cache_dir, num_stages_for_mesh=lambda m, S=S: S)
-            # state: (stage, layers used, devices used) -> list of (sumT, maxT, worst, path)
-            states = {(0, 0, 0): [(0.0, 0.0, -math.inf, [])]}
+            # state: (layers used, devices used, layout of the first stage or None) -> labels
+            states: Dict = {(0, 0, None): [(0.0, 0.0, -math.inf, [])]}
             for s in range(S):
                 k = 3 if S == 1 else (0 if s == 0 else (2 if s == S - 1 else 1))
                 nxt: Dict = {}
-                for (ss, used, dev), labels in states.items():
+                for (used, dev, first_layout), labels in states.items():
                     for m in meshes:
                         nd = m[0] * m[1]
                         if dev + nd > total_dev or (total_dev - dev - nd) < (S - 1 - s):
@@ -222,20 +240,26 @@ def _inter_stage_tune_nonuniform(cfg, ev, cache_dir, tp):
                             if used + l > L or (L - used - l) < (S - 1 - s):
                                 continue
                             for pi, p in enumerate(intra.get(g, tuple(m), k, l)):
+                                layout = (int(p.vector[1]), int(p.vector[2]))
+                                if tied and S > 1:
+                                    if s == S - 1 and layout != first_layout:
+                                        continue
+                                    key_layout = layout if s == 0 else first_layout
+                                else:
+                                    key_layout = None
+                                key = (used + l, dev + nd, key_layout)
+                                cur = nxt.setdefault(key, [])
                                 for (sumT, maxT, worst, path) in labels:
-                                    lab = (sumT + p.stable, max(maxT, p.stable), max(worst, p.delta - sumT),
-                                           path + [(((used, used + l - 1), tuple(m), p.num_ckpt, pi), p.vector)])
-                                    key = (s + 1, used + l, dev + nd)
-                                    cur = nxt.setdefault(key, [])
-                                    cur.append(lab)
-                                    if len(cur) > 16:
-                                        cur.sort(key=lambda x: (g - 1) * x[1] + x[0] + max(x[2], 0.0))
-                                        del cur[8:]
-                states = nxt
-            for lab in states.get((S, L, total_dev), []):
-                cost = (g - 1) * lab[1] + lab[0] + max(lab[2], 0.0)
-                if cost < best_cost:
-                    best_cost, best_sol = cost, [g, lab[3]]
+                                    cur.append((sumT + p.stable, max(maxT, p.stable), max(worst, p.delta - sumT),
+                                                path + [(((used, used + l - 1), tuple(m), p.num_ckpt, pi), p.vector)]))
+                states = {key: _prune_dominated(labels) for key, labels in nxt.items()}
+            for (used, dev, _), labels in states.items():
+                if used != L or dev != total_dev:
+                    continue
+                for lab in labels:
+                    cost = (g - 1) * lab[1] + lab[0] + max(lab[2], 0.0)
+                    if cost < best_cost:
+                        best_cost, best_sol = cost, [g, lab[3]]
     return best_cost, best_sol
 
 

@@ -317,3 +317,35 @@ def test_encoder_decoder_blocks_are_priced_apart(monkeypatch):
                                      f"strategy.pre_post_strategy_array={vec}"], check_world_size=False)
     res = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))
     assert res["stable"][0] < res["stable"][1]
+
+
+def test_nondominated_pruning_keeps_every_possible_winner():
+    """The inter-stage dynamic program drops a partial pipeline only when another one of the same state is
+    no worse in all three numbers the iteration time is built from."""
+    from mist_b200.tuner.inter_stage import _prune_dominated
+    labels = [(1.0, 0.5, 0.1, "a"), (1.0, 0.5, 0.2, "dominated by a"), (0.9, 0.6, 0.1, "b"), (1.2, 0.4, 0.0, "c"),
+              (1.3, 0.6, 0.3, "dominated by all"), (0.9, 0.6, 0.1, "duplicate of b")]
+    kept = {x[3] for x in _prune_dominated(labels)}
+    assert kept == {"a", "b", "c"} or kept == {"a", "duplicate of b", "c"}
+    # every label that wins for some gradient-accumulation count survives
+    for g in (1, 2, 8, 64):
+        best = min(labels, key=lambda x: (g - 1) * x[1] + x[0] + max(x[2], 0.0))
+        cost = (g - 1) * best[1] + best[0] + max(best[2], 0.0)
+        assert any(abs((g - 1) * k[1] + k[0] + max(k[2], 0.0) - cost) < 1e-12 for k in _prune_dominated(labels))
+
+
+def test_inter_stage_search_respects_tied_table_layout(tmp_path, monkeypatch):
+    """A model that ties its output projection to the word table needs the same dp x tp layout on the first and
+    the last pipeline stage; the non-uniform search must only return such pipelines."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_L4")
+    cfg, _ = load_config("test-small-base", ["model.num_hidden_layers=8", "model.tie_word_embeddings=true",
+                                             "hardware.num_gpus_per_node=4", "training.global_batch_size=16",
+                                             "strategy.enabled=false", "tuning.tuning_granularity=inter-stage",
+                                             "tuning.sample_size=6", "hardware.memory_capacity=8.0"],
+                         check_world_size=False)
+    cost, sol = inter_stage_tune(cfg, StageEvaluator(cfg, OpDatabase(allow_profile=False)), cache_dir=str(tmp_path))
+    assert sol is not None and cost < float("inf")
+    stages = sol[1]
+    if len(stages) > 1:
+        first, last = stages[0][1], stages[-1][1]
+        assert (int(first[1]), int(first[2])) == (int(last[1]), int(last[2]))
