@@ -92,8 +92,9 @@ class TrainingSession:
                     dist.broadcast(p.data, src=src, group=self.ps.tp_group)
         # dropout masks of replicated activations must agree over the tensor-parallel group; where the
         # tokens are sharded (sequence parallelism) every rank adds its own offset to the drawn seeds
-        _F.Settings.dropout_generator = torch.Generator()
-        _F.Settings.dropout_generator.manual_seed(seed + 17 * stage + 7919 * self.ps.dp_rank)
+        # (the seeds of dropout calls come from torch's CPU generator: from here on it is the same on every
+        # rank of a tensor-parallel group and differs between data-parallel replicas)
+        torch.manual_seed(seed + 17 * stage + 7919 * self.ps.dp_rank)
         _F.Settings.dropout_seed_offset = 104729 * self.ps.tp_rank if self.sequence_parallel else 0
         # a table tied across the first and the last stage: pair the ranks and copy it over once
         tied_group = None

@@ -40,6 +40,8 @@ struct BwdParams {
   int sq, sk, nh, d, nchunks;
   float scale, scale_log2;
   int causal;
+  const int* seqlens_q;   // per-sample token counts of a right-padded batch, or null
+  const int* seqlens_k;
   int* status;
 };
 
@@ -90,9 +92,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int jb = blockIdx.x;
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
+  // real tokens of this sample (right-padded batches); the tensors keep their padded extents p.sq / p.sk
+  const int sq_b = p.seqlens_q ? min(p.sq, p.seqlens_q[batch]) : p.sq;
+  const int sk_b = p.seqlens_k ? min(p.sk, p.seqlens_k[batch]) : p.sk;
   const int kv0 = jb * BKV;
-  const int coff = p.sk - p.sq;
-  const int nq_blocks = (p.sq + BQ - 1) / BQ;
+  const int coff = sk_b - sq_b;
+  const int nq_blocks = (sq_b + BQ - 1) / BQ;
   int i_start = 0;
   if (p.causal) {
     int first_q = kv0 - coff;  // first query row that can see key kv0
@@ -257,7 +262,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // per-block vectors: thread t < 64 stages lse, 64 <= t < 128 stages delta
     auto fetch_vec = [&](int it) -> float {
       const int q = (i_start + it) * BQ + (threadIdx.x & 63);
-      if (threadIdx.x >= 128 || q >= p.sq) return 0.f;
+      if (threadIdx.x >= 128 || q >= sq_b) return 0.f;
       return threadIdx.x < 64 ? p.lse[row_base + q] * 1.4426950408889634f : p.delta[row_base + q];
     };
     auto stash_vec = [&](int buf, float v) {
@@ -285,12 +290,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_wait();
         // Only blocks on the diagonal or at the end of the queries / keys need the mask (the test
         // is uniform over the CTA): the others take the shorter loop.
-        const bool need_mask = (q0 + BQ > p.sq) || (kv_last >= p.sk) || (p.causal && kv_last > q0 + coff);
+        const bool need_mask = (q0 + BQ > sq_b) || (kv_last >= sk_b) || (p.causal && kv_last > q0 + coff);
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int qi = q0 + c0 + c;
-            const bool valid = (qi < p.sq) && (kv_idx < p.sk) && (!p.causal || kv_idx <= qi + coff);
+            const bool valid = (qi < sq_b) && (kv_idx < sk_b) && (!p.causal || kv_idx <= qi + coff);
             const float e = mb::fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -s_lse[vb * BQ + c0 + c]));
             pf[c] = valid ? e : 0.f;
           }
@@ -489,9 +494,12 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int jb = blockIdx.x;
   const int head = blockIdx.y;
   const int batch = blockIdx.z;
+  // real tokens of this sample (right-padded batches); the tensors keep their padded extents p.sq / p.sk
+  const int sq_b = p.seqlens_q ? min(p.sq, p.seqlens_q[batch]) : p.sq;
+  const int sk_b = p.seqlens_k ? min(p.sk, p.seqlens_k[batch]) : p.sk;
   const int kv0 = jb * BKV;
-  const int coff = p.sk - p.sq;
-  const int nq_blocks = (p.sq + BQ - 1) / BQ;
+  const int coff = sk_b - sq_b;
+  const int nq_blocks = (sq_b + BQ - 1) / BQ;
   int i_start = 0;
   if (p.causal) {
     int first_q = kv0 - coff;
@@ -705,7 +713,7 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     auto fetch_vec = [&](int it) -> float {
       const int q = (i_start + it) * BQ + (threadIdx.x & 63);
-      if (threadIdx.x >= 128 || q >= p.sq) return 0.f;
+      if (threadIdx.x >= 128 || q >= sq_b) return 0.f;
       return threadIdx.x < 64 ? p.lse[row_base + q] * 1.4426950408889634f : p.delta[row_base + q];
     };
     auto stash_vec = [&](int buf, float v) {
@@ -731,12 +739,12 @@ attn_bwd_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         uint32_t sr[32];
         tmem_ld32(t_s + vb * BQ + c0 + lane_off, sr);
         tmem_ld_wait();
-        const bool need_mask = (q0 + BQ > p.sq) || (kv_last >= p.sk) || (p.causal && kv_last > q0 + coff);
+        const bool need_mask = (q0 + BQ > sq_b) || (kv_last >= sk_b) || (p.causal && kv_last > q0 + coff);
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int qi = q0 + c0 + c;
-            const bool valid = (qi < p.sq) && (kv_idx < p.sk) && (!p.causal || kv_idx <= qi + coff);
+            const bool valid = (qi < sq_b) && (kv_idx < sk_b) && (!p.causal || kv_idx <= qi + coff);
             const float e = mb::fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -s_lse[vb * BQ + c0 + c]));
             pf[c] = valid ? e : 0.f;
           }
@@ -929,13 +937,15 @@ MB_API int mb_attn_bwd_last_variant() { return g_bwd_last_variant; }
 
 // dout, o: [b][sq][nh][d] with the given element strides for dout (o is contiguous);
 // delta: [b][nh][sq] fp32 scratch; dq_acc: [b][nh][sq][d] fp32 scratch, zeroed by this call.
-// q/k/v and dq/dk/dv may be strided views (packed qkv).  Requires nh_kv == nh.
+// q/k/v and dq/dk/dv may be strided views (packed qkv).  Requires nh_kv == nh.  seqlens_q / seqlens_k:
+// optional device arrays of `batch` ints (real tokens per sample of a right-padded batch, as in the forward
+// pass): padded queries and keys take no part, their gradient rows are zeros.
 MB_API int mb_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o,
                        const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int batch,
                        int sq, int sk, int nh, int d, long q_bs, long q_ts, long q_hs, long k_bs, long k_ts,
                        long k_hs, long v_bs, long v_ts, long v_hs, long dq_bs, long dq_ts, long dq_hs,
                        long dk_bs, long dk_ts, long dk_hs, long dv_bs, long dv_ts, long dv_hs, float scale,
-                       int causal, cudaStream_t stream) {
+                       int causal, const int* seqlens_q, const int* seqlens_k, cudaStream_t stream) {
   if (d % 16 || d > 128 || d < 16) return -1;
   if ((q_bs | q_ts | q_hs | k_bs | k_ts | k_hs | v_bs | v_ts | v_hs | dq_bs | dq_ts | dq_hs | dk_bs | dk_ts |
        dk_hs | dv_bs | dv_ts | dv_hs) & 7)
@@ -968,6 +978,8 @@ MB_API int mb_attn_bwd(const void* dout, const void* q, const void* k, const voi
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
+  p.seqlens_q = seqlens_q;
+  p.seqlens_k = seqlens_k;
   p.status = mb_status_device_ptr();
   dim3 grid((sk + BKV - 1) / BKV, nh, batch);
   if (g_bwd_variant == 1) {

@@ -34,6 +34,10 @@ struct AttnParams {
   long o_batch_stride, o_tok_stride, o_head_stride;
   float scale_log2;
   int causal;
+  // per-sample lengths of a right-padded batch (null: every sample has sq / sk tokens): queries and keys
+  // at or past a sample's length are padding -- such keys are masked, such query rows come out as zeros
+  const int* seqlens_q;
+  const int* seqlens_k;
   int* status;
 };
 
@@ -95,9 +99,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int batch = blockIdx.z;
   const int head_kv = head / (p.nh / p.nh_kv);
   const int q0 = qt * BM;
-  const int coff = p.sk - p.sq;  // causal: key j visible to query i when j <= i + coff
+  const int sq_b = p.seqlens_q ? min(p.sq, p.seqlens_q[batch]) : p.sq;   // real tokens of this sample
+  const int sk_b = p.seqlens_k ? min(p.sk, p.seqlens_k[batch]) : p.sk;
+  const int coff = sk_b - sq_b;  // causal: key j visible to query i when j <= i + coff
 
-  int nblocks = (p.sk + BN - 1) / BN;
+  int nblocks = (q0 < sq_b) ? (sk_b + BN - 1) / BN : 0;   // a tile of padding rows has nothing to attend to
   if (p.causal) {
     int last = q0 + BM - 1 + coff;  // last visible key of the tile's last row
     int nb = last < 0 ? 0 : last / BN + 1;
@@ -271,10 +277,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive(&s_empty[b]);
 
       const int kv0 = j * BN;
-      const int vis = p.causal ? min(p.sk - 1, qi + coff) : p.sk - 1;  // last visible key
+      const int vis = p.causal ? min(sk_b - 1, qi + coff) : sk_b - 1;  // last visible key
       // Only tiles that touch the diagonal or the end of the keys need the mask; the test is the
       // same for every thread of the CTA (first row of the tile has the smallest horizon).
-      const int vis_tile = p.causal ? min(p.sk - 1, q0 + coff) : p.sk - 1;
+      const int vis_tile = p.causal ? min(sk_b - 1, q0 + coff) : sk_b - 1;
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
       if (kv0 + BN - 1 > vis_tile) {
 #pragma unroll
@@ -362,7 +368,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (ok) {
       tc_fence_after();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const bool real_row = qi < sq_b;
+      const float inv = (real_row && l_run > 0.f) ? 1.f / l_run : 0.f;
       __nv_bfloat16* orow = p.o + batch * p.o_batch_stride + static_cast<long>(qi) * p.o_tok_stride +
                             static_cast<long>(head) * p.o_head_stride;
       for (int c = 0; c < p.d_mma / 16; ++c) {
@@ -384,7 +391,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       if (qi < p.sq)
         p.lse[(static_cast<long>(batch) * p.nh + head) * p.sq + qi] =
-            l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+            (real_row && l_run > 0.f) ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
@@ -444,12 +451,15 @@ MB_API void mb_attn_fwd_set_variant(int v) { g_fwd_variant = (v >= 0 && v <= 5) 
 // q: [batch][sq][nh][d], k/v: [batch][sk][nh_kv][d], element strides given per tensor
 // (so views into a packed qkv buffer work).  o: [batch][sq][nh][d] with its own strides.
 // lse: [batch][nh][sq] fp32.  Head size d: multiple of 16, <= 128; all strides
-// multiples of 8 elements and base pointers 16-byte aligned.
+// multiples of 8 elements and base pointers 16-byte aligned.  seqlens_q / seqlens_k: optional device
+// arrays of `batch` ints, the number of real tokens of each sample of a right-padded batch (what the
+// reference handles by removing the padding and calling its variable-length kernels,
+// csrc/flash_attn/flash_api.cpp:427); padded query rows get zeros and lse = -inf.
 MB_API int mb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch,
                        int sq, int sk, int nh, int nh_kv, int d, long q_bs, long q_ts, long q_hs,
                        long k_bs, long k_ts, long k_hs, long v_bs, long v_ts, long v_hs, long o_bs,
-                       long o_ts, long o_hs, float scale, int causal, int block_n,
-                       cudaStream_t stream) {
+                       long o_ts, long o_hs, float scale, int causal, int block_n, const int* seqlens_q,
+                       const int* seqlens_k, cudaStream_t stream) {
   if (d % 16 || d > 128 || d < 16 || nh % nh_kv) return -1;
   if ((q_ts | q_hs | q_bs | k_ts | k_hs | k_bs | v_ts | v_hs | v_bs | o_ts | o_hs | o_bs) & 7) return -1;
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
@@ -470,6 +480,8 @@ MB_API int mb_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   p.o_batch_stride = o_bs; p.o_tok_stride = o_ts; p.o_head_stride = o_hs;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
+  p.seqlens_q = seqlens_q;
+  p.seqlens_k = seqlens_k;
   p.status = mb_status_device_ptr();
   dim3 grid((sq + BM - 1) / BM, nh, batch);
 #define MB_ATTN_LAUNCH(BN_, SPLIT_, EMU_)                                                          \

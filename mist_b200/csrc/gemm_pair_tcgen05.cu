@@ -464,13 +464,14 @@ MB_API int mb_gemm_pair_bf16(const void* A, const void* B, void* C, int M, int N
   if (tiles < max_ctas / 2) return 1;     // cannot fill the machine with 256 x 256 tiles
   CUtensorMap ta, tb, tc, tx;
   memset(&tx, 0, sizeof(tx));
-  bool ok = a_mn_major ? make_map(&ta, A, K, M, lda, 64, BK, false, true) : make_map(&ta, A, M, K, lda, 64, BM, false, true);
-  ok = ok && (b_mn_major ? make_map(&tb, B, K, N, ldb, 64, BK, false, true)
-                         : make_map(&tb, B, N, K, ldb, 64, BNH, false, true));
-  ok = ok && make_map(&tc, C, M, N, ldc, out_fp32 ? 32 : 64, BM, out_fp32, false);
+  // a tensor map that cannot be encoded: -21 (A), -22 (B), -23 (C), -24 (second epilogue operand)
+  if (!(a_mn_major ? make_map(&ta, A, K, M, lda, 64, BK, false, true) : make_map(&ta, A, M, K, lda, 64, BM, false, true)))
+    return -21;
+  if (!(b_mn_major ? make_map(&tb, B, K, N, ldb, 64, BK, false, true) : make_map(&tb, B, N, K, ldb, 64, BNH, false, true)))
+    return -22;
+  if (!make_map(&tc, C, M, N, ldc, out_fp32 ? 32 : 64, BM, out_fp32, false)) return -23;
   const bool has_aux = (flags & (EPI_DGELU | EPI_RESIDUAL)) != 0;
-  if (ok && ((flags & EPI_SAVE_PRE) || has_aux)) ok = make_map(&tx, aux, M, N, ldc, 64, BM, false, false);
-  if (!ok) return -2;
+  if (((flags & EPI_SAVE_PRE) || has_aux) && !make_map(&tx, aux, M, N, ldc, 64, BM, false, false)) return -24;
   PairParams p;
   p.M = M; p.N = N; p.K = K;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);

@@ -620,3 +620,16 @@ MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const f
       nparts, h, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// Column sums of partial-gradient matrices ([nparts][h] fp32 each, part_dbeta may be null) into the bf16
+// gradient vectors; used after the pipelined backward kernel (norm_pipe.cu), which writes one partial row
+// per CTA.
+MB_API int mb_norm_bwd_finalize(const float* part_dgamma, const float* part_dbeta, void* dgamma, void* dbeta,
+                                int nparts, int h, cudaStream_t stream) {
+  if (nparts <= 0 || h <= 0) return -1;
+  dim3 fb(32, 32);
+  norm_bwd_finalize_kernel<<<(h + 31) / 32, fb, 0, stream>>>(part_dgamma, part_dbeta,
+                                                             reinterpret_cast<__nv_bfloat16*>(dgamma),
+                                                             reinterpret_cast<__nv_bfloat16*>(dbeta), nparts, h, 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

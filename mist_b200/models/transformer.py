@@ -41,9 +41,9 @@ class ParallelTransformerLayer(nn.Module):
         # prenorm = False: each residual connection starts from the *normalised* stream (the norm's
         # output) instead of the norm's input (reference: mist/model/transformer.py:260-264,309-314)
         self.residual_from_norm = not cfg.prenorm
-        if cfg.fp32_residual_connection:
-            raise NotImplementedError("fp32_residual_connection: the residual stream has the parameter dtype here "
-                                      "(the fused norm kernels read and write it in bf16)")
+        # the residual stream in fp32 while the branches stay in the parameter dtype (reference:
+        # fp32_residual_connection, mist/model/transformer.py:120; residual_in_fp32 of its norm kernels)
+        self.fp32_residual = bool(cfg.fp32_residual_connection)
         self.parallel_block = cfg.parallel_block
         self.tied_norm = cfg.parallel_block_tied_norm
         self.sequence_parallel = sequence_parallel
@@ -92,33 +92,55 @@ class ParallelTransformerLayer(nn.Module):
             return F.bias_dropout_add(x, None, None, self.hidden_dropout, seed)
         return x
 
+    def _drop_args(self):
+        """Keyword arguments that make a norm apply this block's hidden dropout to its input, inside the
+        norm kernel, before the residual add (one pass instead of a separate element-wise kernel)."""
+        if self.hidden_dropout > 0 and self.training:
+            return dict(dropout_p=self.hidden_dropout, seed=F.next_dropout_seed())
+        return {}
+
     def forward(self, hidden, residual=None, encoder_output=None, batch_size: Optional[int] = None,
                 attn_mask=None, enc_mask=None):
         """Returns ``(hidden, residual)``; the caller's next norm adds them.  ``attn_mask`` /
         ``enc_mask``: prepared padding masks (:class:`~mist_b200.modules.layers.PaddingMask`) of this
-        stack's tokens and of the encoder output that cross attention reads."""
+        stack's tokens and of the encoder output that cross attention reads.
+
+        Dropout of the attention and cross-attention outputs runs inside the norm that consumes them;
+        the MLP output leaves the block already dropped out (its consumer is another block, the final
+        norm or a pipeline boundary)."""
         bs = batch_size if batch_size is not None else hidden.shape[0]
+        if self.fp32_residual and residual is None and isinstance(hidden, torch.Tensor) and not F._sym(hidden):
+            if hidden.dtype == torch.float32 and self.norm1.weight.dtype != torch.float32:
+                # the stream of the previous pipeline stage, handed over as one fp32 tensor
+                residual, hidden = hidden, torch.zeros(hidden.shape, dtype=self.norm1.weight.dtype, device=hidden.device)
+            else:
+                residual = torch.zeros(hidden.shape, dtype=torch.float32, device=hidden.device)   # the fp32 stream starts here
         if not self.parallel_block:
             x, residual = self.norm1(hidden, residual)
             if self.residual_from_norm:
                 residual = x
-            hidden = self._drop(self.attn(x, batch_size=bs, attention_mask=attn_mask))
+            hidden = self.attn(x, batch_size=bs, attention_mask=attn_mask)
             if hidden.shape != residual.shape:
                 hidden = hidden.reshape(residual.shape)
             if self.is_decoder:
-                x, residual = self.norm_cross(hidden, residual)
+                x, residual = self.norm_cross(hidden, residual, **self._drop_args())
                 if self.residual_from_norm:
                     residual = x
-                hidden = self._drop(self.cross_attn(x, x_kv=encoder_output, batch_size=bs, attention_mask=attn_mask,
-                                                    kv_mask=enc_mask)).reshape(residual.shape)
-            x, residual = self.norm2(hidden, residual)
+                hidden = self.cross_attn(x, x_kv=encoder_output, batch_size=bs, attention_mask=attn_mask,
+                                         kv_mask=enc_mask).reshape(residual.shape)
+            x, residual = self.norm2(hidden, residual, **self._drop_args())
             if self.residual_from_norm:
                 residual = x
             hidden = self._drop(self.mlp(x)).reshape(residual.shape)
             return hidden, residual
-        # parallel block: attention and MLP read the same stream
-        x1, residual = self.norm1(hidden, residual)
-        x2 = x1 if self.tied_norm else self.norm2(residual, None)[0]
+        # parallel block: attention and MLP read the same stream; both norms of it come from one kernel
+        if self.tied_norm or F._sym(hidden):
+            x1, residual = self.norm1(hidden, residual)
+            x2 = x1 if self.tied_norm else self.norm2(residual, None)[0]
+        else:
+            n1, n2 = self.norm1, self.norm2
+            x1, x2, residual = F.parallel_residual_norm(hidden, None, residual, n1.weight, n1.bias, n2.weight, n2.bias,
+                                                        eps=n1.eps, rms=n1.bias is None)
         a = self._drop(self.attn(x1, batch_size=bs, attention_mask=attn_mask)).reshape(residual.shape)
         m = self._drop(self.mlp(x2)).reshape(residual.shape)
         return a + m, residual

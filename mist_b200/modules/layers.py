@@ -48,8 +48,10 @@ class LayerNorm(nn.Module):
             nn.init.ones_(self.weight)
             nn.init.zeros_(self.bias)
 
-    def forward(self, x, residual=None):
-        return F.layer_norm(x, self.weight, self.bias, self.eps, residual=residual, prenorm=self.prenorm)
+    def forward(self, x, residual=None, dropout_p: float = 0.0, seed: int = 0):
+        """``dropout_p`` / ``seed``: dropout applied to ``x`` before the residual add, inside the kernel."""
+        return F.layer_norm(x, self.weight, self.bias, self.eps, residual=residual, prenorm=self.prenorm,
+                            dropout_p=dropout_p, seed=seed)
 
 
 class RMSNorm(nn.Module):
@@ -65,8 +67,9 @@ class RMSNorm(nn.Module):
         if self.weight.device.type != "meta":
             nn.init.ones_(self.weight)
 
-    def forward(self, x, residual=None):
-        return F.rms_norm(x, self.weight, self.eps, residual=residual, prenorm=self.prenorm)
+    def forward(self, x, residual=None, dropout_p: float = 0.0, seed: int = 0):
+        return F.rms_norm(x, self.weight, self.eps, residual=residual, prenorm=self.prenorm,
+                          dropout_p=dropout_p, seed=seed)
 
 
 def get_norm(kind: str, hidden_size, eps, prenorm=False, sequence_parallel=False, device=None, dtype=None):
@@ -248,22 +251,37 @@ class PaddingMask:
     the rows of padded positions come back as zeros -- the same result as removing the padding,
     running variable-length attention and padding the output again (reference:
     ``unpad_input`` / ``pad_input`` around the attention core, mist/modules/mha.py:1233-1243,1332-1334).
-    Preparing the mask reads it back to the host once; a mask without padding costs nothing after that.
+    When every sample is padded on the right (the usual batch layout) the whole batch runs as one launch
+    of the attention kernels with the per-sample lengths passed on the device (``lengths_dev``).
+    Preparing the mask reads it back to the host once, to find out whether that is the case and whether
+    there is any padding at all; with ``assume_right_padded`` (class attribute, or the argument) nothing
+    is read back: the mask is taken to be right-padded and only the lengths are computed, on the device.
     """
 
-    def __init__(self, mask: torch.Tensor):
+    #: trust that masks are right-padded (no validation, no host read-back)
+    assume_right_padded = False
+
+    def __init__(self, mask: torch.Tensor, assume_right_padded: Optional[bool] = None):
         assert mask.dim() == 2, "padding mask: [batch, seq] expected"
         valid = mask != 0
         b, s = valid.shape
         lens = valid.sum(1)
-        prefix = (valid == (torch.arange(s, device=valid.device)[None, :] < lens[:, None])).all(1)
-        host = torch.stack([lens, prefix.long()], 1).tolist()
         self.valid = valid
         self.seq_len = s
+        #: real tokens per sample, int32 on the mask's device (what the kernels take)
+        self.lengths_dev = lens.to(torch.int32)
+        trust = PaddingMask.assume_right_padded if assume_right_padded is None else assume_right_padded
+        if trust:
+            self.lengths, self.is_prefix, self.indices = None, None, None
+            self.right_padded, self.all_valid = True, False
+            return
+        prefix = (valid == (torch.arange(s, device=valid.device)[None, :] < lens[:, None])).all(1)
+        host = torch.stack([lens, prefix.long()], 1).tolist()
         self.lengths = [int(n) for n, _ in host]
         self.is_prefix = [bool(p) for _, p in host]
         self.indices = [None if self.is_prefix[i] else valid[i].nonzero().squeeze(1) for i in range(b)]
         self.all_valid = all(n == s for n in self.lengths)
+        self.right_padded = all(self.is_prefix)
 
     @staticmethod
     def prepare(mask) -> Optional["PaddingMask"]:
@@ -367,7 +385,13 @@ class ParallelMHA(nn.Module):
         return qk
 
     def _attend_masked(self, q, k, v, causal, q_mask: Optional[PaddingMask], k_mask: Optional[PaddingMask]):
-        """Attention per sample over its real tokens; rows of padded queries are zero."""
+        """Attention over the real tokens of every sample; rows of padded queries are zero.  Right-padded
+        batches run as one launch with the lengths on the device; other masks go sample by sample."""
+        if (self.use_flash_attn and (q_mask is None or q_mask.right_padded)
+                and (k_mask is None or k_mask.right_padded)):
+            return F.attention(q, k, v, self.softmax_scale, causal,
+                               seqlens_q=None if q_mask is None else q_mask.lengths_dev,
+                               seqlens_k=None if k_mask is None else k_mask.lengths_dev)
         outs = []
         for i in range(q.shape[0]):
             qi = q_mask.select(q, i) if q_mask is not None else q[i:i + 1]

@@ -20,11 +20,11 @@ native.register_signature("mb_attn_bwd_set_variant", [C.c_int], None)
 native.register_signature("mb_attn_bwd_last_variant", [], C.c_int)
 
 
-def _reference(dout, q, k, v, scale, causal):
+def _reference(dout, q, k, v, scale, causal, seqlens=(None, None)):
     from .functional import _ref_attention
     qq, kk, vv = (t.detach().float().requires_grad_(True) for t in (q, k, v))
     with torch.enable_grad():
-        out, _ = _ref_attention(qq, kk, vv, scale, causal)
+        out, _ = _ref_attention(qq, kk, vv, scale, causal, *seqlens)
     dq, dk, dv = torch.autograd.grad(out, (qq, kk, vv), dout.float())
     return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
 
@@ -43,25 +43,27 @@ def has_native_backward() -> bool:
     return lib is not None and hasattr(lib, "mb_attn_bwd")
 
 
-def backward(dout, q, k, v, o, lse, scale, causal, out=None):
-    """Returns (dq, dk, dv); with ``out=(dq, dk, dv)`` writes into those (possibly strided) views."""
-    if not q.is_cuda:
-        grads = _reference(dout, q, k, v, scale, causal)
+def backward(dout, q, k, v, o, lse, scale, causal, out=None, seqlens=(None, None)):
+    """Returns (dq, dk, dv); with ``out=(dq, dk, dv)`` writes into those (possibly strided) views.
+    ``seqlens``: (per-sample query lengths, per-sample key lengths) of a right-padded batch, or Nones."""
+    padded = seqlens[0] is not None or seqlens[1] is not None
+    if not q.is_cuda or (padded and not has_native_backward()):
+        grads = _reference(dout, q, k, v, scale, causal, seqlens)
     elif has_native_backward():
         from .functional import Settings
         if Settings.attn_backend == "tcgen05":
             if q.shape[2] == k.shape[2]:
-                return _native_backward(dout, q, k, v, o, lse, scale, causal, out)
+                return _native_backward(dout, q, k, v, o, lse, scale, causal, out, seqlens)
             # grouped-query heads: every query head gets its own copy of its group's key / value head,
             # and the gradients of the copies are summed over the group afterwards
             g = q.shape[2] // k.shape[2]
             dq, dk, dv = _native_backward(dout, q, k.repeat_interleave(g, dim=2), v.repeat_interleave(g, dim=2),
-                                          o, lse, scale, causal, None)
+                                          o, lse, scale, causal, None, seqlens)
             b, sk, nkv, d = k.shape
             grads = (dq, dk.view(b, sk, nkv, g, d).float().sum(3).to(k.dtype),
                      dv.view(b, sk, nkv, g, d).float().sum(3).to(v.dtype))
         else:
-            grads = _library(dout, q, k, v, scale, causal)
+            grads = _reference(dout, q, k, v, scale, causal, seqlens) if padded else _library(dout, q, k, v, scale, causal)
     else:
         grads = _library(dout, q, k, v, scale, causal)
     if out is not None:
@@ -71,7 +73,7 @@ def backward(dout, q, k, v, o, lse, scale, causal, out=None):
     return grads
 
 
-def _native_backward(dout, q, k, v, o, lse, scale, causal, out):
+def _native_backward(dout, q, k, v, o, lse, scale, causal, out, seqlens=(None, None)):
     b, sq, nh, d = q.shape
     sk = k.shape[1]
     if out is None:
@@ -90,5 +92,6 @@ def _native_backward(dout, q, k, v, o, lse, scale, causal, out):
          q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
          v.stride(0), v.stride(1), v.stride(2),
          dq.stride(0), dq.stride(1), dq.stride(2), dk.stride(0), dk.stride(1), dk.stride(2),
-         dv.stride(0), dv.stride(1), dv.stride(2), float(scale), int(causal), stream())
+         dv.stride(0), dv.stride(1), dv.stride(2), float(scale), int(causal), ptr(seqlens[0]), ptr(seqlens[1]),
+         stream())
     return dq, dk, dv

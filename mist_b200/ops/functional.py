@@ -63,18 +63,16 @@ class Settings:
     gemm_pair = True              # large GEMMs on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2)
     fuse_mlp_gelu = True          # GELU MLP as one autograd node (gelu' folded into a dgrad GEMM epilogue)
     tp_backend = "nccl"           # "nccl" | "fused": sequence-parallel linears on the GEMM+collective kernels
-    # Source of the seeds of hidden-state dropout.  Seeded alike on every rank of a tensor-parallel group
-    # (the training session does that), so replicated activations get the same mask on every rank.
-    dropout_generator = None
+    norm_pipe = os.environ.get("MB_NORM_PIPE", "1") != "0"    # norms on the bulk-copy pipelined kernels
     dropout_seed_offset = 0       # added to every drawn seed; differs per rank only where tokens are sharded
 
 
 def next_dropout_seed() -> int:
-    """Seed for one dropout call, drawn from :attr:`Settings.dropout_generator`."""
-    if Settings.dropout_generator is None:
-        Settings.dropout_generator = torch.Generator()
-        Settings.dropout_generator.manual_seed(torch.initial_seed() & 0x7FFFFFFF)
-    s = int(torch.randint(0, 2 ** 31 - 1, (1,), generator=Settings.dropout_generator).item())
+    """Seed for one dropout call, drawn from torch's CPU generator.  The training session seeds that
+    generator alike on every rank of a tensor-parallel group, so replicated activations get the same mask
+    on every rank; and it is the generator whose state activation checkpointing saves and restores, so a
+    recomputed forward pass draws the seeds of the original one."""
+    s = int(torch.randint(0, 2 ** 31 - 1, (1,)).item())
     return (s + Settings.dropout_seed_offset) % (2 ** 31 - 1)
 
 
@@ -461,91 +459,203 @@ def _ref_norm(x, gamma, beta, eps, rms):
     return z, mean, rstd
 
 
+def _keep_mask(seed: int, shape, p: float, device, second: bool = False):
+    """Dropout mask of the reference (CPU) path: reproducible from the seed, one stream per branch."""
+    gen = torch.Generator(device="cpu").manual_seed((int(seed) + (0x5DEECE66D if second else 0)) & 0x7FFFFFFFFFFFFFFF)
+    return (torch.rand(shape, generator=gen) >= p).to(device)
+
+
 class _NormFn(torch.autograd.Function):
-    """z = norm(x0 + residual); optionally returns the sum as the new residual stream."""
+    """``z = norm(dropout(x0) [+ dropout(x1)] [+ residual])`` and, for parallel blocks, a second norm ``z1``
+    of the same stream with its own weights; optionally returns the sum as the new residual stream.
+
+    The residual stream may be fp32 while the branches and the outputs are bf16
+    (``residual_in_fp32`` of the reference, mist/modules/layer_norm.py:28, 133, 241).  Dropout masks are
+    not stored: the backward pass regenerates them from ``seed``.  One kernel per pass
+    (csrc/norm_pipe.cu); shapes it does not take, and runs with ``MB_NORM_PIPE=0``, use the older
+    kernels of csrc/norm.cu, which cover the plain form only."""
 
     @staticmethod
-    def forward(ctx, x0, residual, gamma, beta, eps, rms, prenorm):
+    def forward(ctx, x0, residual, gamma, beta, eps, rms, prenorm, x1=None, gamma1=None, beta1=None,
+                dropout_p=0.0, seed=0):
         ctx.rms, ctx.prenorm = rms, prenorm
         ctx.has_res = residual is not None
         ctx.has_beta = beta is not None
+        ctx.has_x1, ctx.parallel, ctx.has_beta1 = x1 is not None, gamma1 is not None, beta1 is not None
+        ctx.p, ctx.seed = float(dropout_p), int(seed)
         shp = x0.shape
         h = shp[-1]
         x0_2 = x0.reshape(-1, h)
         rows = x0_2.shape[0]
+        res_fp32 = residual is not None and residual.dtype == torch.float32
+        ctx.res_fp32 = res_fp32
+        extras = ctx.has_x1 or ctx.parallel or ctx.p > 0 or res_fp32
+        z1 = None
         if not use_native(x0):
-            x = x0_2.float() if residual is None else x0_2.float() + residual.reshape(-1, h).float()
-            x = x.to(x0.dtype)
+            xf = x0_2.float()
+            if ctx.p > 0:
+                xf = xf * _keep_mask(seed, xf.shape, ctx.p, xf.device) / (1.0 - ctx.p)
+            if x1 is not None:
+                yf = x1.reshape(-1, h).float()
+                if ctx.p > 0:
+                    yf = yf * _keep_mask(seed, yf.shape, ctx.p, yf.device, True) / (1.0 - ctx.p)
+                xf = xf + yf
+            if residual is not None:
+                xf = xf + residual.reshape(-1, h).float()
+            x = xf if res_fp32 else xf.to(x0.dtype)
             z, mean, rstd = _ref_norm(x, gamma, beta, eps, rms)
             z = z.to(x0.dtype)
+            if gamma1 is not None:
+                z1 = _ref_norm(x, gamma1, beta1, eps, rms)[0].to(x0.dtype)
             mean = None if mean is None else mean.reshape(-1)
             rstd = rstd.reshape(-1)
         else:
             x0_2 = x0_2.contiguous()
             res2 = None if residual is None else residual.reshape(-1, h).contiguous()
+            x1_2 = None if x1 is None else x1.reshape(-1, h).contiguous()
             z = torch.empty_like(x0_2)
-            need_x = residual is not None
-            x = torch.empty_like(x0_2) if need_x else x0_2
+            z1 = torch.empty_like(x0_2) if gamma1 is not None else None
+            need_x = residual is not None or extras
+            x = (torch.empty(rows, h, dtype=torch.float32 if res_fp32 else x0.dtype, device=x0.device)
+                 if need_x else x0_2)
             mean = None if rms else torch.empty(rows, dtype=torch.float32, device=x0.device)
             rstd = torch.empty(rows, dtype=torch.float32, device=x0.device)
-            call("mb_norm_fwd", ptr(x0_2), ptr(res2), ptr(gamma), ptr(beta), ptr(z),
-                 ptr(x) if need_x else 0, ptr(mean), ptr(rstd), rows, h, float(eps), int(rms), stream())
-        ctx.save_for_backward(x, gamma, mean, rstd)
-        z = z.reshape(shp)
+            rc = 1
+            if Settings.norm_pipe:
+                rc = native.kernels().mb_norm_fwd_pipe(
+                    ptr(x0_2), ptr(x1_2), ptr(res2), ptr(gamma), ptr(beta), ptr(gamma1), ptr(beta1), ptr(z), ptr(z1),
+                    ptr(x) if need_x else 0, ptr(mean), ptr(rstd), rows, h, float(eps), int(rms), int(res_fp32),
+                    float(ctx.p), int(seed) & 0xFFFFFFFFFFFFFFFF, stream())
+                if rc == 0:
+                    native.launch_count += 1
+                elif rc != 1:
+                    raise RuntimeError(f"mb_norm_fwd_pipe failed with code {rc}")
+            if rc == 1:
+                if extras:
+                    raise NotImplementedError("dropout, a second branch, a second norm and an fp32 residual stream "
+                                              "need the pipelined norm kernel (hidden size a multiple of 8)")
+                call("mb_norm_fwd", ptr(x0_2), ptr(res2), ptr(gamma), ptr(beta), ptr(z),
+                     ptr(x) if need_x else 0, ptr(mean), ptr(rstd), rows, h, float(eps), int(rms), stream())
+        ctx.save_for_backward(x, gamma, mean, rstd, gamma1)
+        ctx.branch_dtype = x0.dtype
+        outs = [z.reshape(shp)]
+        if gamma1 is not None:
+            outs.append(z1.reshape(shp))
         if prenorm:
-            return z, x.reshape(shp)
-        return z
+            outs.append(x.reshape(shp))
+        return outs[0] if len(outs) == 1 else tuple(outs)
 
     @staticmethod
     def backward(ctx, dz, *args):
-        x, gamma, mean, rstd = ctx.saved_tensors
-        dres_in = args[0] if (ctx.prenorm and len(args) > 0) else None
+        x, gamma, mean, rstd, gamma1 = ctx.saved_tensors
+        args = list(args)
+        dz1 = args.pop(0) if ctx.parallel else None
+        dres_in = args.pop(0) if (ctx.prenorm and args) else None
         shp = dz.shape
         h = shp[-1]
         dz2 = dz.reshape(-1, h)
         rows = dz2.shape[0]
+        dgamma1 = dbeta1 = None
+        bdt = ctx.branch_dtype
+        split = ctx.p > 0 or ctx.res_fp32          # branch gradients differ from the stream's gradient
         if not use_native(dz):
             xf = x.reshape(-1, h).float()
-            g = gamma.float()
-            if ctx.rms:
-                xh = xf * rstd[:, None]
-                m1 = 0.0
-            else:
-                xh = (xf - mean[:, None]) * rstd[:, None]
-            dy = dz2.float() * g
-            if not ctx.rms:
-                m1 = dy.mean(-1, keepdim=True)
+            xh = xf * rstd[:, None] if ctx.rms else (xf - mean[:, None]) * rstd[:, None]
+            dy = dz2.float() * gamma.float()
+            if dz1 is not None:
+                dy = dy + dz1.reshape(-1, h).float() * gamma1.float()
+            m1 = 0.0 if ctx.rms else dy.mean(-1, keepdim=True)
             m2 = (dy * xh).mean(-1, keepdim=True)
-            dx = rstd[:, None] * (dy - m1 - xh * m2)
+            dxf = rstd[:, None] * (dy - m1 - xh * m2)
             if dres_in is not None:
-                dx = dx + dres_in.reshape(-1, h).float()
-            dx = dx.to(dz.dtype)
+                dxf = dxf + dres_in.reshape(-1, h).float()
+            dx = dxf.to(x.dtype)
             dgamma = (dz2.float() * xh).sum(0).to(gamma.dtype)
             dbeta = dz2.float().sum(0).to(gamma.dtype) if ctx.has_beta else None
+            if dz1 is not None:
+                dgamma1 = (dz1.reshape(-1, h).float() * xh).sum(0).to(gamma.dtype)
+                dbeta1 = dz1.reshape(-1, h).float().sum(0).to(gamma.dtype) if ctx.has_beta1 else None
+            dx0 = dx1 = None
+            if split:
+                dx0 = dxf
+                if ctx.p > 0:
+                    dx0 = dxf * _keep_mask(ctx.seed, dxf.shape, ctx.p, dxf.device) / (1.0 - ctx.p)
+                dx0 = dx0.to(bdt)
+                if ctx.has_x1:
+                    dx1 = dxf
+                    if ctx.p > 0:
+                        dx1 = dxf * _keep_mask(ctx.seed, dxf.shape, ctx.p, dxf.device, True) / (1.0 - ctx.p)
+                    dx1 = dx1.to(bdt)
         else:
             dz2 = dz2.contiguous()
+            dz1_2 = None if dz1 is None else dz1.reshape(-1, h).contiguous()
             dr = None if dres_in is None else dres_in.reshape(-1, h).contiguous()
-            dx = torch.empty_like(dz2)
             dgamma = torch.empty_like(gamma)
             dbeta = torch.empty_like(gamma) if ctx.has_beta else None
-            nrows = native.kernels().mb_norm_bwd_scratch_rows(rows, h)
-            scratch = _get_scratch(2 * nrows * h, dz.device, "norm")
-            call("mb_norm_bwd", ptr(dz2), ptr(x), ptr(gamma), ptr(mean), ptr(rstd), ptr(dr), ptr(dx),
-                 ptr(dgamma), ptr(dbeta), ptr(scratch), rows, h, int(ctx.rms), 0, stream())
-        dx = dx.reshape(shp)
-        return dx, (dx if ctx.has_res else None), dgamma, dbeta, None, None, None
+            lib = native.kernels()
+            parts = lib.mb_norm_pipe_parts(rows, h, int(ctx.res_fp32), int(dz1 is not None), int(dr is not None),
+                                           int(ctx.rms)) if Settings.norm_pipe else 0
+            dx0 = dx1 = None
+            if parts > 0:
+                need_stream = ctx.has_res or not split
+                dx = torch.empty(rows, h, dtype=x.dtype, device=dz.device) if need_stream else None
+                if split:
+                    dx0 = torch.empty(rows, h, dtype=bdt, device=dz.device)
+                    dx1 = torch.empty(rows, h, dtype=bdt, device=dz.device) if ctx.has_x1 else None
+                nvecs = 2 * (2 if dz1 is not None else 1)
+                scratch = _get_scratch(nvecs * parts * h, dz.device, "norm")
+                pg, pb = scratch[: parts * h], scratch[parts * h: 2 * parts * h]
+                pg1 = scratch[2 * parts * h: 3 * parts * h] if dz1 is not None else None
+                pb1 = scratch[3 * parts * h: 4 * parts * h] if dz1 is not None else None
+                call("mb_norm_bwd_pipe", ptr(dz2), ptr(dz1_2), ptr(x), ptr(dr), ptr(gamma), ptr(gamma1), ptr(mean),
+                     ptr(rstd), ptr(dx), ptr(dx0), ptr(dx1), ptr(pg), ptr(pb), ptr(pg1), ptr(pb1), rows, h,
+                     int(ctx.rms), int(ctx.res_fp32), float(ctx.p), ctx.seed & 0xFFFFFFFFFFFFFFFF, stream())
+                call("mb_norm_bwd_finalize", ptr(pg), ptr(pb) if ctx.has_beta else 0, ptr(dgamma), ptr(dbeta), parts, h,
+                     stream())
+                if dz1 is not None:
+                    dgamma1 = torch.empty_like(gamma)
+                    dbeta1 = torch.empty_like(gamma) if ctx.has_beta1 else None
+                    call("mb_norm_bwd_finalize", ptr(pg1), ptr(pb1) if ctx.has_beta1 else 0, ptr(dgamma1), ptr(dbeta1),
+                         parts, h, stream())
+            else:
+                if split or dz1 is not None:
+                    raise NotImplementedError("this shape needs the pipelined norm kernel for its options")
+                dx = torch.empty_like(dz2)
+                nrows = lib.mb_norm_bwd_scratch_rows(rows, h)
+                scratch = _get_scratch(2 * nrows * h, dz.device, "norm")
+                call("mb_norm_bwd", ptr(dz2), ptr(x), ptr(gamma), ptr(mean), ptr(rstd), ptr(dr), ptr(dx),
+                     ptr(dgamma), ptr(dbeta), ptr(scratch), rows, h, int(ctx.rms), 0, stream())
+        g_x0 = (dx0 if split else dx).reshape(shp)
+        g_res = dx.reshape(shp) if ctx.has_res else None
+        g_x1 = None
+        if ctx.has_x1:
+            g_x1 = (dx1 if split else dx).reshape(shp)
+        return g_x0, g_res, dgamma, dbeta, None, None, None, g_x1, dgamma1, dbeta1, None, None
 
 
-def layer_norm(x, gamma, beta, eps=1e-5, residual=None, prenorm=False):
+def layer_norm(x, gamma, beta, eps=1e-5, residual=None, prenorm=False, dropout_p: float = 0.0, seed: int = 0):
+    """``norm(dropout(x) + residual)``; with ``prenorm`` also returns the sum (the new residual stream,
+    in the residual's dtype: bf16 or fp32)."""
     if _sym(x):
         return _rules().norm(x, residual, gamma, beta, eps, False, prenorm)
-    return _NormFn.apply(x, residual, gamma, beta, eps, False, prenorm)
+    return _NormFn.apply(x, residual, gamma, beta, eps, False, prenorm, None, None, None, float(dropout_p), int(seed))
 
 
-def rms_norm(x, gamma, eps=1e-5, residual=None, prenorm=False):
+def rms_norm(x, gamma, eps=1e-5, residual=None, prenorm=False, dropout_p: float = 0.0, seed: int = 0):
     if _sym(x):
         return _rules().norm(x, residual, gamma, None, eps, True, prenorm)
-    return _NormFn.apply(x, residual, gamma, None, eps, True, prenorm)
+    return _NormFn.apply(x, residual, gamma, None, eps, True, prenorm, None, None, None, float(dropout_p), int(seed))
+
+
+def parallel_residual_norm(x0, x1, residual, gamma0, beta0, gamma1, beta1, eps=1e-5, rms=False,
+                           dropout_p: float = 0.0, seed: int = 0):
+    """Parallel blocks (attention and MLP read the same stream): ``x = dropout(x0) + dropout(x1) + residual``,
+    ``z0 = norm(x; gamma0, beta0)``, ``z1 = norm(x; gamma1, beta1)``, one kernel.  Returns ``(z0, z1, x)``;
+    ``x1`` and ``residual`` may be ``None``; ``gamma1 = None`` gives ``(z0, x)`` (reference:
+    ``dropout_add_ln_parallel_residual_fwd / bwd``, csrc/layer_norm/ln_api.cpp:832-846, used at
+    mist/modules/layer_norm.py:808)."""
+    return _NormFn.apply(x0, residual, gamma0, None if rms else beta0, eps, rms, True, x1, gamma1,
+                         None if rms else beta1, float(dropout_p), int(seed))
 
 
 # ------------------------------------------------------------------------------ rotary
@@ -616,19 +726,25 @@ def decode_attention(q, k_cache, v_cache, seq_len: int, scale: Optional[float] =
     return out
 
 
-def _ref_attention(q, k, v, scale, causal):
-    # q: [b, sq, nh, d]; k, v: [b, sk, nh_kv, d]
+def _ref_attention(q, k, v, scale, causal, seqlens_q=None, seqlens_k=None):
+    # q: [b, sq, nh, d]; k, v: [b, sk, nh_kv, d]; seqlens_*: [b] real tokens per sample (right padding)
     b, sq, nh, d = q.shape
     sk, nkv = k.shape[1], k.shape[2]
     if nkv != nh:
         k = k.repeat_interleave(nh // nkv, dim=2)
         v = v.repeat_interleave(nh // nkv, dim=2)
     s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
-    if causal:
-        mask = torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(sk - sq)
-        s = s.masked_fill(~mask, float("-inf"))
+    lq = torch.full((b,), sq, device=q.device) if seqlens_q is None else seqlens_q.to(q.device).long().clamp(max=sq)
+    lk = torch.full((b,), sk, device=q.device) if seqlens_k is None else seqlens_k.to(q.device).long().clamp(max=sk)
+    qi = torch.arange(sq, device=q.device)[None, :, None]
+    kj = torch.arange(sk, device=q.device)[None, None, :]
+    visible = kj < lk[:, None, None]
+    if causal:      # aligned at the end of each sample's real tokens
+        visible = visible & (kj <= qi + (lk - lq)[:, None, None])
+    real_q = (qi < lq[:, None, None])
+    s = s.masked_fill(~(visible & real_q)[:, None], float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
-    p = torch.softmax(s, dim=-1)
+    p = torch.softmax(s, dim=-1).nan_to_num(0.0)      # rows without a visible key (padding) give zeros
     o = torch.einsum("bhqk,bkhd->bqhd", p, v.float())
     return o.to(q.dtype), lse
 
@@ -644,10 +760,11 @@ def _select_variant(setter: str, want: int):
         _VARIANTS[setter] = want
 
 
-def attn_fwd(q, k, v, scale, causal, block_n=None):
-    """Forward only: returns (o [b,sq,nh,d], lse [b,nh,sq] fp32)."""
+def attn_fwd(q, k, v, scale, causal, block_n=None, seqlens_q=None, seqlens_k=None):
+    """Forward only: returns (o [b,sq,nh,d], lse [b,nh,sq] fp32).  ``seqlens_q`` / ``seqlens_k``: int32
+    device tensors ``[b]`` with the number of real tokens of each sample of a right-padded batch."""
     if not use_native(q):
-        return _ref_attention(q, k, v, scale, causal)
+        return _ref_attention(q, k, v, scale, causal, seqlens_q, seqlens_k)
     b, sq, nh, d = q.shape
     sk, nkv = k.shape[1], k.shape[2]
     assert q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1
@@ -658,7 +775,7 @@ def attn_fwd(q, k, v, scale, causal, block_n=None):
     call("mb_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), b, sq, sk, nh, nkv, d,
          q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
          v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
-         float(scale), int(causal), block_n or Settings.attn_block_n, stream())
+         float(scale), int(causal), block_n or Settings.attn_block_n, ptr(seqlens_q), ptr(seqlens_k), stream())
     return o, lse
 
 
@@ -668,9 +785,10 @@ class _AttnFn(torch.autograd.Function):
     """Attention over separate q / k / v tensors (views allowed)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal):
-        o, lse = attn_fwd(q, k, v, scale, causal)
+    def forward(ctx, q, k, v, scale, causal, seqlens_q=None, seqlens_k=None):
+        o, lse = attn_fwd(q, k, v, scale, causal, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
         ctx.scale, ctx.causal = scale, causal
+        ctx.seqlens = (seqlens_q, seqlens_k)
         ctx.save_for_backward(q, k, v, o, lse)
         return o
 
@@ -678,17 +796,23 @@ class _AttnFn(torch.autograd.Function):
     def backward(ctx, dout):
         q, k, v, o, lse = ctx.saved_tensors
         from . import attention_bwd
-        dq, dk, dv = attention_bwd.backward(dout, q, k, v, o, lse, ctx.scale, ctx.causal)
-        return dq, dk, dv, None, None
+        dq, dk, dv = attention_bwd.backward(dout, q, k, v, o, lse, ctx.scale, ctx.causal, seqlens=ctx.seqlens)
+        return dq, dk, dv, None, None, None, None
 
 
-def attention(q, k, v, scale: Optional[float] = None, causal: bool = True):
-    """Multi-head attention; q ``[b,sq,nh,d]``, k/v ``[b,sk,nh_kv,d]`` (views allowed)."""
+def attention(q, k, v, scale: Optional[float] = None, causal: bool = True, seqlens_q=None, seqlens_k=None):
+    """Multi-head attention; q ``[b,sq,nh,d]``, k/v ``[b,sk,nh_kv,d]`` (views allowed).
+
+    ``seqlens_q`` / ``seqlens_k`` (int32 ``[b]``, on the device): real tokens per sample of a right-padded
+    batch.  One launch covers the whole batch and nothing is read back to the host: padded keys are masked
+    inside the kernels and padded query rows come out as zeros -- the result of removing the padding,
+    running variable-length attention and padding again (reference: csrc/flash_attn/flash_api.cpp:427, 814
+    ``varlen_fwd`` / ``varlen_bwd`` behind mist/modules/mha.py:1233-1243)."""
     if _sym(q):
         return _rules().attention(q, k, v, scale, causal)
     if scale is None:
         scale = 1.0 / math.sqrt(q.shape[-1])
-    return _AttnFn.apply(q, k, v, float(scale), bool(causal))
+    return _AttnFn.apply(q, k, v, float(scale), bool(causal), seqlens_q, seqlens_k)
 
 
 def attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k=None, scale: Optional[float] = None, causal: bool = True):

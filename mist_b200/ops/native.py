@@ -40,6 +40,10 @@ _SIGNATURES = {
     "mb_norm_set_variant": ([_i], None),
     "mb_norm_fwd": ([_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _p], _i),
     "mb_norm_bwd": ([_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p], _i),
+    "mb_norm_pipe_parts": ([_i, _i, _i, _i, _i, _i], _i),
+    "mb_norm_fwd_pipe": ([_p] * 12 + [_i, _i, _f, _i, _i, _f, _u64, _p], _i),
+    "mb_norm_bwd_pipe": ([_p] * 15 + [_i, _i, _i, _i, _f, _u64, _p], _i),
+    "mb_norm_bwd_finalize": ([_p, _p, _p, _p, _i, _i, _p], _i),
     "mb_gelu_fwd": ([_p, _p, _p, _z, _i, _p], _i),
     "mb_gelu_bwd": ([_p, _p, _p, _p, _z, _i, _p], _i),
     "mb_swiglu_fwd": ([_p, _p, _z, _i, _p], _i),
@@ -59,9 +63,9 @@ _SIGNATURES = {
     "mb_causal_softmax_fwd": ([_p, _p, _z, _i, _i, _f, _i, _p], _i),
     "mb_causal_softmax_bwd": ([_p, _p, _p, _z, _i, _f, _p], _i),
     "mb_adam_step": ([_p, _p, _p, _p, _i, _p, _z, _f, _f, _f, _f, _f, _i, _f, _i, _p], _i),
-    "mb_attn_bwd": ([_p] * 11 + [_i] * 5 + [_l] * 18 + [_f, _i, _p], _i),
+    "mb_attn_bwd": ([_p] * 11 + [_i] * 5 + [_l] * 18 + [_f, _i, _p, _p, _p], _i),
     "mb_attn_fwd_set_variant": ([_i], None),
-    "mb_attn_fwd": ([_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i] + [_l] * 12 + [_f, _i, _i, _p], _i),
+    "mb_attn_fwd": ([_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i] + [_l] * 12 + [_f, _i, _i, _p, _p, _p], _i),
 }
 
 _OPTIONAL = {}

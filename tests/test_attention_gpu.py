@@ -148,6 +148,55 @@ def test_attn_bwd_grouped_query_heads(nh, nkv, d, s, causal):
     _check_grads((dq, dk, dv), attention_bwd._reference(g, q, k, v, scale, causal))
 
 
+@pytest.mark.parametrize("d", [64, 80, 128])
+@pytest.mark.parametrize("causal", [True, False])
+def test_right_padded_batch_runs_as_one_launch(d, causal):
+    """Per-sample lengths on the device: padded keys are masked, padded query rows are zeros, gradients of
+    padded positions are zeros -- against the fp32 reference with the same lengths, forward and backward."""
+    from mist_b200.ops import attention_bwd, native
+    torch.manual_seed(8)
+    b, s, nh = 4, 700, 3
+    lens = torch.tensor([700, 1, 333, 512], dtype=torch.int32, device=DEV)
+    scale = 1 / math.sqrt(d)
+    q, k, v, g = (torch.randn(b, s, nh, d, device=DEV, dtype=torch.bfloat16) for _ in range(4))
+    launches = native.launch_count
+    o, lse = F.attn_fwd(q, k, v, scale, causal, seqlens_q=lens, seqlens_k=lens)
+    assert native.launch_count - launches == 1
+    o_ref, lse_ref = F._ref_attention(q.float(), k.float(), v.float(), scale, causal, lens, lens)
+    assert _rel_err(o, o_ref) < 2e-2
+    for i, n in enumerate(lens.tolist()):
+        assert float(o[i, n:].abs().max()) == 0.0 if n < s else True
+        assert torch.allclose(lse[i, :, :n], lse_ref[i, :, :n], atol=2e-2, rtol=1e-3)
+    dq, dk, dv = attention_bwd.backward(g, q, k, v, o, lse, scale, causal, seqlens=(lens, lens))
+    torch.cuda.synchronize()
+    native.check_status()
+    ref = attention_bwd._reference(g, q, k, v, scale, causal, (lens, lens))
+    _check_grads((dq, dk, dv), ref)
+    for i, n in enumerate(lens.tolist()):
+        if n < s:
+            assert float(dq[i, n:].abs().max()) == 0.0 and float(dk[i, n:].abs().max()) == 0.0
+            assert float(dv[i, n:].abs().max()) == 0.0
+
+
+def test_cross_attention_with_padded_keys_and_queries():
+    """Decoder queries over encoder keys, both right-padded with their own lengths, through autograd."""
+    torch.manual_seed(9)
+    b, sq, sk, nh, d = 3, 200, 456, 4, 64
+    lq = torch.tensor([200, 77, 130], dtype=torch.int32, device=DEV)
+    lk = torch.tensor([456, 300, 9], dtype=torch.int32, device=DEV)
+    q = torch.randn(b, sq, nh, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(b, sk, nh, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(b, sk, nh, d, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(b, sq, nh, d, device=DEV, dtype=torch.bfloat16)
+    o = F.attention(q, k, v, None, False, seqlens_q=lq, seqlens_k=lk)
+    dq, dk, dv = torch.autograd.grad(o, (q, k, v), g)
+    qr, kr, vr = (t.detach().cpu().float().requires_grad_(True) for t in (q, k, v))
+    o_ref = F.attention(qr, kr, vr, None, False, seqlens_q=lq.cpu(), seqlens_k=lk.cpu())
+    rq, rk, rv = torch.autograd.grad(o_ref, (qr, kr, vr), g.cpu().float())
+    assert _rel_err(o.cpu(), o_ref) < 2e-2
+    _check_grads((dq.cpu(), dk.cpu(), dv.cpu()), (rq, rk, rv))
+
+
 @pytest.mark.parametrize("nh,nkv,d,seq_len", [(8, 8, 128, 300), (8, 2, 64, 5), (4, 4, 80, 1), (16, 4, 256, 1031)])
 def test_single_query_attention_over_kv_cache(nh, nkv, d, seq_len):
     """Decode step: one query per sequence against the first ``seq_len`` positions of a cache

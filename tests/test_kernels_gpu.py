@@ -31,6 +31,37 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn, tile_n):
     b_in = b.t().contiguous() if b_mn else b
     out = F.gemm(a_in, b_in, a_mn=a_mn, b_mn=b_mn, tile_n=tile_n)
     assert _rel_err(out, ref) < 1e-2
+    _check_edges(out, ref)
+
+
+def _check_edges(out, ref, tol=0.02):
+    """Element-wise check of the last rows and columns (the ragged tiles): a wrong vector there does not
+    move a norm over the whole matrix.  bf16 output of a K-long dot product of unit-variance operands:
+    the error per element stays far below ``tol`` times the largest reference magnitude."""
+    scale = ref.abs().max().item()
+    o, r = out.float(), ref.float()
+    for region in (o[-130:] - r[-130:], o[:, -130:] - r[:, -130:], o[:8] - r[:8], o[:, :8] - r[:, :8]):
+        assert region.abs().max().item() < tol * scale
+
+
+@pytest.mark.parametrize("M,N,K", [(1000, 520, 264), (8192 + 40, 2560 + 8, 328), (300, 7680 + 24, 2560)])
+def test_gemm_pair_ragged_edges(M, N, K):
+    """Shapes large enough for the CTA-pair kernel with ragged last tiles in both directions."""
+    torch.manual_seed(7)
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    out = F.gemm(a, b)
+    assert _rel_err(out, ref) < 1e-2
+    _check_edges(out, ref)
+    # weight-gradient layout with fp32 accumulation into an existing bucket
+    dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    acc = torch.randn(N, K, device=DEV, dtype=torch.float32)
+    ref2 = acc + dy.float().t() @ a.float()
+    if M % 8 == 0:
+        F.gemm(dy, a, a_mn=True, b_mn=True, out=acc, flags=F.EPI_ACCUM)
+        assert _rel_err(acc, ref2) < 1e-3
+        _check_edges(acc, ref2, tol=0.01)
 
 
 def test_gemm_epilogues():
@@ -346,3 +377,84 @@ def test_cast_and_accumulate():
     acc = torch.ones(10001, device=DEV)
     F.accumulate_grad(dst, acc, 0.5, True)
     assert _rel_err(acc, 1 + dst.float() * 0.5) < 1e-5
+
+
+def _rc(a, b):
+    return _rel_err(a.detach().cpu(), b.detach().cpu())
+
+
+def _norm_cpu(args, kwargs):
+    """The same autograd function on CPU copies in fp32 (the reference path of the operator)."""
+    cpu = [None if a is None else (a.detach().cpu().float().requires_grad_(a.requires_grad) if a.is_floating_point() else a.cpu())
+           for a in args]
+    return cpu, F.parallel_residual_norm(*cpu, **kwargs)
+
+
+@pytest.mark.parametrize("h", [1024, 2560, 4096, 8192])
+@pytest.mark.parametrize("rms", [False, True])
+@pytest.mark.parametrize("res_fp32", [False, True])
+def test_pipelined_norm_plain_and_fp32_stream(h, rms, res_fp32):
+    """Pipelined norm kernels (forward and backward), ragged row count, bf16 and fp32 residual streams."""
+    torch.manual_seed(h + rms)
+    rows = 1000
+    x0 = torch.randn(rows, h, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    res = torch.randn(rows, h, device="cuda", dtype=torch.float32 if res_fp32 else torch.bfloat16, requires_grad=True)
+    g = (1 + 0.1 * torch.randn(h, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    b = None if rms else (0.1 * torch.randn(h, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    fn = F.rms_norm if rms else F.layer_norm
+    a = (x0, g) if rms else (x0, g, b)
+    z, xs = fn(*a, 1e-5, residual=res, prenorm=True)
+    assert xs.dtype == res.dtype
+    wz, wx = torch.randn_like(z), torch.randn_like(xs)
+    leaves = [t for t in (x0, res, g, b) if t is not None]
+    grads = torch.autograd.grad([z, xs], leaves, [wz, wx])
+    c = [t.detach().cpu().float().requires_grad_(True) for t in leaves]
+    ca = (c[0], c[2]) if rms else (c[0], c[2], c[3])
+    zr, xr = fn(*ca, 1e-5, residual=c[1], prenorm=True)
+    gr = torch.autograd.grad([zr, xr], c, [wz.cpu().float(), wx.cpu().float()])
+    assert _rc(z, zr) < 1e-2 and _rc(xs, xr) < 1e-2
+    assert (z.float().cpu() - zr).abs().max().item() < 0.1
+    for got, ref, name in zip(grads, gr, ("x0", "res", "gamma", "beta")):
+        assert _rc(got, ref) < 2e-2, name
+    from mist_b200.ops import native
+    native.check_status()
+
+
+@pytest.mark.parametrize("rms", [False, True])
+def test_pipelined_norm_parallel_block_and_dropout(rms):
+    """Two branches, two norms of one stream, dropout on both branches: the masks are read off the returned
+    stream (x = m0 * x0 / (1 - p) + m1 * x1 / (1 - p) + residual) and everything else is checked against them."""
+    torch.manual_seed(3)
+    rows, h, p = 777, 2560, 0.25
+    mk = lambda scale=1.0: (scale * torch.randn(rows, h, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    x0, x1, res = mk(), mk(), mk()
+    g0 = torch.ones(h, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g1 = (1 + 0.1 * torch.randn(h, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    b0 = b1 = None
+    if not rms:
+        b0 = (0.1 * torch.randn(h, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+        b1 = (0.1 * torch.randn(h, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    # without dropout: against the CPU path
+    z0, z1, xs = F.parallel_residual_norm(x0, x1, res, g0, b0, g1, b1, rms=rms)
+    cpu, (r0, r1, rx) = _norm_cpu((x0, x1, res, g0, b0, g1, b1), dict(rms=rms))
+    assert _rc(z0, r0) < 1e-2 and _rc(z1, r1) < 1e-2 and _rc(xs, rx) < 1e-2
+    w = [torch.randn_like(z0) for _ in range(3)]
+    leaves = [t for t in (x0, x1, res, g0, b0, g1, b1) if t is not None]
+    got = torch.autograd.grad([z0, z1, xs], leaves, w)
+    ref = torch.autograd.grad([r0, r1, rx], [t for t in cpu if t is not None], [t.cpu().float() for t in w])
+    for a_, r_ in zip(got, ref):
+        assert _rc(a_, r_) < 2e-2
+    # with dropout: masks from the returned stream, in fp32 arithmetic on the device
+    z0, z1, xs = F.parallel_residual_norm(x0, None, res, g0, b0, g1, b1, rms=rms, dropout_p=p, seed=1234)
+    kept = ((xs.float() - res.float()).abs() > 1e-3) | (x0.float().abs() < 2e-2)
+    frac = 1.0 - kept.float().mean().item()
+    assert abs(frac - p) < 0.02, frac
+    z0b, _, xsb = F.parallel_residual_norm(x0, None, res, g0, b0, g1, b1, rms=rms, dropout_p=p, seed=1234)
+    assert torch.equal(xs, xsb) and torch.equal(z0, z0b)          # same seed, same mask
+    xr = (x0.float() * kept / (1 - p) + res.float()).to(torch.bfloat16)
+    assert _rc(xs, xr) < 1e-2
+    dx0, dres = torch.autograd.grad([xs], [x0, res], [w[2]])
+    assert _rc(dres, w[2]) == 0.0
+    assert _rc(dx0, (w[2].float() * kept / (1 - p))) < 1e-2
+    from mist_b200.ops import native
+    native.check_status()
