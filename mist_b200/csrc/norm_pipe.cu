@@ -1,9 +1,9 @@
 // LayerNorm / RMSNorm forward and backward as software pipelines over rows: a producer thread streams
-// whole rows from global memory into per-warp rings of shared-memory slots with bulk async copies
-// (cp.async.bulk, completion on mbarriers), consumer warps own one row each, normalise it out of shared
+// whole rows from global memory into rings of shared-memory slots with bulk async copies (cp.async.bulk,
+// completion on mbarriers); teams of four consumer warps own one row each, normalise it out of shared
 // memory and write the results with coalesced 16-byte stores.  The loads of the next rows are always in
-// flight while a row is reduced, and no CTA-wide barrier sits in the loop, which is what the register-
-// resident kernels of norm.cu lack (they reach 0.3-0.4 of the copy rate; see the kernel profiles).
+// flight while a row is reduced, and no CTA-wide barrier sits in the loop (a team meets on a named barrier
+// of its own for the two row sums).
 //
 // Folded into the same pass, as in the reference's dropout_add_ln extension
 // (csrc/layer_norm/ln_api.cpp:832-846 dropout_add_ln_fwd / bwd and the parallel-residual pair,
@@ -14,18 +14,22 @@
 //   dx = norm'(dz) [+ norm1'(dz1)] [+ dres_in];   dx0 = mask0 * dx / (1 - p)   [dx1 = mask1 * dx / (1 - p)]
 // with the dropout masks regenerated from (seed, element index) instead of being stored.
 //
-// dgamma / dbeta: every consumer warp adds its rows' contributions into its own fp32 vectors in shared
-// memory (no atomics: a fixed summation order, the same result on every run); the CTA then writes one
-// partial row, and norm_bwd_finalize (norm.cu) sums the partial rows.
+// dgamma / dbeta: every team adds its rows' contributions into its own fp32 vectors in shared memory (each
+// thread owns fixed columns, no atomics: a fixed summation order, the same result on every run); the CTA
+// then writes one partial row, and norm_bwd_finalize (norm.cu) sums the partial rows.
 #include "sm100.cuh"
 
 using namespace sm100;
 
 namespace {
 
-constexpr int kMaxWarps = 4;          // consumer warps per CTA (one more warp produces)
-constexpr int kMaxSlots = 4;          // ring depth per consumer warp
-constexpr int kSmemBudget = 200 * 1024;
+constexpr int kMaxWarps = 4;          // teams of consumer warps per CTA (one more warp produces)
+constexpr int kTeamWarps = 4;         // warps per team, i.e. per row
+constexpr int kTeam = kTeamWarps * 32;
+constexpr int kThreadsPipe = (kMaxWarps * kTeamWarps + 1) * 32;
+constexpr int kMaxSlots = 4;          // ring depth per team
+constexpr int kHeaderBytes = 2 * kMaxWarps * kMaxSlots * 8 + kMaxWarps * 2 * 8 * 4;   // barriers + team sums
+constexpr int kSmemBudget = 225 * 1024;      // of the 227 KB a CTA may have
 
 __device__ __forceinline__ uint4 philox4(uint64_t seed, uint64_t ctr) {
   uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
@@ -49,6 +53,19 @@ __device__ __forceinline__ void dropout_scale8(uint64_t seed, uint64_t vec, floa
   const uint32_t thr = static_cast<uint32_t>(fminf(p, 1.f) * 4294967295.f);
 #pragma unroll
   for (int k = 0; k < 8; ++k) s[k] = r[k] >= thr ? inv_keep : 0.f;
+}
+
+// Sums (a, b) over the four warps of a team.  `red`: 8 floats of this team for this row parity.
+__device__ __forceinline__ void team_sum2(float& a, float& b, float* red, int wit, int lane, int bar_id) {
+  a = mb::warp_sum(a);
+  b = mb::warp_sum(b);
+  if (lane == 0) {
+    red[2 * wit] = a;
+    red[2 * wit + 1] = b;
+  }
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "n"(kTeam) : "memory");
+  a = (red[0] + red[2]) + (red[4] + red[6]);
+  b = (red[1] + red[3]) + (red[5] + red[7]);
 }
 
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
@@ -82,14 +99,18 @@ struct FwdArgs {
 
 // Slot layout: [x0 row: 2h bytes][x1 row: 2h bytes, if any][residual row: 2h or 4h bytes, if any]
 template <bool RMS>
-__global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
+__global__ void __launch_bounds__(kThreadsPipe, 1)
 norm_fwd_pipe_kernel(const FwdArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int NW = a.nwarps, NS = a.nslots;
+  const int NW = a.nwarps, NS = a.nslots;                              // NW: teams
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);                  // [NW][NS]
   uint64_t* empty = full + kMaxWarps * kMaxSlots;                      // [NW][NS]
-  uint8_t* slots = smem + 2 * kMaxWarps * kMaxSlots * 8;               // 64-byte header keeps 16-byte alignment
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* red_all = reinterpret_cast<float*>(smem + 2 * kMaxWarps * kMaxSlots * 8);   // [teams][2 parities][8]
+  uint8_t* slots = smem + 2 * kMaxWarps * kMaxSlots * 8 + kMaxWarps * 2 * 8 * 4;     // header: 512 bytes
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 7;                                   // team index; kMaxWarps.. = producer warp
+  const int wit = (threadIdx.x >> 5) & 3;                              // warp within the team
+  const int tid = threadIdx.x & (kTeam - 1);
   const int h = a.h, nvec = h >> 3;
   const size_t x_bytes = static_cast<size_t>(h) * 2;
   const size_t res_bytes = a.residual ? static_cast<size_t>(h) * (a.res_fp32 ? 4 : 2) : 0;
@@ -99,16 +120,16 @@ norm_fwd_pipe_kernel(const FwdArgs a) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxWarps * kMaxSlots; ++i) {
       mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
+      mbar_init(&empty[i], kTeamWarps);
     }
     fence_barrier_init();
   }
   __syncthreads();
 
-  // rows of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; its k-th row goes to warp k % NW
+  // rows of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...; its k-th row goes to team k % NW
   const int my_rows = (a.rows > static_cast<int>(blockIdx.x)) ? (a.rows - 1 - blockIdx.x) / gridDim.x + 1 : 0;
 
-  if (warp == NW) {
+  if (threadIdx.x >= kMaxWarps * kTeam) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       for (int k = 0; k < my_rows; ++k) {
@@ -132,7 +153,7 @@ norm_fwd_pipe_kernel(const FwdArgs a) {
     // ------------------------------------------------------------------ consumers
     const bool drop = a.drop_p > 0.f;
     const float inv_keep = drop ? 1.f / (1.f - a.drop_p) : 1.f;
-    for (int k = warp, j = 0; k < my_rows; k += NW, ++j) {
+    for (int k = warp, j = 0; k < my_rows; k += NW, ++j) {   // all four warps of the team walk the same rows
       const int s = j % NS;
       if (!mbar_wait(&full[warp * kMaxSlots + s], (j / NS) & 1)) {
         if (lane == 0 && a.status) atomicCAS(a.status, 0, MB_ERR_TIMEOUT_FULL);
@@ -143,7 +164,7 @@ norm_fwd_pipe_kernel(const FwdArgs a) {
       // pass 1: x = dropout(x0) + dropout(x1) + residual, kept in the slot (bf16 over x0, or fp32 over the
       // fp32 residual); row sums of x and x^2 taken from the values as they are stored
       float s1 = 0.f, s2 = 0.f;
-      for (int vi = lane; vi < nvec; vi += 32) {
+      for (int vi = tid; vi < nvec; vi += kTeam) {
         float x[8];
         mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(slot + 16 * vi), x);
         if (drop) {
@@ -190,18 +211,17 @@ norm_fwd_pipe_kernel(const FwdArgs a) {
           s2 += x[e] * x[e];
         }
       }
-      s1 = mb::warp_sum(s1);
-      s2 = mb::warp_sum(s2);
+      team_sum2(s1, s2, red_all + (warp * 2 + (j & 1)) * 8, wit, lane, 1 + warp);
       const float mean = RMS ? 0.f : s1 / h;
       const float var = s2 / h - mean * mean;
       const float rstd = rsqrtf(fmaxf(var, 0.f) + a.eps);
-      if (lane == 0) {
+      if (tid == 0) {
         if (a.mean) a.mean[row] = mean;
         a.rstd[row] = rstd;
       }
       // pass 2: normalise out of the slot
       const bool f32x = a.residual && a.res_fp32;
-      for (int vi = lane; vi < nvec; vi += 32) {
+      for (int vi = tid; vi < nvec; vi += kTeam) {
         float x[8], g[8], o[8];
         if (f32x) {
           const float4* rp = reinterpret_cast<const float4*>(slot + off_res + 32 * vi);
@@ -273,14 +293,18 @@ struct BwdArgs {
 // Slot layout: [dz row: 2h][dz1 row: 2h, if any][x row: 2h or 4h][dres_in row: 2h or 4h, if any]
 // After the slots: per consumer warp, fp32 vectors of h floats: dgamma, dbeta [, dgamma1, dbeta1].
 template <bool RMS>
-__global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
+__global__ void __launch_bounds__(kThreadsPipe, 1)
 norm_bwd_pipe_kernel(const BwdArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  const int NW = a.nwarps, NS = a.nslots;
+  const int NW = a.nwarps, NS = a.nslots;                              // NW: teams
   uint64_t* full = reinterpret_cast<uint64_t*>(smem);
   uint64_t* empty = full + kMaxWarps * kMaxSlots;
-  uint8_t* slots = smem + 2 * kMaxWarps * kMaxSlots * 8;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* red_all = reinterpret_cast<float*>(smem + 2 * kMaxWarps * kMaxSlots * 8);
+  uint8_t* slots = smem + 2 * kMaxWarps * kMaxSlots * 8 + kMaxWarps * 2 * 8 * 4;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 7;                                   // team index
+  const int wit = (threadIdx.x >> 5) & 3;
+  const int tid = threadIdx.x & (kTeam - 1);
   const int h = a.h, nvec = h >> 3;
   const size_t dz_bytes = static_cast<size_t>(h) * 2;
   const size_t x_bytes = static_cast<size_t>(h) * (a.x_fp32 ? 4 : 2);
@@ -293,19 +317,19 @@ norm_bwd_pipe_kernel(const BwdArgs a) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxWarps * kMaxSlots; ++i) {
       mbar_init(&full[i], 1);
-      mbar_init(&empty[i], 1);
+      mbar_init(&empty[i], kTeamWarps);
     }
     fence_barrier_init();
   }
   if (warp < NW) {
     float* acc = acc_base + static_cast<size_t>(warp) * nacc * h;
-    for (int i = lane; i < nacc * h; i += 32) acc[i] = 0.f;
+    for (int i = tid; i < nacc * h; i += kTeam) acc[i] = 0.f;
   }
   __syncthreads();
 
   const int my_rows = (a.rows > static_cast<int>(blockIdx.x)) ? (a.rows - 1 - blockIdx.x) / gridDim.x + 1 : 0;
 
-  if (warp == NW) {
+  if (threadIdx.x >= kMaxWarps * kTeam) {
     if (lane == 0) {
       for (int k = 0; k < my_rows; ++k) {
         const int w = k % NW, j = k / NW, s = j % NS;
@@ -333,7 +357,7 @@ norm_bwd_pipe_kernel(const BwdArgs a) {
     float* db1_s = (a.dz1 && !RMS) ? acc + 3 * h : nullptr;
     const bool drop = a.drop_p > 0.f;
     const float inv_keep = drop ? 1.f / (1.f - a.drop_p) : 1.f;
-    for (int k = warp, j = 0; k < my_rows; k += NW, ++j) {
+    for (int k = warp, j = 0; k < my_rows; k += NW, ++j) {   // all four warps of the team walk the same rows
       const int s = j % NS;
       if (!mbar_wait(&full[warp * kMaxSlots + s], (j / NS) & 1)) {
         if (lane == 0 && a.status) atomicCAS(a.status, 0, MB_ERR_TIMEOUT_FULL);
@@ -354,7 +378,7 @@ norm_bwd_pipe_kernel(const BwdArgs a) {
       };
       // pass 1: row sums of dy and dy * xhat; the warp's dgamma / dbeta vectors take this row's share
       float s1 = 0.f, s2 = 0.f;
-      for (int vi = lane; vi < nvec; vi += 32) {
+      for (int vi = tid; vi < nvec; vi += kTeam) {
         float x[8], dz[8], g[8];
         load_x(vi, x);
         mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(slot + 16 * vi), dz);
@@ -407,12 +431,11 @@ norm_bwd_pipe_kernel(const BwdArgs a) {
           }
         }
       }
-      s1 = mb::warp_sum(s1);
-      s2 = mb::warp_sum(s2);
+      team_sum2(s1, s2, red_all + (warp * 2 + (j & 1)) * 8, wit, lane, 1 + warp);
       const float m1 = RMS ? 0.f : s1 / h;
       const float m2 = s2 / h;
       // pass 2: dx
-      for (int vi = lane; vi < nvec; vi += 32) {
+      for (int vi = tid; vi < nvec; vi += kTeam) {
         float x[8], dz[8], g[8], o[8];
         load_x(vi, x);
         mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(slot + 16 * vi), dz);
@@ -512,11 +535,12 @@ int sms() {
   return g_sms;
 }
 
-// Consumer warps and ring depth for a slot of `row_bytes` plus `acc_bytes` of accumulators per warp.
+// Teams and ring depth for a slot of `row_bytes` plus `acc_bytes` of accumulators per team.
 bool plan(int row_bytes, int acc_bytes, int& nwarps, int& nslots) {
   for (nwarps = kMaxWarps; nwarps >= 1; nwarps >>= 1) {
     for (nslots = kMaxSlots; nslots >= 2; --nslots) {
-      if (static_cast<long>(nwarps) * (static_cast<long>(nslots) * row_bytes + acc_bytes) <= kSmemBudget) return true;
+      if (kHeaderBytes + static_cast<long>(nwarps) * (static_cast<long>(nslots) * row_bytes + acc_bytes) <= kSmemBudget)
+        return true;
     }
   }
   return false;
@@ -564,7 +588,7 @@ MB_API int mb_norm_fwd_pipe(const void* x0, const void* x1, const void* residual
   a.row_bytes = h * 2 * (x1 ? 2 : 1) + (residual ? h * (res_fp32 ? 4 : 2) : 0);
   if (!plan(a.row_bytes, 0, a.nwarps, a.nslots)) return 1;
   a.status = mb_status_device_ptr();
-  const int smem = 2 * kMaxWarps * kMaxSlots * 8 + a.nwarps * a.nslots * a.row_bytes;
+  const int smem = kHeaderBytes + a.nwarps * a.nslots * a.row_bytes;
   int grid = sms();
   if (grid > rows) grid = rows;
   auto kern = rms ? norm_fwd_pipe_kernel<true> : norm_fwd_pipe_kernel<false>;
@@ -573,7 +597,7 @@ MB_API int mb_norm_fwd_pipe(const void* x0, const void* x1, const void* residual
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024) != cudaSuccess) return -3;
     cfg[rms ? 1 : 0] = true;
   }
-  kern<<<grid, (kMaxWarps + 1) * 32, smem, stream>>>(a);
+  kern<<<grid, kThreadsPipe, smem, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -602,7 +626,7 @@ MB_API int mb_norm_bwd_pipe(const void* dz, const void* dz1, const void* x, cons
   const int acc_bytes = h * 4 * (rms ? 1 : 2) * (dz1 ? 2 : 1);
   if (!plan(a.row_bytes, acc_bytes, a.nwarps, a.nslots)) return 1;
   a.status = mb_status_device_ptr();
-  const int smem = 2 * kMaxWarps * kMaxSlots * 8 + a.nwarps * (a.nslots * a.row_bytes + acc_bytes);
+  const int smem = kHeaderBytes + a.nwarps * (a.nslots * a.row_bytes + acc_bytes);
   int grid = sms();
   if (grid > rows) grid = rows;
   auto kern = rms ? norm_bwd_pipe_kernel<true> : norm_bwd_pipe_kernel<false>;
@@ -611,6 +635,6 @@ MB_API int mb_norm_bwd_pipe(const void* dz, const void* dz1, const void* x, cons
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 1024) != cudaSuccess) return -3;
     cfg[rms ? 1 : 0] = true;
   }
-  kern<<<grid, (kMaxWarps + 1) * 32, smem, stream>>>(a);
+  kern<<<grid, kThreadsPipe, smem, stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

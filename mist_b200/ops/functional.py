@@ -63,7 +63,10 @@ class Settings:
     gemm_pair = True              # large GEMMs on CTA pairs (256 x 256 tiles, tcgen05 cta_group::2)
     fuse_mlp_gelu = True          # GELU MLP as one autograd node (gelu' folded into a dgrad GEMM epilogue)
     tp_backend = "nccl"           # "nccl" | "fused": sequence-parallel linears on the GEMM+collective kernels
-    norm_pipe = os.environ.get("MB_NORM_PIPE", "1") != "0"    # norms on the bulk-copy pipelined kernels
+    # Norms on the bulk-copy pipelined kernels (csrc/norm_pipe.cu): "always", "never", or "auto" = only where
+    # their extra options are used (dropout inside the kernel, two norms of one stream, an fp32 residual
+    # stream); MB_NORM_PIPE=1 / 0 selects always / never.
+    norm_pipe = {"1": "always", "0": "never"}.get(os.environ.get("MB_NORM_PIPE", ""), "auto")
     dropout_seed_offset = 0       # added to every drawn seed; differs per rank only where tokens are sharded
 
 
@@ -521,7 +524,8 @@ class _NormFn(torch.autograd.Function):
             mean = None if rms else torch.empty(rows, dtype=torch.float32, device=x0.device)
             rstd = torch.empty(rows, dtype=torch.float32, device=x0.device)
             rc = 1
-            if Settings.norm_pipe:
+            ctx.pipe = Settings.norm_pipe == "always" or (Settings.norm_pipe == "auto" and extras)
+            if ctx.pipe:
                 rc = native.kernels().mb_norm_fwd_pipe(
                     ptr(x0_2), ptr(x1_2), ptr(res2), ptr(gamma), ptr(beta), ptr(gamma1), ptr(beta1), ptr(z), ptr(z1),
                     ptr(x) if need_x else 0, ptr(mean), ptr(rstd), rows, h, float(eps), int(rms), int(res_fp32),
@@ -594,7 +598,7 @@ class _NormFn(torch.autograd.Function):
             dbeta = torch.empty_like(gamma) if ctx.has_beta else None
             lib = native.kernels()
             parts = lib.mb_norm_pipe_parts(rows, h, int(ctx.res_fp32), int(dz1 is not None), int(dr is not None),
-                                           int(ctx.rms)) if Settings.norm_pipe else 0
+                                           int(ctx.rms)) if getattr(ctx, "pipe", False) else 0
             dx0 = dx1 = None
             if parts > 0:
                 need_stream = ctx.has_res or not split
