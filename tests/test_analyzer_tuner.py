@@ -349,3 +349,36 @@ def test_inter_stage_search_respects_tied_table_layout(tmp_path, monkeypatch):
     if len(stages) > 1:
         first, last = stages[0][1], stages[-1][1]
         assert (int(first[1]), int(first[2])) == (int(last[1]), int(last[2]))
+
+
+def test_kick_the_tires_memory_account(monkeypatch):
+    """GPT-1.3B on 2 x L4, DP 2, micro batch 8, G = 2, every block checkpointed, no flash attention (the
+    reference's README walk-through: 19 255 / 19 503 MB predicted, 19 274 MB measured there).  This executor
+    differs from the reference's in three accountable ways, and the analyzer must price them:
+
+    * gradients accumulated over micro steps are kept in fp32 (the reference accumulates in fp16): + one more
+      copy of the fp16 weights, 2 705 MB;
+    * a checkpointed block keeps its (hidden, residual) input pair, not one tensor: + 24 x 64 MB = 1 536 MB;
+    * the recomputation of a block in the backward pass holds the block's forward and backward working sets
+      together.
+
+    The numbers below pin the analyzer's own account (states 16 230 MB, block inputs 3 072 MB) so that a change
+    of the memory model shows up here."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_L4")
+    cfg, _ = load_config("test-small-base", check_world_size=False)
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=False))
+    res = analyze_strategy(cfg, ev)
+    fwd, bwd = (x / 2 ** 20 for x in res["peak_memories"][0])
+    blk = ev.layer_numbers(1, 8, "block_layer")
+    pre, post = ev.layer_numbers(1, 8, "pre_layer"), ev.layer_numbers(1, 8, "post_layer")
+    mb = 2 ** 20
+    weights = (24 * blk.weight_bytes + pre.weight_bytes + post.weight_bytes) / mb
+    assert weights == pytest.approx(2705.0, rel=0.01)                      # fp16 weights of 1.3 B parameters
+    states = weights + 2 * weights + 6 * weights / 2                       # + fp32 gradients + Adam state / dp
+    assert states == pytest.approx(16230.0, rel=0.01)
+    assert 24 * blk.input_bytes / mb == pytest.approx(3072.0, rel=0.01)    # kept inputs of the 24 checkpointed blocks
+    assert fwd == pytest.approx(states + 3072.0 + blk.fwd_peak / mb + post.saved / mb, rel=0.02)
+    assert fwd == pytest.approx(23372.6, rel=0.02) and bwd == pytest.approx(26892.7, rel=0.02)
+    # the same account with the reference's executor choices lands on its own prediction
+    ref_like = (weights + weights + 6 * weights / 2) + 24 * blk.input_bytes / 2 / mb + (fwd - states - 3072.0)
+    assert ref_like == pytest.approx(19255.0, rel=0.04)

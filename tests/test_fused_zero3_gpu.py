@@ -146,10 +146,15 @@ def _engine_worker(rank, world, port, ret):
                 "strategy.pre_post_strategy_array=[2,2,1,1,1,1,0,0,0,0]"]
         prov = get_inputs_provider("gpt2")
         out = {}
-        for mode in ("nccl", "fused"):
-            cfg, _ = load_config("config", base + [f"+zero3_gather={mode}"], check_world_size=False)
+        # "library": every collective on NCCL; "nccl" / "fused": the data-parallel gradient path on the fused
+        # NVLink kernel (the default on one node) with the weight gather prefetched by NCCL / fused into the
+        # first GEMM of each block
+        for mode in ("library", "nccl", "fused"):
+            extra = ["+zero3_gather=nccl", "+comm_backend=nccl"] if mode == "library" else [f"+zero3_gather={mode}"]
+            cfg, _ = load_config("config", base + extra, check_world_size=False)
             sess = TrainingSession(cfg, seed=0, hp=dict(lr=1e-3))
             assert (sess.engine.param_gather is not None) == (mode == "fused")
+            assert (sess.engine.fused is not None) == (mode != "library")
             losses = []
             for it in range(3):
                 b = prov(4, 128, 1024, "cuda", seed=100 * it + rank)
@@ -159,7 +164,8 @@ def _engine_worker(rank, world, port, ret):
             native.check_status()
             out[mode] = (losses, torch.cat([u.master.detach().float().cpu() for u in sess.engine.units]))
             del sess
-        ret[rank] = (out["nccl"][0], out["fused"][0], _rel(out["fused"][1], out["nccl"][1]))
+        ret[rank] = (out["library"][0], out["fused"][0], max(_rel(out["fused"][1], out["library"][1]),
+                                                             _rel(out["nccl"][1], out["library"][1])))
     finally:
         dist.destroy_process_group()
 
