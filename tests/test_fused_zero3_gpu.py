@@ -80,7 +80,7 @@ def test_emulated_ranks_large_tiles_on_cta_pairs():
     assert _rel(y, ref) < 1e-2
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, h=512, ffn=2048, M=1024, n_gather=4, chunk_bytes=256 << 10):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -89,10 +89,9 @@ def _worker(rank, world, port, ret):
         from mist_b200.ops import native
         from mist_b200.parallel.fused_zero3 import ParamGatherContext
         g = dist.new_group(list(range(world)))
-        h, ffn, M = 512, 2048, 1024
         offs, numel = _layout(h, ffn)
         padded = (numel + 128 * world - 1) // (128 * world) * (128 * world)
-        ctx = ParamGatherContext(g, padded, n_gather=4, chunk_bytes=256 << 10)
+        ctx = ParamGatherContext(g, padded, n_gather=n_gather, chunk_bytes=chunk_bytes)
         sh = ctx.shard_numel
         errs = []
         for it in range(3):
@@ -115,13 +114,18 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_two_gpus_gather_and_gemm():
+@pytest.mark.parametrize("shape", ["small", "gpt3-2.7b block"])
+def test_two_gpus_gather_and_gemm(shape):
+    """Every rank seeds the same full parameter vector, stages only its own shard and must end up with the
+    whole vector bit for bit, and with the right product.  The second case is a whole GPT-3 2.7B block
+    (78.7 M parameters, 157 MB) with the wrapper's own choice of gather CTAs and 1 MiB chunks."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     mgr = mp.Manager()
     ret = mgr.dict()
     port = free_port()
-    mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
+    args = (2, port, ret) if shape == "small" else (2, port, ret, 2560, 9 * 2560, 8192, 0, 1 << 20)
+    mp.spawn(_worker, args=args, nprocs=2, join=True)
     for r in range(2):
         for mismatch, err in ret[r]:
             assert mismatch == 0.0 and err < 1e-2, (r, ret[r])
