@@ -233,11 +233,8 @@ def main():
                        "l2": "per-step working set (weights+activations, tens of GB) far exceeds the 126 MB L2",
                        "gemm_backend": F.Settings.gemm_backend, "attn_backend": F.Settings.attn_backend,
                        "comm_backend": session.comm_backend,
-                       # opt-in kernel variants (all off unless the environment turns them on)
-                       "kernel_variants": {"attn_fwd_split_producers": bool(F.Settings.attn_fwd_split_producers),
-                                           "attn_fwd_exp_emulation": int(F.Settings.attn_fwd_exp_emulation),
-                                           "attn_bwd_pipelined": bool(F.Settings.attn_bwd_pipelined),
-                                           "norm_variant": int(os.environ.get("MB_NORM_VARIANT", "0") or 0)}},
+                       "kernel_variants": {"attn_bwd_pipelined": bool(F.Settings.attn_bwd_pipelined),
+                                           "norm_pipe": str(F.Settings.norm_pipe)}},
             "model_tflops_per_gpu": flops / world / (ms_per_step / 1e3) / 1e12,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,

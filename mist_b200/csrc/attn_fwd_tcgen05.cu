@@ -66,15 +66,8 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 
-// SPLIT: the V tiles are requested by a producer warp of their own (warp 6) instead of by the thread
-// that also requests K.  In the single-producer loop the request for K of block j+1 sits behind the
-// wait for V's stage of block j (free only after the PV product of block j-2), so it is issued about
-// one block time before the S product needs it; with two producers K is requested as soon as the S
-// product of block j-1 has read its stage, two block times ahead.
-// EMU: every EMU-th exponential of the softmax loop is computed on the FMA pipe (mb::poly_exp2) instead
-// of the special-function unit; 0 = none.
-template <int BN, bool SPLIT, int EMU>
-__global__ void __launch_bounds__(kThreads + (SPLIT ? 32 : 0), (BN == 64 ? 2 : 1))
+template <int BN>
+__global__ void __launch_bounds__(kThreads, (BN == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   using L = Smem<BN>;
@@ -165,27 +158,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_expect_tx(&k_full[st], p.nchunks * chunk_kv);
         for (int c = 0; c < p.nchunks; ++c)
           tma_load_4d(sk_ + c * chunk_kv, &tm_k, &k_full[st], 64 * c, head_kv, j * BN, batch);
-        if (SPLIT) continue;      // warp 6 requests V
         if (j >= kStages && !mbar_wait(&kv_empty[st], ((j / kStages) - 1) & 1)) {
           report(p.status, MB_ERR_TIMEOUT_EMPTY);
           ok = false;
           break;
         }
-        mbar_expect_tx(&v_full[st], p.nchunks * chunk_kv);
-        for (int c = 0; c < p.nchunks; ++c)
-          tma_load_4d(sv_ + c * chunk_kv, &tm_v, &v_full[st], 64 * c, head_kv, j * BN, batch);
-      }
-    }
-  } else if (SPLIT && warp == 6) {
-    // ---------------------------------------------------------- TMA producer for V
-    if (lane == 0) {
-      for (int j = 0; j < nblocks; ++j) {
-        int st = j % kStages;
-        if (j >= kStages && !mbar_wait(&kv_empty[st], ((j / kStages) - 1) & 1)) {
-          report(p.status, MB_ERR_TIMEOUT_EMPTY);
-          break;
-        }
-        uint8_t* sv_ = smem + L::oV + st * L::kKV;
         mbar_expect_tx(&v_full[st], p.nchunks * chunk_kv);
         for (int c = 0; c < p.nchunks; ++c)
           tma_load_4d(sv_ + c * chunk_kv, &tm_v, &v_full[st], 64 * c, head_kv, j * BN, batch);
@@ -316,9 +293,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int i = 0; i < BN; i += 2) {
         const float xa = fmaf(__uint_as_float(sr[i]), p.scale_log2, m_neg);
         const float xc = fmaf(__uint_as_float(sr[i + 1]), p.scale_log2, m_neg);
-        constexpr int kEmu = EMU ? EMU : 1;
-        float a = (EMU != 0 && (i % kEmu) == kEmu - 1) ? mb::poly_exp2(xa) : mb::fast_exp2(xa);
-        float c = (EMU != 0 && ((i + 1) % kEmu) == kEmu - 1) ? mb::poly_exp2(xc) : mb::fast_exp2(xc);
+        const float a = mb::fast_exp2(xa);
+        const float c = mb::fast_exp2(xc);
         sum0 += a;
         sum1 += c;
         pk[i >> 1] = pack_bf16x2(a, c);
@@ -437,16 +413,9 @@ bool make_map(CUtensorMap* m, const void* base, int batch, int tokens, int heads
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int g_fwd_variant = 0;      // block size 64: bit 0 separate producer warp for V; bits 1-2 share of exponentials on the FMA pipe
-
 }  // namespace
 
 MB_API int* mb_status_device_ptr();
-
-// Chooses the forward kernel for later calls with block size 64.  Bit 0: K and V requested by two
-// producer warps instead of one thread.  Bits 1-2: 0 = every exponential on the special-function
-// unit, 1 = every fourth on the FMA pipe, 2 = every second.  0 is the default kernel.
-MB_API void mb_attn_fwd_set_variant(int v) { g_fwd_variant = (v >= 0 && v <= 5) ? v : 0; }
 
 // q: [batch][sq][nh][d], k/v: [batch][sk][nh_kv][d], element strides given per tensor
 // (so views into a packed qkv buffer work).  o: [batch][sq][nh][d] with its own strides.
@@ -484,29 +453,19 @@ MB_API int mb_attn_fwd(const void* q, const void* k, const void* v, void* o, flo
   p.seqlens_k = seqlens_k;
   p.status = mb_status_device_ptr();
   dim3 grid((sq + BM - 1) / BM, nh, batch);
-#define MB_ATTN_LAUNCH(BN_, SPLIT_, EMU_)                                                          \
+#define MB_ATTN_LAUNCH(BN_)                                                                        \
   do {                                                                                             \
-    auto kern = attn_fwd_kernel<BN_, SPLIT_, EMU_>;                                                \
+    auto kern = attn_fwd_kernel<BN_>;                                                              \
     static bool cfg = false;                                                                       \
     if (!cfg) {                                                                                    \
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
                                Smem<BN_>::kTotal) != cudaSuccess) return -3;                       \
       cfg = true;                                                                                  \
     }                                                                                              \
-    kern<<<grid, kThreads + (SPLIT_ ? 32 : 0), Smem<BN_>::kTotal, stream>>>(tq, tk, tv, p);        \
+    kern<<<grid, kThreads, Smem<BN_>::kTotal, stream>>>(tq, tk, tv, p);                            \
   } while (0)
-  if (bn == 64) {
-    const bool split = (g_fwd_variant & 1) != 0;
-    const int emu = (g_fwd_variant >> 1) & 3;      // 0: none, 1: every fourth, 2: every second
-    if (!split && emu == 0) MB_ATTN_LAUNCH(64, false, 0);
-    else if (split && emu == 0) MB_ATTN_LAUNCH(64, true, 0);
-    else if (!split && emu == 1) MB_ATTN_LAUNCH(64, false, 4);
-    else if (split && emu == 1) MB_ATTN_LAUNCH(64, true, 4);
-    else if (!split) MB_ATTN_LAUNCH(64, false, 2);
-    else MB_ATTN_LAUNCH(64, true, 2);
-  } else {
-    MB_ATTN_LAUNCH(128, false, 0);
-  }
+  if (bn == 64) MB_ATTN_LAUNCH(64);
+  else MB_ATTN_LAUNCH(128);
 #undef MB_ATTN_LAUNCH
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -103,19 +103,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x without the special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a
-// cubic (relative error 7.5e-5, far below bf16 rounding), 2^n by adding n to the exponent field.
-// Inputs below -125 (including -inf) give 2^-125.  Lets a softmax loop split its exponentials between
-// the special-function unit (4 lanes per scheduler) and the FMA pipe.
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;          // 1.5 * 2^23: the low mantissa bits of t hold round(x)
-  const float f = x - (t - 12582912.f);
-  float p = fmaf(0.05517166f, f, 0.24261112f);
-  p = fmaf(p, f, 0.69326099f);
-  p = fmaf(p, f, 0.99992807f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
 }  // namespace mb

@@ -36,6 +36,7 @@
 // weight cast), disabled in the reference's models (mist/model/transformer.py:477-479).
 #include "sm100_pair.cuh"
 #include <string.h>
+#include <algorithm>
 
 using namespace sm100;
 
@@ -54,6 +55,9 @@ constexpr int kCopyBytes = 16384;
 // be pending then, so the wait before a load never drains the whole store queue.
 constexpr int kCopyLoads = 6;
 constexpr int kCopyStoresPending = kCopyBufs - 1 - kCopyLoads;
+constexpr int kSubBytes = 16 * kCopyBytes;  // unit of work of a gather CTA
+constexpr int kPublishLag = 6;              // a sub-chunk is counted once this many younger stores were issued
+constexpr int kAgCounterOffset = 2048;      // AG: the chunk counters follow the chunk flags at this index
 
 enum Mode : int { MODE_AG = 1, MODE_RS = 2, MODE_AGW = 3 };
 
@@ -69,6 +73,7 @@ struct CommParams {
   const uint8_t* a_peer[kMaxRanks];
   uint8_t* a_local;
   int* chunk_flags;                     // local: [nranks][chunks_per_rank]
+  int* chunk_cnt;                       // local, same shape, zero between launches: finished sub-chunks per chunk
   // weight-AG: layout of the flat parameter buffer (bytes)
   unsigned long long shard_bytes, chunk_bytes, b_off, bias_off;
   int chunks_per_rank;
@@ -265,89 +270,161 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   if (is_gather) {
     // ------------------------------------------------------------------ gather CTAs
+    // The remote chunks are cut into sub-chunks of kSubBytes, dealt to the gather CTAs in fetch order, so that
+    // every gather CTA works on the chunk that the GEMM needs next (a whole chunk on one CTA would arrive only
+    // after ~100 us).  A CTA streams the 16 KB pieces of all its sub-chunks through one ring without draining
+    // it in between, counts a finished sub-chunk on the chunk's counter once its stores have completed, and the
+    // CTA that counts the last one publishes the chunk's flag.
     if (threadIdx.x == 0) {
       const int g = blockIdx.x - n_compute;
       uint8_t* bufs = smem;                                              // reuse the stage area
-      uint32_t issued = 0, stored = 0;
       bool ok = true;
       unsigned ready_mask = 0;
-
-      // Copies `bytes` from a peer to local memory through the shared-memory ring, keeping up to
-      // kCopyBufs loads in flight, then publishes `flag`.
-      auto copy_chunk = [&](int r, const uint8_t* src, uint8_t* dst, size_t bytes, int* flag) {
-        if (!(ready_mask >> r & 1u)) {
-          ok = wait_flag(my_flags + r, p.epoch, true, p.wait_ns, p.status);
-          if (!ok) return;
-          ready_mask |= 1u << r;
+      const bool ag = (p.mode == MODE_AG);
+      const size_t row_bytes = static_cast<size_t>(p.K) * 2;
+      const unsigned long long cbytes = ag ? static_cast<unsigned long long>(BM) * row_bytes : p.chunk_bytes;
+      const int cpr = ag ? ag_chunks_per_rank : p.chunks_per_rank;
+      const int subs = static_cast<int>((cbytes + kSubBytes - 1) / kSubBytes);
+      const int total_subs = (R - 1) * cpr * subs;      // < 2^31: at most a few thousand per GB
+      // weight-AG: the rank that owns the first weights of this GEMM, and the chunk they start in
+      int r0 = -1, c0 = 0;
+      if (!ag) {
+        const unsigned long long first = p.b_off + static_cast<unsigned long long>(p.n_shift) * BN * p.K * 2;
+        r0 = static_cast<int>(first / p.shard_bytes);
+        c0 = static_cast<int>((first - r0 * p.shard_bytes) / p.chunk_bytes);
+      }
+      struct Seg {
+        const uint8_t* src;
+        uint8_t* dst;
+        uint32_t bytes;
+        int flag, expected, r;
+      };
+      // q-th sub-chunk in fetch order; false when it lies beyond the end of a short last chunk.
+      //   AG: the peers in turn, starting with the next rank (every rank reads from a different source);
+      //   weight-AG: the peers' chunks alternate, each peer's in address order (the owner of the first weights
+      //   from the chunk they start in), so that a rank reads from all peers at once: every rank needs the
+      //   same weights first, and one source could not feed all readers at the full rate.
+      auto segment = [&](int q, Seg& s) -> bool {
+        const int w = q / subs;
+        const int sub = q - w * subs;
+        int r, c;
+        unsigned long long bytes, off;
+        if (ag) {
+          const int k = w / cpr;
+          c = w - k * cpr;
+          r = (p.me + 1 + k) % R;
+          off = (static_cast<unsigned long long>(r) * p.rows_per_rank + static_cast<unsigned long long>(c) * BM) * row_bytes;
+          bytes = cbytes;
+        } else {
+          const int i = w / (R - 1);
+          const int k = w - i * (R - 1);
+          r = (p.me + 1 + k) % R;
+          c = (r == r0) ? (c0 + i) % cpr : i;
+          const unsigned long long in_shard = static_cast<unsigned long long>(c) * p.chunk_bytes;
+          bytes = min(p.chunk_bytes, p.shard_bytes - in_shard);
+          off = static_cast<unsigned long long>(r) * p.shard_bytes + in_shard;
         }
-        const int pieces = static_cast<int>((bytes + kCopyBytes - 1) / kCopyBytes);
-        int ld = 0, stp = 0;
-        while (stp < pieces && ok) {
-          while (ld < pieces && issued - stored < kCopyLoads) {
-            const uint32_t b = issued % kCopyBufs;
-            if (issued >= kCopyBufs) tma_wait_read<kCopyStoresPending>();   // the store that last used this buffer has read it
-            const uint32_t nb = static_cast<uint32_t>(min(static_cast<size_t>(kCopyBytes),
-                                                         bytes - static_cast<size_t>(ld) * kCopyBytes));
-            mbar_expect_tx(&copy_bar[b], nb);
-            bulk_load(bufs + b * kCopyBytes, src + static_cast<size_t>(ld) * kCopyBytes, nb, &copy_bar[b]);
-            ++issued;
-            ++ld;
+        const unsigned long long lo = static_cast<unsigned long long>(sub) * kSubBytes;
+        if (lo >= bytes) return false;
+        s.src = p.a_peer[r] + off + lo;
+        s.dst = p.a_local + off + lo;
+        s.bytes = static_cast<uint32_t>(min(static_cast<unsigned long long>(kSubBytes), bytes - lo));
+        s.flag = r * cpr + c;
+        s.expected = (bytes == cbytes) ? subs : static_cast<int>((bytes + kSubBytes - 1) / kSubBytes);
+        s.r = r;
+        return true;
+      };
+      struct Cursor {
+        int q;
+        int piece, pieces;
+        bool live;
+        Seg s;
+      };
+      auto seek = [&](Cursor& c) {           // moves to this CTA's next sub-chunk that has bytes, from c.q on
+        c.live = false;
+        for (; c.q < total_subs; c.q += p.n_gather) {
+          if (segment(c.q, c.s)) {
+            c.live = true;
+            c.piece = 0;
+            c.pieces = static_cast<int>((c.s.bytes + kCopyBytes - 1) / kCopyBytes);
+            return;
           }
-          const uint32_t b = stored % kCopyBufs;
-          if (!mbar_wait(&copy_bar[b], (stored / kCopyBufs) & 1)) {
-            report(p.status, MB_ERR_TIMEOUT_FULL);
-            ok = false;
-            break;
-          }
-          const uint32_t nb = static_cast<uint32_t>(min(static_cast<size_t>(kCopyBytes),
-                                                       bytes - static_cast<size_t>(stp) * kCopyBytes));
-          bulk_store(dst + static_cast<size_t>(stp) * kCopyBytes, bufs + b * kCopyBytes, nb);
-          tma_commit();
-          ++stored;
-          ++stp;
-        }
-        if (ok) {
-          tma_wait_all<0>();          // the chunk is in local memory
-          fence_proxy_async_all();
-          __threadfence();
-          st_release_gpu(flag, p.epoch);
         }
       };
-
-      if (p.mode == MODE_AG) {
-        const size_t row_bytes = static_cast<size_t>(p.K) * 2;
-        const size_t chunk_bytes = static_cast<size_t>(BM) * row_bytes;    // one flag per 128-row block
-        const int chunks_per_rank = ag_chunks_per_rank;
-        int work = 0;
-        for (int k = 0; k < R - 1 && ok; ++k) {
-          const int r = (p.me + 1 + k) % R;
-          for (int c = 0; c < chunks_per_rank && ok; ++c, ++work) {
-            if (work % p.n_gather != g) continue;
-            const size_t off = (static_cast<size_t>(r) * p.rows_per_rank + static_cast<size_t>(c) * BM) * row_bytes;
-            copy_chunk(r, p.a_peer[r] + off, p.a_local + off, chunk_bytes, p.chunk_flags + r * chunks_per_rank + c);
+      Cursor ld, st;
+      ld.q = st.q = g;
+      seek(ld);
+      seek(st);
+      uint32_t issued = 0, stored = 0;
+      // sub-chunks whose last store has been issued but not yet counted: (flag, expected, stores issued by then)
+      constexpr int kFifo = 8;
+      int f_flag[kFifo], f_expected[kFifo];
+      uint32_t f_mark[kFifo];
+      uint32_t f_head = 0, f_tail = 0;
+      auto count_done = [&](int flag, int expected) {
+        fence_proxy_async_all();
+        __threadfence();
+        const int old = atomicAdd(p.chunk_cnt + flag, 1);
+        if (old == expected - 1) {
+          p.chunk_cnt[flag] = 0;                    // for the next launch
+          __threadfence();
+          st_release_gpu(p.chunk_flags + flag, p.epoch);
+        }
+      };
+      while (st.live && ok) {
+        while (ld.live && issued - stored < kCopyLoads) {
+          if (!(ready_mask >> ld.s.r & 1u)) {
+            ok = wait_flag(my_flags + ld.s.r, p.epoch, true, p.wait_ns, p.status);
+            if (!ok) break;
+            ready_mask |= 1u << ld.s.r;
+          }
+          const uint32_t b = issued % kCopyBufs;
+          if (issued >= kCopyBufs) tma_wait_read<kCopyStoresPending>();   // the store that last used this buffer has read it
+          const uint32_t nb = min(static_cast<uint32_t>(kCopyBytes), ld.s.bytes - static_cast<uint32_t>(ld.piece) * kCopyBytes);
+          mbar_expect_tx(&copy_bar[b], nb);
+          bulk_load(bufs + b * kCopyBytes, ld.s.src + static_cast<size_t>(ld.piece) * kCopyBytes, nb, &copy_bar[b]);
+          ++issued;
+          if (++ld.piece == ld.pieces) {
+            ld.q += p.n_gather;
+            seek(ld);
           }
         }
-      } else {
-        // flat parameter buffer: chunks in address order starting at the one that holds the first
-        // weights this GEMM needs, wrapping around; the local shard is skipped
-        const int cpr = p.chunks_per_rank;
-        const int total = R * cpr;
-        const unsigned long long first = p.b_off + static_cast<unsigned long long>(p.n_shift) * BN * p.K * 2;
-        const int r0 = static_cast<int>(first / p.shard_bytes);
-        const int g0 = r0 * cpr + static_cast<int>((first - r0 * p.shard_bytes) / p.chunk_bytes);
-        int work = 0;
-        for (int i = 0; i < total && ok; ++i) {
-          const int gi = (g0 + i) % total;
-          const int r = gi / cpr, c = gi - r * cpr;
-          if (r == p.me) continue;
-          if ((work++) % p.n_gather != g) continue;
-          const unsigned long long in_shard = static_cast<unsigned long long>(c) * p.chunk_bytes;
-          const size_t bytes = static_cast<size_t>(min(p.chunk_bytes, p.shard_bytes - in_shard));
-          const size_t off = static_cast<size_t>(r * p.shard_bytes + in_shard);
-          copy_chunk(r, p.a_peer[r] + off, p.a_local + off, bytes, p.chunk_flags + gi);
+        if (!ok) break;
+        const uint32_t b = stored % kCopyBufs;
+        if (!mbar_wait(&copy_bar[b], (stored / kCopyBufs) & 1)) {
+          report(p.status, MB_ERR_TIMEOUT_FULL);
+          ok = false;
+          break;
+        }
+        const uint32_t nb = min(static_cast<uint32_t>(kCopyBytes), st.s.bytes - static_cast<uint32_t>(st.piece) * kCopyBytes);
+        bulk_store(st.s.dst + static_cast<size_t>(st.piece) * kCopyBytes, bufs + b * kCopyBytes, nb);
+        tma_commit();
+        ++stored;
+        if (++st.piece == st.pieces) {
+          f_flag[f_tail % kFifo] = st.s.flag;
+          f_expected[f_tail % kFifo] = st.s.expected;
+          f_mark[f_tail % kFifo] = stored;
+          ++f_tail;
+          st.q += p.n_gather;
+          seek(st);
+        }
+        // stores complete in order: all but the kPublishLag youngest are done after this wait
+        if (f_head != f_tail && stored - f_mark[f_head % kFifo] >= kPublishLag) {
+          tma_wait_all<kPublishLag>();
+          while (f_head != f_tail && stored - f_mark[f_head % kFifo] >= kPublishLag) {
+            count_done(f_flag[f_head % kFifo], f_expected[f_head % kFifo]);
+            ++f_head;
+          }
         }
       }
-      if (!ok) tma_wait_all<0>();
+      tma_wait_all<0>();
+      if (ok) {
+        for (; f_head != f_tail; ++f_head) count_done(f_flag[f_head % kFifo], f_expected[f_head % kFifo]);
+      } else {
+        // loads still in flight land in this CTA's shared memory: wait for them (bounded) before leaving
+        for (; stored < issued; ++stored)
+          if (!mbar_wait(&copy_bar[stored % kCopyBufs], (stored / kCopyBufs) & 1)) break;
+      }
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -665,6 +742,22 @@ int launch(bool b_mn, bool pair, int grid, cudaStream_t stream, const CUtensorMa
               : launch_t<false, false>(grid, stream, ta, tb, tc, acc, p);
 }
 
+// Gather CTAs for a launch that brings `inbound` bytes over NVLink beside a GEMM of `flops`.  One gather CTA keeps
+// 96 KB in flight and moved 13-15 GB/s in measurements; the link stops scaling near 520 GB/s; the GEMM slows down by
+// the share of SMs that it gives up.  More CTAs are taken only for a clear gain.
+int pick_gather_ctas(double inbound, double flops) {
+  const int cand[] = {8, 16, 24, 32, 48, 64};
+  double best = 1e30;
+  int arg = 8;
+  for (int n : cand) {
+    const double t_gather = inbound / std::min(n * 14e9, 520e9);
+    const double t_gemm = flops / 1.4e15 * g_sms / (g_sms - n);
+    const double t = std::max(t_gather, t_gemm);
+    if (t < best * 0.97) best = t, arg = n;
+  }
+  return arg;
+}
+
 // Grid for one launch: `n_gather` gather CTAs after the compute CTAs; with pairs both counts are even.
 int plan_grid(bool pair, long tiles, int& n_gather) {
   if (pair) {
@@ -687,7 +780,7 @@ MB_API int* mb_status_device_ptr();
 // [M/R][N] that rank r keeps for tiles from this rank (nothing to zero; sum the slots with mb_rs_sum after the
 // launch).  acc_bf16 = 0 / 1 (add form): acc_ptrs[r] = rank r's fp32 / bf16 accumulator [M/R][N], zeroed by its
 // owner before the launch.  B: [N][K] (b_mn = 0) or [K][N] (b_mn = 1).  chunk_flags: local int array
-// [R][M/R/128] (AG only).  flag_ptrs[r]: per-rank flag block (2R + 1 ints) reserved for this call site; `epoch`
+// of 4096 (AG only: flags [R][M/R/128] from 0, counters of the same shape from 2048; zero before the first launch).  flag_ptrs[r]: per-rank flag block (2R + 1 ints) reserved for this call site; `epoch`
 // counts launches on it from 1.  M/R must be a multiple of 128, K of 8.
 MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void* B, void* C, void* const* acc_ptrs,
                         void* const* flag_ptrs, int* chunk_flags, int M, int N, int K, int ldb, int ldc, int b_mn,
@@ -706,11 +799,17 @@ MB_API int mb_gemm_comm(int mode, void* const* a_ptrs, const void* A, const void
   p.M = M; p.N = N; p.K = K; p.mode = mode;
   p.nranks = nranks; p.me = me; p.epoch = epoch;
   p.rows_per_rank = rows_per_rank;
-  p.n_gather = (mode == MODE_AG) ? (n_gather > 0 ? n_gather : 8) : 0;
+  if (mode == MODE_AG && M / BM > kAgCounterOffset) return -1;
+  p.n_gather = 0;
+  if (mode == MODE_AG)
+    p.n_gather = n_gather > 0 ? n_gather
+                              : pick_gather_ctas(2.0 * (M - rows_per_rank) * static_cast<double>(K),
+                                                 2.0 * M * static_cast<double>(N) * K);
   p.acc_bf16 = acc_bf16 ? 1 : 0;
   p.rs_store = (acc_bf16 == 2) ? 1 : 0;
   if (nranks == 1) p.n_gather = 0, p.mode = (mode == MODE_AG) ? MODE_AG : MODE_RS;
   p.chunk_flags = chunk_flags;
+  p.chunk_cnt = chunk_flags ? chunk_flags + kAgCounterOffset : nullptr;
   p.C = C; p.ldc = ldc;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.status = mb_status_device_ptr();
@@ -756,7 +855,7 @@ MB_API int mb_gemm_comm_last_pair(void) { return g_last_pair; }
 //              shard [r * shard_elems, (r + 1) * shard_elems) must be valid there before the launch.
 //   C[M][N] = A[M][K] * W^T (+ bias), W = [N][K] row-major at element b_off of the flat buffer, bias (N
 //   elements) at bias_off or none when bias_off < 0.  On return of the kernel the local flat buffer holds
-//   every rank's shard.  chunk_flags: local int array [R][ceil(shard_bytes / chunk_bytes)], zero before the
+//   every rank's shard.  chunk_flags: local int array [2][R][ceil(shard_bytes / chunk_bytes)] (flags, then counters), zero before the
 //   first launch.  shard_elems % 8 == 0, chunk_bytes % 16 == 0, b_off % 8 == 0, K % 8 == 0.
 MB_API int mb_gemm_param_gather(void* const* w_ptrs, const void* A, void* C, void* const* flag_ptrs,
                                 int* chunk_flags, int M, int N, int K, int ldc, long long b_off, long long bias_off,
@@ -776,11 +875,11 @@ MB_API int mb_gemm_param_gather(void* const* w_ptrs, const void* A, void* C, voi
   p.M = M; p.N = N; p.K = K; p.mode = MODE_AGW;
   p.nranks = nranks; p.me = me; p.epoch = epoch;
   p.rows_per_rank = M;
-  // Gather CTAs pull ~15 GB/s each (measured); 32 of them when fetching the remote shards takes longer than
-  // the GEMM itself, 16 when the GEMM dominates and needs the SMs more.
-  const double gather_s = static_cast<double>(shard_elems) * 2.0 * (nranks - 1) / 450e9;
-  const double gemm_s = 2.0 * M * static_cast<double>(N) * K / 1.4e15;
-  p.n_gather = nranks > 1 ? (n_gather > 0 ? n_gather : (gather_s > gemm_s ? 32 : 16)) : 0;
+  p.n_gather = 0;
+  if (nranks > 1)
+    p.n_gather = n_gather > 0 ? n_gather
+                              : pick_gather_ctas(static_cast<double>(shard_elems) * 2.0 * (nranks - 1),
+                                                 2.0 * M * static_cast<double>(N) * K);
   p.chunk_flags = chunk_flags;
   p.C = C; p.ldc = ldc;
   p.status = mb_status_device_ptr();
@@ -788,6 +887,7 @@ MB_API int mb_gemm_param_gather(void* const* w_ptrs, const void* A, void* C, voi
   p.shard_bytes = static_cast<unsigned long long>(shard_elems) * 2;
   p.chunk_bytes = static_cast<unsigned long long>(chunk_bytes);
   p.chunks_per_rank = static_cast<int>((p.shard_bytes + p.chunk_bytes - 1) / p.chunk_bytes);
+  p.chunk_cnt = chunk_flags + static_cast<long>(nranks) * p.chunks_per_rank;
   p.b_off = static_cast<unsigned long long>(b_off) * 2;
   for (int r = 0; r < nranks; ++r) {
     p.flags[r] = reinterpret_cast<int*>(flag_ptrs[r]);

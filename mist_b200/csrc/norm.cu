@@ -116,94 +116,6 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __res
   }
 }
 
-// One warp per row: the row lives in the warp's registers (NV 16-byte vectors per lane, lane l holds
-// vectors l, l + 32, ...), the two row sums are warp shuffles, and nothing in the loop is a CTA-wide
-// barrier, so every warp keeps its loads in flight independently of the others.  Same arithmetic and
-// rounding points as norm_fwd_kernel.  For hidden sizes up to 8 * 32 * NV (NV <= 10 keeps the row and
-// the residual in 128 registers without spills).
-template <bool RMS, int NV>
-__global__ void __launch_bounds__(256, 2)
-norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x0, const __nv_bfloat16* __restrict__ residual,
-                     const __nv_bfloat16* __restrict__ gamma, const __nv_bfloat16* __restrict__ beta,
-                     __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ x_out,
-                     float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int h, float eps) {
-  const int lane = threadIdx.x & 31;
-  const int warps_per_cta = blockDim.x >> 5;
-  const int nvec = h >> 3;
-  for (int row = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_cta) {
-    const size_t base = static_cast<size_t>(row) * h;
-    mb::bf16x8 xp[NV];
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int vi = lane + 32 * i;
-      if (vi < nvec) xp[i] = *reinterpret_cast<const mb::bf16x8*>(x0 + base + 8 * vi);
-    }
-    if (residual) {
-      mb::bf16x8 rp[NV];
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int vi = lane + 32 * i;
-        if (vi < nvec) rp[i] = *reinterpret_cast<const mb::bf16x8*>(residual + base + 8 * vi);
-      }
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int vi = lane + 32 * i;
-        if (vi < nvec) {
-          float x[8], r[8];
-          mb::unpack8(xp[i], x);
-          mb::unpack8(rp[i], r);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) x[k] += r[k];
-          xp[i] = mb::pack8(x);
-        }
-      }
-    }
-    float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int vi = lane + 32 * i;
-      if (vi < nvec) {
-        if (x_out) *reinterpret_cast<mb::bf16x8*>(x_out + base + 8 * vi) = xp[i];
-        float x[8];
-        mb::unpack8(xp[i], x);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          a0 += x[k];
-          a1 += x[k] * x[k];
-        }
-      }
-    }
-    a0 = mb::warp_sum(a0);
-    a1 = mb::warp_sum(a1);
-    const float mean = RMS ? 0.f : a0 / h;
-    const float var = a1 / h - mean * mean;
-    const float rstd = rsqrtf(fmaxf(var, 0.f) + eps);
-    if (lane == 0) {
-      if (mean_out) mean_out[row] = mean;
-      rstd_out[row] = rstd;
-    }
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int vi = lane + 32 * i;
-      if (vi < nvec) {
-        float x[8], g[8], o[8];
-        mb::unpack8(xp[i], x);
-        mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(gamma + 8 * vi), g);
-        if (!RMS && beta) {
-          float b[8];
-          mb::unpack8(*reinterpret_cast<const mb::bf16x8*>(beta + 8 * vi), b);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) o[k] = (x[k] - mean) * rstd * g[k] + b[k];
-        } else {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) o[k] = (x[k] - mean) * rstd * g[k];
-        }
-        *reinterpret_cast<mb::bf16x8*>(z + base + 8 * vi) = mb::pack8(o);
-      }
-    }
-  }
-}
-
 template <bool RMS, int VPT>
 __global__ void __launch_bounds__(256, 2)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const __nv_bfloat16* __restrict__ x,
@@ -502,15 +414,6 @@ int pick_vpt(int h) {
   return (nvec <= 2 * 256) ? 2 : 4;
 }
 
-// Kernel variants that are not the default yet: bit 0 = forward with one warp per row (hidden <= 2560),
-// bit 1 = backward that loads the next row group before it reduces the current one (two vectors per thread).
-// MB_NORM_VARIANT sets the start value; mb_norm_set_variant changes it.
-int g_norm_variant = -1;
-int norm_variant() {
-  if (g_norm_variant < 0) g_norm_variant = env_int("MB_NORM_VARIANT", 2);
-  return g_norm_variant;
-}
-
 void pick_shape(int h, int& tpr, int& rpc) {
   const int VPT = pick_vpt(h);
   int nvec = h / 8;
@@ -522,8 +425,6 @@ void pick_shape(int h, int& tpr, int& rpc) {
 }
 
 }  // namespace
-
-MB_API void mb_norm_set_variant(int v) { g_norm_variant = v < 0 ? 0 : v; }
 
 // Number of scratch rows (each of `h` floats, once for dgamma and once for dbeta)
 // that mb_norm_bwd needs for a given problem.
@@ -553,21 +454,6 @@ MB_API int mb_norm_fwd(const void* x0, const void* residual, const void* gamma, 
   auto b = reinterpret_cast<const __nv_bfloat16*>(beta);
   auto zz = reinterpret_cast<__nv_bfloat16*>(z);
   auto xo = reinterpret_cast<__nv_bfloat16*>(x_out);
-  if ((norm_variant() & 1) && h <= 2560) {
-    // one warp per row, eight rows per CTA pass
-    const int nvl = (h / 8 + 31) / 32;      // vectors per lane
-    int wgrid = num_sms() * 4;
-    const int need = (rows + 7) / 8;
-    if (wgrid > need) wgrid = need;
-#define MB_FWDW(R_, N_) norm_fwd_warp_kernel<R_, N_><<<wgrid, 256, 0, stream>>>(a, r, g, b, zz, xo, mean, rstd, rows, h, eps)
-    if (rms) {
-      if (nvl <= 4) MB_FWDW(true, 4); else if (nvl <= 8) MB_FWDW(true, 8); else MB_FWDW(true, 10);
-    } else {
-      if (nvl <= 4) MB_FWDW(false, 4); else if (nvl <= 8) MB_FWDW(false, 8); else MB_FWDW(false, 10);
-    }
-#undef MB_FWDW
-    return cudaGetLastError() == cudaSuccess ? 0 : -4;
-  }
   const bool v2 = pick_vpt(h) == 2;
 #define MB_FWD(R_, V_) norm_fwd_kernel<R_, V_><<<grid, tpr * rpc, 0, stream>>>(a, r, g, b, zz, xo, mean, rstd, rows, h, eps, tpr, rpc)
   if (rms) { if (v2) MB_FWD(true, 2); else MB_FWD(true, 4); }
@@ -598,7 +484,8 @@ MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const f
   auto dxx = reinterpret_cast<__nv_bfloat16*>(dx);
   const bool v2 = pick_vpt(h) == 2;
 #define MB_BWD(K_, R_, V_) K_<R_, V_><<<grid, tpr * rpc, 0, stream>>>(dzz, xx, g, mean, rstd, dr, dxx, pg, pb, rows, h, tpr, rpc)
-  if ((norm_variant() & 2) && v2) {
+  if (v2) {
+    // two vectors per thread: the kernel that loads the next row group before it reduces the current one
     // 121 registers: three CTAs of up to 256 threads stay resident per SM, so the persistent grid is
     // sized for three (the scratch matrix was sized for the larger default grid)
     const int g3 = num_sms() * 3;
@@ -609,9 +496,9 @@ MB_API int mb_norm_bwd(const void* dz, const void* x, const void* gamma, const f
     }
     if (rms) MB_BWD(norm_bwd_prefetch_kernel, true, 2); else MB_BWD(norm_bwd_prefetch_kernel, false, 2);
   } else if (rms) {
-    if (v2) MB_BWD(norm_bwd_kernel, true, 2); else MB_BWD(norm_bwd_kernel, true, 4);
+    MB_BWD(norm_bwd_kernel, true, 4);
   } else {
-    if (v2) MB_BWD(norm_bwd_kernel, false, 2); else MB_BWD(norm_bwd_kernel, false, 4);
+    MB_BWD(norm_bwd_kernel, false, 4);
   }
 #undef MB_BWD
   dim3 fb(32, 32);

@@ -47,14 +47,6 @@ class Settings:
     gemm_backend = "tcgen05"      # "tcgen05" (ours) | "cublas" (library, A/B baseline)
     attn_backend = "tcgen05"      # "tcgen05" (ours) | "sdpa" (library, A/B baseline)
     attn_block_n = 64
-    # Forward kernel with K and V requested by two producer warps (K is then requested two blocks ahead of
-    # its S product instead of one).  Same barriers as the default kernel; not yet timed or checked on a
-    # device, so it is opt-in (also MIST_B200_ATTN_FWD_SPLIT=1).
-    attn_fwd_split_producers = os.environ.get("MIST_B200_ATTN_FWD_SPLIT") == "1"
-    # Share of the forward softmax's exponentials computed on the FMA pipe by a cubic instead of the
-    # special-function unit: 0 none, 1 every fourth, 2 every second (MIST_B200_ATTN_FWD_EMU).  The
-    # arithmetic is checked on the CPU; the kernel variant is opt-in like the one above.
-    attn_fwd_exp_emulation = int(os.environ.get("MIST_B200_ATTN_FWD_EMU", "0") or 0)
     # Backward kernel that overlaps the next block's S / dP products with the current block's softmax
     # (6 % faster than the unpipelined kernel at head sizes 80 and 128; MIST_B200_ATTN_BWD_PIPELINED=0
     # selects the unpipelined one).
@@ -774,8 +766,6 @@ def attn_fwd(q, k, v, scale, causal, block_n=None, seqlens_q=None, seqlens_k=Non
     assert q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1
     o = torch.empty(b, sq, nh, d, dtype=q.dtype, device=q.device)
     lse = torch.empty(b, nh, sq, dtype=torch.float32, device=q.device)
-    _select_variant("mb_attn_fwd_set_variant", (1 if Settings.attn_fwd_split_producers else 0)
-                    | ((int(Settings.attn_fwd_exp_emulation) & 3) << 1))
     call("mb_attn_fwd", ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), b, sq, sk, nh, nkv, d,
          q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
          v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),

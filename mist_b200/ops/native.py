@@ -37,7 +37,6 @@ _SIGNATURES = {
     "mb_gemm_pair_bf16": ([_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p, _p, _f, _i, _p], _i),
     "mb_decode_attn": ([_p, _p, _p, _p, _i, _i, _i, _i, _i, _l, _l, _l, _l, _l, _l, _f, _p], _i),
     "mb_norm_bwd_scratch_rows": ([_i, _i], _i),
-    "mb_norm_set_variant": ([_i], None),
     "mb_norm_fwd": ([_p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _f, _i, _p], _i),
     "mb_norm_bwd": ([_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _p], _i),
     "mb_norm_pipe_parts": ([_i, _i, _i, _i, _i, _i], _i),
@@ -64,7 +63,6 @@ _SIGNATURES = {
     "mb_causal_softmax_bwd": ([_p, _p, _p, _z, _i, _f, _p], _i),
     "mb_adam_step": ([_p, _p, _p, _p, _i, _p, _z, _f, _f, _f, _f, _f, _i, _f, _i, _p], _i),
     "mb_attn_bwd": ([_p] * 11 + [_i] * 5 + [_l] * 18 + [_f, _i, _p, _p, _p], _i),
-    "mb_attn_fwd_set_variant": ([_i], None),
     "mb_attn_fwd": ([_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i] + [_l] * 12 + [_f, _i, _i, _p, _p, _p], _i),
 }
 

