@@ -44,7 +44,7 @@ FLAG_INTS = 32
 class FusedTPContext:
     """Symmetric buffers and flag blocks of one tensor-parallel group."""
 
-    def __init__(self, group, heap_bytes: int, device=None, n_gather: int = 8, emulate_ranks: int = 0):
+    def __init__(self, group, heap_bytes: int, device=None, n_gather: int = 0, emulate_ranks: int = 0):
         self.group = group
         self.n_gather = n_gather
         if emulate_ranks:

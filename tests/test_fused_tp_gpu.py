@@ -138,7 +138,7 @@ def _worker(rank, world, port, ret):
             torch.cuda.synchronize()
             native.check_status()
             errs = {"y": _rel(y, yr), "gx": _rel(gx, gxr), "gw1": _rel(gw1, gw1r), "gw2": _rel(gw2, gw2r),
-                    "gres": _rel(gres, gy), "max_y": ((y.float() - yr.float()).abs() / (yr.float().abs() + 1.0)).max().item()}
+                    "gres": _rel(gres, gy), "max_y": ((y.float() - yr.float()).abs().max() / yr.float().abs().max()).item()}
             # the same inputs give the same bits on every launch, whatever order the peers' tiles arrive in
             if firsts is None:
                 firsts = (y.clone(), gx.clone())
@@ -164,8 +164,9 @@ def test_multi_gpu_matches_nccl_path(world):
         assert ret[r]["repeat"] == 0.0, (r, "results differ between launches")
         for k, v in ret[r].items():
             if k == "max_y":
-                # worst element, relative: bf16 partial sums round once per source and once in the sum,
-                # so two or three units in the last place (2^-8 each) at most
+                # worst element against the largest output: each source's partial product is rounded to bf16
+                # before the sum (as NCCL's bf16 reduce-scatter does), so the error of an element follows the size
+                # of the partials, which cancel, not the size of the element
                 assert v < 0.02, (r, k, v)
             else:
                 assert v < 2e-2, (r, k, v)
