@@ -209,6 +209,14 @@ class StageEvaluator:
                     tpf += comm_t(comm)
                 else:
                     tpb += comm_t(comm)
+        # the host issues a block no faster than it can dispatch its operators: with small micro batches on
+        # many-way tensor-parallel layouts that, not the kernels, bounds the block
+        hd = getattr(self.db, "host_dispatch", None) or {}
+        if hd:
+            host_f = float(hd.get("fwd_s_per_op", 0.0)) * len(nodes)
+            host_b = float(hd.get("bwd_s_per_op", 0.0)) * len(nodes)
+            ef = max(ef, host_f - tpf)
+            eb = max(eb, host_b - tpb)
         num = LayerNumbers(ef, eb, tpf, tpb, self._val(info.fwd.peak, b), self._val(info.bwd.peak, b),
                            self._val(info.fwd.saved, b), self._val(info.input_bytes, b), self._val(info.fwd.output, b),
                            float(info.weight_bytes), float(info.num_params), first_gemm)

@@ -49,15 +49,18 @@ class OpDatabase:
         # An entry holds two timings of its operator: one cold call on a quiet chip (``fwd`` / ``bwd``,
         # boost clock, L2 flushed) and a quarter of a second of back-to-back calls (``fwd_sus`` /
         # ``bwd_sus``) with the SM clock that the chip settled at under that load (``sm_mhz_fwd`` /
-        # ``sm_mhz_bwd``).  A training step keeps the chip at its own power-capped clock; the time of an
-        # operator that is bound by the SMs (tensor cores, exponentials) scales with the inverse of the
-        # clock, so its sustained timing is multiplied by ``sm_mhz / sm_mhz_under_load``.  ``_meta.json``
-        # beside the entries names the operators this applies to and the clock measured under a training
-        # load (the median that bench.py samples during its timed region); nothing in it is fitted to a
-        # training-step time.  Entries without sustained timings fall back to the fixed
+        # ``sm_mhz_bwd``, kept for the record).  A training step keeps the chip at its power limit just as
+        # the back-to-back loop does, so an operator that is bound by the SMs (tensor cores, exponentials;
+        # ``scaled_ops`` in ``_meta.json``) is priced with its sustained timing, every other operator with
+        # its cold timing.  Nothing in the meta file is fitted to a training-step time.  (Scaling the
+        # sustained timing to one clock "under load" for all operators was tried and dropped: that clock
+        # depends on the share of GEMM time in the step; it fitted the 2.7B step and was 18-20 % optimistic
+        # on steps with larger GEMMs.)  Entries without sustained timings fall back to the fixed
         # ``sustained_scale`` of the file applied to the cold timing.
         self.sustained_scale, self.scaled_ops, self.sm_mhz_under_load = 1.0, (), None
         self.fused_overlap = {}
+        #: host seconds per traced operator of a block (tools/profile_host_dispatch.py); empty: no host bound
+        self.host_dispatch = {}
         meta = self.dir / "_meta.json"
         if meta.exists():
             try:
@@ -69,6 +72,7 @@ class OpDatabase:
                     self.sm_mhz_under_load = float(m["sm_mhz_under_load"])
                 # overlap of the fused GEMM + collective kernels: {"ag_gemm": {"kappa", "tau"}, ...}
                 self.fused_overlap = dict(m.get("fused_overlap", {}))
+                self.host_dispatch = dict(m.get("host_dispatch", {}))
             except (json.JSONDecodeError, OSError, ValueError):
                 pass
         self.hits = self.misses = self.profiled = 0
@@ -153,12 +157,8 @@ class OpDatabase:
         fwd, bwd = float(e["fwd"]), float(e["bwd"])
         if op not in self.scaled_ops:
             return fwd, bwd
-        if self.sm_mhz_under_load and e.get("fwd_sus") and e.get("sm_mhz_fwd"):
-            f = float(e["fwd_sus"]) * float(e["sm_mhz_fwd"]) / self.sm_mhz_under_load
-            b = bwd * self.sustained_scale
-            if e.get("bwd_sus") is not None and e.get("sm_mhz_bwd"):
-                b = float(e["bwd_sus"]) * float(e["sm_mhz_bwd"]) / self.sm_mhz_under_load
-            return f, b
+        if e.get("fwd_sus"):
+            return float(e["fwd_sus"]), float(e["bwd_sus"]) if e.get("bwd_sus") is not None else bwd * self.sustained_scale
         return fwd * self.sustained_scale, bwd * self.sustained_scale
 
     def add(self, spec: NodeSpec, fwd: float, bwd: float, **extra):

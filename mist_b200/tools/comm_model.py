@@ -167,8 +167,8 @@ def fit_interference_params(C, G2G, C2G, G2C, measured, x0: Optional[Sequence[fl
 def fit_fused_overlap(rows: List[Dict]) -> Dict[str, Dict[str, float]]:
     """Fits ``fused = max(gemm, coll) + kappa * min(gemm, coll) + tau`` per kind of fused kernel from the rows
     that :mod:`mist_b200.tools.bench_fused_collectives` writes (``fused_ms``, ``gemm_ms``, ``collective_ms``).
-    ``kappa`` is kept in [0, 1] (0: the shorter part is hidden completely, 1: nothing overlaps), ``tau`` >= 0.
-    With a single row per kind ``tau`` stays 0."""
+    ``kappa`` is kept in [0, 1.5] (0: the shorter part is hidden completely, 1: nothing overlaps), ``tau`` >= 0;
+    the fit minimises relative residuals.  With fewer than three rows per kind ``tau`` stays 0."""
     kinds = {"AG->GEMM": "ag_gemm", "GEMM->RS": "gemm_rs", "ZeRO-3": "zero3_gather"}
     groups: Dict[str, List[Tuple[float, float, float]]] = {}
     for r in rows:
@@ -177,20 +177,23 @@ def fit_fused_overlap(rows: List[Dict]) -> Dict[str, Dict[str, float]]:
         for prefix, key in kinds.items():
             if r["kernel"].startswith(prefix):
                 groups.setdefault(key, []).append((r["fused_ms"] * 1e-3, r["gemm_ms"] * 1e-3, r["collective_ms"] * 1e-3))
+    from scipy.optimize import least_squares
     out = {}
     for key, pts in groups.items():
         f = np.array([p[0] for p in pts])
         hi = np.array([max(p[1], p[2]) for p in pts])
         lo = np.array([min(p[1], p[2]) for p in pts])
+
+        def resid(x):
+            return (hi + x[0] * lo + x[1] - f) / f          # relative: short and long kernels weigh the same
+
         if len(pts) >= 3:
-            A = np.stack([lo, np.ones_like(lo)], axis=1)
-            sol, *_ = np.linalg.lstsq(A, f - hi, rcond=None)
-            kappa, tau = float(sol[0]), float(sol[1])
+            sol = least_squares(resid, x0=[0.5, 0.0], bounds=([0.0, 0.0], [1.5, 1e-2]))
+            kappa, tau = float(sol.x[0]), float(sol.x[1])
         else:
-            kappa, tau = float(np.sum((f - hi) * lo) / max(np.sum(lo * lo), 1e-30)), 0.0
-        if tau < 0:
-            kappa, tau = float(np.sum((f - hi) * lo) / max(np.sum(lo * lo), 1e-30)), 0.0
-        out[key] = {"kappa": round(min(max(kappa, 0.0), 1.5), 4), "tau": round(max(tau, 0.0), 7), "rows": len(pts)}
+            sol = least_squares(lambda x: resid([x[0], 0.0]), x0=[0.5], bounds=([0.0], [1.5]))
+            kappa, tau = float(sol.x[0]), 0.0
+        out[key] = {"kappa": round(kappa, 4), "tau": round(tau, 7), "rows": len(pts)}
     return out
 
 
@@ -220,8 +223,33 @@ def fit_all(records: List[Dict]) -> Dict[str, List[float]]:
     return out
 
 
-if __name__ == "__main__":
+def main(argv=None):
+    """``comm_model.py calib.json [more.json ...]`` prints the fitted communication and interference
+    parameters of the calibration records in the files; ``--fused rows.json [...]`` fits the overlap terms of
+    the fused GEMM + collective kernels instead and, with ``--meta <_meta.json>``, writes them into the
+    operator database's meta file under ``fused_overlap``."""
+    import argparse
     import json
-    import sys
-    recs = json.load(open(sys.argv[1]))
-    print(json.dumps(fit_all(recs), indent=1))
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("files", nargs="+")
+    ap.add_argument("--fused", action="store_true", help="the files hold rows of bench_fused_collectives")
+    ap.add_argument("--meta", default=None, help="operator database meta file to update (with --fused)")
+    args = ap.parse_args(argv)
+    recs = []
+    for f in args.files:
+        recs.extend(json.load(open(f)))
+    if not args.fused:
+        print(json.dumps(fit_all(recs), indent=1))
+        return
+    fit = fit_fused_overlap(recs)
+    print(json.dumps(fit, indent=1))
+    if args.meta:
+        meta = json.load(open(args.meta))
+        meta["fused_overlap"] = fit
+        with open(args.meta, "w") as fh:
+            json.dump(meta, fh, indent=1)
+            fh.write("\n")
+
+
+if __name__ == "__main__":
+    main()
