@@ -109,8 +109,10 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
     if prof is not None:
         prof.stop()
     native.check_status()
-    alloc = torch.cuda.max_memory_allocated() if cuda else 0
-    reserved = torch.cuda.max_memory_reserved() if cuda else 0
+    # buffers of the fused NVLink kernels live in symmetric arenas outside torch's allocator
+    from mist_b200.parallel.symm import SymmetricHeap
+    alloc = (torch.cuda.max_memory_allocated() + SymmetricHeap.live_bytes) if cuda else 0
+    reserved = (torch.cuda.max_memory_reserved() + SymmetricHeap.live_bytes) if cuda else 0
     stats = torch.tensor([latency, float(alloc), float(reserved)], dtype=torch.float64, device=dev)
     S = ps.num_stages
     per_stage = torch.zeros(S, 2, dtype=torch.float64, device=dev)

@@ -108,6 +108,10 @@ class LayerNumbers:
     weight_bytes: float
     params: float
     first_gemm_fwd: float = 0.0      # forward seconds of the block's first GEMM (the one a fused weight gather rides on)
+    # seconds the host needs to issue the layer's passes (Python, autograd, launches); a pass takes at least that
+    host_fwd: float = 0.0
+    host_bwd: float = 0.0
+    host_recompute: float = 0.0
 
 
 def fused_time(compute, comm, kappa: float, tau: float):
@@ -209,17 +213,20 @@ class StageEvaluator:
                     tpf += comm_t(comm)
                 else:
                     tpb += comm_t(comm)
-        # the host issues a block no faster than it can dispatch its operators: with small micro batches on
-        # many-way tensor-parallel layouts that, not the kernels, bounds the block
+        # The host issues a layer no faster than it can dispatch its operators.  Measured on a model with
+        # negligible kernels (tools/profile_host_dispatch.py): seconds per block for forward + backward (a third
+        # of it is charged to the forward pass) and for a recomputed forward pass under activation
+        # checkpointing (which costs the host more than a plain one: saved-tensor hooks, RNG state), scaled by
+        # the number of traced operators of this layer.
         hd = getattr(self.db, "host_dispatch", None) or {}
-        if hd:
-            host_f = float(hd.get("fwd_s_per_op", 0.0)) * len(nodes)
-            host_b = float(hd.get("bwd_s_per_op", 0.0)) * len(nodes)
-            ef = max(ef, host_f - tpf)
-            eb = max(eb, host_b - tpb)
+        host = (0.0, 0.0, 0.0)
+        if hd.get("ops_per_block"):
+            k_ops = len(nodes) / float(hd["ops_per_block"])
+            both = float(hd.get("block_fwd_bwd_s", 0.0)) * k_ops
+            host = (both / 3.0, both * 2.0 / 3.0, float(hd.get("block_recompute_s", 0.0)) * k_ops)
         num = LayerNumbers(ef, eb, tpf, tpb, self._val(info.fwd.peak, b), self._val(info.bwd.peak, b),
                            self._val(info.fwd.saved, b), self._val(info.input_bytes, b), self._val(info.fwd.output, b),
-                           float(info.weight_bytes), float(info.num_params), first_gemm)
+                           float(info.weight_bytes), float(info.num_params), first_gemm, *host)
         self._numbers[key] = num
         return num
 
@@ -275,7 +282,7 @@ class StageEvaluator:
 
         def gather(which: str) -> Dict[str, np.ndarray]:
             fields = ("exec_fwd", "exec_bwd", "tp_fwd", "tp_bwd", "fwd_peak", "bwd_peak", "saved", "input_bytes",
-                      "output_bytes", "weight_bytes", "params", "first_gemm_fwd")
+                      "output_bytes", "weight_bytes", "params", "first_gemm_fwd", "host_fwd", "host_bwd", "host_recompute")
             out = {f: np.zeros(N) for f in fields}
             for (t, bb) in set(zip(tp.tolist(), b.tolist())):
                 sel = (tp == t) & (b == bb)
@@ -295,7 +302,7 @@ class StageEvaluator:
             kept = x["input_bytes"] if ckpt else x["saved"]
             shard_params = np.where(u_ore, x["params"] / dp, x["params"])
             opt_bytes = 12.0 * shard_params * u_oo
-            cf = x["exec_fwd"] + x["tp_fwd"]
+            cf = np.maximum(x["exec_fwd"] + x["tp_fwd"], x["host_fwd"])
             ag_all = np.where(u_wre, self._coll("all_gather", W, dp), 0.0)
             ag_fwd = ag_all
             if block and self.zero3_fused and not (self.tp_fused and np.any(tp > 1)):
@@ -308,7 +315,8 @@ class StageEvaluator:
                 ag_fwd = np.where(plain, 0.0, ag_all)
             return dict(
                 cf=cf, ag_fwd=ag_fwd,
-                cb=x["exec_bwd"] + x["tp_bwd"] + ((x["exec_fwd"] + x["tp_fwd"]) if ckpt else 0.0),
+                cb=np.maximum(x["exec_bwd"] + x["tp_bwd"], x["host_bwd"])
+                + (np.maximum(x["exec_fwd"] + x["tp_fwd"], x["host_recompute"]) if ckpt else 0.0),
                 ag=ag_all,
                 rs=np.where(u_gre, self._coll("reduce_scatter", W, dp), 0.0),
                 # only at the last micro batch: the reduction that waited for it, the refresh of the

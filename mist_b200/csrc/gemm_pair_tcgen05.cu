@@ -14,6 +14,7 @@
 // Reference counterpart: the cuBLAS(Lt) calls of csrc/fused_dense_lib/fused_dense_cuda.cu:19-167.
 #include "sm100_pair.cuh"
 #include <string.h>
+#include <stdio.h>
 
 using namespace sm100;
 
@@ -434,6 +435,10 @@ MB_API int* mb_status_device_ptr();
 // multiplication by gelu'(aux) or addition of aux).  Returns 1 without
 // launching when the arguments need the single-CTA kernel (other epilogue flags, unaligned C,
 // fewer than two 256 x 256 tiles); the caller then uses mb_gemm_bf16.
+static char g_pair_err[256] = "";
+// Arguments of the last mb_gemm_pair_bf16 call that got as far as building its tensor maps.
+MB_API const char* mb_gemm_pair_last_error(void) { return g_pair_err; }
+
 MB_API int mb_gemm_pair_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                              int a_mn_major, int b_mn_major, int flags, const void* bias, void* aux, float alpha,
                              int max_ctas, cudaStream_t stream) {
@@ -464,7 +469,10 @@ MB_API int mb_gemm_pair_bf16(const void* A, const void* B, void* C, int M, int N
   if (tiles < max_ctas / 2) return 1;     // cannot fill the machine with 256 x 256 tiles
   CUtensorMap ta, tb, tc, tx;
   memset(&tx, 0, sizeof(tx));
-  // a tensor map that cannot be encoded: -21 (A), -22 (B), -23 (C), -24 (second epilogue operand)
+  // a tensor map that cannot be encoded: -21 (A), -22 (B), -23 (C), -24 (second epilogue operand); the arguments
+  // of the refused call can be read back with mb_gemm_pair_last_error
+  snprintf(g_pair_err, sizeof(g_pair_err), "A=%p B=%p C=%p aux=%p M=%d N=%d K=%d lda=%d ldb=%d ldc=%d a_mn=%d b_mn=%d flags=%d",
+           A, B, C, aux, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, flags);
   if (!(a_mn_major ? make_map(&ta, A, K, M, lda, 64, BK, false, true) : make_map(&ta, A, M, K, lda, 64, BM, false, true)))
     return -21;
   if (!(b_mn_major ? make_map(&tb, B, K, N, ldb, 64, BK, false, true) : make_map(&tb, B, N, K, ldb, 64, BNH, false, true)))

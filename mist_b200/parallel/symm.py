@@ -82,6 +82,9 @@ def group_on_one_node(group) -> bool:
 
 class SymmetricHeap:
     ALIGN = 1024
+    #: bytes of all live arenas of this process: they come from the driver, not from torch's caching allocator,
+    #: so ``torch.cuda.max_memory_allocated`` does not see them (memory reports add this figure)
+    live_bytes = 0
 
     def __init__(self, nbytes: int, group, device=None):
         lib = native.kernels()
@@ -96,6 +99,7 @@ class SymmetricHeap:
         if rc != 0:
             raise RuntimeError(f"could not allocate a {self.nbytes >> 20} MiB symmetric arena")
         self.base = base.value
+        SymmetricHeap.live_bytes += self.nbytes
         lib.mb_symm_memset(self.base, 0, self.nbytes, None)
         torch.cuda.synchronize()
         hsize = lib.mb_ipc_handle_size()
@@ -138,3 +142,4 @@ class SymmetricHeap:
             if r != self.rank:
                 lib.mb_ipc_close_handle(b)
         lib.mb_symm_free(self.base)
+        SymmetricHeap.live_bytes -= self.nbytes

@@ -2,13 +2,14 @@
 and writes it into the operator database's meta file.
 
 A training step cannot run faster than its host thread issues it.  With small micro batches on many-way tensor
-parallel layouts the kernels of a block take a few milliseconds and the host becomes the bound (GPT-3 13B on
-PP2 x TP4 with two sequences per micro batch: 5.4 ms per block and micro batch measured against 4.0 ms of
-kernels).  The cost model therefore prices a block with ``max(device time, host time)``; the host time comes
+parallel layouts the kernels of a block take a few milliseconds, of the same order as what the host needs for
+the block (about 1 ms for forward + backward, another 1 ms for a recomputed forward pass under activation
+checkpointing).  The cost model therefore prices a block with ``max(device time, host time)``; the host time comes
 from here, not from a fit to step times: a model whose kernels are negligible (hidden 256, sequence 128, one
 sequence) is stepped with 8 and with 24 blocks, with and without recomputation, and the differences give the
-host seconds per block for a forward pass and for a backward pass.  They are stored per operator of the
-block's trace, so layouts with more operators per block (tensor-parallel collectives) are charged more.
+host seconds per block for forward + backward and for a recomputed forward pass.  They are stored with the
+number of operators of the block's trace, so layouts with more operators per block (tensor-parallel collectives)
+are charged more.
 
     python -m mist_b200.tools.profile_host_dispatch [--meta <_meta.json>] [--steps 20]
 
@@ -62,12 +63,10 @@ def measure(steps: int = 20):
     t24 = _step_seconds(24, 0, steps)
     t24c = _step_seconds(24, 24, steps)
     both = (t24 - t8) / 16.0                 # forward + backward of one block
-    fwd = max((t24c - t24) / 24.0, 0.0)      # the recomputed forward pass of one block
-    bwd = max(both - fwd, 0.0)
+    rec = max((t24c - t24) / 24.0, 0.0)      # the recomputed forward pass of one block (activation checkpointing)
     cfg, _ = load_config("config", _overrides(8, 0), check_world_size=False)
     nodes = len(StageEvaluator(cfg).analysis(1).layer("block_layer").nodes)
-    return {"fwd_s_per_op": fwd / nodes, "bwd_s_per_op": bwd / nodes, "ops_per_block": nodes,
-            "block_fwd_s": fwd, "block_bwd_s": bwd,
+    return {"block_fwd_bwd_s": both, "block_recompute_s": rec, "ops_per_block": nodes,
             "step_s": {"8 blocks": t8, "24 blocks": t24, "24 blocks recomputed": t24c}}
 
 

@@ -382,3 +382,58 @@ def test_kick_the_tires_memory_account(monkeypatch):
     # the same account with the reference's executor choices lands on its own prediction
     ref_like = (weights + weights + 6 * weights / 2) + 24 * blk.input_bytes / 2 / mb + (fwd - states - 3072.0)
     assert ref_like == pytest.approx(19255.0, rel=0.04)
+
+
+def test_sm_bound_operators_are_priced_with_their_sustained_timing(tmp_path):
+    """An entry with a back-to-back timing gives that timing for operators the meta file lists as bound by the
+    SMs and its cold timing for every other operator; nothing is scaled by a clock."""
+    import json
+    d = tmp_path / "cache_TEST_GPU"
+    d.mkdir()
+    (d / "_meta.json").write_text(json.dumps({"scaled_ops": ["linear"], "sustained_scale": 1.0, "sm_mhz_under_load": 1530.0}))
+    db = OpDatabase(device="TEST_GPU", root=tmp_path, allow_profile=False)
+    lin = NodeSpec.from_dict({"op": "linear", "m": 64, "n": 16, "k": 32, "act": "", "bias": False}, {})
+    norm = NodeSpec.from_dict({"op": "layer_norm", "rows": 64, "h": 32, "residual": True}, {})
+    db.add(lin, 1.0e-3, 2.0e-3, fwd_sus=1.2e-3, bwd_sus=2.6e-3, sm_mhz_fwd=1100.0, sm_mhz_bwd=1200.0)
+    db.add(norm, 1.0e-4, 2.0e-4, fwd_sus=0.8e-4, bwd_sus=1.5e-4, sm_mhz_fwd=1900.0, sm_mhz_bwd=1900.0)
+    assert db.latency(lin) == (1.2e-3, 2.6e-3)
+    assert db.latency(norm) == (1.0e-4, 2.0e-4)
+
+
+def test_fused_overlap_fit_recovers_its_parameters():
+    rows = []
+    for kind, kappa, tau in (("AG->GEMM qkv", 0.25, 40e-6), ("GEMM->RS fc2 (store)", 0.5, 0.0)):
+        for g, c in ((0.5, 0.2), (0.1, 0.12), (1.0, 0.21), (0.06, 0.1), (0.3, 0.3)):
+            fused = max(g, c) + kappa * min(g, c) + tau * 1e3
+            rows.append(dict(kernel=kind, fused_ms=fused, gemm_ms=g, collective_ms=c))
+    rows.append(dict(kernel="GEMM->RS fc2 (add)", fused_ms=9.0, gemm_ms=0.1, collective_ms=0.1))    # ignored form
+    fit = comm_model.fit_fused_overlap(rows)
+    assert abs(fit["ag_gemm"]["kappa"] - 0.25) < 1e-3 and abs(fit["ag_gemm"]["tau"] - 40e-6) < 1e-6
+    assert abs(fit["gemm_rs"]["kappa"] - 0.5) < 1e-3 and fit["gemm_rs"]["tau"] < 1e-6 and fit["gemm_rs"]["rows"] == 5
+
+
+def test_host_dispatch_bounds_a_block_from_below(monkeypatch):
+    """With the host's seconds per block in the operator database's meta data, a block whose kernels are
+    faster than the host can issue them is charged the host time; a recomputed block pays the (larger)
+    host cost of a checkpointed forward pass."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    cfg, _ = load_config("config", check_world_size=False)
+    vec = np.array([[1, 8, 1, 0, 1, 1, 0, 0, 0, 0]], dtype=float)      # one sequence per micro batch: small kernels
+    db = OpDatabase(allow_profile=False)
+    db.host_dispatch = {}
+    base = StageEvaluator(cfg, db)
+    t0 = base.evaluate(vec, 32, 0, 1, True, True)["stable"][0]
+    c0 = base.evaluate(vec, 32, 32, 1, True, True)["stable"][0]
+    nodes = len(base.analysis(1).layer("block_layer").nodes)
+    slow = OpDatabase(allow_profile=False)
+    slow.host_dispatch = {"block_fwd_bwd_s": 0.3, "block_recompute_s": 0.5, "ops_per_block": nodes}
+    ev = StageEvaluator(cfg, slow)
+    num = ev.layer_numbers(1, 1, "block_layer")
+    assert (num.host_fwd, num.host_bwd, num.host_recompute) == pytest.approx((0.1, 0.2, 0.5))
+    t1 = ev.evaluate(vec, 32, 0, 1, True, True)["stable"][0]
+    c1 = ev.evaluate(vec, 32, 32, 1, True, True)["stable"][0]
+    assert t1 >= 32 * 0.3 and t1 > t0
+    assert c1 - t1 == pytest.approx(32 * 0.5, rel=0.05) and c1 > c0
+    quick = OpDatabase(allow_profile=False)
+    quick.host_dispatch = {"block_fwd_bwd_s": 1e-9, "block_recompute_s": 1e-9, "ops_per_block": nodes}
+    assert StageEvaluator(cfg, quick).evaluate(vec, 32, 0, 1, True, True)["stable"][0] == pytest.approx(t0)
