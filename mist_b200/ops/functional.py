@@ -14,6 +14,7 @@ The ops mirror the fused operators the reference's module library is built on
 """
 from __future__ import annotations
 
+import ctypes
 import math
 import os
 from typing import Optional
@@ -114,7 +115,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             native.launch_count += 1
             return out
         if rc != 1:
-            raise RuntimeError(f"mb_gemm_pair_bf16 failed with code {rc}")
+            detail = ""
+            if rc <= -21:        # a tensor map could not be encoded: the library kept the call's arguments
+                info = native.kernels().mb_gemm_pair_last_error
+                info.restype = ctypes.c_char_p
+                detail = f" ({info().decode()})"
+            raise RuntimeError(f"mb_gemm_pair_bf16 failed with code {rc}{detail}")
     call("mb_gemm_bf16", ptr(a), ptr(b), ptr(out), M, N, K, a.stride(0), b.stride(0), out.stride(0),
          int(a_mn), int(b_mn), flags, ptr(bias), ptr(aux), float(alpha), tile_n,
          Settings.gemm_max_ctas, stream())

@@ -144,12 +144,7 @@ def call(name: str, *args):
     rc = fn(*args)
     launch_count += 1
     if rc != 0:
-        detail = ""
-        if name == "mb_gemm_pair_bf16" and rc <= -21:
-            info = kernels().mb_gemm_pair_last_error
-            info.restype = C.c_char_p
-            detail = f" ({info().decode()})"
-        raise RuntimeError(f"{name} failed with code {rc}{detail}")
+        raise RuntimeError(f"{name} failed with code {rc}")
     return rc
 
 
