@@ -904,9 +904,11 @@ bool make_map4(CUtensorMap* m, const void* base, int batch, int tokens, int head
                            static_cast<cuuint64_t>(bs) * 2};
   cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(box_rows), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+  return encode_with_context([&] {
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
 }
 
 // dq accumulator [b*nh][sq][d] fp32, box [1][64][32]
@@ -917,9 +919,11 @@ bool make_map_dq(CUtensorMap* m, float* base, int bh, int sq, int d) {
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(d) * 4, static_cast<cuuint64_t>(sq) * d * 4};
   cuuint32_t box[3] = {32, static_cast<cuuint32_t>(BQ), 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  return encode_with_context([&] {
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  });
 }
 
 int g_bwd_variant = 0;        // 0: one block at a time; 1: pipelined

@@ -441,10 +441,11 @@ bool make_tmap_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
   cuuint64_t strides[1] = {ld * 2};
   cuuint32_t box[2] = {64, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+  return encode_with_context([&] {
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  });
 }
 
 // Output tile map: [rows][cols] of bf16 (64-column box) or fp32 (32-column box), i.e. 128-byte
@@ -456,10 +457,11 @@ bool make_tmap_out(CUtensorMap* map, void* base, uint64_t rows, uint64_t cols, u
   cuuint64_t strides[1] = {ld * (fp32 ? 4u : 2u)};
   cuuint32_t box[2] = {fp32 ? 32u : 64u, static_cast<cuuint32_t>(BM)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
+  return encode_with_context([&] {
+    return fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
+  });
 }
 
 int g_num_sms = 0;

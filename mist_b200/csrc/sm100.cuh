@@ -9,6 +9,18 @@
 #include "common.cuh"
 #include <cuda.h>
 
+// cuTensorMapEncodeTiled is a driver call and needs a context that is current on the calling thread.  A thread
+// that has made no runtime call yet has none: an autograd worker whose allocations were all served by the
+// caching allocator reaches the first GEMM of a backward pass that way, and the encode fails with the same
+// arguments that succeed on the main thread.  On a failure the primary context of the thread's device is bound
+// by a runtime call and the encode is tried once more.
+template <typename Encode>
+inline bool encode_with_context(Encode&& encode) {
+  if (encode() == CUDA_SUCCESS) return true;
+  cudaFree(nullptr);
+  return encode() == CUDA_SUCCESS;
+}
+
 namespace sm100 {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
