@@ -1,7 +1,7 @@
 #!/bin/bash
 # Installs the unmodified reference (Dazz993/Mist) under baseline/_ref for `bench.py --impl reference`.
 #
-#   bash baseline/install_reference.sh [/path/to/reference]
+#   bash baseline/install_reference.sh /path/to/reference [/path/to/wheelhouse]
 #
 # Step 1 is the plain offline pip install.  The reference's setup.py lists `packages=["mist"]` only, so
 # pip copies the top-level modules and none of the sub-packages; step 2 completes the package by copying
@@ -9,14 +9,15 @@
 # tree (they live outside the package, under benchmark/mist).  Step 3 writes a checksum listing and
 # verifies that every file equals its source.  Nothing under baseline/_ref is edited.
 set -euo pipefail
-SRC=${1:-/root/reference}
+SRC=${1:?usage: install_reference.sh <reference checkout> [wheelhouse]}
+WHEELS=${2:-/opt/wheelhouse}
 HERE=$(cd "$(dirname "$0")" && pwd)
 DST=$HERE/_ref
 TMP=$(mktemp -d /tmp/mist_ref_src.XXXXXX)
 cp -r "$SRC"/. "$TMP"/
 rm -rf "$TMP/build" "$TMP/mist.egg-info"
 rm -rf "$DST"
-python -m pip install --no-index --no-build-isolation --no-deps --find-links /opt/wheelhouse \
+python -m pip install --no-index --no-build-isolation --no-deps --find-links "$WHEELS" \
     --target "$DST" "$TMP" 2>&1 | tail -2
 # 2. the sub-packages setup.py leaves out, and the driver + configs
 cp -r "$SRC/mist/." "$DST/mist/"
