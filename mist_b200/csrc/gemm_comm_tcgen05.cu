@@ -35,6 +35,7 @@
 // mist/modules/fused_dense.py:54-75 and :320-327 (NCCL + cuBLAS, overlapped at best with a
 // weight cast), disabled in the reference's models (mist/model/transformer.py:477-479).
 #include "sm100_pair.cuh"
+#include "gather_plan.cuh"
 #include <string.h>
 #include <algorithm>
 
@@ -55,9 +56,11 @@ constexpr int kCopyBytes = 16384;
 // be pending then, so the wait before a load never drains the whole store queue.
 constexpr int kCopyLoads = 6;
 constexpr int kCopyStoresPending = kCopyBufs - 1 - kCopyLoads;
-constexpr int kSubBytes = 16 * kCopyBytes;  // unit of work of a gather CTA
 constexpr int kPublishLag = 6;              // a sub-chunk is counted once this many younger stores were issued
 constexpr int kAgCounterOffset = 2048;      // AG: the chunk counters follow the chunk flags at this index
+
+static_assert(kGatherRowsPerChunk == BM, "one gather flag per row block of a tile");
+static_assert(kGatherSubBytes % kCopyBytes == 0, "sub-chunks are whole ring buffers");
 
 enum Mode : int { MODE_AG = 1, MODE_RS = 2, MODE_AGW = 3 };
 
@@ -270,9 +273,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   if (is_gather) {
     // ------------------------------------------------------------------ gather CTAs
-    // The remote chunks are cut into sub-chunks of kSubBytes, dealt to the gather CTAs in fetch order, so that
-    // every gather CTA works on the chunk that the GEMM needs next (a whole chunk on one CTA would arrive only
-    // after ~100 us).  A CTA streams the 16 KB pieces of all its sub-chunks through one ring without draining
+    // The remote chunks are cut into sub-chunks dealt to the gather CTAs in fetch order (gather_plan.cuh), so
+    // that every gather CTA works on the chunk that the GEMM needs next (a whole chunk on one CTA would arrive
+    // only after ~100 us).  A CTA streams the 16 KB pieces of all its sub-chunks through one ring without draining
     // it in between, counts a finished sub-chunk on the chunk's counter once its stores have completed, and the
     // CTA that counts the last one publishes the chunk's flag.
     if (threadIdx.x == 0) {
@@ -280,70 +283,23 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint8_t* bufs = smem;                                              // reuse the stage area
       bool ok = true;
       unsigned ready_mask = 0;
-      const bool ag = (p.mode == MODE_AG);
-      const size_t row_bytes = static_cast<size_t>(p.K) * 2;
-      const unsigned long long cbytes = ag ? static_cast<unsigned long long>(BM) * row_bytes : p.chunk_bytes;
-      const int cpr = ag ? ag_chunks_per_rank : p.chunks_per_rank;
-      const int subs = static_cast<int>((cbytes + kSubBytes - 1) / kSubBytes);
-      const int total_subs = (R - 1) * cpr * subs;      // < 2^31: at most a few thousand per GB
-      // weight-AG: the rank that owns the first weights of this GEMM, and the chunk they start in
-      int r0 = -1, c0 = 0;
-      if (!ag) {
-        const unsigned long long first = p.b_off + static_cast<unsigned long long>(p.n_shift) * BN * p.K * 2;
-        r0 = static_cast<int>(first / p.shard_bytes);
-        c0 = static_cast<int>((first - r0 * p.shard_bytes) / p.chunk_bytes);
-      }
-      struct Seg {
-        const uint8_t* src;
-        uint8_t* dst;
-        uint32_t bytes;
-        int flag, expected, r;
-      };
-      // q-th sub-chunk in fetch order; false when it lies beyond the end of a short last chunk.
-      //   AG: the peers in turn, starting with the next rank (every rank reads from a different source);
-      //   weight-AG: the peers' chunks alternate, each peer's in address order (the owner of the first weights
-      //   from the chunk they start in), so that a rank reads from all peers at once: every rank needs the
-      //   same weights first, and one source could not feed all readers at the full rate.
-      auto segment = [&](int q, Seg& s) -> bool {
-        const int w = q / subs;
-        const int sub = q - w * subs;
-        int r, c;
-        unsigned long long bytes, off;
-        if (ag) {
-          const int k = w / cpr;
-          c = w - k * cpr;
-          r = (p.me + 1 + k) % R;
-          off = (static_cast<unsigned long long>(r) * p.rows_per_rank + static_cast<unsigned long long>(c) * BM) * row_bytes;
-          bytes = cbytes;
-        } else {
-          const int i = w / (R - 1);
-          const int k = w - i * (R - 1);
-          r = (p.me + 1 + k) % R;
-          c = (r == r0) ? (c0 + i) % cpr : i;
-          const unsigned long long in_shard = static_cast<unsigned long long>(c) * p.chunk_bytes;
-          bytes = min(p.chunk_bytes, p.shard_bytes - in_shard);
-          off = static_cast<unsigned long long>(r) * p.shard_bytes + in_shard;
-        }
-        const unsigned long long lo = static_cast<unsigned long long>(sub) * kSubBytes;
-        if (lo >= bytes) return false;
-        s.src = p.a_peer[r] + off + lo;
-        s.dst = p.a_local + off + lo;
-        s.bytes = static_cast<uint32_t>(min(static_cast<unsigned long long>(kSubBytes), bytes - lo));
-        s.flag = r * cpr + c;
-        s.expected = (bytes == cbytes) ? subs : static_cast<int>((bytes + kSubBytes - 1) / kSubBytes);
-        s.r = r;
-        return true;
-      };
+      GatherPlan plan;
+      if (p.mode == MODE_AG)
+        plan.init_activations(R, p.me, p.K, p.rows_per_rank);
+      else
+        plan.init_weights(R, p.me, p.shard_bytes, p.chunk_bytes,
+                          p.b_off + static_cast<unsigned long long>(p.n_shift) * BN * p.K * 2);
+      const int total_subs = plan.total_subs;
       struct Cursor {
         int q;
         int piece, pieces;
         bool live;
-        Seg s;
+        GatherSeg s;
       };
       auto seek = [&](Cursor& c) {           // moves to this CTA's next sub-chunk that has bytes, from c.q on
         c.live = false;
         for (; c.q < total_subs; c.q += p.n_gather) {
-          if (segment(c.q, c.s)) {
+          if (plan.segment(c.q, c.s)) {
             c.live = true;
             c.piece = 0;
             c.pieces = static_cast<int>((c.s.bytes + kCopyBytes - 1) / kCopyBytes);
@@ -382,7 +338,8 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if (issued >= kCopyBufs) tma_wait_read<kCopyStoresPending>();   // the store that last used this buffer has read it
           const uint32_t nb = min(static_cast<uint32_t>(kCopyBytes), ld.s.bytes - static_cast<uint32_t>(ld.piece) * kCopyBytes);
           mbar_expect_tx(&copy_bar[b], nb);
-          bulk_load(bufs + b * kCopyBytes, ld.s.src + static_cast<size_t>(ld.piece) * kCopyBytes, nb, &copy_bar[b]);
+          bulk_load(bufs + b * kCopyBytes, p.a_peer[ld.s.r] + ld.s.off + static_cast<size_t>(ld.piece) * kCopyBytes, nb,
+                    &copy_bar[b]);
           ++issued;
           if (++ld.piece == ld.pieces) {
             ld.q += p.n_gather;
@@ -397,7 +354,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           break;
         }
         const uint32_t nb = min(static_cast<uint32_t>(kCopyBytes), st.s.bytes - static_cast<uint32_t>(st.piece) * kCopyBytes);
-        bulk_store(st.s.dst + static_cast<size_t>(st.piece) * kCopyBytes, bufs + b * kCopyBytes, nb);
+        bulk_store(p.a_local + st.s.off + static_cast<size_t>(st.piece) * kCopyBytes, bufs + b * kCopyBytes, nb);
         tma_commit();
         ++stored;
         if (++st.piece == st.pieces) {
@@ -921,4 +878,28 @@ MB_API int mb_gemm_param_gather(void* const* w_ptrs, const void* A, void* C, voi
   const long tiles = static_cast<long>((M + (pair ? 2 : 1) * BM - 1) / ((pair ? 2 : 1) * BM)) * num_n;
   const int compute = plan_grid(pair, tiles, p.n_gather);
   return launch(false, pair, compute + p.n_gather, stream, ta, tb, tc, acc, p);
+}
+
+// The gather CTAs' fetch order computed on the host, for tests (the same GatherPlan code that the kernel runs).
+// weights = 0: activation gather of AG -> GEMM (K, rows_per_rank); weights = 1: flat parameter buffer
+// (shard_bytes, chunk_bytes, first_byte = offset of the first weights the GEMM reads).  q < 0: returns the length
+// of the sequence.  Otherwise fills out[0..4] = byte offset, bytes, flag index, sub-chunks of that chunk, source
+// rank and returns 1, or returns 0 for an empty entry (beyond the end of a short last chunk).
+MB_API int mb_gather_plan_segment(int weights, int nranks, int me, int K, int rows_per_rank, long long shard_bytes,
+                                  long long chunk_bytes, long long first_byte, int q, long long* out) {
+  GatherPlan plan;
+  if (weights)
+    plan.init_weights(nranks, me, static_cast<unsigned long long>(shard_bytes),
+                      static_cast<unsigned long long>(chunk_bytes), static_cast<unsigned long long>(first_byte));
+  else
+    plan.init_activations(nranks, me, K, rows_per_rank);
+  if (q < 0) return plan.total_subs;
+  GatherSeg s;
+  if (!plan.segment(q, s)) return 0;
+  out[0] = static_cast<long long>(s.off);
+  out[1] = s.bytes;
+  out[2] = s.flag;
+  out[3] = s.expected;
+  out[4] = s.r;
+  return 1;
 }
