@@ -470,7 +470,7 @@ def analyze_strategy(cfg: MistConfig, evaluator: Optional[StageEvaluator] = None
             kind = "dec_block_layer" if s == S - 1 else "enc_block_layer"
         # the decoder stage of an encoder-decoder pipeline holds its own copy of the embedding tables
         has_pre = s == 0 or kind == "dec_block_layer"
-        ppa = st.pre_post_strategy_array if st.pre_post_strategy == "preset" else None
+        ppa = st.pre_post_vector(s)
         res = ev.evaluate(vec, st.layer_partitions[s], st.gradient_checkpointing[s], G, has_pre=has_pre,
                           has_post=(s == S - 1), inflight_extra=warm, block_kind=kind,
                           tied_copy=(S > 1 and s == S - 1 and ties_across_stages(cfg)),

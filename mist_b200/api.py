@@ -108,7 +108,8 @@ class TrainingSession:
                 tied = [] if one is None else [one]
             for t in tied:
                 dist.broadcast(t.data, src=self.ps.embedding_src, group=tied_group)
-        pre_post = StageStrategy.from_vector(st.pre_post_strategy_array) if st.pre_post_strategy == "preset" else None
+        ppv = st.pre_post_vector(stage)
+        pre_post = StageStrategy.from_vector(ppv) if ppv is not None else None
         self.engine = TrainEngine(self.model, self.ps, self.strategy, self.G, st.gradient_checkpointing[stage],
                                   hp=hp, comm_backend=self.comm_backend, overlap=bool(cfg.get("overlap", True)),
                                   zero3_gather=self.zero3_gather,

@@ -340,6 +340,22 @@ class StrategyConfig:
     def stage(self, idx: int) -> StageStrategy:
         return StageStrategy.from_vector(self.stage_strategies[idx])
 
+    def pre_post_vector(self, idx: int) -> Optional[Tuple]:
+        """Strategy vector of the embedding / head units of stage ``idx``, or ``None`` when they follow the
+        stage's own vector (``heuristic``).  The named choices set the redundancy flags as the reference does
+        (mist/analyzer/batched_module_analyzer.py:799-839): ``dp`` shards the optimizer states only,
+        ``intra-node-tp-with-ore`` gradients and optimizer states, ``intra-node-tp-without-ore`` gradients only.
+        The reference also gives the pre / post layers a mesh of their own under the named choices (all GPUs as
+        data parallel, or a node as tensor parallel); here the embedding and the head always run on their
+        stage's mesh, so micro batch, dp and tp are the stage's."""
+        if self.pre_post_strategy == "preset":
+            return tuple(self.pre_post_strategy_array)
+        flags = {"dp": (0, 0, 1), "intra-node-tp-with-ore": (0, 1, 1), "intra-node-tp-without-ore": (0, 1, 0)}
+        if self.pre_post_strategy in flags:
+            v = self.stage_strategies[idx]
+            return normalize_strategy_vector([v[0], v[1], v[2], *flags[self.pre_post_strategy], 0, 0, 0, 0])
+        return None
+
     def verify_with_other_config(self, model: ModelConfig, training: TrainingConfig, hardware: HardwareConfig):
         gbs = training.global_batch_size
         G = self.gradient_accumulation_steps

@@ -119,3 +119,18 @@ def test_collect_results_table(tmp_path):
     rows = mod.main([str(tmp_path), "--csv", str(tmp_path / "out.csv")])
     assert len(rows) == 2 and rows[0]["prediction_error_pct"] == "+10.0" and rows[1]["run"].endswith("mist")
     assert (tmp_path / "out.csv").read_text().startswith("run,")
+
+
+def test_named_pre_post_strategies_set_the_redundancy_flags():
+    """`preset` takes the array, the reference's named choices map to its flag triples
+    (mist/analyzer/batched_module_analyzer.py:799-839) on the stage's own mesh, `heuristic` follows the stage."""
+    cfg, _ = load_config("config", ["experiment=b200-gpt3-2.7b-dp8-zero2"], check_world_size=False)
+    st = cfg.strategy
+    assert st.pre_post_strategy == "preset" and tuple(st.pre_post_vector(0)) == tuple(st.pre_post_strategy_array)
+    b, dp, tp = st.stage_strategies[0][:3]
+    for name, flags in (("dp", (0, 0, 1)), ("intra-node-tp-with-ore", (0, 1, 1)), ("intra-node-tp-without-ore", (0, 1, 0))):
+        st.pre_post_strategy = name
+        v = st.pre_post_vector(0)
+        assert tuple(v[:3]) == (b, dp, tp) and tuple(int(x) for x in v[3:6]) == flags and not any(v[6:])
+    st.pre_post_strategy = "heuristic"
+    assert st.pre_post_vector(0) is None
