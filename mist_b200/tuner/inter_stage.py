@@ -114,7 +114,8 @@ def _layer_range(total_layers: int, num_stages: int, offset: int) -> range:
 
 
 def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache_dir: Optional[str] = None,
-                     tp: Optional[int] = None, verbose: bool = False) -> Tuple[float, Optional[Solution]]:
+                     tp: Optional[int] = None, verbose: bool = False, single_stage: bool = False
+                     ) -> Tuple[float, Optional[Solution]]:
     """Returns ``(best_cost, solution)`` with ``solution = [G, [(((layer_start, layer_end),
     (nodes, gpus), num_ckpt, point_index), strategy_vector), ...]]``."""
     ev = ev or StageEvaluator(cfg, cache_dir=cache_dir)
@@ -122,10 +123,15 @@ def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache
     gran = tun.tuning_granularity
     L = cfg.model.num_hidden_layers
     offset = int(getattr(tun, "layers_offset", 2))
-    # Encoder-decoder models run over pipeline stages in one fixed form only (encoder blocks on the
-    # first stages, the whole decoder on the last), which the layer-partition search does not
-    # describe: their strategies are searched within one stage.
-    if cfg.model.add_decoder:
+    # Encoder-decoder models run over pipeline stages in one fixed form (encoder blocks on the first
+    # stages, the whole decoder on the last): searched by a routine of its own, beside the one-stage case.
+    if cfg.model.add_decoder and not single_stage:
+        one = inter_stage_tune(cfg, ev, cache_dir, tp, verbose, single_stage=True)
+        if gran == "no-pp":
+            return one
+        piped = _enc_dec_pipeline_tune(cfg, ev, tp, verbose)
+        return piped if piped[0] < one[0] else one
+    if single_stage:
         gran = "no-pp"
     if gran == "inter-stage":
         return _inter_stage_tune_nonuniform(cfg, ev, cache_dir, tp)
@@ -187,6 +193,65 @@ def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache
             for ci in chosen:
                 k, l, pi, p = opt_ref[ci]
                 stages.append((((start, start + l - 1), mesh, p.num_ckpt, pi), p.vector))
+                start += l
+            best_sol = [g, stages]
+    return best_cost, best_sol
+
+
+def _enc_dec_pipeline_tune(cfg, ev, tp, verbose=False):
+    """Encoder-decoder models over S >= 2 stages of equal meshes: the L encoder blocks are split over the
+    first S - 1 stages (the split is searched), the last stage holds the L decoder blocks, the head and its own
+    copies of the embedding tables (what the executor runs, ``StrategyConfig.verify_with_other_config``).
+    Every stage cell is tuned with its own kind of block; the exact stage-assignment solver then picks one
+    Pareto point per stage."""
+    from .intra_stage import tune_stage_cell
+    hw, tun = cfg.hardware, cfg.tuning
+    L = cfg.model.num_hidden_layers
+    offset = int(getattr(tun, "layers_offset", 2))
+    uniform_layers = tun.tuning_granularity in ("uniform-pp", "uniform-device-pp", "uniform-pp-simple-heuristic-mem-opt")
+    best_cost, best_sol = math.inf, None
+    for S in stage_count_candidates(hw.num_devices, L + 1):
+        if S < 2:
+            continue
+        mesh = uniform_mesh_for(S, hw.num_nodes, hw.num_gpus_per_node)
+        if mesh is None:
+            continue
+        enc_stages = S - 1
+        if uniform_layers:
+            if L % enc_stages:
+                continue
+            counts = [L // enc_stages]
+        else:
+            counts = list(_layer_range(L, enc_stages, offset)) if enc_stages > 1 else [L]
+        for g in grad_accum_candidates(cfg.training.global_batch_size):
+            opt_kind, opt_layers, opt_T, opt_D, opt_ref = [], [], [], [], []
+            cells = [(0, l, "enc_block_layer", None, 0) for l in counts]
+            if enc_stages > 1:
+                cells += [(1, l, "enc_block_layer", None, 1) for l in counts]
+            cells.append((2, L, "dec_block_layer", True, S - 1))
+            for kind, l, block_kind, has_pre, stage_index in cells:
+                pts, _ = tune_stage_cell(ev, cfg, g, mesh, kind, l, S, stage_index, tp, block_kind=block_kind,
+                                         has_pre=has_pre)
+                for pi, p in enumerate(pts):
+                    opt_kind.append(kind)
+                    opt_layers.append(l)
+                    opt_T.append(p.stable)
+                    opt_D.append(p.delta)
+                    opt_ref.append((kind, l, pi, p))
+            if not any(k == 2 for k in opt_kind) or not any(k == 0 for k in opt_kind):
+                continue
+            # the solver counts layers over all stages: L encoder blocks plus the decoder stage's L
+            cost, chosen = solve_stage_assignment(S, 2 * L, g, opt_kind, opt_layers, opt_T, opt_D)
+            if verbose:
+                print(f"  encoder-decoder stages={S} mesh={mesh} G={g}: cost={cost:.6f}")
+            if not chosen or not math.isfinite(cost) or cost >= best_cost:
+                continue
+            best_cost = cost
+            start, stages = 0, []
+            for ci in chosen:
+                k, l, pi, p = opt_ref[ci]
+                rng = (0, L - 1) if k == 2 else (start, start + l - 1)
+                stages.append(((rng, mesh, p.num_ckpt, pi), p.vector))
                 start += l
             best_sol = [g, stages]
     return best_cost, best_sol

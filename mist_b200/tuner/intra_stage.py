@@ -55,19 +55,23 @@ def ckpt_candidates(layers: int, cfg: MistConfig) -> List[int]:
 
 
 def tune_stage_cell(ev: StageEvaluator, cfg: MistConfig, g: int, mesh: Tuple[int, int], kind: int, layers: int,
-                    num_stages: int, stage_index: int, tp: Optional[int] = None) -> Tuple[List[StagePoint], int]:
+                    num_stages: int, stage_index: int, tp: Optional[int] = None, block_kind: str = "block_layer",
+                    has_pre: Optional[bool] = None) -> Tuple[List[StagePoint], int]:
+    """Pareto points (stable time, delta) of one stage cell.  ``block_kind`` / ``has_pre``: for the stages of an
+    encoder-decoder pipeline (encoder or decoder blocks; the decoder stage keeps its own embedding tables)."""
     gbs = cfg.training.global_batch_size
     space = create_search_space(mesh[0], mesh[1], gbs, g, cfg, tp_size=tp)
     if space.shape[0] == 0:
         return [], 0
-    has_pre, has_post = KINDS[kind]
+    kind_pre, has_post = KINDS[kind]
+    has_pre = kind_pre if has_pre is None else bool(has_pre)
     warm = min(num_stages - 1 - stage_index, max(g - 1, 0))
     S = cfg.tuning.sample_size if cfg.tuning else 30
     all_points: List[StagePoint] = []
     evaluated = 0
     for c in ckpt_candidates(layers, cfg):
         # kinds: 0 first stage of a pipeline, 1 middle, 2 last, 3 the only stage (no neighbours to exchange with)
-        res = ev.evaluate(space, layers, c, g, has_pre, has_post, inflight_extra=warm,
+        res = ev.evaluate(space, layers, c, g, has_pre, has_post, inflight_extra=warm, block_kind=block_kind,
                           tied_copy=(kind == 2 and ties_across_stages(cfg)),
                           has_prev_stage=kind in (1, 2), has_next_stage=kind in (0, 1))
         evaluated += space.shape[0]

@@ -437,3 +437,40 @@ def test_host_dispatch_bounds_a_block_from_below(monkeypatch):
     quick = OpDatabase(allow_profile=False)
     quick.host_dispatch = {"block_fwd_bwd_s": 1e-9, "block_recompute_s": 1e-9, "ops_per_block": nodes}
     assert StageEvaluator(cfg, quick).evaluate(vec, 32, 0, 1, True, True)["stable"][0] == pytest.approx(t0)
+
+
+def test_encoder_decoder_models_are_searched_over_pipeline_stages(monkeypatch, tmp_path):
+    """T5 on 4 devices with too little memory for one stage's worth of replicas: the tuner may put the encoder
+    blocks on the first stages and the decoder on the last.  Whatever it returns must load as a strategy
+    (encoder blocks split over all stages but the last, which holds all decoder blocks) and be priced by the
+    analyzer at the tuner's own cost; the pipelined search alone must agree with the analyzer as well."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    from mist_b200.tuner.inter_stage import _enc_dec_pipeline_tune
+    from mist_b200.utils import yamlconf
+    over = ["experiment=gpt2-1.3b", "model=t5/1.7b", "model.num_hidden_layers=8", "hardware.num_gpus_per_node=4",
+            "training.global_batch_size=16", "training.max_sequence_length=512", "strategy.enabled=false",
+            "tuning.tuning_granularity=uniform-device-pp-mip", "tuning.sample_size=6"]
+    cfg, node = load_config("config", over, check_world_size=False)
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=False))
+
+    def check(cost, sol, name):
+        assert sol is not None and math.isfinite(cost)
+        strat = solution_to_strategy(cfg, sol)
+        S = len(strat["layer_partitions"])
+        if S > 1:
+            assert strat["layer_partitions"][-1] == 8 and sum(strat["layer_partitions"][:-1]) == 8
+        assert sum(n * m for n, m in strat["device_assignment"]) == 4
+        plain = node.to_dict()
+        plain["strategy"] = strat
+        yamlconf.dump(plain, tmp_path / f"{name}.yaml")
+        cfg2, _ = load_config(name, config_dirs=[tmp_path], check_world_size=False)       # validates the layout
+        again = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))["total"]
+        assert again == pytest.approx(cost, rel=1e-6)
+        return S
+
+    piped_cost, piped = _enc_dec_pipeline_tune(cfg, ev, None)
+    assert check(piped_cost, piped, "piped") >= 2
+    cost, sol = inter_stage_tune(cfg, ev)
+    check(cost, sol, "best")
+    one_cost, _ = inter_stage_tune(cfg, ev, single_stage=True)
+    assert cost == pytest.approx(min(one_cost, piped_cost))
