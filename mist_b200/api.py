@@ -41,6 +41,10 @@ class TrainingSession:
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = device
+        if device.type == "cuda":
+            # optional: restrict this rank to the cores next to its GPU (MIST_B200_BIND_CPU=node|exclusive)
+            from .utils.affinity import bind_to_gpu
+            self.cpu_cores = bind_to_gpu(device.index or 0, int(os.environ.get("LOCAL_WORLD_SIZE", "1")))
         self.ps = ParallelState.from_config(cfg) if world > 1 else ParallelState.from_config(cfg, rank=0, create_groups=False)
         st = cfg.strategy
         stage = self.ps.stage

@@ -71,3 +71,34 @@ def test_device_name_follows_the_override(monkeypatch):
     assert device.device_name() == ("cpu" if not torch.cuda.is_available() else device.device_name())
     device.join_streams(None, None)      # no GPU: nothing to do
     assert device.current_device().type in ("cpu", "cuda")
+
+
+def test_cpu_binding_plan_with_a_fake_nvml():
+    """Ranks are bound to the cores NVML names for their GPU: shared per NUMA node (`node`), or split into
+    disjoint slices among the ranks of a node (`exclusive`); never outside the cores the process may use."""
+    from mist_b200.utils import affinity
+
+    class FakeNvml:
+        # GPUs 0-3 hang off cores 0-31, GPUs 4-7 off cores 32-63
+        def nvmlDeviceGetHandleByIndex(self, i):
+            return i
+
+        def nvmlDeviceGetCpuAffinity(self, handle, words):
+            return [0xFFFFFFFF if handle < 4 else 0xFFFFFFFF << 32] + [0] * (words - 1)
+
+    nv = FakeNvml()
+    assert affinity.gpu_cpu_set(1, nv) == set(range(32)) and affinity.gpu_cpu_set(6, nv) == set(range(32, 64))
+    sets = [affinity.gpu_cpu_set(r, nv) for r in range(8)]
+    assert affinity.plan(sets, 5, "node") == set(range(32, 64))
+    slices = [affinity.plan(sets, r, "exclusive") for r in range(8)]
+    assert all(len(s) == 8 for s in slices)
+    assert set().union(*slices[:4]) == set(range(32)) and set().union(*slices[4:]) == set(range(32, 64))
+    assert sum(len(s) for s in slices) == 64                       # disjoint
+    assert affinity.plan(sets, 2, "off") == set()
+    # a container that may only use cores 0-3: stay inside, share when there are fewer cores than ranks
+    assert affinity.plan(sets, 1, "node", allowed={0, 1, 2, 3}) == {0, 1, 2, 3}
+    assert affinity.plan(sets, 1, "exclusive", allowed={0, 1, 2}) == {0, 1, 2}
+    assert affinity.plan(sets, 5, "node", allowed={0, 1, 2, 3}) == set()      # nothing near that GPU: unbound
+    # no NVML at all: unbound
+    assert affinity.bind_to_gpu(0, 8, "node", nvml=object(), apply=False) == set()
+    assert affinity.bind_to_gpu(3, 8, "exclusive", nvml=nv, apply=False) <= set(range(32))
