@@ -44,7 +44,7 @@ RT_API int rt_pareto_sample(const double* stable, const double* delta, const uin
 namespace {
 
 struct Option {
-  int kind;      // 0 first, 1 middle, 2 last, 3 only stage
+  int kind;      // 0 first, 1 any middle stage, 2 last, 3 only stage, 10 + s the middle stage at index s
   int layers;
   double T, D;
   int id;        // caller's identifier
@@ -101,10 +101,18 @@ RT_API double rt_inter_stage_solve(int num_stages, int total_layers, int grad_ac
     if (s == num_stages - 1) return 2;
     return 1;
   };
-  // options grouped per stage kind
-  std::vector<std::vector<int>> by_kind(4);
+  // options grouped per stage kind; a middle stage takes the options priced for exactly its index (kind 10 + s:
+  // its own 1F1B warm-up depth) when the caller supplied some, else the ones priced for any middle stage
+  constexpr int kExact = 10;
+  std::vector<std::vector<int>> by_kind(kExact + num_stages);
   for (int i = 0; i < static_cast<int>(opts.size()); ++i)
-    if (opts[i].kind >= 0 && opts[i].kind < 4 && std::isfinite(opts[i].T)) by_kind[opts[i].kind].push_back(i);
+    if (opts[i].kind >= 0 && opts[i].kind < static_cast<int>(by_kind.size()) && std::isfinite(opts[i].T))
+      by_kind[opts[i].kind].push_back(i);
+  auto candidates_of_stage = [&](int s) -> const std::vector<int>& {
+    const int k = kind_of_stage(s);
+    if (k == 1 && !by_kind[kExact + s].empty()) return by_kind[kExact + s];
+    return by_kind[k];
+  };
 
   const size_t kFrontCap = 64;
   for (double tmax : tvals) {
@@ -115,7 +123,7 @@ RT_API double rt_inter_stage_solve(int num_stages, int total_layers, int grad_ac
     fronts[0][0].push_back({0.0, -inf, -1, -1, -1});
     bool uses_tmax = false;
     for (int s = 0; s < num_stages; ++s) {
-      const auto& cand = by_kind[kind_of_stage(s)];
+      const auto& cand = candidates_of_stage(s);
       for (int used = 0; used <= total_layers; ++used) {
         const auto& cur = fronts[s][used];
         if (cur.empty()) continue;

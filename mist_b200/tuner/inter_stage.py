@@ -32,6 +32,12 @@ from .intra_stage import intra_stage_tune
 Solution = Tuple[int, List[Tuple[Tuple[Tuple[int, int], Tuple[int, int], int, int], Tuple[float, ...]]]]
 
 
+#: stage kinds: 0 first, 1 any middle stage, 2 last, 3 the only stage; EXACT_MIDDLE + s: the middle stage at
+#: pipeline position s, priced with that position's 1F1B warm-up depth (the reference's
+#: pre_saved_micro_batches dimension, mist/analyzer/batched_module_analyzer.py:581-685)
+EXACT_MIDDLE = 10
+
+
 def uniform_mesh_for(num_stages: int, num_nodes: int, gpus_per_node: int) -> Optional[Tuple[int, int]]:
     total = num_nodes * gpus_per_node
     if total % num_stages:
@@ -74,7 +80,13 @@ def _solve_python(num_stages, total_layers, g, kinds, layers, T, D) -> Tuple[flo
             return 3
         return 0 if s == 0 else (2 if s == num_stages - 1 else 1)
 
-    by_kind = {k: [i for i in range(n) if kinds[i] == k and math.isfinite(T[i])] for k in range(4)}
+    by_kind = {k: [i for i in range(n) if kinds[i] == k and math.isfinite(T[i])] for k in set(kinds) | {0, 1, 2, 3}}
+
+    def candidates(s):
+        k = kind_of(s)
+        if k == 1 and by_kind.get(EXACT_MIDDLE + s):
+            return by_kind[EXACT_MIDDLE + s]      # priced for exactly this stage index (its own warm-up depth)
+        return by_kind[k]
 
     def rec(s, used, sumT, worst, tmax, choice):
         if s == num_stages:
@@ -85,7 +97,7 @@ def _solve_python(num_stages, total_layers, g, kinds, layers, T, D) -> Tuple[flo
             return
         if (g - 1) * tmax + sumT >= best[0]:
             return
-        for i in by_kind[kind_of(s)]:
+        for i in candidates(s):
             nu = used + layers[i]
             if nu > total_layers or total_layers - nu < num_stages - 1 - s:
                 continue
@@ -153,7 +165,8 @@ def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache
             counts = [L // S]
         else:
             counts = list(_layer_range(L, S, offset)) if S > 1 else [L]
-        kinds = [3] if S == 1 else [0, 1, 2]
+        # pipelines deeper than three stages price every middle position with its own warm-up depth
+        kinds = [3] if S == 1 else ([0, 1, 2] if S <= 3 else [0] + [EXACT_MIDDLE + i for i in range(1, S - 1)] + [2])
         lc = {(mesh, k): counts for k in kinds}
         g_cands = [g for g in grad_accum_candidates(cfg.training.global_batch_size)]
         intra = intra_stage_tune(cfg, ev, grad_accums=g_cands, meshes=[mesh], layer_counts=lc, tp=tp,
@@ -177,7 +190,7 @@ def inter_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, cache
                 layouts = {(int(r[3].vector[1]), int(r[3].vector[2])) for r in opt_ref if r[0] in (0, 2)}
                 for lay in sorted(layouts):
                     keep = [i for i, r in enumerate(opt_ref)
-                            if r[0] == 1 or (int(r[3].vector[1]), int(r[3].vector[2])) == lay]
+                            if r[0] not in (0, 2) or (int(r[3].vector[1]), int(r[3].vector[2])) == lay]
                     c, ch = solve_stage_assignment(S, L, g, [opt_kind[i] for i in keep], [opt_layers[i] for i in keep],
                                                    [opt_T[i] for i in keep], [opt_D[i] for i in keep])
                     if ch and c < cost:

@@ -22,6 +22,7 @@ from ..config import MistConfig
 from .pareto import dedup_samples, sample_pareto_frontier
 
 KINDS = {0: (True, False), 1: (False, False), 2: (False, True), 3: (True, True)}   # (has_pre, has_post)
+EXACT_MIDDLE = 10      # kind EXACT_MIDDLE + s: the middle stage at pipeline position s (see tuner/inter_stage.py)
 
 
 @dataclass
@@ -63,17 +64,18 @@ def tune_stage_cell(ev: StageEvaluator, cfg: MistConfig, g: int, mesh: Tuple[int
     space = create_search_space(mesh[0], mesh[1], gbs, g, cfg, tp_size=tp)
     if space.shape[0] == 0:
         return [], 0
-    kind_pre, has_post = KINDS[kind]
+    kind_pre, has_post = KINDS[1 if kind >= EXACT_MIDDLE else kind]
     has_pre = kind_pre if has_pre is None else bool(has_pre)
     warm = min(num_stages - 1 - stage_index, max(g - 1, 0))
     S = cfg.tuning.sample_size if cfg.tuning else 30
     all_points: List[StagePoint] = []
     evaluated = 0
     for c in ckpt_candidates(layers, cfg):
-        # kinds: 0 first stage of a pipeline, 1 middle, 2 last, 3 the only stage (no neighbours to exchange with)
+        # kinds: 0 first stage of a pipeline, 1 middle (EXACT_MIDDLE + s: the one at position s), 2 last,
+        # 3 the only stage (no neighbours to exchange with)
         res = ev.evaluate(space, layers, c, g, has_pre, has_post, inflight_extra=warm, block_kind=block_kind,
                           tied_copy=(kind == 2 and ties_across_stages(cfg)),
-                          has_prev_stage=kind in (1, 2), has_next_stage=kind in (0, 1))
+                          has_prev_stage=kind not in (0, 3), has_next_stage=kind not in (2, 3))
         evaluated += space.shape[0]
         idx = dedup_samples(sample_pareto_frontier(res["stable"], res["delta"], res["feasible"], S))
         for i in idx:
@@ -120,11 +122,14 @@ def intra_stage_tune(cfg: MistConfig, ev: Optional[StageEvaluator] = None, grad_
             n_dev = mesh[0] * mesh[1]
             S = num_stages_for_mesh(mesh) if num_stages_for_mesh else max(total_devices // n_dev, 1)
             kinds = [3] if S == 1 else [0, 1, 2]
+            asked = sorted({k for (m, k) in (layer_counts or {}) if tuple(m) == tuple(mesh)})
+            if asked:
+                kinds = asked                      # the caller names the stage kinds it wants priced
             for kind in kinds:
                 counts = (layer_counts or {}).get((tuple(mesh), kind))
                 if counts is None:
                     counts = [L] if S == 1 else range(1, L - S + 2)
-                stage_index = {0: 0, 1: 1 if S > 2 else 0, 2: S - 1, 3: 0}[kind]
+                stage_index = kind - EXACT_MIDDLE if kind >= EXACT_MIDDLE else {0: 0, 1: 1 if S > 2 else 0, 2: S - 1, 3: 0}[kind]
                 for layers in counts:
                     pts, n = tune_stage_cell(ev, cfg, g, tuple(mesh), kind, int(layers), S, stage_index, tp)
                     out.evaluated += n

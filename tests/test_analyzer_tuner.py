@@ -474,3 +474,65 @@ def test_encoder_decoder_models_are_searched_over_pipeline_stages(monkeypatch, t
     check(cost, sol, "best")
     one_cost, _ = inter_stage_tune(cfg, ev, single_stage=True)
     assert cost == pytest.approx(min(one_cost, piped_cost))
+
+
+def test_middle_stages_are_priced_with_their_own_warm_up_depth(monkeypatch, tmp_path):
+    """A four-stage pipeline: stage 1 keeps the activations of two extra micro batches alive, stage 2 of one.
+    Both solvers take the options priced for exactly a stage's position when there are some; the tuner's cost
+    on a memory-tight four-GPU case equals the analyzer's, which prices every stage at its own depth (the
+    four-stage layout itself is forced in the next test)."""
+    from mist_b200.tuner.inter_stage import EXACT_MIDDLE
+    # options: first, exact middles for positions 1 and 2, a generic middle that must be ignored, last
+    kinds = [0, EXACT_MIDDLE + 1, EXACT_MIDDLE + 2, 1, 2]
+    layers = [2, 2, 2, 2, 2]
+    T = [1.0, 3.0, 2.0, 0.1, 1.0]
+    D = [0.0, 0.0, 0.0, 0.0, 0.0]
+    for solve in (_solve_native, _solve_python):
+        cost, chosen = solve(4, 8, 3, kinds, layers, T, D)
+        assert chosen == [0, 1, 2, 4]                          # the cheap generic middle option is not eligible
+        assert cost == pytest.approx(sum(T[i] for i in chosen) + 2 * 3.0)
+    # without exact options the generic one serves every middle position
+    cost, chosen = _solve_python(4, 8, 3, [0, 1, 2], [2, 2, 2], [1.0, 0.5, 1.0], [0.0, 0.0, 0.0])
+    assert chosen == [0, 1, 1, 2]
+
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    from mist_b200.utils import yamlconf
+    over = ["experiment=gpt2-1.3b", "model.num_hidden_layers=8", "hardware.num_gpus_per_node=4",
+            "training.global_batch_size=16", "training.max_sequence_length=512", "strategy.enabled=false",
+            "tuning.tuning_granularity=uniform-pp", "tuning.sample_size=4", "hardware.memory_capacity=6.0"]
+    cfg, node = load_config("config", over, check_world_size=False)
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=False))
+    cost, sol = inter_stage_tune(cfg, ev)
+    assert sol is not None and math.isfinite(cost)
+    strat = solution_to_strategy(cfg, sol)
+    plain = node.to_dict()
+    plain["strategy"] = strat
+    yamlconf.dump(plain, tmp_path / "deep.yaml")
+    cfg2, _ = load_config("deep", config_dirs=[tmp_path], check_world_size=False)
+    again = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))["total"]
+    assert again == pytest.approx(cost, rel=1e-6)
+
+
+def test_four_stage_pipeline_cost_matches_the_analyzer(monkeypatch):
+    """The uniform search restricted to four stages (1 GPU each): what the solver adds up for its chosen
+    Pareto points equals what the analyzer computes for the resulting strategy, stage by stage."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    from mist_b200.tuner import inter_stage as IS
+    over = ["experiment=gpt2-1.3b", "model.num_hidden_layers=8", "hardware.num_gpus_per_node=4",
+            "training.global_batch_size=16", "training.max_sequence_length=512", "strategy.enabled=false",
+            "tuning.tuning_granularity=uniform-pp", "tuning.sample_size=4"]
+    cfg, node = load_config("config", over, check_world_size=False)
+    monkeypatch.setattr(IS, "stage_count_candidates", lambda n, L: [4])
+    ev = StageEvaluator(cfg, OpDatabase(allow_profile=False))
+    cost, sol = IS.inter_stage_tune(cfg, ev)
+    assert sol is not None and len(sol[1]) == 4
+    strat = solution_to_strategy(cfg, sol)
+    plain = node.to_dict()
+    plain["strategy"] = strat
+    import tempfile
+    from mist_b200.utils import yamlconf
+    with tempfile.TemporaryDirectory() as d:
+        yamlconf.dump(plain, os.path.join(d, "four.yaml"))
+        cfg2, _ = load_config("four", config_dirs=[d], check_world_size=False)
+    again = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))["total"]
+    assert again == pytest.approx(cost, rel=1e-6)
