@@ -536,3 +536,24 @@ def test_four_stage_pipeline_cost_matches_the_analyzer(monkeypatch):
         cfg2, _ = load_config("four", config_dirs=[d], check_world_size=False)
     again = analyze_strategy(cfg2, StageEvaluator(cfg2, OpDatabase(allow_profile=False)))["total"]
     assert again == pytest.approx(cost, rel=1e-6)
+
+
+def test_tuned_configurations_stay_within_tolerance_of_their_measured_runs(monkeypatch):
+    """Regression harness on the shipped tuned strategies (measured on 8 x B200): the installed cost model
+    prices each of them within 10 % of the measured iteration time and 5 % of the measured peak memory, and
+    reproduces the predictions recorded beside the measurements."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    import importlib.util
+    import json
+    root = os.path.join(os.path.dirname(__file__), "..", "benchmark", "mist_b200", "tuned_configs")
+    spec = importlib.util.spec_from_file_location("tuned_accuracy", os.path.join(root, "test_performance_accuracy.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    folder = os.path.join(root, "b200-180gb")
+    rows = mod.report(folder, fresh=True)
+    recorded = json.load(open(os.path.join(folder, "expected_summary.json")))
+    assert len(rows) == 4
+    for r in rows:
+        assert abs(r["time_error"]) < 0.10, r
+        assert abs(r["memory_error"]) < 0.05, r
+        assert r["predicted_s"] == pytest.approx(recorded[r["name"]]["tuned_predicted_s"], rel=5e-3), r
