@@ -557,3 +557,18 @@ def test_tuned_configurations_stay_within_tolerance_of_their_measured_runs(monke
         assert abs(r["time_error"]) < 0.10, r
         assert abs(r["memory_error"]) < 0.05, r
         assert r["predicted_s"] == pytest.approx(recorded[r["name"]]["tuned_predicted_s"], rel=5e-3), r
+
+
+def test_hand_written_b200_workloads_stay_within_tolerance_of_their_measured_runs(monkeypatch):
+    """The four 8 x B200 workloads with hand-written strategies: predicted iteration time within 10 % and
+    predicted peak memory per stage within 10 % of what the exec entry point measured."""
+    monkeypatch.setenv("FAKE_DEVICE_NAME", "NVIDIA_B200")
+    import json
+    path = os.path.join(os.path.dirname(__file__), "..", "benchmark", "mist_b200", "prediction-accuracy", "measured_b200.json")
+    for w in json.load(open(path))["workloads"]:
+        cfg, _ = load_config("config", w["overrides"], check_world_size=False)
+        res = analyze_strategy(cfg, StageEvaluator(cfg))
+        assert abs(res["total"] / w["measured_s"] - 1.0) < 0.10, (w["name"], res["total"])
+        if w["measured_peak_mb"]:
+            for (pf, pb), m in zip(res["peak_memories"], w["measured_peak_mb"]):
+                assert abs(max(pf, pb) / 2 ** 20 / m - 1.0) < 0.10, (w["name"], pf, pb, m)
