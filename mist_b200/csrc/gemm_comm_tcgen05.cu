@@ -1,12 +1,14 @@
 // Tensor-parallel GEMMs fused with their sequence-parallel collective, one kernel each.
 //
 //   mode AG -> GEMM   C = allgather(A_shard) * B^T
-//       A lives in a symmetric [T][K] buffer; every rank has written its own rows.  A few
-//       CTAs of the persistent grid ("gather CTAs") pull the peers' row chunks over NVLink
-//       with bulk async copies (peer global -> shared -> local global) and publish a flag
-//       per chunk; the compute CTAs' TMA warp waits for the flag that covers its tile before
-//       loading it, and visits the locally owned rows first.  Each remote byte crosses NVLink
-//       once; afterwards the whole gathered A sits in local memory for any other consumer.
+//       A lives in a symmetric [T][K] buffer; every rank has written its own rows.  Some
+//       CTAs of the persistent grid ("gather CTAs", 8 to 64, chosen per launch from the bytes
+//       to fetch and the FLOPs of the GEMM) pull the peers' row chunks over NVLink with bulk
+//       async copies (peer global -> shared -> local global), sharing every chunk among them
+//       (gather_plan.cuh), and publish a flag per chunk; the compute CTAs' TMA warp waits for
+//       the flag that covers its tile before loading it, and visits the locally owned rows
+//       first.  Each remote byte crosses NVLink once; afterwards the whole gathered A sits in
+//       local memory for any other consumer.
 //
 //   mode GEMM -> RS   C_shard = reduce_scatter(A * B^T)
 //       The epilogue sends every output tile to the rank that owns those rows as soon as the tile is
@@ -22,9 +24,9 @@
 //   mode weight-AG -> GEMM   C = A * W^T + bias, W inside a flat parameter buffer sharded over ranks
 //       ZeRO-3 keeps 1/R of a block's flat bf16 parameters per rank.  Every rank holds its
 //       shard at its place in a symmetric full-size buffer; the gather CTAs pull all remote
-//       shards in pieces ("chunks", one flag each), starting with the pieces that hold the
-//       weight matrix of this GEMM, and the TMA warp of a compute CTA waits for the chunks
-//       under its B tile.  When the kernel ends the whole block's parameters are local for
+//       shards in pieces ("chunks", one flag each), from all peers at once and starting with
+//       the pieces that hold the weight matrix of this GEMM, and the TMA warp of a compute CTA
+//       waits for the chunks under its B tile.  When the kernel ends the whole block's parameters are local for
 //       the block's other operators.
 //
 // All share the tcgen05 main loop of the plain GEMM (TMA-fed smem stages, accumulators in
