@@ -93,6 +93,10 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
         (sess.step_on_device if decoder_only else sess.step_on_device_batch)(*data[i])
     sess.finish()
     sync()
+    sampler = None
+    if cuda and rank == 0:
+        from mist_b200.utils.clocks import ClockSampler
+        sampler = ClockSampler(dev.index or 0).start()       # SM clock and throttle reasons during the timed region
     if cuda:
         torch.cuda.reset_peak_memory_stats()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -106,6 +110,7 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
         t1.record()
     sync()
     latency = (t0.elapsed_time(t1) / 1e3 if cuda else time.perf_counter() - wall) / number
+    clocks = sampler.stop() if sampler is not None else None
     if prof is not None:
         prof.stop()
     native.check_status()
@@ -128,7 +133,7 @@ def run(cfg, node, warmup=None, number=None, comm_backend=None, seed=12345):
     return {"latency": latency, "tokens_per_s": tokens / latency, "loss": float(loss) if loss is not None else None,
             "peak_allocated": per_stage[:, 0].tolist(), "peak_reserved": per_stage[:, 1].tolist(), "rank": rank,
             "backends": {"comm_backend": sess.comm_backend, "tp_backend": sess.tp_backend,
-                         "zero3_gather": sess.zero3_gather}}
+                         "zero3_gather": sess.zero3_gather}, "clocks": clocks}
 
 
 def main(argv=None):
@@ -153,12 +158,16 @@ def main(argv=None):
         print(f"Total Latency: {res['latency']:.4f}")
         print(f"Throughput: {res['tokens_per_s']:.1f} tokens/s")
         print(f"Collective back ends: {res['backends']}")
+        if res.get("clocks"):
+            c = res["clocks"]
+            print(f"SM clock under load: {c.get('sm_mhz')} MHz of {c.get('sm_max_mhz')} ({', '.join(c.get('reasons', [])) or 'no throttle reason'})")
         print(f"Peak allocated memory per stage: {fmt_memories(res['peak_allocated'])}")
         print(f"Peak reserved memory per stage: {fmt_memories(res['peak_reserved'])}")
         update_summary(os.path.join(output_dir(node), "summary.json"), {
             "exec_total_cost": fmt_cost(res["latency"]),
             "exec_throughput": f"{res['tokens_per_s']:.1f}",
             "exec_backends": res["backends"],
+            "exec_clocks": res.get("clocks"),
             "exec_stage_peak_allocated_memories": fmt_memories(res["peak_allocated"]),
             "exec_stage_peak_reserved_memories": fmt_memories(res["peak_reserved"]),
         })

@@ -102,3 +102,24 @@ def test_cpu_binding_plan_with_a_fake_nvml():
     # no NVML at all: unbound
     assert affinity.bind_to_gpu(0, 8, "node", nvml=object(), apply=False) == set()
     assert affinity.bind_to_gpu(3, 8, "exclusive", nvml=nv, apply=False) <= set(range(32))
+
+
+def test_clock_sampler_with_a_stand_in_for_nvidia_smi(tmp_path):
+    """The sampler runs the query tool in a helper process and summarises its CSV lines; a missing tool gives
+    an empty summary instead of an error."""
+    import os
+    import stat
+    import time
+    from mist_b200.utils.clocks import ClockSampler, summarise
+    fake = tmp_path / "fake-smi"
+    fake.write_text("#!/bin/bash\nwhile true; do echo '0, 1530, 1965, 987.5, 0x4, Not Active, Not Active, Not Active, Active'; "
+                    "echo '0, 1560, 1965, 990.1, 0x4, Not Active, Not Active, Not Active, Active'; sleep 0.05; done\n")
+    os.chmod(fake, os.stat(fake).st_mode | stat.S_IEXEC)
+    s = ClockSampler(0, executable=str(fake)).start()
+    time.sleep(0.5)
+    out = s.stop()
+    assert out["samples"] >= 2 and out["sm_mhz"] in (1530.0, 1545.0, 1560.0) and out["sm_max_mhz"] == 1965.0
+    assert out["reasons"] == ["sw_power_cap"] and out["power_w_max"] == 990.1
+    assert ClockSampler(0, executable=str(tmp_path / "missing")).start().stop()["sm_mhz"] is None
+    bad = summarise(["garbage", "0, [N/A], 1965, 1, x, Active, Not Active, Not Active, Not Active"])
+    assert bad["samples"] == 0 and bad["reasons"] == []
