@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import enum
 import os
-from dataclasses import dataclass, field, fields
+from dataclasses import dataclass, fields
 from typing import Any, List, Optional, Sequence, Tuple
 
 import torch

@@ -8,7 +8,6 @@ Generating the files from tables keeps the model zoo and the B200 presets in one
 """
 from __future__ import annotations
 
-import os
 from pathlib import Path
 
 import yaml

@@ -10,7 +10,6 @@ always take precedence.
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass, field
 from typing import Dict, Tuple
 

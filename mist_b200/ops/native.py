@@ -11,7 +11,6 @@ PyTorch implementation, which is also the oracle of the numerics tests.
 from __future__ import annotations
 
 import ctypes as C
-import os
 from pathlib import Path
 
 import torch

@@ -10,7 +10,6 @@ compute stream continues with the backward pass of the previous block.
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import Dict
 
 import torch
