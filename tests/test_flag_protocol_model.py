@@ -81,3 +81,68 @@ def test_protocol_never_reads_stale_or_future_data(R, epochs):
 def test_without_the_final_wait_a_buffer_is_overwritten_under_a_reader():
     trace = _explore(2, 2, wait_done=False)
     assert trace is not None and "saw version" in trace[-1][-1]
+
+
+# --------------------------------------------------------------------------------------------------
+# GEMM -> reduce-scatter, store form: launch e of rank s stores its tile for owner o into the slot
+# slots[o][e % 2][s] (peer store), then announces done[o][s] := e; it then waits until every source has
+# announced e on its own done row and sums its slots of set e % 2 (a separate kernel, in stream order
+# before launch e + 1).  There is no opening flag round: the two slot sets alternate instead.  Property:
+# an owner's sum of launch e reads, from every source, the tile of launch e.
+
+def _explore_store_form(R: int, epochs: int, sets: int = 2, closing_round: bool = True):
+    prog = []
+    for r in range(R):
+        steps = [("store", o) for o in range(R)]
+        steps += [("done", o) for o in range(R) if o != r]
+        if closing_round:
+            steps += [("wait_done", s) for s in range(R) if s != r]
+        steps += [("sum", s) for s in range(R)]
+        prog.append(steps)
+    # slots[o][set][s] = launch number of the tile it holds
+    slots0 = tuple(0 for _ in range(R * sets * R))
+    start = (tuple((1, 0) for _ in range(R)), slots0, (0,) * (R * R))
+    seen = {start}
+    stack = [(start, ())]
+    while stack:
+        (pcs, slots, done), trace = stack.pop()
+        for r in range(R):
+            e, i = pcs[r]
+            if e > epochs:
+                continue
+            op, arg = prog[r][i]
+            slots2, done2 = slots, done
+            if op == "store":
+                k = (arg * sets + e % sets) * R + r
+                slots2 = slots[:k] + (e,) + slots[k + 1:]
+            elif op == "done":
+                k = arg * R + r
+                done2 = done[:k] + (e,) + done[k + 1:]
+            elif op == "wait_done":
+                if done[r * R + arg] < e:
+                    continue
+            elif op == "sum":
+                got = slots[(r * sets + e % sets) * R + arg]
+                if got != e:
+                    return trace + ((r, e, op, arg, f"summed the tile of launch {got}"),)
+            ni = i + 1
+            npc = (e + 1, 0) if ni == len(prog[r]) else (e, ni)
+            state = (pcs[:r] + (npc,) + pcs[r + 1:], slots2, done2)
+            if state not in seen:
+                seen.add(state)
+                stack.append((state, trace + ((r, e, op, arg),)))
+    return None
+
+
+@pytest.mark.parametrize("R,epochs", [(2, 4), (3, 3)])
+def test_store_form_reduce_scatter_sums_the_tiles_of_its_own_launch(R, epochs):
+    assert _explore_store_form(R, epochs) is None
+
+
+def test_store_form_needs_two_slot_sets_and_the_closing_round():
+    """With one slot set a fast source overwrites a tile before its owner has summed it; without the closing
+    flag round an owner sums before every tile has landed."""
+    bad = _explore_store_form(2, 3, sets=1)
+    assert bad is not None and "summed the tile of launch" in bad[-1][-1]
+    bad = _explore_store_form(2, 2, closing_round=False)
+    assert bad is not None
