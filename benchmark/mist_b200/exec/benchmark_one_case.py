@@ -158,6 +158,8 @@ def main(argv=None):
         print(f"Total Latency: {res['latency']:.4f}")
         print(f"Throughput: {res['tokens_per_s']:.1f} tokens/s")
         print(f"Collective back ends: {res['backends']}")
+        if res.get("loss") is not None:
+            print(f"Loss of the last iteration (this rank's stage): {res['loss']:.4f}")
         if res.get("clocks"):
             c = res["clocks"]
             print(f"SM clock under load: {c.get('sm_mhz')} MHz of {c.get('sm_max_mhz')} ({', '.join(c.get('reasons', [])) or 'no throttle reason'})")
