@@ -31,9 +31,28 @@ def collect(root):
     return rows
 
 
+def collect_measured(path):
+    """Rows for a file of measured runs (``measured_b200.json`` beside this script): every workload is priced
+    again with the installed cost model (CPU only; set ``FAKE_DEVICE_NAME`` to the GPU of the operator database)."""
+    sys.path.insert(0, os.path.abspath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..")))
+    from mist_b200.analyzer.stage_evaluator import StageEvaluator, analyze_strategy
+    from mist_b200.config import load_config
+    rows = []
+    with open(path) as f:
+        workloads = json.load(f)["workloads"]
+    for w in workloads:
+        cfg, _ = load_config("config", w["overrides"], check_world_size=False)
+        res = analyze_strategy(cfg, StageEvaluator(cfg))
+        rows.append({"name": w["name"], "pred": float(res["total"]), "meas": float(w["measured_s"]),
+                     "pred_mem": [max(p) / 2 ** 20 for p in res["peak_memories"]] if w.get("measured_peak_mb") else [],
+                     "meas_mem": [float(m) for m in (w.get("measured_peak_mb") or [])]})
+    return rows
+
+
 def main(argv=None):
+    """``<folder>``: walk its ``summary.json`` files; ``<file>.json``: a list of measured runs to price again."""
     root = (argv or sys.argv[1:] or ["."])[0]
-    rows = collect(root)
+    rows = collect_measured(root) if root.endswith(".json") else collect(root)
     if not rows:
         print("no summary.json with both analyzed and exec results under", root)
         return
